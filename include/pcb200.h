@@ -1,0 +1,209 @@
+/* pcb200.h — C ABI of libpcb200.so: the probabilistic-circuit hot path of
+ * LVD-PG / VariationalJuice.jl on NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *  - Every entry point returns an int32 status (PCB_OK == 0).  No C++ exception
+ *    crosses the boundary; pcb_last_error() gives the message of the last
+ *    failure on the calling thread.
+ *  - Pointers named *_dev are device pointers on the circuit's GPU, everything
+ *    else is host memory.  All device work is enqueued on the cudaStream_t given
+ *    by the caller (pass 0 for the legacy default stream).
+ *  - Node, edge, variable and row ids in the descriptor and in row_ids are
+ *    1-based, exactly as the Julia side holds them; the conversion to 0-based
+ *    happens once inside pcb_circuit_create.
+ *  - Matrices are column-major with the example (or parameter-set) index
+ *    fastest, i.e. element (b, n) of a [B, N] matrix lives at b + ld*n, which is
+ *    the layout of the reference's CuMatrix buffers.
+ *  - The library never falls back to the CPU.
+ */
+#ifndef PCB200_H
+#define PCB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  PCB_OK = 0,
+  PCB_ERR_INVALID = 1,   /* bad argument / malformed circuit            */
+  PCB_ERR_CUDA = 2,      /* a CUDA runtime call failed                  */
+  PCB_ERR_NCCL = 3,      /* NCCL missing or a collective failed         */
+  PCB_ERR_TOO_LARGE = 4, /* exceeds a stated static limit               */
+  PCB_ERR_STATE = 5      /* call order violated (e.g. backward first)   */
+};
+
+enum { PCB_INPUT = 0, PCB_PRODUCT = 1, PCB_SUM = 2 };
+
+/* Edge tag bits, meaning fixed by their use in
+ * VariationalJuice.jl/src/queries/likelihood.jl:23-27 and queries/flow.jl:38-47. */
+enum {
+  PCB_TAG_FIRST = 1,
+  PCB_TAG_LAST = 2,
+  PCB_TAG_PARTIAL = 4,
+  PCB_TAG_ONLYSUB = 8,
+  PCB_TAG_USER = 16
+};
+
+/* Flattened compiled circuit in the reference's order: the content of
+ * BitsProbCircuit (fields used at VariationalJuice.jl/src/bits_circuit.jl:40-42,76-99
+ * and regularization/reg_em.jl:171-174).  Nodes are ordered children-before-parent
+ * with the root last; a parent's up-edges are contiguous; up-edges are grouped by
+ * layer (up_layer_ends are 1-based inclusive ends); down-edges are described by
+ * down2up (down-edge id -> up-edge id) and their own layer ends. */
+typedef struct pcb_circuit_desc {
+  uint32_t num_nodes;
+  uint32_t num_edges;
+  uint32_t num_up_layers;
+  uint32_t num_down_layers;
+  uint32_t num_input_nodes;
+  uint32_t num_vars;
+  uint64_t heap_len;
+  const uint8_t* node_kind;        /* [N] PCB_INPUT / PCB_PRODUCT / PCB_SUM          */
+  const uint32_t* node_var;        /* [N] variable of an input node, 0 otherwise      */
+  const uint32_t* node_num_cats;   /* [N] categories of an input node                 */
+  const uint32_t* node_heap_start; /* [N] 1-based heap index of the first log-prob    */
+  const uint8_t* node_fixed;       /* [N] 1: input has no learnable parameters        */
+  const uint32_t* up_parent;       /* [E]                                             */
+  const uint32_t* up_prime;        /* [E]                                             */
+  const uint32_t* up_sub;          /* [E] 0 when the edge has a single child          */
+  const float* up_logp;            /* [E] log-parameter of a sum edge, 0 for products */
+  const uint8_t* up_tag;           /* [E] PCB_TAG_* bits (may be NULL)                */
+  const uint32_t* up_layer_ends;   /* [num_up_layers]                                 */
+  const uint32_t* down2up;         /* [E]                                             */
+  const uint32_t* down_layer_ends; /* [num_down_layers]                               */
+  const uint32_t* input_node_ids;  /* [num_input_nodes]                               */
+  const float* heap;               /* [heap_len] leaf storage, layout of
+                                      nodes/fixable_categorical_dist.jl:54-64: C log-probs,
+                                      then (learnable leaves only) C flow slots + 1 missing slot */
+} pcb_circuit_desc;
+
+typedef struct pcb_circuit pcb_circuit;     /* compiled circuit + parameters on one GPU */
+typedef struct pcb_workspace pcb_workspace; /* mars / flows buffers for a max batch      */
+typedef void* pcb_stream;                   /* cudaStream_t                              */
+
+/* Counters of a compiled circuit (bits_circuit.jl:119-131 num_parameters, num_nodes,
+ * num_edges, num_input_params, plus what the layout compiler found). */
+typedef struct pcb_circuit_info {
+  uint32_t num_nodes, num_edges, num_sum_edges, num_up_layers;
+  uint32_t num_inner_params, num_input_params, num_param_groups;
+  uint32_t num_dense_blocks, num_sum_regions, max_group_size, max_num_cats;
+  uint64_t num_dense_edges;
+  uint64_t device_bytes;
+} pcb_circuit_info;
+
+const char* pcb_last_error(void);
+int32_t pcb_version(void);
+
+/* ---- circuit ------------------------------------------------------------------------ */
+/* Replaces cu(BitsProbCircuit) + CuMetaBitsProbCircuit(pc) (bits_circuit.jl:39-113):
+ * uploads the circuit to `device`, builds the flat parameter maps and the packed layout. */
+int32_t pcb_circuit_create(const pcb_circuit_desc* desc, int32_t device, pcb_circuit** out);
+int32_t pcb_circuit_destroy(pcb_circuit* c);
+int32_t pcb_circuit_get_info(const pcb_circuit* c, pcb_circuit_info* info);
+
+/* prep_memory(mars_mem / flows_mem, (batch_size, num_nodes)) of reg_em.jl:226-235.
+ * `sets` != 0 additionally reserves the per-parameter-set buffers the KLD and
+ * sampling calls need (klds, edge_klds, grads, ... of utils/cuda_preallocation.jl:6-45). */
+int32_t pcb_workspace_create(pcb_circuit* c, uint32_t max_batch, int32_t sets, pcb_workspace** out);
+int32_t pcb_workspace_destroy(pcb_workspace* ws);
+
+/* ---- parameters --------------------------------------------------------------------- */
+/* vectorize_parameters / update_parameters (misc.jl:5-68, 73-135): flat order = inner
+ * (sum-edge) params in param2edge order, then leaf params in input_node_ids order. */
+int32_t pcb_get_params(pcb_circuit* c, float* params_host, uint64_t n);
+int32_t pcb_set_params(pcb_circuit* c, const float* params_host, uint64_t n);
+int32_t pcb_get_params_dev(pcb_circuit* c, float* params_dev, uint64_t n, pcb_stream s);
+int32_t pcb_set_params_dev(pcb_circuit* c, const float* params_dev, uint64_t n, pcb_stream s);
+/* Copies of bpc.heap and of edge_aggr in down-edge order (conditional_pc/custom_em_tests.jl:88-90). */
+int32_t pcb_get_heap(pcb_circuit* c, float* heap_host, uint64_t n);
+int32_t pcb_get_edge_aggr(pcb_circuit* c, float* edge_aggr_host, uint64_t n);
+/* Flat parameter maps of CuMetaBitsProbCircuit (bits_circuit.jl:44-70), 1-based. */
+int32_t pcb_get_edge2param(pcb_circuit* c, uint32_t* edge2param_host, uint64_t n);
+int32_t pcb_get_sum_regions(pcb_circuit* c, uint32_t* node_region_host, uint64_t n);
+
+/* ---- forward / backward / EM -------------------------------------------------------- */
+/* Forward pass: init_mar!_with_reg + layer_up over all layers
+ * (regularization/reg_likelihood.jl:16-49,126-137, queries/likelihood.jl:4-113).
+ * data_dev: [num_rows, num_vars] uint8 column-major; miss_dev: same shape, nonzero = missing
+ * (may be NULL); row_ids_dev: B 1-based row ids (NULL => rows row_start .. row_start+B-1,
+ * 1-based).  ll_out_dev (may be NULL) receives mars[1:B, end]. */
+int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev,
+                    const uint8_t* miss_dev, uint64_t num_rows, const int32_t* row_ids_dev,
+                    uint32_t row_start, uint32_t B, float* ll_out_dev, pcb_stream s);
+/* Backward pass of the batch last given to pcb_forward: reg_flows_circuit +
+ * input_flows_circuit_with_reg (regularization/reg_flow.jl:24-48,120-274,
+ * queries/flow.jl:8-159).  Adds to edge_aggr and to the leaf flow slots;
+ * weights_dev (per data row, may be NULL) scales leaf flows only, as the reference does. */
+int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* weights_dev, pcb_stream s);
+/* edge_aggr .*= rate and clear_input_node_mem(bpc; rate) (reg_em.jl:276-284,
+ * nodes/fixable_categorical_dist.jl:250-260). */
+int32_t pcb_clear_flows(pcb_circuit* c, float rate, pcb_stream s);
+/* add_pseudocount + aggr_node_flows + update_params + update_input_node_params
+ * (reg_em.jl:292-299; arithmetic of pretrain/mini_batch_warmup.jl:4-76,
+ * sgd/adam.jl:27-37, nodes/fixable_categorical_dist.jl:223-248). */
+int32_t pcb_em_update(pcb_circuit* c, float pseudocount, float inertia, pcb_stream s);
+/* One mini-batch step, the per-batch body of mini_batch_em_with_reg (reg_em.jl:273-301):
+ * clear (rate), forward, backward, [all-reduce when a communicator is attached],
+ * update.  ll_sum_dev receives sum(mars[1:B,end]) of the local shard. */
+int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev,
+                    const uint8_t* miss_dev, uint64_t num_rows, const int32_t* row_ids_dev,
+                    uint32_t row_start, uint32_t B, const float* weights_dev, float clear_rate,
+                    float pseudocount, float inertia, float* ll_sum_dev, pcb_stream s);
+/* Parity accessors: mars / flows of the last batch, [B, num_nodes] column-major, ld = B. */
+int32_t pcb_get_mars(pcb_circuit* c, pcb_workspace* ws, float* mars_host, uint64_t n);
+int32_t pcb_get_flows(pcb_circuit* c, pcb_workspace* ws, float* flows_host, uint64_t n);
+
+/* ---- KLD, its gradient, Adam -------------------------------------------------------- */
+/* kld(mbpc, params1, params2) (queries/kld.jl:6-206): params are [S, P] column-major
+ * log-parameters; kld_out_dev receives klds[1:S, end]. */
+int32_t pcb_kld(pcb_circuit* c, pcb_workspace* ws, const float* params1_dev,
+                const float* params2_dev, uint32_t S, float* kld_out_dev, pcb_stream s);
+/* kld_backward (queries/kld.jl:212-320,471-577,593-649 + misc.jl:710-754) of the last pcb_kld
+ * call: gradients w.r.t. the log-parameters, [S, P] column-major. */
+int32_t pcb_kld_backward(pcb_circuit* c, pcb_workspace* ws, const float* params1_dev,
+                         const float* params2_dev, uint32_t S, float* grads1_dev,
+                         float* grads2_dev, pcb_stream s);
+/* Parity accessors for the `reuse` tuple of kld() (queries/kld.jl:177-206): klds [S, N] of the
+ * last pcb_kld call (host), and edge_klds [S, E] in up-edge order, which are not stored but
+ * recomputed from the node values and the same two parameter matrices (device buffer). */
+int32_t pcb_get_klds(pcb_circuit* c, pcb_workspace* ws, uint32_t S, float* klds_host);
+int32_t pcb_kld_edge_klds(pcb_circuit* c, pcb_workspace* ws, const float* params1_dev,
+                          const float* params2_dev, uint32_t S, float* edge_klds_dev, pcb_stream s);
+/* Adam on a flat log-parameter vector followed by re-normalisation of every sum group and
+ * every leaf (sgd/adam.jl:63-127,218-242).  sign = +1 ascends, -1 descends. */
+int32_t pcb_adam_step(pcb_circuit* c, float* theta_dev, const float* grad_dev, float* m_dev,
+                      float* v_dev, int32_t t, float lr, float beta1, float beta2, float eps,
+                      float sign, pcb_stream s);
+
+/* ---- sampling ----------------------------------------------------------------------- */
+/* Hard Gumbel-max top-down sampling, the temperature -> 0 limit of
+ * queries/sample.jl:8-148,233-296 with caller-supplied uniforms.
+ * params_dev: [Sp, P] column-major with Sp == 1 (shared) or Sp == S.
+ * u_sum_dev: [S][num_sum_regions][max_group_size] uniforms (last index fastest);
+ * u_leaf_dev: [S][num_vars][max_num_cats]; x_out_dev: [S, num_vars] column-major int32
+ * 0-based categories; -1 for variables the walk did not reach. */
+int32_t pcb_sample_hard(pcb_circuit* c, pcb_workspace* ws, const float* params_dev, uint32_t Sp,
+                        const float* u_sum_dev, const float* u_leaf_dev, uint32_t S,
+                        int32_t* x_out_dev, pcb_stream s);
+/* Soft Gumbel-softmax sampling (queries/sample.jl:8-383): u_dev [S, num_inner_params]
+ * column-major uniforms or NULL for no_gumbel=true; out_dev is input_aggr_params
+ * [S, num_vars, max_num_cats] column-major. */
+int32_t pcb_sample_soft(pcb_circuit* c, pcb_workspace* ws, const float* params_dev, uint32_t Sp,
+                        const float* u_dev, float temperature, uint32_t S, float* out_dev,
+                        pcb_stream s);
+
+/* ---- multi-GPU ---------------------------------------------------------------------- */
+/* One NCCL communicator per process; pcb_em_step then sums [edge_aggr | leaf flows | LL]
+ * over ranks before the replicated update.  The reference has no counterpart (it runs one
+ * independent job per GPU, exps/progressive_growing/pg.sh:2-7). */
+int32_t pcb_comm_unique_id(uint8_t* id_out_128);
+int32_t pcb_comm_init(pcb_circuit* c, const uint8_t* id_128, int32_t rank, int32_t nranks);
+int32_t pcb_comm_destroy(pcb_circuit* c);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PCB200_H */

@@ -1,0 +1,48 @@
+"""Builds libpcb200.so (hand-written CUDA for sm_100a behind the C ABI of include/pcb200.h)
+in-tree with nvcc.  `python -m lvd_pg_b200.build [--force] [--verbose]`."""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libpcb200.so")
+SOURCES = ["pcb_compile.cu", "pcb_em.cu", "pcb_dense.cu", "pcb_kld.cu", "pcb_sample.cu", "pcb_comm.cu"]
+NVCC = os.environ.get("PCB_NVCC", "/usr/local/cuda/bin/nvcc")
+FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
+         "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
+
+
+def _deps():
+    files = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
+    inc = os.path.join(HERE, "..", "include")
+    files += [os.path.join(inc, f) for f in os.listdir(inc)]
+    return files
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    stale = not os.path.exists(LIB) or any(os.path.getmtime(f) > os.path.getmtime(LIB) for f in _deps())
+    if not (force or stale):
+        return LIB
+    objs = []
+    for src in SOURCES:
+        obj = os.path.join(CSRC, src.replace(".cu", ".o"))
+        cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if verbose or r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed on " + src)
+        objs.append(obj)
+    cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-lcudart", "-ldl"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("link failed")
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

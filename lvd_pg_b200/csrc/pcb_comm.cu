@@ -1,0 +1,109 @@
+// pcb_comm.cu — the one collective of the multi-GPU EM step: a float sum all-reduce of the
+// statistics vector [edge flows | leaf flow slots | batch log-likelihood] over NCCL.
+//
+// The reference has no multi-GPU data path (it runs independent jobs, one per GPU:
+// exps/progressive_growing/pg.sh:2-7).  Here every rank holds a replica of the parameters,
+// processes its shard of the batch, and after this all-reduce applies the identical update.
+//
+// NCCL is bound at run time with dlopen so that libpcb200.so loads on machines without it and so
+// that a host process which already carries NCCL (PyTorch, CUDA.jl) shares the one copy.
+#include <dlfcn.h>
+
+#include <cstring>
+
+#include "pcb_internal.h"
+
+namespace {
+
+typedef struct { char internal[128]; } nccl_uid;
+typedef int (*fn_get_uid)(nccl_uid*);
+typedef int (*fn_init_rank)(void** comm, int nranks, nccl_uid id, int rank);
+typedef int (*fn_allreduce)(const void*, void*, size_t, int dtype, int op, void* comm, cudaStream_t);
+typedef int (*fn_destroy)(void* comm);
+typedef const char* (*fn_errstr)(int);
+
+struct NcclApi {
+  void* handle = nullptr;
+  fn_get_uid get_uid = nullptr;
+  fn_init_rank init_rank = nullptr;
+  fn_allreduce allreduce = nullptr;
+  fn_destroy destroy = nullptr;
+  fn_errstr errstr = nullptr;
+};
+NcclApi g_nccl;
+
+int32_t load_nccl() {
+  if (g_nccl.handle) return PCB_OK;
+  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  void* h = nullptr;
+  for (const char* n : names) {
+    h = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (h) break;
+  }
+  if (!h) return pcb_fail(PCB_ERR_NCCL, std::string("cannot load NCCL: ") + dlerror());
+  g_nccl.get_uid = (fn_get_uid)dlsym(h, "ncclGetUniqueId");
+  g_nccl.init_rank = (fn_init_rank)dlsym(h, "ncclCommInitRank");
+  g_nccl.allreduce = (fn_allreduce)dlsym(h, "ncclAllReduce");
+  g_nccl.destroy = (fn_destroy)dlsym(h, "ncclCommDestroy");
+  g_nccl.errstr = (fn_errstr)dlsym(h, "ncclGetErrorString");
+  if (!g_nccl.get_uid || !g_nccl.init_rank || !g_nccl.allreduce || !g_nccl.destroy || !g_nccl.errstr)
+    return pcb_fail(PCB_ERR_NCCL, "NCCL library lacks a required symbol");
+  g_nccl.handle = h;
+  return PCB_OK;
+}
+
+int32_t nccl_fail(const char* what, int code) {
+  return pcb_fail(PCB_ERR_NCCL, std::string(what) + ": " + (g_nccl.errstr ? g_nccl.errstr(code) : "?"));
+}
+
+}  // namespace
+
+extern "C" int32_t pcb_comm_unique_id(uint8_t* id_out_128) {
+  PCB_REQUIRE(id_out_128, "null argument");
+  int32_t st = load_nccl();
+  if (st != PCB_OK) return st;
+  nccl_uid id;
+  int rc = g_nccl.get_uid(&id);
+  if (rc != 0) return nccl_fail("ncclGetUniqueId", rc);
+  memcpy(id_out_128, id.internal, 128);
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_comm_init(pcb_circuit* c, const uint8_t* id_128, int32_t rank, int32_t nranks) {
+  PCB_REQUIRE(c && id_128, "null argument");
+  PCB_REQUIRE(nranks >= 1 && rank >= 0 && rank < nranks, "bad rank / nranks");
+  PCB_REQUIRE(c->comm == nullptr, "communicator already attached");
+  int32_t st = load_nccl();
+  if (st != PCB_OK) return st;
+  PCB_CUDA(cudaSetDevice(c->device));
+  nccl_uid id;
+  memcpy(id.internal, id_128, 128);
+  void* comm = nullptr;
+  int rc = g_nccl.init_rank(&comm, nranks, id, rank);
+  if (rc != 0) return nccl_fail("ncclCommInitRank", rc);
+  c->comm = comm;
+  c->rank = rank;
+  c->nranks = nranks;
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_comm_destroy(pcb_circuit* c) {
+  PCB_REQUIRE(c, "null argument");
+  if (c->comm && g_nccl.destroy) {
+    cudaSetDevice(c->device);
+    cudaDeviceSynchronize();
+    g_nccl.destroy(c->comm);
+  }
+  c->comm = nullptr;
+  c->nranks = 1;
+  c->rank = 0;
+  return PCB_OK;
+}
+
+int32_t pcb_allreduce_aggr(pcb_circuit* c, cudaStream_t st) {
+  if (!c->comm || c->nranks == 1) return PCB_OK;
+  // ncclFloat32 = 7, ncclSum = 0 (nccl.h: ncclDataType_t / ncclRedOp_t)
+  int rc = g_nccl.allreduce(c->aggr, c->aggr, (size_t)c->aggr_len, 7, 0, c->comm, st);
+  if (rc != 0) return nccl_fail("ncclAllReduce", rc);
+  return PCB_OK;
+}

@@ -1,0 +1,371 @@
+// pcb_em.cu — forward pass, backward flow pass, leaf statistics and the fused EM update.
+//
+// Reference kernels replaced (paths relative to VariationalJuice.jl/src):
+//   leaf_forward_kernel    init_mar!_with_reg_kernel       regularization/reg_likelihood.jl:16-49
+//   sparse_up_kernel       layer_up_kernel                 queries/likelihood.jl:4-68
+//   sparse_down_kernel     layer_down_kernel / reg_layer_down_kernel
+//                                                          queries/flow.jl:8-106, regularization/reg_flow.jl:120-222
+//   leaf_flow_kernel       input_flows_circuit_with_reg_kernel   regularization/reg_flow.jl:24-48
+//   em_update_*_kernel     add_pseudocount + aggr_node_flows + update_params + update_input_node_params
+//                                                          regularization/reg_em.jl:292-299 (arithmetic:
+//                                                          pretrain/mini_batch_warmup.jl:4-76, sgd/adam.jl:27-37,
+//                                                          nodes/fixable_categorical_dist.jl:223-248)
+//
+// All kernels put the example index on threadIdx.x, so every access to a work matrix is a
+// 128-byte coalesced row segment and edge metadata is a warp-wide broadcast.  The top-down pass
+// is pull-based (CSR by child): a node sums the flows of its incoming edges itself, so node flows
+// need no atomics and no zero-fill; only the per-edge statistics are reduced (warp shuffle, then
+// one atomic per warp and edge).
+#include <algorithm>
+
+#include "pcb_internal.h"
+
+namespace {
+
+constexpr int TPB = 128;  // threads per block along the example axis
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ int64_t data_row(const int32_t* row_ids, uint32_t row_start, uint32_t b) {
+  return row_ids ? (int64_t)row_ids[b] - 1 : (int64_t)row_start - 1 + b;
+}
+
+// mars[leaf][b] = log p(x_b) ; missing -> 0
+__global__ void leaf_forward_kernel(float* __restrict__ mars, uint32_t ld, uint32_t B,
+                                    const float* __restrict__ theta, const uint32_t* __restrict__ in_node,
+                                    const uint32_t* __restrict__ in_var, const uint64_t* __restrict__ in_poff,
+                                    const uint8_t* __restrict__ data, const uint8_t* __restrict__ miss,
+                                    uint64_t num_rows, const int32_t* __restrict__ row_ids, uint32_t row_start) {
+  uint32_t i = blockIdx.x;
+  uint32_t b = blockIdx.y * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  int64_t row = data_row(row_ids, row_start, b);
+  size_t di = (size_t)row + (size_t)num_rows * in_var[i];
+  float v = 0.0f;
+  if (!(miss && miss[di])) v = __ldg(theta + in_poff[i] + data[di]);
+  mars[(size_t)in_node[i] * ld + b] = v;
+}
+
+// One thread per (example, node).  Sum nodes: two passes over the children (max, then
+// sum of exp), which needs one exp per edge instead of the exp+log of a binary fold.
+__global__ void sparse_up_kernel(float* __restrict__ mars, uint32_t ld, uint32_t B,
+                                 const uint32_t* __restrict__ nodes, const uint8_t* __restrict__ kind,
+                                 const uint32_t* __restrict__ n_estart, const uint32_t* __restrict__ n_ecount,
+                                 const uint32_t* __restrict__ n_pid0, const uint32_t* __restrict__ e_prime,
+                                 const uint32_t* __restrict__ e_sub, const float* __restrict__ theta) {
+  uint32_t n = nodes[blockIdx.x];
+  uint32_t b = blockIdx.y * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  uint32_t e0 = n_estart[n], cnt = n_ecount[n];
+  float out;
+  if (kind[n] == PCB_SUM) {
+    const float* w = theta + n_pid0[n];
+    float mx = -INFINITY;
+    for (uint32_t j = 0; j < cnt; ++j) {
+      float v = mars[(size_t)e_prime[e0 + j] * ld + b];
+      uint32_t sb = e_sub[e0 + j];
+      if (sb != PCB_NONE) v += mars[(size_t)sb * ld + b];
+      v += __ldg(w + j);
+      mx = fmaxf(mx, v);
+    }
+    if (mx == -INFINITY) {
+      out = -INFINITY;
+    } else {
+      float acc = 0.0f;
+      for (uint32_t j = 0; j < cnt; ++j) {
+        float v = mars[(size_t)e_prime[e0 + j] * ld + b];
+        uint32_t sb = e_sub[e0 + j];
+        if (sb != PCB_NONE) v += mars[(size_t)sb * ld + b];
+        v += __ldg(w + j);
+        acc += __expf(v - mx);
+      }
+      out = mx + __logf(acc);
+    }
+  } else {
+    out = 0.0f;
+    for (uint32_t j = 0; j < cnt; ++j) {
+      out += mars[(size_t)e_prime[e0 + j] * ld + b];
+      uint32_t sb = e_sub[e0 + j];
+      if (sb != PCB_NONE) out += mars[(size_t)sb * ld + b];
+    }
+  }
+  mars[(size_t)n * ld + b] = out;
+}
+
+// Pull-based top-down pass: flows[n][b] = sum over incoming edges of the edge flow
+//   product parent: flows[parent]; sum parent: flows[parent] * exp(child value + logp - mars[parent]).
+// The root (no incoming edge, last node) gets 1, any other parentless node 0.
+__global__ void sparse_down_kernel(float* __restrict__ flows, const float* __restrict__ mars, uint32_t ld,
+                                   uint32_t B, const uint32_t* __restrict__ nodes, uint32_t root,
+                                   const uint32_t* __restrict__ in_off, const PcbInEntry* __restrict__ in_ent,
+                                   const float* __restrict__ theta, float* __restrict__ aggr) {
+  uint32_t n = nodes[blockIdx.x];
+  uint32_t b = blockIdx.y * blockDim.x + threadIdx.x;
+  bool active = b < B;
+  uint32_t bb = active ? b : 0;
+  uint32_t i0 = in_off[n], i1 = in_off[n + 1];
+  float acc = (i0 == i1 && n == root) ? 1.0f : 0.0f;
+  float my = mars[(size_t)n * ld + bb];
+  for (uint32_t i = i0; i < i1; ++i) {
+    PcbInEntry en = in_ent[i];
+    float f = flows[(size_t)en.parent * ld + bb];
+    if (en.pid != PCB_NONE) {
+      float pm = mars[(size_t)en.parent * ld + bb];
+      float lp = __ldg(theta + en.pid);
+      // order of additions as in flow.jl:55-58: prime + logp, then + sub
+      float child;
+      if (en.sib == PCB_NONE) {
+        child = my + lp;
+      } else {
+        float sv = mars[(size_t)en.sib * ld + bb];
+        child = (en.flags & 1u) ? (my + lp) + sv : (sv + lp) + my;
+      }
+      f = f * __expf(child - pm);
+      if (en.flags & 1u) {
+        float s = warp_sum(active ? f : 0.0f);
+        if ((threadIdx.x & 31) == 0) atomicAdd(aggr + en.pid, s);
+      }
+    }
+    acc += f;
+  }
+  if (active) flows[(size_t)n * ld + b] = acc;
+}
+
+// leaf statistics: aggr[foff + x_b] += flows[leaf][b] * w_b ; missing -> slot C
+__global__ void leaf_flow_kernel(const float* __restrict__ flows, uint32_t ld, uint32_t B,
+                                 float* __restrict__ aggr, const uint32_t* __restrict__ in_node,
+                                 const uint32_t* __restrict__ in_var, const uint32_t* __restrict__ in_cats,
+                                 const uint64_t* __restrict__ in_foff, const uint8_t* __restrict__ data,
+                                 const uint8_t* __restrict__ miss, uint64_t num_rows,
+                                 const int32_t* __restrict__ row_ids, uint32_t row_start,
+                                 const float* __restrict__ weights) {
+  uint32_t i = blockIdx.x;
+  uint64_t fo = in_foff[i];
+  if (fo == ~0ull) return;  // fixed leaf
+  uint32_t b = blockIdx.y * blockDim.x + threadIdx.x;
+  bool active = b < B;
+  uint32_t slot = 0xffffffffu;
+  float f = 0.0f;
+  if (active) {
+    int64_t row = data_row(row_ids, row_start, b);
+    size_t di = (size_t)row + (size_t)num_rows * in_var[i];
+    f = flows[(size_t)in_node[i] * ld + b];
+    if (weights) f *= weights[row];
+    slot = (miss && miss[di]) ? in_cats[i] : (uint32_t)data[di];
+  }
+  // combine the lanes of a warp that hit the same category before touching memory
+  uint32_t peers = __match_any_sync(0xffffffffu, slot);
+  uint32_t lane = threadIdx.x & 31;
+  uint32_t leader = __ffs(peers) - 1;
+  float total = 0.0f;
+  for (uint32_t m = peers; m; m &= m - 1) {
+    uint32_t src = __ffs(m) - 1;
+    total += __shfl_sync(peers, f, src);
+  }
+  if (active && lane == leader) atomicAdd(aggr + fo + slot, total);
+}
+
+__global__ void scale_kernel(float* __restrict__ x, uint64_t n, float rate) {
+  uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) x[i] = rate == 0.0f ? 0.0f : x[i] * rate;
+}
+
+// One warp per sum node: pseudocount, node normaliser, inertia blend, all in one pass.
+__global__ void em_update_sum_kernel(float* __restrict__ theta, float* __restrict__ aggr,
+                                     const uint32_t* __restrict__ grp_node, uint32_t n_groups,
+                                     const uint32_t* __restrict__ n_pid0, const uint32_t* __restrict__ n_ecount,
+                                     float pseudocount, float inertia) {
+  uint32_t g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  uint32_t lane = threadIdx.x & 31;
+  if (g >= n_groups) return;
+  uint32_t n = grp_node[g];
+  uint32_t p0 = n_pid0[n], cnt = n_ecount[n];
+  float pc = pseudocount / (float)cnt;
+  float tot = 0.0f;
+  for (uint32_t j = lane; j < cnt; j += 32) {
+    float a = aggr[p0 + j] + pc;
+    aggr[p0 + j] = a;  // the reference keeps the pseudocount in edge_aggr
+    tot += a;
+  }
+  tot = warp_sum(tot);
+  if (cnt == 1) return;  // single-edge sum nodes keep their parameter (reg_em.jl:150)
+  for (uint32_t j = lane; j < cnt; j += 32) {
+    float oldv = inertia * expf(theta[p0 + j]);
+    float newv = (1.0f - inertia) * aggr[p0 + j] / tot;
+    theta[p0 + j] = logf(oldv + newv);
+  }
+}
+
+// One warp per learnable leaf (fixable_categorical_dist.jl:223-248).
+__global__ void em_update_leaf_kernel(float* __restrict__ theta, const float* __restrict__ aggr,
+                                      uint32_t n_inputs, const uint32_t* __restrict__ in_cats,
+                                      const uint64_t* __restrict__ in_poff, const uint64_t* __restrict__ in_foff,
+                                      float pseudocount, float inertia) {
+  uint32_t i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  uint32_t lane = threadIdx.x & 31;
+  if (i >= n_inputs) return;
+  uint64_t fo = in_foff[i];
+  if (fo == ~0ull) return;
+  uint32_t C = in_cats[i];
+  uint64_t po = in_poff[i];
+  float s = 0.0f;
+  for (uint32_t k = lane; k < C; k += 32) s += aggr[fo + k];
+  s = warp_sum(s);
+  float missing_flow = aggr[fo + C];
+  float node_flow = s + (missing_flow + pseudocount);
+  float cat_pc = pseudocount / (float)C;
+  for (uint32_t k = lane; k < C; k += 32) {
+    float oldp = expf(theta[po + k]);
+    float oldv = inertia * oldp;
+    float newv = (1.0f - inertia) * (aggr[fo + k] + cat_pc + missing_flow * oldp) / node_flow;
+    theta[po + k] = logf(oldv + newv);
+  }
+}
+
+__global__ void ll_sum_kernel(const float* __restrict__ root_mars, uint32_t B, float* __restrict__ out) {
+  __shared__ float sh[32];
+  float s = 0.0f;
+  for (uint32_t b = threadIdx.x; b < B; b += blockDim.x) s += root_mars[b];
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : 0.0f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) *out = v;
+  }
+}
+
+dim3 grid2(uint32_t items, uint32_t B) { return dim3(items, (B + TPB - 1) / TPB, 1); }
+
+}  // namespace
+
+#define PCB_TRY(expr)              \
+  do {                             \
+    int32_t _s = (expr);           \
+    if (_s != PCB_OK) return _s;   \
+  } while (0)
+
+extern "C" int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev,
+                               const uint8_t* miss_dev, uint64_t num_rows, const int32_t* row_ids_dev,
+                               uint32_t row_start, uint32_t B, float* ll_out_dev, pcb_stream s) {
+  PCB_REQUIRE(c && ws && data_dev, "null argument");
+  PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
+  PCB_REQUIRE(B >= 1 && B <= ws->max_batch, "batch size exceeds the workspace");
+  PCB_REQUIRE(row_ids_dev || (row_start >= 1 && (uint64_t)row_start - 1 + B <= num_rows), "row range out of bounds");
+  PCB_CUDA(cudaSetDevice(c->device));
+  cudaStream_t st = (cudaStream_t)s;
+  ws->B = B; ws->data = data_dev; ws->miss = miss_dev; ws->num_rows = num_rows;
+  ws->row_ids = row_ids_dev; ws->row_start = row_start; ws->have_forward = false;
+  if (c->n_inputs)
+    leaf_forward_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(ws->mars, ws->ld, B, c->theta, c->in_node, c->in_var,
+                                                               c->in_poff, data_dev, miss_dev, num_rows,
+                                                               row_ids_dev, row_start);
+  for (uint32_t lay = 1; lay <= c->L; ++lay) {
+    uint32_t o0 = c->h_up_sparse_off[lay - 1], o1 = c->h_up_sparse_off[lay];
+    if (o1 > o0)
+      sparse_up_kernel<<<grid2(o1 - o0, B), TPB, 0, st>>>(ws->mars, ws->ld, B, c->up_sparse + o0, c->kind,
+                                                          c->n_estart, c->n_ecount, c->n_pid0, c->e_prime,
+                                                          c->e_sub, c->theta);
+    PCB_TRY(pcb_dense_forward(c, ws, lay, st));
+  }
+  if (ll_out_dev)
+    PCB_CUDA(cudaMemcpyAsync(ll_out_dev, ws->mars + (size_t)(c->N - 1) * ws->ld, B * sizeof(float),
+                             cudaMemcpyDeviceToDevice, st));
+  PCB_CUDA(cudaGetLastError());
+  ws->have_forward = true;
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* weights_dev, pcb_stream s) {
+  PCB_REQUIRE(c && ws, "null argument");
+  PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
+  if (!ws->have_forward) return pcb_fail(PCB_ERR_STATE, "pcb_backward needs a preceding pcb_forward on this workspace");
+  PCB_CUDA(cudaSetDevice(c->device));
+  cudaStream_t st = (cudaStream_t)s;
+  const uint32_t B = ws->B;
+  for (int64_t lay = c->L; lay >= 0; --lay) {
+    uint32_t o0 = c->h_down_sparse_off[lay], o1 = c->h_down_sparse_off[lay + 1];
+    if (o1 > o0)
+      sparse_down_kernel<<<grid2(o1 - o0, B), TPB, 0, st>>>(ws->flows, ws->mars, ws->ld, B, c->down_sparse + o0,
+                                                            c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr);
+    if (lay >= 1) PCB_TRY(pcb_dense_backward(c, ws, (uint32_t)lay, st));
+  }
+  if (c->n_inputs)
+    leaf_flow_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(ws->flows, ws->ld, B, c->aggr, c->in_node, c->in_var,
+                                                            c->in_cats, c->in_foff, ws->data, ws->miss,
+                                                            ws->num_rows, ws->row_ids, ws->row_start, weights_dev);
+  PCB_CUDA(cudaGetLastError());
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_clear_flows(pcb_circuit* c, float rate, pcb_stream s) {
+  PCB_REQUIRE(c, "null argument");
+  PCB_CUDA(cudaSetDevice(c->device));
+  cudaStream_t st = (cudaStream_t)s;
+  if (rate == 0.0f) {
+    PCB_CUDA(cudaMemsetAsync(c->aggr, 0, c->aggr_len * sizeof(float), st));
+  } else {
+    uint64_t n = c->aggr_len - 1;
+    uint32_t blocks = (uint32_t)std::min<uint64_t>((n + 255) / 256, 148 * 16);
+    if (n) scale_kernel<<<blocks, 256, 0, st>>>(c->aggr, n, rate);
+    PCB_CUDA(cudaMemsetAsync(c->aggr + n, 0, sizeof(float), st));
+    PCB_CUDA(cudaGetLastError());
+  }
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_em_update(pcb_circuit* c, float pseudocount, float inertia, pcb_stream s) {
+  PCB_REQUIRE(c, "null argument");
+  PCB_CUDA(cudaSetDevice(c->device));
+  cudaStream_t st = (cudaStream_t)s;
+  if (c->n_groups)
+    em_update_sum_kernel<<<(c->n_groups + 7) / 8, 256, 0, st>>>(c->theta, c->aggr, c->grp_node, c->n_groups,
+                                                                c->n_pid0, c->n_ecount, pseudocount, inertia);
+  if (c->n_inputs)
+    em_update_leaf_kernel<<<(c->n_inputs + 7) / 8, 256, 0, st>>>(c->theta, c->aggr, c->n_inputs, c->in_cats,
+                                                                 c->in_poff, c->in_foff, pseudocount, inertia);
+  PCB_CUDA(cudaGetLastError());
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev,
+                               const uint8_t* miss_dev, uint64_t num_rows, const int32_t* row_ids_dev,
+                               uint32_t row_start, uint32_t B, const float* weights_dev, float clear_rate,
+                               float pseudocount, float inertia, float* ll_sum_dev, pcb_stream s) {
+  PCB_REQUIRE(c && ws, "null argument");
+  cudaStream_t st = (cudaStream_t)s;
+  PCB_TRY(pcb_clear_flows(c, clear_rate, s));
+  PCB_TRY(pcb_forward(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, nullptr, s));
+  PCB_TRY(pcb_backward(c, ws, weights_dev, s));
+  // batch log-likelihood into the last slot of the statistics vector, so it is reduced with them
+  ll_sum_kernel<<<1, 256, 0, st>>>(ws->mars + (size_t)(c->N - 1) * ws->ld, B, c->aggr + c->aggr_len - 1);
+  if (c->comm) PCB_TRY(pcb_allreduce_aggr(c, st));
+  if (ll_sum_dev)
+    PCB_CUDA(cudaMemcpyAsync(ll_sum_dev, c->aggr + c->aggr_len - 1, sizeof(float), cudaMemcpyDeviceToDevice, st));
+  PCB_TRY(pcb_em_update(c, pseudocount, inertia, s));
+  PCB_CUDA(cudaGetLastError());
+  return PCB_OK;
+}
+
+static int32_t get_matrix(pcb_circuit* c, pcb_workspace* ws, const float* src, float* host, uint64_t n) {
+  PCB_REQUIRE(c && ws && host, "null argument");
+  PCB_REQUIRE(ws->have_forward, "no batch has been evaluated on this workspace");
+  PCB_REQUIRE(n == (uint64_t)ws->B * c->N, "matrix has the wrong size");
+  PCB_CUDA(cudaSetDevice(c->device));
+  PCB_CUDA(cudaDeviceSynchronize());
+  PCB_CUDA(cudaMemcpy2D(host, ws->B * sizeof(float), src, ws->ld * sizeof(float), ws->B * sizeof(float), c->N,
+                        cudaMemcpyDeviceToHost));
+  return PCB_OK;
+}
+extern "C" int32_t pcb_get_mars(pcb_circuit* c, pcb_workspace* ws, float* mars_host, uint64_t n) {
+  return get_matrix(c, ws, ws ? ws->mars : nullptr, mars_host, n);
+}
+extern "C" int32_t pcb_get_flows(pcb_circuit* c, pcb_workspace* ws, float* flows_host, uint64_t n) {
+  return get_matrix(c, ws, ws ? ws->flows : nullptr, flows_host, n);
+}

@@ -1,0 +1,158 @@
+// pcb_internal.h — data layout of a compiled circuit in HBM, shared by the translation units
+// of libpcb200.so.
+//
+// Layout decisions (all ids 0-based on the device):
+//  * Work matrices (mars, flows, klds, ...) are node-major with the example index contiguous:
+//    element (b, n) at n*ld + b, ld a multiple of 32 floats.  This is the reference's column-major
+//    [B, N] matrix with a padded leading dimension, so a warp that covers 32 examples of one node
+//    reads and writes 128 contiguous bytes.
+//  * Parameters live in ONE flat vector `theta` in the reference's flat order
+//    (sum-edge log-params in up-edge order, then the log-probs of learnable leaves in input-node
+//    order; log-probs of fixed leaves are appended behind it).  vectorize/update_parameters are
+//    plain copies and KLD / Adam / sampling read the same vector the EM step updates.
+//  * Sufficient statistics live in ONE flat vector `aggr` = [edge flows by param id |
+//    leaf flow slots (C+1 per learnable leaf) | batch log-likelihood sum], which is exactly the
+//    buffer the multi-GPU step all-reduces.
+//  * A dense block is a run of R sum nodes with consecutive ids that all have the same K children
+//    (prime ids c0..c0+K-1, optional sub ids d0..d0+K-1); its R*K parameters are consecutive in
+//    theta (row = parent, child index fastest).  HCLT latent transitions are such blocks.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/pcb200.h"
+
+#define PCB_NONE 0xffffffffu
+
+struct PcbDenseBlock {
+  uint32_t p0;    // first parent node
+  uint32_t R;     // number of parents
+  uint32_t K;     // number of children
+  uint32_t c0;    // first prime child
+  uint32_t d0;    // first sub child or PCB_NONE
+  uint32_t pid0;  // first parameter id
+  uint32_t mx_row;  // row of the per-block max buffer in the workspace
+  uint32_t pad;
+};
+
+// incoming-edge entry of a node (CSR by child, used by every top-down pass)
+struct PcbInEntry {
+  uint32_t parent;
+  uint32_t sib;   // the other child of the edge or PCB_NONE
+  uint32_t pid;   // parameter id of a sum edge, PCB_NONE for product edges
+  uint32_t flags; // bit0: this node is the prime child of the edge (aggregating entry)
+};
+
+struct pcb_circuit {
+  int device = 0;
+  uint32_t N = 0, E = 0, V = 0, L = 0;  // nodes, edges, variables, up layers (layer 0 = inputs)
+  uint32_t n_inner = 0, n_input_params = 0, n_groups = 0, n_inputs = 0;
+  uint32_t n_regions = 0, max_group = 0, max_cats = 0;
+  uint64_t P = 0;            // n_inner + n_input_params
+  uint64_t theta_len = 0;    // P + log-probs of fixed leaves
+  uint64_t n_leaf_flow = 0;  // total leaf flow slots
+  uint64_t aggr_len = 0;     // n_inner + n_leaf_flow + 1
+  uint64_t dense_edges = 0;
+  uint64_t device_bytes = 0;
+
+  // ---- device arrays ----
+  float* theta = nullptr;
+  float* aggr = nullptr;
+  uint8_t* kind = nullptr;        // [N]
+  uint32_t* n_estart = nullptr;   // [N] first up-edge of an inner node
+  uint32_t* n_ecount = nullptr;   // [N]
+  uint32_t* n_pid0 = nullptr;     // [N] first parameter id of a sum node
+  uint32_t* n_region = nullptr;   // [N] 0-based sum region or PCB_NONE
+  uint32_t* e_prime = nullptr;    // [E]
+  uint32_t* e_sub = nullptr;      // [E]
+  // leaves, indexed by input index i (input_node_ids order)
+  uint32_t* in_node = nullptr;    // [n_inputs] node id
+  uint32_t* in_var = nullptr;     // [n_inputs] 0-based variable
+  uint32_t* in_cats = nullptr;    // [n_inputs]
+  uint64_t* in_poff = nullptr;    // [n_inputs] offset of the log-probs in theta
+  uint64_t* in_foff = nullptr;    // [n_inputs] offset of the flow slots in aggr, ~0 for fixed
+  uint32_t* node2input = nullptr; // [N] input index or PCB_NONE
+  // layer lists: all inner nodes by layer / only those outside dense blocks
+  uint32_t* up_all = nullptr;     // [n_inner_nodes]
+  uint32_t* up_sparse = nullptr;
+  uint32_t* down_all = nullptr;   // [N] every node, by layer
+  uint32_t* down_sparse = nullptr;
+  uint32_t* in_off = nullptr;     // [N+1] CSR by child
+  PcbInEntry* in_ent = nullptr;
+  PcbDenseBlock* dense = nullptr; // sorted by parent layer
+  uint32_t* grp_node = nullptr;   // [n_groups] sum node of each parameter group
+
+  // ---- host copies of the small per-layer tables ----
+  std::vector<uint32_t> h_up_all_off, h_up_sparse_off;      // [L+1] (index = layer-1)
+  std::vector<uint32_t> h_down_all_off, h_down_sparse_off;  // [L+2] (index = layer)
+  std::vector<uint32_t> h_dense_off;                        // [L+1] blocks by parent layer
+  std::vector<PcbDenseBlock> h_dense;
+  uint32_t n_dense = 0;
+  uint32_t max_dense_K = 0, max_dense_R = 0;
+
+  // ---- host data kept for accessors ----
+  std::vector<uint32_t> h_down2up;       // 0-based
+  std::vector<uint32_t> h_edge2param;    // [E] 1-based pid or 0
+  std::vector<uint32_t> h_region1;       // [N] 1-based region or 0
+  std::vector<uint32_t> h_in_node, h_in_cats, h_heap_start;
+  std::vector<uint8_t> h_in_fixed;
+  std::vector<uint64_t> h_in_poff, h_in_foff;
+  uint64_t heap_len = 0;
+
+  // ---- multi-GPU ----
+  void* comm = nullptr;  // ncclComm_t
+  int nranks = 1, rank = 0;
+};
+
+struct pcb_workspace {
+  pcb_circuit* c = nullptr;
+  uint32_t max_batch = 0, ld = 0;
+  float* mars = nullptr;    // [N][ld]
+  float* flows = nullptr;   // [N][ld]
+  float* blk_mx = nullptr;  // [n_dense][ld] per-example max of a dense block's children
+  // state of the last forward
+  uint32_t B = 0;
+  const uint8_t* data = nullptr;
+  const uint8_t* miss = nullptr;
+  uint64_t num_rows = 0;
+  const int32_t* row_ids = nullptr;
+  uint32_t row_start = 1;
+  bool have_forward = false;
+  // per-parameter-set buffers, allocated on first use
+  uint32_t S_cap = 0, ldS = 0;
+  float* klds = nullptr;     // [N][ldS]
+  float* grads = nullptr;    // [N][ldS]  (also td_probs)
+  float* eprob = nullptr;    // [n_inner][ldS]
+  float* cum = nullptr;      // [n_groups][ldS]
+  uint32_t* stack = nullptr; // [S_cap][stack_cap]
+  uint32_t stack_cap = 0;
+  uint32_t kld_S = 0;
+  bool have_kld = false;
+};
+
+// ---- helpers ----
+void pcb_set_error(const std::string& msg);
+int32_t pcb_fail(int32_t code, const std::string& msg);
+
+#define PCB_CUDA(expr)                                                                     \
+  do {                                                                                     \
+    cudaError_t _e = (expr);                                                               \
+    if (_e != cudaSuccess)                                                                 \
+      return pcb_fail(PCB_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(_e));   \
+  } while (0)
+
+#define PCB_REQUIRE(cond, msg) \
+  do {                         \
+    if (!(cond)) return pcb_fail(PCB_ERR_INVALID, msg); \
+  } while (0)
+
+static inline uint32_t pcb_round_up(uint32_t x, uint32_t m) { return (x + m - 1) / m * m; }
+
+// entry points implemented across translation units and used by pcb_em_step
+int32_t pcb_allreduce_aggr(pcb_circuit* c, cudaStream_t st);
+int32_t pcb_dense_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
+int32_t pcb_dense_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
+int32_t pcb_ws_ensure_sets(pcb_workspace* ws, uint32_t S, bool need_stack);

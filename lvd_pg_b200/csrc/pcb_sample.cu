@@ -1,0 +1,262 @@
+// pcb_sample.cu — top-down sampling.
+//
+//  * pcb_sample_hard: Gumbel-max walk, one warp per sample.  At a sum node the lanes split the
+//    edges, each computes key = logp + g(u) in fp64 with the shared host/device routine of
+//    include/pcb200_gumbel.h, and a shuffle arg-max (lowest index on ties) picks the edge; a
+//    product node pushes all its children; a leaf does the same arg-max over its categories.
+//    This is the temperature -> 0 limit of the reference's relaxed sampler
+//    (VariationalJuice.jl/src/queries/sample.jl:8-148,233-296), fed with caller-supplied
+//    uniforms instead of the in-kernel rand(Float32) of sample.jl:45.
+//  * pcb_sample_soft: the relaxed sampler itself — gumbel_params_down_kernel (sample.jl:8-58),
+//    gumbel_sample_down_kernel (:60-148), gumbel_input_sample_down_kernel (:233-296).
+#include <algorithm>
+
+#include "../../include/pcb200_gumbel.h"
+#include "pcb_internal.h"
+
+namespace {
+
+struct Shape2 {
+  dim3 block, grid;
+};
+Shape2 shape_for(uint32_t S, uint32_t items) {
+  uint32_t bx = 1;
+  while (bx < S && bx < 32) bx <<= 1;
+  uint32_t by = 128 / bx;
+  Shape2 s;
+  s.block = dim3(bx, by, 1);
+  s.grid = dim3((items + by - 1) / by, (S + bx - 1) / bx, 1);
+  return s;
+}
+
+__device__ __forceinline__ void warp_argmax(double& key, uint32_t& idx) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    double ok = __shfl_xor_sync(0xffffffffu, key, o);
+    uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (oi != 0xffffffffu && (idx == 0xffffffffu || ok > key || (ok == key && oi < idx))) {
+      key = ok;
+      idx = oi;
+    }
+  }
+}
+
+// status word: 0 ok, 1 stack overflow, 2 iteration limit (malformed circuit)
+__global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params, uint32_t Sp,
+                                   const float* __restrict__ u_sum, const float* __restrict__ u_leaf, uint32_t R,
+                                   uint32_t kmax, uint32_t cmax, uint32_t V, uint32_t N,
+                                   const uint8_t* __restrict__ kind, const uint32_t* __restrict__ n_estart,
+                                   const uint32_t* __restrict__ n_ecount, const uint32_t* __restrict__ n_pid0,
+                                   const uint32_t* __restrict__ n_region, const uint32_t* __restrict__ e_prime,
+                                   const uint32_t* __restrict__ e_sub, const uint32_t* __restrict__ node2input,
+                                   const uint32_t* __restrict__ in_var, const uint32_t* __restrict__ in_cats,
+                                   const uint64_t* __restrict__ in_poff, uint64_t P,
+                                   const float* __restrict__ theta, uint32_t* __restrict__ stack_all,
+                                   uint32_t stack_cap, int32_t* __restrict__ x_out, int32_t* __restrict__ status) {
+  const uint32_t s = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  if (s >= S) return;
+  const size_t ps = Sp == 1 ? 0 : s, pld = Sp;
+  uint32_t* stack = stack_all + (size_t)s * stack_cap;
+  for (uint32_t v = lane; v < V; v += 32) x_out[s + (size_t)S * v] = -1;
+  uint32_t sp = 1;
+  if (lane == 0) stack[0] = N - 1;
+  __syncwarp();
+  const uint32_t max_iter = 4u * N + 8u;
+  for (uint32_t it = 0; sp > 0; ++it) {
+    if (it >= max_iter) {
+      if (lane == 0) atomicMax(status, 2);
+      break;
+    }
+    uint32_t n = stack[--sp];
+    __syncwarp();
+    uint8_t kd = kind[n];
+    if (kd == PCB_INPUT) {
+      uint32_t i = node2input[n];
+      uint32_t C = in_cats[i], var = in_var[i];
+      uint64_t off = in_poff[i];
+      const float* us = u_leaf + ((size_t)s * V + var) * cmax;
+      double best = 0.0;
+      uint32_t bi = 0xffffffffu;
+      for (uint32_t c = lane; c < C; c += 32) {
+        // fixed leaves keep their log-probs in the circuit, not in the caller's parameter matrix
+        float lp = off < P ? params[ps + pld * (off + c)] : theta[off + c];
+        double key = pcb_gumbel_key(lp, us[c]);
+        if (bi == 0xffffffffu || key > best) { best = key; bi = c; }
+      }
+      warp_argmax(best, bi);
+      if (lane == 0) x_out[s + (size_t)S * var] = (int32_t)bi;
+    } else if (kd == PCB_PRODUCT) {
+      uint32_t e0 = n_estart[n], cnt = n_ecount[n];
+      // count pushes first so that every lane keeps the same stack pointer
+      uint32_t pushes = 0;
+      for (uint32_t j = lane; j < cnt; j += 32) pushes += e_sub[e0 + j] != PCB_NONE ? 2 : 1;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) pushes += __shfl_xor_sync(0xffffffffu, pushes, o);
+      if (sp + pushes > stack_cap) {
+        if (lane == 0) atomicMax(status, 1);
+        break;
+      }
+      if (lane == 0) {
+        uint32_t q = sp;
+        for (uint32_t j = 0; j < cnt; ++j) {
+          stack[q++] = e_prime[e0 + j];
+          uint32_t sb = e_sub[e0 + j];
+          if (sb != PCB_NONE) stack[q++] = sb;
+        }
+      }
+      sp += pushes;
+      __syncwarp();
+    } else {
+      uint32_t e0 = n_estart[n], cnt = n_ecount[n], pid0 = n_pid0[n];
+      const float* us = u_sum + ((size_t)s * R + n_region[n]) * kmax;
+      double best = 0.0;
+      uint32_t bi = 0xffffffffu;
+      for (uint32_t j = lane; j < cnt; j += 32) {
+        double key = pcb_gumbel_key(params[ps + pld * (size_t)(pid0 + j)], us[j]);
+        if (bi == 0xffffffffu || key > best) { best = key; bi = j; }
+      }
+      warp_argmax(best, bi);
+      uint32_t e = e0 + bi;
+      uint32_t pr = e_prime[e], sb = e_sub[e];
+      uint32_t pushes = sb != PCB_NONE ? 2 : 1;
+      if (sp + pushes > stack_cap) {
+        if (lane == 0) atomicMax(status, 1);
+        break;
+      }
+      if (lane == 0) {
+        stack[sp] = pr;
+        if (sb != PCB_NONE) stack[sp + 1] = sb;
+      }
+      sp += pushes;
+      __syncwarp();
+    }
+  }
+}
+
+// ---- soft sampling ------------------------------------------------------------------------------
+// unnormalised relaxed edge probabilities and their per-node sums; cum is stored per sum NODE
+__global__ void soft_params_kernel(float* __restrict__ eprob, float* __restrict__ cum, uint32_t ld, uint32_t S,
+                                   const float* __restrict__ params, uint32_t Sp, const float* __restrict__ u,
+                                   float temperature, const uint32_t* __restrict__ grp_node, uint32_t n_groups,
+                                   const uint32_t* __restrict__ n_pid0, const uint32_t* __restrict__ n_ecount) {
+  uint32_t g = blockIdx.x * blockDim.y + threadIdx.y;
+  uint32_t s = blockIdx.y * blockDim.x + threadIdx.x;
+  if (g >= n_groups || s >= S) return;
+  uint32_t n = grp_node[g];
+  uint32_t pid0 = n_pid0[n], cnt = n_ecount[n];
+  const size_t ps = Sp == 1 ? 0 : s, pld = Sp;
+  float sum = 0.0f;
+  for (uint32_t j = 0; j < cnt; ++j) {
+    float logp = params[ps + pld * (size_t)(pid0 + j)];
+    double gv = 0.0;
+    if (u) gv = -log(-log((double)u[s + (size_t)S * (pid0 + j)] * (1.0 - 1e-6) + 1e-6));
+    float unnorm = (float)exp(((double)logp + gv) / (double)temperature);
+    eprob[(size_t)(pid0 + j) * ld + s] = unnorm;
+    sum += unnorm;
+  }
+  cum[(size_t)n * ld + s] = sum;
+}
+
+__global__ void soft_down_kernel(float* __restrict__ td, uint32_t ld, uint32_t S, const float* __restrict__ eprob,
+                                 const float* __restrict__ cum, const uint32_t* __restrict__ nodes, uint32_t count,
+                                 uint32_t root, const uint32_t* __restrict__ in_off,
+                                 const PcbInEntry* __restrict__ in_ent) {
+  uint32_t i = blockIdx.x * blockDim.y + threadIdx.y;
+  uint32_t s = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= count || s >= S) return;
+  uint32_t n = nodes[i];
+  uint32_t i0 = in_off[n], i1 = in_off[n + 1];
+  float acc = (i0 == i1 && n == root) ? 1.0f : 0.0f;
+  for (uint32_t x = i0; x < i1; ++x) {
+    PcbInEntry en = in_ent[x];
+    float tp = td[(size_t)en.parent * ld + s];
+    if (en.pid != PCB_NONE) tp *= eprob[(size_t)en.pid * ld + s] / cum[(size_t)en.parent * ld + s];
+    acc += tp;
+  }
+  td[(size_t)n * ld + s] = acc;
+}
+
+__global__ void soft_leaf_kernel(const float* __restrict__ td, uint32_t ld, uint32_t S,
+                                 const float* __restrict__ params, uint32_t Sp, uint32_t n_inputs, uint32_t V,
+                                 const uint32_t* __restrict__ in_node, const uint32_t* __restrict__ in_var,
+                                 const uint32_t* __restrict__ in_cats, const uint64_t* __restrict__ in_poff,
+                                 uint64_t P, const float* __restrict__ theta, float* __restrict__ out) {
+  uint32_t i = blockIdx.x * blockDim.y + threadIdx.y;
+  uint32_t s = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= n_inputs || s >= S) return;
+  const size_t ps = Sp == 1 ? 0 : s, pld = Sp;
+  float tp = td[(size_t)in_node[i] * ld + s];
+  uint32_t C = in_cats[i], var = in_var[i];
+  uint64_t off = in_poff[i];
+  for (uint32_t k = 0; k < C; ++k) {
+    // fixed leaves keep their log-probs in the circuit, not in the caller's parameter matrix
+    float lp = off < P ? params[ps + pld * (off + k)] : theta[off + k];
+    atomicAdd(out + s + (size_t)S * (var + (size_t)V * k), tp * expf(lp));
+  }
+}
+
+}  // namespace
+
+extern "C" int32_t pcb_sample_hard(pcb_circuit* c, pcb_workspace* ws, const float* params_dev, uint32_t Sp,
+                                   const float* u_sum_dev, const float* u_leaf_dev, uint32_t S, int32_t* x_out_dev,
+                                   pcb_stream s) {
+  PCB_REQUIRE(c && ws && params_dev && u_leaf_dev && x_out_dev, "null argument");
+  PCB_REQUIRE(u_sum_dev || c->n_regions == 0, "u_sum missing");
+  PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
+  PCB_REQUIRE(S >= 1 && (Sp == 1 || Sp == S), "params must hold 1 or S parameter sets");
+  PCB_CUDA(cudaSetDevice(c->device));
+  int32_t st0 = pcb_ws_ensure_sets(ws, S, true);
+  if (st0 != PCB_OK) return st0;
+  cudaStream_t st = (cudaStream_t)s;
+  int32_t* status = reinterpret_cast<int32_t*>(ws->cum);  // scratch word
+  PCB_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
+  uint32_t warps_per_block = 4;
+  sample_hard_kernel<<<(S + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, st>>>(
+      S, params_dev, Sp, u_sum_dev, u_leaf_dev, c->n_regions, c->max_group, c->max_cats, c->V, c->N, c->kind,
+      c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime, c->e_sub, c->node2input, c->in_var, c->in_cats,
+      c->in_poff, c->P, c->theta, ws->stack, ws->stack_cap, x_out_dev, status);
+  PCB_CUDA(cudaGetLastError());
+  int32_t h = 0;
+  PCB_CUDA(cudaMemcpyAsync(&h, status, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  PCB_CUDA(cudaStreamSynchronize(st));
+  if (h == 1) return pcb_fail(PCB_ERR_TOO_LARGE, "sampling walk overflowed its stack (circuit not decomposable?)");
+  if (h == 2) return pcb_fail(PCB_ERR_INVALID, "sampling walk exceeded its iteration limit (malformed circuit)");
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_sample_soft(pcb_circuit* c, pcb_workspace* ws, const float* params_dev, uint32_t Sp,
+                                   const float* u_dev, float temperature, uint32_t S, float* out_dev, pcb_stream s) {
+  PCB_REQUIRE(c && ws && params_dev && out_dev, "null argument");
+  PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
+  PCB_REQUIRE(S >= 1 && (Sp == 1 || Sp == S), "params must hold 1 or S parameter sets");
+  PCB_REQUIRE(temperature > 0.0f, "temperature must be positive");
+  PCB_CUDA(cudaSetDevice(c->device));
+  int32_t st0 = pcb_ws_ensure_sets(ws, S, true);
+  if (st0 != PCB_OK) return st0;
+  cudaStream_t st = (cudaStream_t)s;
+  const uint32_t ld = ws->ldS;
+  ws->have_kld = false;  // klds rows are reused for the per-node normalisers
+  float* cum = ws->klds;
+  float* td = ws->grads;
+  PCB_CUDA(cudaMemsetAsync(out_dev, 0, (size_t)S * c->V * c->max_cats * sizeof(float), st));
+  if (c->n_groups) {
+    Shape2 sh = shape_for(S, c->n_groups);
+    soft_params_kernel<<<sh.grid, sh.block, 0, st>>>(ws->eprob, cum, ld, S, params_dev, Sp, u_dev, temperature,
+                                                     c->grp_node, c->n_groups, c->n_pid0, c->n_ecount);
+  }
+  for (int64_t lay = c->L; lay >= 0; --lay) {
+    uint32_t o0 = c->h_down_all_off[lay], o1 = c->h_down_all_off[lay + 1];
+    if (o1 == o0) continue;
+    Shape2 sh = shape_for(S, o1 - o0);
+    soft_down_kernel<<<sh.grid, sh.block, 0, st>>>(td, ld, S, ws->eprob, cum, c->down_all + o0, o1 - o0, c->N - 1,
+                                                   c->in_off, c->in_ent);
+  }
+  if (c->n_inputs) {
+    Shape2 sh = shape_for(S, c->n_inputs);
+    soft_leaf_kernel<<<sh.grid, sh.block, 0, st>>>(td, ld, S, params_dev, Sp, c->n_inputs, c->V, c->in_node, c->in_var,
+                                                   c->in_cats, c->in_poff, c->P, c->theta, out_dev);
+  }
+  PCB_CUDA(cudaGetLastError());
+  return PCB_OK;
+}

@@ -1,0 +1,229 @@
+"""ctypes front-end of the CPU oracle (oracle/pc_oracle.c).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by `__graft_entry__.smoke()` and by the
+`cpu_baseline` / `--impl reference` legs of bench.py.  The product package never imports it.
+
+All matrices are handed back as numpy arrays of shape [B, N] in Fortran order (the
+reference's column-major layout), so `mars[b, n]` reads like the Julia code (0-based).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+def build(force: bool = False) -> str:
+    path = os.path.join(_HERE, "libpc_oracle.so")
+    src = os.path.join(_HERE, "pc_oracle.c")
+    hdrs = [os.path.join(_HERE, "..", "include", h) for h in ("pcb200.h", "pcb200_gumbel.h")]
+    stale = (not os.path.exists(path)) or any(
+        os.path.exists(p) and os.path.getmtime(p) > os.path.getmtime(path) for p in [src] + hdrs)
+    if force or stale:
+        subprocess.run(["make", "-C", _HERE, "-B", "libpc_oracle.so"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return path
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = C.CDLL(build())
+        _LIB.orc_num_threads.restype = C.c_int
+        _LIB.orc_gumbel_key.restype = C.c_double
+        _LIB.orc_log.restype = C.c_double
+    return _LIB
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _f(shape):
+    return np.zeros(shape, dtype=np.float32, order="F")
+
+
+def gumbel_key(logp: float, u: float) -> float:
+    return float(lib().orc_gumbel_key(C.c_float(logp), C.c_float(u)))
+
+
+def det_log(x: float) -> float:
+    return float(lib().orc_log(C.c_double(x)))
+
+
+def num_threads() -> int:
+    return int(lib().orc_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    lib().orc_set_num_threads(C.c_int(n))
+
+
+def counts(fc):
+    d = fc.desc()
+    a, b, g = C.c_uint32(), C.c_uint32(), C.c_uint32()
+    lib().orc_counts(C.byref(d), C.byref(a), C.byref(b), C.byref(g))
+    return a.value, b.value, g.value
+
+
+def meta(fc):
+    d = fc.desc()
+    ni, nl, ng = counts(fc)
+    e2p = np.zeros(fc.num_edges, np.uint32)
+    p2e = np.zeros(ni, np.uint32)
+    p2g = np.zeros(ni, np.uint32)
+    cum = np.zeros(len(fc.input_node_ids), np.uint32)
+    lib().orc_meta(C.byref(d), _p(e2p), _p(p2e), _p(p2g), _p(cum))
+    return {"edge2param": e2p, "param2edge": p2e, "param2group": p2g, "innode2ncumparam": cum,
+            "num_inner_params": ni, "num_input_params": nl, "num_param_groups": ng}
+
+
+def vectorize(fc) -> np.ndarray:
+    d = fc.desc()
+    ni, nl, _ = counts(fc)
+    out = np.zeros(ni + nl, np.float32)
+    lib().orc_vectorize(C.byref(d), _p(fc.up_logp), _p(fc.heap), _p(out))
+    return out
+
+
+def update_parameters(fc, params) -> None:
+    d = fc.desc()
+    params = np.ascontiguousarray(params, np.float32)
+    lib().orc_update_parameters(C.byref(d), _p(fc.up_logp), _p(fc.heap), _p(params))
+
+
+def _data_args(data, miss, row_ids, row_start, B):
+    data = np.asfortranarray(data, dtype=np.uint8)
+    miss = None if miss is None else np.asfortranarray(miss, dtype=np.uint8)
+    rid = None if row_ids is None else np.ascontiguousarray(row_ids, np.int32)
+    if B is None:
+        B = len(rid) if rid is not None else data.shape[0] - (row_start - 1)
+    return data, miss, rid, int(B)
+
+
+def forward(fc, data, row_ids=None, row_start=1, B=None, miss=None, want_edge_mars=False):
+    d = fc.desc()
+    data, miss, rid, B = _data_args(data, miss, row_ids, row_start, B)
+    mars = _f((B, fc.num_nodes))
+    em = _f((B, fc.num_edges)) if want_edge_mars else None
+    lib().orc_forward(C.byref(d), _p(fc.up_logp), _p(fc.heap), _p(data), _p(miss),
+                      C.c_uint64(data.shape[0]), _p(rid), C.c_uint32(row_start), C.c_uint32(B),
+                      _p(mars), _p(em))
+    return (mars, em) if want_edge_mars else mars
+
+
+def backward(fc, mars, edge_aggr=None, want_edge_flows=False):
+    d = fc.desc()
+    B = mars.shape[0]
+    flows = _f((B, fc.num_nodes))
+    ef = _f((B, fc.num_edges)) if want_edge_flows else None
+    if edge_aggr is None:
+        edge_aggr = np.zeros(fc.num_edges, np.float32)
+    lib().orc_backward(C.byref(d), _p(fc.up_logp), _p(np.asfortranarray(mars)), C.c_uint32(B),
+                       _p(flows), _p(ef), _p(edge_aggr))
+    return (flows, ef, edge_aggr) if want_edge_flows else (flows, edge_aggr)
+
+
+def input_flows(fc, flows, data, row_ids=None, row_start=1, miss=None, weights=None):
+    d = fc.desc()
+    data, miss, rid, B = _data_args(data, miss, row_ids, row_start, flows.shape[0])
+    w = None if weights is None else np.ascontiguousarray(weights, np.float32)
+    lib().orc_input_flows(C.byref(d), _p(fc.heap), _p(np.asfortranarray(flows)), _p(data), _p(miss),
+                          C.c_uint64(data.shape[0]), _p(rid), C.c_uint32(row_start), C.c_uint32(B), _p(w))
+
+
+def clear_flows(fc, edge_aggr, rate=0.0):
+    d = fc.desc()
+    lib().orc_clear_flows(C.byref(d), _p(edge_aggr), _p(fc.heap), C.c_float(rate))
+
+
+def em_update(fc, edge_aggr, pseudocount, inertia):
+    d = fc.desc()
+    lib().orc_em_update(C.byref(d), _p(fc.up_logp), _p(edge_aggr), _p(fc.heap),
+                        C.c_float(pseudocount), C.c_float(inertia))
+
+
+def em_step(fc, data, row_ids=None, row_start=1, B=None, pseudocount=0.1, inertia=0.0, miss=None,
+            weights=None, edge_aggr=None, clear_rate=0.0):
+    """Per-batch body of mini_batch_em_with_reg (regularization/reg_em.jl:273-301).
+    Mutates fc.up_logp and fc.heap; returns (sum of batch LLs, edge_aggr before the update)."""
+    if edge_aggr is None:
+        edge_aggr = np.zeros(fc.num_edges, np.float32)
+    clear_flows(fc, edge_aggr, clear_rate)
+    mars = forward(fc, data, row_ids, row_start, B, miss)
+    flows, edge_aggr = backward(fc, mars, edge_aggr)
+    input_flows(fc, flows, data, row_ids, row_start, miss, weights)
+    ll = float(mars[:, -1].astype(np.float64).sum())
+    aggr_before = edge_aggr.copy()
+    em_update(fc, edge_aggr, pseudocount, inertia)
+    return ll, aggr_before
+
+
+def kld(fc, params1, params2):
+    d = fc.desc()
+    p1 = np.asfortranarray(np.atleast_2d(params1), np.float32)
+    p2 = np.asfortranarray(np.atleast_2d(params2), np.float32)
+    S = p1.shape[0]
+    klds = _f((S, fc.num_nodes))
+    ek = _f((S, fc.num_edges))
+    lib().orc_kld(C.byref(d), _p(p1), _p(p2), C.c_uint32(S), _p(klds), _p(ek))
+    return klds, ek
+
+
+def kld_backward(fc, params1, params2, klds, edge_klds):
+    d = fc.desc()
+    p1 = np.asfortranarray(np.atleast_2d(params1), np.float32)
+    p2 = np.asfortranarray(np.atleast_2d(params2), np.float32)
+    S, P = p1.shape
+    grads = _f((S, fc.num_nodes))
+    eg1, eg2 = _f((S, fc.num_edges)), _f((S, fc.num_edges))
+    g1, g2 = _f((S, P)), _f((S, P))
+    lib().orc_kld_backward(C.byref(d), _p(p1), _p(p2), C.c_uint32(S), _p(np.asfortranarray(klds)),
+                           _p(np.asfortranarray(edge_klds)), _p(grads), _p(eg1), _p(eg2), _p(g1), _p(g2))
+    return {"grads": grads, "edge_grads1": eg1, "edge_grads2": eg2, "param_grads1": g1, "param_grads2": g2}
+
+
+def adam_step(fc, theta, grad, m, v, t, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, sign=-1.0):
+    d = fc.desc()
+    for a in (theta, m, v):
+        assert a.dtype == np.float32 and a.flags.c_contiguous
+    grad = np.ascontiguousarray(grad, np.float32)
+    lib().orc_adam_step(C.byref(d), _p(theta), _p(grad), _p(m), _p(v), C.c_int32(t), C.c_float(lr),
+                        C.c_float(beta1), C.c_float(beta2), C.c_float(eps), C.c_float(sign))
+
+
+def sum_regions(fc):
+    d = fc.desc()
+    reg = np.zeros(fc.num_nodes, np.uint32)
+    R = C.c_uint32()
+    lib().orc_sum_regions(C.byref(d), _p(reg), C.byref(R))
+    return reg, R.value
+
+
+def sample_hard(fc, params, u_sum, u_leaf, S):
+    """params [Sp, P]; u_sum [S, R, kmax], u_leaf [S, V, cmax] C-order. Returns x [S, V] int32."""
+    d = fc.desc()
+    p = np.asfortranarray(np.atleast_2d(params), np.float32)
+    u_sum = np.ascontiguousarray(u_sum, np.float32)
+    u_leaf = np.ascontiguousarray(u_leaf, np.float32)
+    x = np.zeros((S, fc.num_vars), np.int32, order="F")
+    lib().orc_sample_hard(C.byref(d), _p(fc.heap), _p(p), C.c_uint32(p.shape[0]), _p(u_sum), _p(u_leaf),
+                          C.c_uint32(S), C.c_uint32(u_sum.shape[2]), C.c_uint32(u_leaf.shape[2]), _p(x))
+    return x
+
+
+def sample_soft(fc, params, u, temperature, S, cmax):
+    d = fc.desc()
+    p = np.asfortranarray(np.atleast_2d(params), np.float32)
+    ni, _, ng = counts(fc)
+    uu = None if u is None else np.asfortranarray(u, np.float32)
+    ep, cp, td = _f((S, ni)), _f((S, ng)), _f((S, fc.num_nodes))
+    out = _f((S, fc.num_vars, cmax))
+    lib().orc_sample_soft(C.byref(d), _p(fc.heap), _p(p), C.c_uint32(p.shape[0]), _p(uu),
+                          C.c_float(temperature), C.c_uint32(S), C.c_uint32(cmax), _p(ep), _p(cp), _p(td), _p(out))
+    return out, {"edge_probs": ep, "cum_probs": cp, "td_probs": td}

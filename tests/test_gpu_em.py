@@ -1,0 +1,119 @@
+"""CUDA path vs the CPU oracle: forward, backward, leaf statistics, EM update (through the C ABI)."""
+import numpy as np
+import pytest
+
+from tests.helpers import random_data, random_hclt, rel_err, simple3
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4  # relative, fp32 (the tolerance the north star states)
+
+
+def _cuda():
+    import torch
+    from lvd_pg_b200 import api
+    assert torch.cuda.is_available()
+    return torch, api
+
+
+CASES = [
+    ("simple3", lambda: simple3(False, 5, 0), 5, 2),
+    ("hclt_k4", lambda: random_hclt(9, 4, 3, 1), 3, 37),
+    ("hclt_k16_dense", lambda: random_hclt(12, 16, 2, 2), 2, 100),
+    ("hclt_k32_dense", lambda: random_hclt(20, 32, 7, 3), 7, 130),
+    ("hclt_k48_ragged", lambda: random_hclt(7, 48, 5, 4), 5, 33),
+]
+
+
+@pytest.mark.parametrize("name,make,c,rows", CASES, ids=[c[0] for c in CASES])
+@pytest.mark.parametrize("missing", [0.0, 0.2])
+def test_forward_backward_update(oracle, name, make, c, rows, missing):
+    torch, api = _cuda()
+    fc = make()
+    data, miss = random_data(rows, fc.num_vars, c, 11, missing)
+    ref = fc.copy()
+    m = api.CuMetaBitsProbCircuit(fc)
+    dd = api.DeviceData(data, m.device, miss)
+
+    # forward
+    mars_ref = oracle.forward(ref, data, miss=miss)
+    ll = torch.empty(rows, device=m.device)
+    ws, B = api.forward(m, dd, ll_out=ll)
+    mars = m.mars(ws, B)
+    assert np.abs(mars - mars_ref).max() <= TOL * max(1.0, np.abs(mars_ref).max())
+    assert rel_err(ll.cpu().numpy(), mars_ref[:, -1]) <= TOL
+
+    # backward + leaf statistics
+    flows_ref, aggr_ref = oracle.backward(ref, mars_ref)
+    oracle.input_flows(ref, flows_ref, data, miss=miss)
+    m.lib.pcb_clear_flows(m.handle, 0.0, None)
+    api.backward(m, ws)
+    flows = m.flows(ws, B)
+    assert rel_err(flows, flows_ref) <= 2 * TOL
+    sum_edges = ref.edge_is_sum[ref.down2up.astype(np.int64) - 1]
+    assert rel_err(m.edge_aggr()[sum_edges], aggr_ref[sum_edges]) <= 2 * TOL
+    assert rel_err(m.heap(), ref.heap) <= 2 * TOL
+
+    # M-step
+    oracle.em_update(ref, aggr_ref, 0.1, 0.3)
+    m.lib.pcb_em_update(m.handle, 0.1, 0.3, None)
+    p = api.vectorize_parameters(m)
+    p_ref = oracle.vectorize(ref)
+    assert np.abs(p - p_ref).max() <= TOL * max(1.0, np.abs(p_ref).max())
+    assert np.abs(np.exp(p) - np.exp(p_ref)).max() <= TOL
+
+
+def test_dense_and_sparse_paths_agree(oracle, monkeypatch):
+    torch, api = _cuda()
+    fc = random_hclt(15, 32, 4, 7)
+    data, _ = random_data(64, fc.num_vars, 4, 3)
+    m_dense = api.CuMetaBitsProbCircuit(fc)
+    assert m_dense.info.num_dense_blocks > 0
+    monkeypatch.setenv("PCB_DISABLE_DENSE", "1")
+    m_sparse = api.CuMetaBitsProbCircuit(fc)
+    assert m_sparse.info.num_dense_blocks == 0
+    outs = []
+    for m in (m_dense, m_sparse):
+        api.em_step(m, data, pseudocount=0.1, inertia=0.5)
+        outs.append((api.vectorize_parameters(m), m.edge_aggr()))
+    assert np.abs(outs[0][0] - outs[1][0]).max() <= TOL
+    assert rel_err(outs[0][1], outs[1][1]) <= 2 * TOL
+
+
+def test_em_steps_track_oracle_with_row_ids(oracle):
+    torch, api = _cuda()
+    fc = random_hclt(10, 16, 3, 5)
+    data, _ = random_data(300, fc.num_vars, 3, 9)
+    ref = fc.copy()
+    m = api.CuMetaBitsProbCircuit(fc)
+    dd = api.DeviceData(data, m.device)
+    rng = np.random.default_rng(0)
+    ll_dev = torch.zeros(1, device=m.device)
+    for step in range(3):
+        ids = (rng.permutation(300)[:128] + 1).astype(np.int32)
+        ll_ref, _ = oracle.em_step(ref, data, row_ids=ids, pseudocount=0.1, inertia=0.9)
+        api.em_step(m, dd, torch.from_numpy(ids).to(m.device), pseudocount=0.1, inertia=0.9, ll_sum=ll_dev)
+        assert abs(ll_dev.item() - ll_ref) <= TOL * abs(ll_ref)
+        p, p_ref = api.vectorize_parameters(m), oracle.vectorize(ref)
+        assert np.abs(np.exp(p) - np.exp(p_ref)).max() <= TOL
+
+
+def test_params_roundtrip_and_errors(oracle):
+    torch, api = _cuda()
+    from lvd_pg_b200._lib import PcbError
+    fc = simple3(False)
+    m = api.CuMetaBitsProbCircuit(fc)
+    assert api.num_parameters(m) == 32
+    p = api.vectorize_parameters(m)
+    assert np.array_equal(p, oracle.vectorize(fc))
+    q = p + 0.25
+    api.update_parameters(m, q)
+    assert np.array_equal(api.vectorize_parameters(m), q)
+    with pytest.raises(AssertionError):
+        api.update_parameters(m, q[:-1])
+    ws = m.workspace(4)
+    with pytest.raises(PcbError):  # backward without forward
+        api.backward(m, ws)
+    bad = fc.copy()
+    bad.up_prime[0] = 99
+    with pytest.raises(PcbError):
+        api.CuMetaBitsProbCircuit(bad)
