@@ -203,6 +203,18 @@ int32_t pcb_comm_unique_id(uint8_t* id_out_128);
 int32_t pcb_comm_init(pcb_circuit* c, const uint8_t* id_128, int32_t rank, int32_t nranks);
 int32_t pcb_comm_destroy(pcb_circuit* c);
 
+/* ---- launch accounting ---------------------------------------------------------------- */
+/* The library counts its kernel launches per kernel class; with profiling enabled every launch
+ * is also bracketed by two CUDA events on the caller's stream.  pcb_profile_read synchronises the
+ * device and returns, per class, the summed event time in milliseconds and the launch count
+ * (arrays of pcb_profile_num_classes() entries; either may be NULL); reset != 0 clears both.
+ * The reference's counterpart is its debug=true path, which wraps each launch in CUDA.@time
+ * (queries/likelihood.jl:86-92). */
+int32_t pcb_profile_num_classes(void);
+const char* pcb_profile_class_name(int32_t i);
+int32_t pcb_profile_enable(pcb_circuit* c, int32_t on);
+int32_t pcb_profile_read(pcb_circuit* c, double* ms_out, uint64_t* launches_out, int32_t reset);
+
 #ifdef __cplusplus
 }
 #endif

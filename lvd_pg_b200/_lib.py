@@ -59,6 +59,9 @@ SIGNATURES = {
     "pcb_comm_unique_id": [_vp],
     "pcb_comm_init": [_vp, _vp, _i32, _i32],
     "pcb_comm_destroy": [_vp],
+    "pcb_profile_num_classes": [],
+    "pcb_profile_enable": [_vp, _i32],
+    "pcb_profile_read": [_vp, _vp, _vp, _i32],
 }
 
 
@@ -74,6 +77,8 @@ def lib():
             fn = getattr(_lib, name)
             fn.argtypes = args
             fn.restype = _i32
+        _lib.pcb_profile_class_name.argtypes = [_i32]
+        _lib.pcb_profile_class_name.restype = C.c_char_p
     return _lib
 
 

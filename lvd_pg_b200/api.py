@@ -46,6 +46,15 @@ class DeviceData:
         self.miss = None if miss is None else self._put(miss, device)
         self.num_vars, self.num_rows = int(self.t.shape[0]), int(self.t.shape[1])
 
+    @classmethod
+    def from_colmajor(cls, t: torch.Tensor, miss: Optional[torch.Tensor] = None) -> "DeviceData":
+        """Wrap a CUDA uint8 tensor that already is [num_vars, num_rows] contiguous."""
+        assert t.is_cuda and t.dtype == torch.uint8 and t.is_contiguous() and t.dim() == 2
+        self = cls.__new__(cls)
+        self.t, self.miss = t, miss
+        self.num_vars, self.num_rows = int(t.shape[0]), int(t.shape[1])
+        return self
+
     @staticmethod
     def _put(a: ArrayLike, device) -> torch.Tensor:
         if isinstance(a, np.ndarray):
@@ -137,6 +146,18 @@ class CuMetaBitsProbCircuit:
 
     def flows(self, ws, B) -> np.ndarray:
         return self._matrix(self.lib.pcb_get_flows, ws, B)
+
+    # ---- launch accounting ----
+    def profile_enable(self, on: bool) -> None:
+        _lib.check(self.lib.pcb_profile_enable(self.handle, int(on)))
+
+    def profile_read(self, reset: bool = True) -> dict:
+        """{kernel class: (milliseconds under event timing, launches)} since the last reset."""
+        n = self.lib.pcb_profile_num_classes()
+        ms = (C.c_double * n)()
+        cnt = (C.c_uint64 * n)()
+        _lib.check(self.lib.pcb_profile_read(self.handle, C.cast(ms, C.c_void_p), C.cast(cnt, C.c_void_p), int(reset)))
+        return {self.lib.pcb_profile_class_name(i).decode(): (float(ms[i]), int(cnt[i])) for i in range(n)}
 
     # ---- multi-GPU ----
     def attach_comm(self, unique_id: bytes, rank: int, nranks: int):

@@ -495,3 +495,36 @@ extern "C" int32_t pcb_get_sum_regions(pcb_circuit* c, uint32_t* out, uint64_t n
   memcpy(out, c->h_region1.data(), n * sizeof(uint32_t));
   return PCB_OK;
 }
+
+// ---- launch counters and per-class event timing ----------------------------------------------
+static const char* kClassNames[PCB_K_COUNT] = {"leaf_forward", "sparse_up", "dense_fwd", "sparse_down",
+                                               "dense_bwd_child", "dense_bwd_edge", "leaf_flow", "em_update",
+                                               "misc", "allreduce"};
+extern "C" int32_t pcb_profile_num_classes(void) { return PCB_K_COUNT; }
+extern "C" const char* pcb_profile_class_name(int32_t i) { return (i >= 0 && i < PCB_K_COUNT) ? kClassNames[i] : ""; }
+extern "C" int32_t pcb_profile_enable(pcb_circuit* c, int32_t on) {
+  PCB_REQUIRE(c, "null argument");
+  c->prof.on = on != 0;
+  return PCB_OK;
+}
+// Synchronises the device, adds up the event-bracketed time per kernel class (milliseconds) and
+// returns the launch counters; reset != 0 clears both.
+extern "C" int32_t pcb_profile_read(pcb_circuit* c, double* ms_out, uint64_t* launches_out, int32_t reset) {
+  PCB_REQUIRE(c, "null argument");
+  PCB_CUDA(cudaSetDevice(c->device));
+  PCB_CUDA(cudaDeviceSynchronize());
+  if (ms_out) {
+    for (int i = 0; i < PCB_K_COUNT; ++i) ms_out[i] = 0.0;
+    for (auto& e : c->prof.ev) {
+      float ms = 0.0f;
+      if (cudaEventElapsedTime(&ms, e.e0, e.e1) == cudaSuccess) ms_out[e.cls] += ms;
+    }
+  }
+  if (launches_out) for (int i = 0; i < PCB_K_COUNT; ++i) launches_out[i] = c->prof.launches[i];
+  if (reset) {
+    for (auto& e : c->prof.ev) { cudaEventDestroy(e.e0); cudaEventDestroy(e.e1); }
+    c->prof.ev.clear();
+    for (int i = 0; i < PCB_K_COUNT; ++i) c->prof.launches[i] = 0;
+  }
+  return PCB_OK;
+}

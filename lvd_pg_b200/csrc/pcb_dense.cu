@@ -283,7 +283,7 @@ int32_t pcb_dense_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cud
   if (o1 == o0) return PCB_OK;
   uint32_t bt = (pcb_round_up(ws->B, 32) + TB - 1) / TB;
   dim3 grid(bt, (c->max_dense_R + TR - 1) / TR, o1 - o0);
-  dense_fwd_kernel<<<grid, NT, 0, st>>>(ws->mars, ws->blk_mx, ws->ld, c->dense + o0, c->theta);
+  { PcbProfScope ps(c, st, PCB_K_DENSE_FWD); dense_fwd_kernel<<<grid, NT, 0, st>>>(ws->mars, ws->blk_mx, ws->ld, c->dense + o0, c->theta); }
   return PCB_OK;
 }
 
@@ -292,7 +292,7 @@ int32_t pcb_dense_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cu
   if (o1 == o0) return PCB_OK;
   uint32_t bt = (pcb_round_up(ws->B, 32) + TB - 1) / TB;
   dim3 grid(bt, (c->max_dense_K + TR - 1) / TR, o1 - o0);
-  dense_bwd_child_kernel<<<grid, NT, 0, st>>>(ws->flows, ws->mars, ws->blk_mx, ws->ld, c->dense + o0, c->theta);
+  { PcbProfScope ps(c, st, PCB_K_DENSE_BWD_CHILD); dense_bwd_child_kernel<<<grid, NT, 0, st>>>(ws->flows, ws->mars, ws->blk_mx, ws->ld, c->dense + o0, c->theta); }
   uint32_t tiles = ((c->max_dense_R + ER - 1) / ER) * ((c->max_dense_K + ET - 1) / ET);
   // enough example slices to fill the GPU when the layer has few blocks
   uint32_t want = std::max(1u, (148u * 4u) / std::max(1u, tiles * (o1 - o0)));
@@ -300,7 +300,7 @@ int32_t pcb_dense_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cu
   uint32_t b_per = pcb_round_up((ws->B + slices - 1) / slices, EB);
   slices = (ws->B + b_per - 1) / b_per;
   dim3 egrid(slices, tiles, o1 - o0);
-  dense_bwd_edge_kernel<<<egrid, NT, 0, st>>>(ws->flows, ws->mars, ws->blk_mx, ws->ld, ws->B, b_per, c->dense + o0,
-                                              c->theta, c->aggr);
+  { PcbProfScope ps(c, st, PCB_K_DENSE_BWD_EDGE); dense_bwd_edge_kernel<<<egrid, NT, 0, st>>>(ws->flows, ws->mars, ws->blk_mx, ws->ld, ws->B, b_per, c->dense + o0,
+                                              c->theta, c->aggr); }
   return PCB_OK;
 }

@@ -263,15 +263,15 @@ extern "C" int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   ws->B = B; ws->data = data_dev; ws->miss = miss_dev; ws->num_rows = num_rows;
   ws->row_ids = row_ids_dev; ws->row_start = row_start; ws->have_forward = false;
   if (c->n_inputs)
-    leaf_forward_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(ws->mars, ws->ld, B, c->theta, c->in_node, c->in_var,
+    { PcbProfScope ps(c, st, PCB_K_LEAF_FWD); leaf_forward_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(ws->mars, ws->ld, B, c->theta, c->in_node, c->in_var,
                                                                c->in_poff, data_dev, miss_dev, num_rows,
-                                                               row_ids_dev, row_start);
+                                                               row_ids_dev, row_start); }
   for (uint32_t lay = 1; lay <= c->L; ++lay) {
     uint32_t o0 = c->h_up_sparse_off[lay - 1], o1 = c->h_up_sparse_off[lay];
     if (o1 > o0)
-      sparse_up_kernel<<<grid2(o1 - o0, B), TPB, 0, st>>>(ws->mars, ws->ld, B, c->up_sparse + o0, c->kind,
+      { PcbProfScope ps(c, st, PCB_K_SPARSE_UP); sparse_up_kernel<<<grid2(o1 - o0, B), TPB, 0, st>>>(ws->mars, ws->ld, B, c->up_sparse + o0, c->kind,
                                                           c->n_estart, c->n_ecount, c->n_pid0, c->e_prime,
-                                                          c->e_sub, c->theta);
+                                                          c->e_sub, c->theta); }
     PCB_TRY(pcb_dense_forward(c, ws, lay, st));
   }
   if (ll_out_dev)
@@ -292,14 +292,14 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
   for (int64_t lay = c->L; lay >= 0; --lay) {
     uint32_t o0 = c->h_down_sparse_off[lay], o1 = c->h_down_sparse_off[lay + 1];
     if (o1 > o0)
-      sparse_down_kernel<<<grid2(o1 - o0, B), TPB, 0, st>>>(ws->flows, ws->mars, ws->ld, B, c->down_sparse + o0,
-                                                            c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr);
+      { PcbProfScope ps(c, st, PCB_K_SPARSE_DOWN); sparse_down_kernel<<<grid2(o1 - o0, B), TPB, 0, st>>>(ws->flows, ws->mars, ws->ld, B, c->down_sparse + o0,
+                                                            c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr); }
     if (lay >= 1) PCB_TRY(pcb_dense_backward(c, ws, (uint32_t)lay, st));
   }
   if (c->n_inputs)
-    leaf_flow_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(ws->flows, ws->ld, B, c->aggr, c->in_node, c->in_var,
+    { PcbProfScope ps(c, st, PCB_K_LEAF_FLOW); leaf_flow_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(ws->flows, ws->ld, B, c->aggr, c->in_node, c->in_var,
                                                             c->in_cats, c->in_foff, ws->data, ws->miss,
-                                                            ws->num_rows, ws->row_ids, ws->row_start, weights_dev);
+                                                            ws->num_rows, ws->row_ids, ws->row_start, weights_dev); }
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
 }
@@ -313,7 +313,7 @@ extern "C" int32_t pcb_clear_flows(pcb_circuit* c, float rate, pcb_stream s) {
   } else {
     uint64_t n = c->aggr_len - 1;
     uint32_t blocks = (uint32_t)std::min<uint64_t>((n + 255) / 256, 148 * 16);
-    if (n) scale_kernel<<<blocks, 256, 0, st>>>(c->aggr, n, rate);
+    if (n) { PcbProfScope ps(c, st, PCB_K_MISC); scale_kernel<<<blocks, 256, 0, st>>>(c->aggr, n, rate); }
     PCB_CUDA(cudaMemsetAsync(c->aggr + n, 0, sizeof(float), st));
     PCB_CUDA(cudaGetLastError());
   }
@@ -325,11 +325,11 @@ extern "C" int32_t pcb_em_update(pcb_circuit* c, float pseudocount, float inerti
   PCB_CUDA(cudaSetDevice(c->device));
   cudaStream_t st = (cudaStream_t)s;
   if (c->n_groups)
-    em_update_sum_kernel<<<(c->n_groups + 7) / 8, 256, 0, st>>>(c->theta, c->aggr, c->grp_node, c->n_groups,
-                                                                c->n_pid0, c->n_ecount, pseudocount, inertia);
+    { PcbProfScope ps(c, st, PCB_K_UPDATE); em_update_sum_kernel<<<(c->n_groups + 7) / 8, 256, 0, st>>>(c->theta, c->aggr, c->grp_node, c->n_groups,
+                                                                c->n_pid0, c->n_ecount, pseudocount, inertia); }
   if (c->n_inputs)
-    em_update_leaf_kernel<<<(c->n_inputs + 7) / 8, 256, 0, st>>>(c->theta, c->aggr, c->n_inputs, c->in_cats,
-                                                                 c->in_poff, c->in_foff, pseudocount, inertia);
+    { PcbProfScope ps(c, st, PCB_K_UPDATE); em_update_leaf_kernel<<<(c->n_inputs + 7) / 8, 256, 0, st>>>(c->theta, c->aggr, c->n_inputs, c->in_cats,
+                                                                 c->in_poff, c->in_foff, pseudocount, inertia); }
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
 }
@@ -344,8 +344,8 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   PCB_TRY(pcb_forward(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, nullptr, s));
   PCB_TRY(pcb_backward(c, ws, weights_dev, s));
   // batch log-likelihood into the last slot of the statistics vector, so it is reduced with them
-  ll_sum_kernel<<<1, 256, 0, st>>>(ws->mars + (size_t)(c->N - 1) * ws->ld, B, c->aggr + c->aggr_len - 1);
-  if (c->comm) PCB_TRY(pcb_allreduce_aggr(c, st));
+  { PcbProfScope ps(c, st, PCB_K_MISC); ll_sum_kernel<<<1, 256, 0, st>>>(ws->mars + (size_t)(c->N - 1) * ws->ld, B, c->aggr + c->aggr_len - 1); }
+  if (c->comm) { PcbProfScope ps(c, st, PCB_K_ALLREDUCE); PCB_TRY(pcb_allreduce_aggr(c, st)); }
   if (ll_sum_dev)
     PCB_CUDA(cudaMemcpyAsync(ll_sum_dev, c->aggr + c->aggr_len - 1, sizeof(float), cudaMemcpyDeviceToDevice, st));
   PCB_TRY(pcb_em_update(c, pseudocount, inertia, s));

@@ -46,8 +46,21 @@ struct PcbInEntry {
   uint32_t flags; // bit0: this node is the prime child of the edge (aggregating entry)
 };
 
+// kernel classes for launch counting and the optional per-class event timing
+enum PcbKernelClass {
+  PCB_K_LEAF_FWD = 0, PCB_K_SPARSE_UP, PCB_K_DENSE_FWD, PCB_K_SPARSE_DOWN, PCB_K_DENSE_BWD_CHILD,
+  PCB_K_DENSE_BWD_EDGE, PCB_K_LEAF_FLOW, PCB_K_UPDATE, PCB_K_MISC, PCB_K_ALLREDUCE, PCB_K_COUNT
+};
+struct PcbProfEvent { int cls; cudaEvent_t e0, e1; };
+struct PcbProf {
+  bool on = false;
+  uint64_t launches[PCB_K_COUNT] = {0};
+  std::vector<PcbProfEvent> ev;
+};
+
 struct pcb_circuit {
   int device = 0;
+  PcbProf prof;
   uint32_t N = 0, E = 0, V = 0, L = 0;  // nodes, edges, variables, up layers (layer 0 = inputs)
   uint32_t n_inner = 0, n_input_params = 0, n_groups = 0, n_inputs = 0;
   uint32_t n_regions = 0, max_group = 0, max_cats = 0;
@@ -150,6 +163,21 @@ int32_t pcb_fail(int32_t code, const std::string& msg);
   } while (0)
 
 static inline uint32_t pcb_round_up(uint32_t x, uint32_t m) { return (x + m - 1) / m * m; }
+
+// Counts a launch of class `cls`; with profiling on, brackets it with two events on `st`.
+struct PcbProfScope {
+  pcb_circuit* c; cudaStream_t st; cudaEvent_t e1 = nullptr;
+  PcbProfScope(pcb_circuit* c_, cudaStream_t st_, int cls) : c(c_), st(st_) {
+    ++c->prof.launches[cls];
+    if (c->prof.on) {
+      cudaEvent_t e0;
+      cudaEventCreate(&e0); cudaEventCreate(&e1);
+      cudaEventRecord(e0, st);
+      c->prof.ev.push_back(PcbProfEvent{cls, e0, e1});
+    }
+  }
+  ~PcbProfScope() { if (e1) cudaEventRecord(e1, st); }
+};
 
 // entry points implemented across translation units and used by pcb_em_step
 int32_t pcb_allreduce_aggr(pcb_circuit* c, cudaStream_t st);

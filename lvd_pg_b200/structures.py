@@ -185,9 +185,12 @@ def _post_order(parent: np.ndarray) -> List[int]:
 
 def _dirichlet_log(rng, rows: int, cols: int) -> np.ndarray:
     """log of `rows` independent Dirichlet(1,...,1) draws of dimension `cols`, fp32."""
-    e = rng.standard_exponential((rows, cols))
-    e = np.maximum(e, 1e-30)
-    return np.log(e / e.sum(1, keepdims=True)).astype(np.float32)
+    e = rng.standard_exponential((rows, cols), dtype=np.float32)
+    np.maximum(e, np.float32(1e-30), out=e)
+    tot = e.sum(1, keepdims=True, dtype=np.float64)
+    np.log(e, out=e)
+    e -= np.log(tot).astype(np.float32)
+    return e
 
 
 def hclt_graph(parent: np.ndarray, num_cats: int, k: int, rng=None):
@@ -312,6 +315,7 @@ def hclt_flat(parent: np.ndarray, num_cats: int, k: int, seed: Optional[int] = 0
             sum_dl[x] = d_children
     runs = []  # (down layer, prime base, up-edge ids ordered by prime)
     ar = np.arange(k)
+    ar32 = np.arange(k, dtype=np.uint32)
     for gi, (lay, _, gk, y) in enumerate(groups):
         o = int(offs[gi])
         if gk == 0:
@@ -329,22 +333,27 @@ def hclt_flat(parent: np.ndarray, num_cats: int, k: int, seed: Optional[int] = 0
             up_tag[idx[:, h - 1]] |= TAG_LAST
         else:
             r = 1 if y == root else k
-            idx = o + (np.arange(r)[:, None] * k + ar[None, :])            # [c, j]
-            up_parent[idx] = (sum_base[y] + np.arange(r))[:, None]
+            sl = slice(o, o + r * k)
             pb = prod_base[y] if len(ch[y]) > 1 else out_base[ch[y][0]]
-            up_prime[idx] = (pb + ar)[None, :]
-            up_sub[idx] = (leaf_base[y] + ar)[None, :]
-            w = _dirichlet_log(rng, r, k) if rng is not None else np.tile(_loguniform(k), (r, 1))
-            up_logp[idx] = w
-            up_tag[idx[:, 0]] |= TAG_FIRST
-            up_tag[idx[:, k - 1]] |= TAG_LAST
+            up_parent[sl].reshape(r, k)[:] = (sum_base[y] + np.arange(r, dtype=np.uint32))[:, None]
+            up_prime[sl].reshape(r, k)[:] = (pb + ar32)[None, :]
+            up_sub[sl].reshape(r, k)[:] = (leaf_base[y] + ar32)[None, :]
+            if rng is not None:
+                up_logp[sl].reshape(r, k)[:] = _dirichlet_log(rng, r, k)
+            else:
+                up_logp[sl] = -np.log(k)
+            tg = up_tag[sl].reshape(r, k)
+            tg[:, 0] |= TAG_FIRST
+            tg[:, k - 1] |= TAG_LAST
             if r == 1:
-                up_tag[idx] |= TAG_ONLYSUB
-            runs.append((int(sum_dl[y]) + 1, int(pb), idx.T.reshape(-1).copy()))  # by prime j, then c
+                tg[:] |= TAG_ONLYSUB
+            # down order of the block: by prime child j, then by parent c
+            runs.append((int(sum_dl[y]) + 1, int(pb), (np.uint32(o) + (ar32[:, None] + np.arange(r, dtype=np.uint32)[None, :] * np.uint32(k))).reshape(-1)))
         if gi + 1 == len(groups) or groups[gi + 1][0] != lay:
             up_ends.append(int(offs[gi + 1]))
     runs.sort(key=lambda t: (t[0], t[1]))
-    down2up = np.concatenate([r[2] for r in runs]).astype(np.uint32) + 1
+    down2up = np.concatenate([np.asarray(r[2], dtype=np.uint32) for r in runs])
+    down2up += np.uint32(1)
     down_ends, pos = [], 0
     for i, r in enumerate(runs):
         pos += len(r[2])
