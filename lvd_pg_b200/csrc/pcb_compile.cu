@@ -309,6 +309,20 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
   PCB_TRY(upload(&c->in_ent, in_ent, &bytes));
   PCB_TRY(upload(&c->dense, c->h_dense, &bytes));
   PCB_TRY(upload(&c->grp_node, grp_node, &bytes));
+  {  // leaf chunks: inputs sorted by variable (stable), cut every PCB_LEAF_CHUNK leaves
+    std::vector<uint32_t> order(NI), lvar, loff;
+    for (uint32_t i = 0; i < NI; ++i) order[i] = i;
+    std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return in_var[a] < in_var[b]; });
+    for (uint32_t i = 0; i < NI; ++i) {
+      bool cut = i == 0 || in_var[order[i]] != in_var[order[i - 1]] || (i - loff.back()) >= PCB_LEAF_CHUNK;
+      if (cut) { lvar.push_back(in_var[order[i]]); loff.push_back(i); }
+    }
+    loff.push_back(NI);
+    c->n_lchunks = (uint32_t)lvar.size();
+    PCB_TRY(upload(&c->lchunk_var, lvar, &bytes));
+    PCB_TRY(upload(&c->lchunk_off, loff, &bytes));
+    PCB_TRY(upload(&c->lchunk_inputs, order, &bytes));
+  }
   c->device_bytes = bytes;
   return PCB_OK;
 }
@@ -317,7 +331,7 @@ void free_circuit(pcb_circuit* c) {
   void* ptrs[] = {c->theta, c->aggr, c->kind, c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime,
                   c->e_sub, c->in_node, c->in_var, c->in_cats, c->in_poff, c->in_foff, c->node2input,
                   c->up_all, c->up_sparse, c->down_all, c->down_sparse, c->in_off, c->in_ent, c->dense,
-                  c->grp_node};
+                  c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs};
   for (void* p : ptrs) if (p) cudaFree(p);
 }
 

@@ -34,22 +34,6 @@ __device__ __forceinline__ int64_t data_row(const int32_t* row_ids, uint32_t row
   return row_ids ? (int64_t)row_ids[b] - 1 : (int64_t)row_start - 1 + b;
 }
 
-// mars[leaf][b] = log p(x_b) ; missing -> 0
-__global__ void leaf_forward_kernel(float* __restrict__ mars, uint32_t ld, uint32_t B,
-                                    const float* __restrict__ theta, const uint32_t* __restrict__ in_node,
-                                    const uint32_t* __restrict__ in_var, const uint64_t* __restrict__ in_poff,
-                                    const uint8_t* __restrict__ data, const uint8_t* __restrict__ miss,
-                                    uint64_t num_rows, const int32_t* __restrict__ row_ids, uint32_t row_start) {
-  uint32_t i = blockIdx.x;
-  uint32_t b = blockIdx.y * blockDim.x + threadIdx.x;
-  if (b >= B) return;
-  int64_t row = data_row(row_ids, row_start, b);
-  size_t di = (size_t)row + (size_t)num_rows * in_var[i];
-  float v = 0.0f;
-  if (!(miss && miss[di])) v = __ldg(theta + in_poff[i] + data[di]);
-  mars[(size_t)in_node[i] * ld + b] = v;
-}
-
 // One thread per (example, node).  Sum nodes: two passes over the children (max, then
 // sum of exp), which needs one exp per edge instead of the exp+log of a binary fold.
 __global__ void sparse_up_kernel(float* __restrict__ mars, uint32_t ld, uint32_t B,
@@ -169,6 +153,92 @@ __global__ void leaf_flow_kernel(const float* __restrict__ flows, uint32_t ld, u
   if (active && lane == leader) atomicAdd(aggr + fo + slot, total);
 }
 
+// ---- chunked leaf kernels -------------------------------------------------------------------------
+// One block serves up to PCB_LEAF_CHUNK leaves of one variable for a tile of LBT examples: the
+// variable's observed values are gathered once into shared memory (0xffff = missing) and reused
+// by every leaf of the chunk, so the per-leaf work is a coalesced row read or write plus a
+// table lookup that stays in L1.
+constexpr int LBT = 2048;
+constexpr int LTH = 256;
+
+__device__ __forceinline__ void stage_values(uint16_t* xs, uint32_t b0, uint32_t nb, uint32_t var,
+                                             const uint8_t* __restrict__ data, const uint8_t* __restrict__ miss,
+                                             uint64_t num_rows, const int32_t* __restrict__ row_ids,
+                                             uint32_t row_start) {
+  for (uint32_t b = threadIdx.x; b < nb; b += blockDim.x) {
+    int64_t row = data_row(row_ids, row_start, b0 + b);
+    size_t di = (size_t)row + (size_t)num_rows * var;
+    xs[b] = (miss && miss[di]) ? (uint16_t)0xffff : (uint16_t)data[di];
+  }
+}
+
+__global__ void __launch_bounds__(LTH) leaf_forward_chunk_kernel(
+    float* __restrict__ mars, uint32_t ld, uint32_t B, const float* __restrict__ theta,
+    const uint32_t* __restrict__ in_node, const uint64_t* __restrict__ in_poff,
+    const uint32_t* __restrict__ lchunk_var, const uint32_t* __restrict__ lchunk_off,
+    const uint32_t* __restrict__ lchunk_inputs, const uint8_t* __restrict__ data,
+    const uint8_t* __restrict__ miss, uint64_t num_rows, const int32_t* __restrict__ row_ids, uint32_t row_start) {
+  __shared__ uint16_t xs[LBT];
+  const uint32_t chunk = blockIdx.x, b0 = blockIdx.y * LBT;
+  const uint32_t nb = min((uint32_t)LBT, B - b0);
+  stage_values(xs, b0, nb, lchunk_var[chunk], data, miss, num_rows, row_ids, row_start);
+  __syncthreads();
+  for (uint32_t li = lchunk_off[chunk]; li < lchunk_off[chunk + 1]; ++li) {
+    uint32_t i = lchunk_inputs[li];
+    const float* tab = theta + in_poff[i];
+    float* out = mars + (size_t)in_node[i] * ld + b0;
+    for (uint32_t b = threadIdx.x; b < nb; b += LTH) {
+      uint16_t x = xs[b];
+      out[b] = x == 0xffff ? 0.0f : __ldg(tab + x);
+    }
+  }
+}
+
+// Leaf statistics through a shared-memory histogram per leaf; a block that covers the whole
+// batch owns its leaves' slots and adds without atomics.
+__global__ void __launch_bounds__(LTH) leaf_flow_chunk_kernel(
+    const float* __restrict__ flows, uint32_t ld, uint32_t B, float* __restrict__ aggr, uint32_t hstride,
+    const uint32_t* __restrict__ in_node, const uint32_t* __restrict__ in_cats,
+    const uint64_t* __restrict__ in_foff, const uint32_t* __restrict__ lchunk_var,
+    const uint32_t* __restrict__ lchunk_off, const uint32_t* __restrict__ lchunk_inputs,
+    const uint8_t* __restrict__ data, const uint8_t* __restrict__ miss, uint64_t num_rows,
+    const int32_t* __restrict__ row_ids, uint32_t row_start, const float* __restrict__ weights) {
+  extern __shared__ float hist[];  // [PCB_LEAF_CHUNK][hstride]
+  __shared__ uint16_t xs[LBT];
+  const uint32_t chunk = blockIdx.x, b0 = blockIdx.y * LBT;
+  const uint32_t nb = min((uint32_t)LBT, B - b0);
+  const uint32_t l0 = lchunk_off[chunk], nl = lchunk_off[chunk + 1] - l0;
+  for (uint32_t x = threadIdx.x; x < nl * hstride; x += LTH) hist[x] = 0.0f;
+  stage_values(xs, b0, nb, lchunk_var[chunk], data, miss, num_rows, row_ids, row_start);
+  __syncthreads();
+  for (uint32_t l = 0; l < nl; ++l) {
+    uint32_t i = lchunk_inputs[l0 + l];
+    if (in_foff[i] == ~0ull) continue;  // fixed leaf
+    const uint32_t C = in_cats[i];
+    const float* f = flows + (size_t)in_node[i] * ld + b0;
+    float* h = hist + l * hstride;
+    for (uint32_t b = threadIdx.x; b < nb; b += LTH) {
+      uint16_t x = xs[b];
+      uint32_t slot = x == 0xffff ? C : (uint32_t)x;
+      if (slot > C) continue;  // value outside the leaf's categories
+      float v = f[b];
+      if (weights) v *= weights[data_row(row_ids, row_start, b0 + b)];
+      atomicAdd(h + slot, v);
+    }
+  }
+  __syncthreads();
+  const bool whole = gridDim.y == 1;
+  for (uint32_t x = threadIdx.x; x < nl * hstride; x += LTH) {
+    uint32_t l = x / hstride, sl = x - l * hstride;
+    uint32_t i = lchunk_inputs[l0 + l];
+    uint64_t fo = in_foff[i];
+    if (fo == ~0ull || sl > in_cats[i]) continue;
+    float v = hist[x];
+    if (v == 0.0f) continue;
+    if (whole) aggr[fo + sl] += v; else atomicAdd(aggr + fo + sl, v);
+  }
+}
+
 __global__ void scale_kernel(float* __restrict__ x, uint64_t n, float rate) {
   uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
@@ -262,10 +332,13 @@ extern "C" int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   cudaStream_t st = (cudaStream_t)s;
   ws->B = B; ws->data = data_dev; ws->miss = miss_dev; ws->num_rows = num_rows;
   ws->row_ids = row_ids_dev; ws->row_start = row_start; ws->have_forward = false;
-  if (c->n_inputs)
-    { PcbProfScope ps(c, st, PCB_K_LEAF_FWD); leaf_forward_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(ws->mars, ws->ld, B, c->theta, c->in_node, c->in_var,
-                                                               c->in_poff, data_dev, miss_dev, num_rows,
-                                                               row_ids_dev, row_start); }
+  if (c->n_inputs) {
+    PcbProfScope ps(c, st, PCB_K_LEAF_FWD);
+    dim3 grid(c->n_lchunks, (B + LBT - 1) / LBT);
+    leaf_forward_chunk_kernel<<<grid, LTH, 0, st>>>(ws->mars, ws->ld, B, c->theta, c->in_node, c->in_poff,
+                                                    c->lchunk_var, c->lchunk_off, c->lchunk_inputs, data_dev,
+                                                    miss_dev, num_rows, row_ids_dev, row_start);
+  }
   for (uint32_t lay = 1; lay <= c->L; ++lay) {
     uint32_t o0 = c->h_up_sparse_off[lay - 1], o1 = c->h_up_sparse_off[lay];
     if (o1 > o0)
@@ -296,10 +369,20 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
                                                             c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr); }
     if (lay >= 1) PCB_TRY(pcb_dense_backward(c, ws, (uint32_t)lay, st));
   }
-  if (c->n_inputs)
-    { PcbProfScope ps(c, st, PCB_K_LEAF_FLOW); leaf_flow_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(ws->flows, ws->ld, B, c->aggr, c->in_node, c->in_var,
-                                                            c->in_cats, c->in_foff, ws->data, ws->miss,
-                                                            ws->num_rows, ws->row_ids, ws->row_start, weights_dev); }
+  if (c->n_inputs) {
+    PcbProfScope ps(c, st, PCB_K_LEAF_FLOW);
+    if (c->max_cats <= 1024) {
+      uint32_t hstride = c->max_cats + 1;
+      dim3 grid(c->n_lchunks, (B + LBT - 1) / LBT);
+      leaf_flow_chunk_kernel<<<grid, LTH, PCB_LEAF_CHUNK * hstride * sizeof(float), st>>>(
+          ws->flows, ws->ld, B, c->aggr, hstride, c->in_node, c->in_cats, c->in_foff, c->lchunk_var, c->lchunk_off,
+          c->lchunk_inputs, ws->data, ws->miss, ws->num_rows, ws->row_ids, ws->row_start, weights_dev);
+    } else {
+      leaf_flow_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(ws->flows, ws->ld, B, c->aggr, c->in_node, c->in_var,
+                                                              c->in_cats, c->in_foff, ws->data, ws->miss,
+                                                              ws->num_rows, ws->row_ids, ws->row_start, weights_dev);
+    }
+  }
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
 }

@@ -26,6 +26,7 @@
 #include "../../include/pcb200.h"
 
 #define PCB_NONE 0xffffffffu
+#define PCB_LEAF_CHUNK 8
 
 struct PcbDenseBlock {
   uint32_t p0;    // first parent node
@@ -88,6 +89,12 @@ struct pcb_circuit {
   uint64_t* in_poff = nullptr;    // [n_inputs] offset of the log-probs in theta
   uint64_t* in_foff = nullptr;    // [n_inputs] offset of the flow slots in aggr, ~0 for fixed
   uint32_t* node2input = nullptr; // [N] input index or PCB_NONE
+  // leaves grouped by variable and cut into chunks of at most PCB_LEAF_CHUNK: one thread block
+  // stages the variable's observed values once and serves every leaf of the chunk
+  uint32_t* lchunk_var = nullptr;   // [n_lchunks] variable of the chunk
+  uint32_t* lchunk_off = nullptr;   // [n_lchunks + 1] range into lchunk_inputs
+  uint32_t* lchunk_inputs = nullptr; // [n_inputs] input indices sorted by variable
+  uint32_t n_lchunks = 0;
   // layer lists: all inner nodes by layer / only those outside dense blocks
   uint32_t* up_all = nullptr;     // [n_inner_nodes]
   uint32_t* up_sparse = nullptr;
