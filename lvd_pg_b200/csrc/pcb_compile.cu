@@ -323,15 +323,35 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
     PCB_TRY(upload(&c->lchunk_off, loff, &bytes));
     PCB_TRY(upload(&c->lchunk_inputs, order, &bytes));
   }
+  PCB_CUDA(cudaMalloc((void**)&c->status, sizeof(int)));
+  PCB_CUDA(cudaMemset(c->status, 0, sizeof(int)));
+  {  // dense blocks run on the tensor cores unless PCB_DENSE_IMPL=simt asks for the fp32 SIMT kernels
+    cudaDeviceProp prop;
+    PCB_CUDA(cudaGetDeviceProperties(&prop, c->device));
+    const char* impl = getenv("PCB_DENSE_IMPL");
+    c->use_tc = prop.major == 10 && !(impl && std::string(impl) == "simt");
+  }
   c->device_bytes = bytes;
   return PCB_OK;
 }
+
+}  // namespace
+
+// Reads the device status word that bounded waits raise; non-zero means a kernel gave up waiting.
+int32_t pcb_check_status(pcb_circuit* c) {
+  int h = 0;
+  PCB_CUDA(cudaMemcpy(&h, c->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (h != 0) return pcb_fail(PCB_ERR_CUDA, "a dense-block kernel gave up a bounded wait (status " + std::to_string(h) + ")");
+  return PCB_OK;
+}
+
+namespace {
 
 void free_circuit(pcb_circuit* c) {
   void* ptrs[] = {c->theta, c->aggr, c->kind, c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime,
                   c->e_sub, c->in_node, c->in_var, c->in_cats, c->in_poff, c->in_foff, c->node2input,
                   c->up_all, c->up_sparse, c->down_all, c->down_sparse, c->in_off, c->in_ent, c->dense,
-                  c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs};
+                  c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status};
   for (void* p : ptrs) if (p) cudaFree(p);
 }
 
@@ -436,6 +456,7 @@ extern "C" int32_t pcb_get_params(pcb_circuit* c, float* params_host, uint64_t n
   PCB_REQUIRE(n == c->P, "parameter vector has the wrong length");
   PCB_CUDA(cudaSetDevice(c->device));
   PCB_CUDA(cudaDeviceSynchronize());
+  PCB_TRY(pcb_check_status(c));
   PCB_CUDA(cudaMemcpy(params_host, c->theta, n * sizeof(float), cudaMemcpyDeviceToHost));
   return PCB_OK;
 }
@@ -488,6 +509,7 @@ extern "C" int32_t pcb_get_edge_aggr(pcb_circuit* c, float* edge_aggr_host, uint
   PCB_REQUIRE(n == c->E, "edge_aggr has the wrong length");
   PCB_CUDA(cudaSetDevice(c->device));
   PCB_CUDA(cudaDeviceSynchronize());
+  PCB_TRY(pcb_check_status(c));
   std::vector<float> aggr(std::max<uint32_t>(1u, c->n_inner));
   PCB_CUDA(cudaMemcpy(aggr.data(), c->aggr, (size_t)c->n_inner * sizeof(float), cudaMemcpyDeviceToHost));
   for (uint32_t de = 0; de < c->E; ++de) {

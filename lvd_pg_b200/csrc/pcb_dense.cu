@@ -279,6 +279,7 @@ __global__ void __launch_bounds__(NT) dense_bwd_edge_kernel(const float* __restr
 }  // namespace
 
 int32_t pcb_dense_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st) {
+  if (c->use_tc) return pcb_dense_tc_forward(c, ws, layer, st);
   uint32_t o0 = c->h_dense_off[layer], o1 = c->h_dense_off[layer + 1];
   if (o1 == o0) return PCB_OK;
   uint32_t bt = (pcb_round_up(ws->B, 32) + TB - 1) / TB;
@@ -288,6 +289,7 @@ int32_t pcb_dense_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cud
 }
 
 int32_t pcb_dense_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st) {
+  if (c->use_tc) return pcb_dense_tc_backward(c, ws, layer, st);
   uint32_t o0 = c->h_dense_off[layer], o1 = c->h_dense_off[layer + 1];
   if (o1 == o0) return PCB_OK;
   uint32_t bt = (pcb_round_up(ws->B, 32) + TB - 1) / TB;

@@ -442,6 +442,7 @@ static int32_t get_matrix(pcb_circuit* c, pcb_workspace* ws, const float* src, f
   PCB_REQUIRE(n == (uint64_t)ws->B * c->N, "matrix has the wrong size");
   PCB_CUDA(cudaSetDevice(c->device));
   PCB_CUDA(cudaDeviceSynchronize());
+  PCB_TRY(pcb_check_status(c));
   PCB_CUDA(cudaMemcpy2D(host, ws->B * sizeof(float), src, ws->ld * sizeof(float), ws->B * sizeof(float), c->N,
                         cudaMemcpyDeviceToHost));
   return PCB_OK;

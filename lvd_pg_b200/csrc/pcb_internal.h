@@ -122,6 +122,10 @@ struct pcb_circuit {
   std::vector<uint64_t> h_in_poff, h_in_foff;
   uint64_t heap_len = 0;
 
+  // ---- dense-block implementation and the device status word bounded waits report to ----
+  bool use_tc = false;
+  int* status = nullptr;
+
   // ---- multi-GPU ----
   void* comm = nullptr;  // ncclComm_t
   int nranks = 1, rank = 0;
@@ -191,3 +195,6 @@ int32_t pcb_allreduce_aggr(pcb_circuit* c, cudaStream_t st);
 int32_t pcb_dense_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
 int32_t pcb_dense_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
 int32_t pcb_ws_ensure_sets(pcb_workspace* ws, uint32_t S, bool need_stack);
+int32_t pcb_dense_tc_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
+int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
+int32_t pcb_check_status(pcb_circuit* c);

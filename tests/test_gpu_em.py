@@ -21,6 +21,9 @@ CASES = [
     ("hclt_k16_dense", lambda: random_hclt(12, 16, 2, 2), 2, 100),
     ("hclt_k32_dense", lambda: random_hclt(20, 32, 7, 3), 7, 130),
     ("hclt_k48_ragged", lambda: random_hclt(7, 48, 5, 4), 5, 33),
+    ("hclt_k128_dense", lambda: random_hclt(5, 128, 3, 5), 3, 260),
+    ("hclt_k256_dense", lambda: random_hclt(4, 256, 2, 6), 2, 131),
+    ("hclt_k272_two_column_tiles", lambda: random_hclt(3, 272, 2, 8), 2, 70),
 ]
 
 
@@ -77,6 +80,23 @@ def test_dense_and_sparse_paths_agree(oracle, monkeypatch):
         outs.append((api.vectorize_parameters(m), m.edge_aggr()))
     assert np.abs(outs[0][0] - outs[1][0]).max() <= TOL
     assert rel_err(outs[0][1], outs[1][1]) <= 2 * TOL
+
+
+def test_tensor_core_and_simt_dense_kernels_agree(monkeypatch):
+    torch, api = _cuda()
+    fc = random_hclt(9, 64, 4, 12)
+    data, _ = random_data(300, fc.num_vars, 4, 5)
+    outs = []
+    for impl in ("tc", "simt"):
+        monkeypatch.setenv("PCB_DENSE_IMPL", impl)
+        m = api.CuMetaBitsProbCircuit(fc)
+        assert m.info.num_dense_blocks > 0
+        ll = torch.zeros(1, device=m.device)
+        api.em_step(m, data, pseudocount=0.1, inertia=0.5, ll_sum=ll)
+        outs.append((api.vectorize_parameters(m), m.edge_aggr(), ll.item()))
+    assert abs(outs[0][2] - outs[1][2]) <= 1e-5 * abs(outs[1][2])
+    assert np.abs(outs[0][0] - outs[1][0]).max() <= TOL
+    assert rel_err(outs[0][1], outs[1][1]) <= TOL
 
 
 def test_em_steps_track_oracle_with_row_ids(oracle):
