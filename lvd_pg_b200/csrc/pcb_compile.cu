@@ -330,6 +330,7 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
     PCB_CUDA(cudaGetDeviceProperties(&prop, c->device));
     const char* impl = getenv("PCB_DENSE_IMPL");
     c->use_tc = prop.major == 10 && !(impl && std::string(impl) == "simt");
+    if (c->use_tc) PCB_TRY(pcb_dense_tc_prepare(c, &bytes));
   }
   c->device_bytes = bytes;
   return PCB_OK;
@@ -351,7 +352,7 @@ void free_circuit(pcb_circuit* c) {
   void* ptrs[] = {c->theta, c->aggr, c->kind, c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime,
                   c->e_sub, c->in_node, c->in_var, c->in_cats, c->in_poff, c->in_foff, c->node2input,
                   c->up_all, c->up_sparse, c->down_all, c->down_sparse, c->in_off, c->in_ent, c->dense,
-                  c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status};
+                  c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status, c->w_img, c->dense_img};
   for (void* p : ptrs) if (p) cudaFree(p);
 }
 
@@ -466,6 +467,7 @@ extern "C" int32_t pcb_set_params(pcb_circuit* c, const float* params_host, uint
   PCB_CUDA(cudaSetDevice(c->device));
   PCB_CUDA(cudaDeviceSynchronize());
   PCB_CUDA(cudaMemcpy(c->theta, params_host, n * sizeof(float), cudaMemcpyHostToDevice));
+  c->w_img_valid = false;
   return PCB_OK;
 }
 extern "C" int32_t pcb_get_params_dev(pcb_circuit* c, float* params_dev, uint64_t n, pcb_stream s) {
@@ -480,6 +482,7 @@ extern "C" int32_t pcb_set_params_dev(pcb_circuit* c, const float* params_dev, u
   PCB_REQUIRE(n == c->P, "parameter vector has the wrong length");
   PCB_CUDA(cudaSetDevice(c->device));
   PCB_CUDA(cudaMemcpyAsync(c->theta, params_dev, n * sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)s));
+  c->w_img_valid = false;
   return PCB_OK;
 }
 
@@ -535,7 +538,7 @@ extern "C" int32_t pcb_get_sum_regions(pcb_circuit* c, uint32_t* out, uint64_t n
 // ---- launch counters and per-class event timing ----------------------------------------------
 static const char* kClassNames[PCB_K_COUNT] = {"leaf_forward", "sparse_up", "dense_fwd", "sparse_down",
                                                "dense_bwd_child", "dense_bwd_edge", "leaf_flow", "em_update",
-                                               "misc", "allreduce"};
+                                               "misc", "allreduce", "dense_max", "w_image"};
 extern "C" int32_t pcb_profile_num_classes(void) { return PCB_K_COUNT; }
 extern "C" const char* pcb_profile_class_name(int32_t i) { return (i >= 0 && i < PCB_K_COUNT) ? kClassNames[i] : ""; }
 extern "C" int32_t pcb_profile_enable(pcb_circuit* c, int32_t on) {

@@ -4,21 +4,30 @@
 //   FWD        D[b][r] = sum_t A[b][t] * W[r][t]          A = exp(M - mx),  W = exp(theta)
 //   BWD_CHILD  D[b][t] = sum_r G[b][r] * W[r][t]          G = flows * exp(mx - mars)
 //   BWD_EDGE   D[r][t] = sum_b G[b][r] * A[b][t]
-// run as 128 x N x K tiles (N <= 256) with fp32 accumulators in tensor memory.  Operands are
-// produced in the kernel: eight producer warps read the fp32 work matrices, apply the exp /
-// rescale, split every value into a TF32 "hi" part (top 19 bits) and the exact fp32 remainder
-// "lo", and write both into shared memory in the K-major 128-byte-swizzled layout the tensor
-// core reads.  One elected thread issues three tcgen05.mma per 8-deep K step
-// (hi*hi + lo*hi + hi*lo; the lo*lo term is below 2^-20 relative), so results carry fp32-class
-// accuracy (about 2^-20 relative per product) while the multiply-accumulates run on the tensor
-// pipe.  The epilogue warps read the accumulators with tcgen05.ld and apply log / rescale /
-// the statistics update, writing rows that are contiguous in the example index.
+// run as 128 x N x K tiles (N <= 256) with fp32 accumulators in tensor memory.
+//
+// Precision: every operand value v is split into a TF32 "hi" part (top 19 bits of the fp32
+// pattern) and the exact fp32 remainder "lo"; three tcgen05.mma per 8-deep K step compute
+// hi*hi + lo*hi + hi*lo (the dropped lo*lo term is below 2^-20 relative), so results carry
+// fp32-class accuracy while the multiply-accumulates run on the tensor pipe.
+//
+// Operands:
+//   * data-dependent operands (A, G) are produced in the kernel: sixteen producer warps read the
+//     fp32 work matrices, apply exp / rescale, split, and store into shared memory in the K-major
+//     128-byte-swizzled layout the tensor core reads;
+//   * the weight operand W is the same for every example tile, so once per parameter update
+//     w_image_kernel writes exp(theta), already split and already in the swizzled tile layout,
+//     to two images (W for FWD, W^T for BWD_CHILD); the GEMM kernels fetch a tile of an image
+//     with two cp.async.bulk copies that complete on the stage's mbarrier.
+//   * the per-example maximum mx is computed by a small full-occupancy kernel per layer.
 //
 // Synchronisation: a two-stage ring of shared-memory tiles guarded by mbarriers
-// (full: 256 producer arrivals, empty: one tcgen05.commit), one more mbarrier for "accumulator
-// complete".  Every wait is bounded; on expiry the thread raises the circuit's status word,
-// leaves its loop and still reaches the common exit where tensor memory is released.
+// (full: one arrival per producer warp + the bulk copies' byte count, empty: one tcgen05.commit), one
+// more mbarrier for "accumulator complete".  Every wait is bounded; on expiry the thread raises
+// the circuit's status word, leaves its loop and still reaches the common exit where tensor
+// memory is released.
 #include <algorithm>
+#include <cstdlib>
 
 #include "pcb_internal.h"
 
@@ -30,14 +39,15 @@ constexpr uint32_t TM = 128;         // tile rows (TMEM lanes)
 constexpr uint32_t TN_MAX = 256;     // tile columns
 constexpr uint32_t KCH = 32;         // K elements per stage (one 128-byte swizzle row of tf32)
 constexpr uint32_t STAGES = 2;
-constexpr uint32_t NPROD = 256;      // producer threads (warps 0..7)
+constexpr uint32_t NPROD = 512;      // producer threads (warps 0..15)
+constexpr uint32_t MMA_WARP = NPROD / 32;
 constexpr uint32_t NTHREADS = NPROD + 32;
 constexpr uint32_t A_BYTES = TM * 128;        // one A sub-tile (hi or lo)
 constexpr uint32_t B_BYTES = TN_MAX * 128;    // one B sub-tile (hi or lo)
 constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 2048 /*barriers, mx*/;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 1024 /*barriers, mx*/;
 constexpr uint32_t TMEM_COLS = 256;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;   // try_wait polls before a wait is declared lost
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -46,6 +56,15 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst_smem)),
+               "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
@@ -62,7 +81,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
   for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) __nanosleep(100);
   }
   atomicExch(status, 1);
   return false;
@@ -75,7 +93,6 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);          // start address
-  d |= (uint64_t)0 << 16;                                // leading byte offset (unused, swizzled K-major)
   d |= (uint64_t)(1024u >> 4) << 32;                     // stride byte offset
   d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
   d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
@@ -112,11 +129,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 }
 
 // byte offset of element (row, kk) inside a K-major SWIZZLE_128B tile of tf32
-__device__ __forceinline__ uint32_t sw_off(uint32_t row, uint32_t kk) {
+__host__ __device__ __forceinline__ uint32_t sw_off(uint32_t row, uint32_t kk) {
   return row * 128u + ((((kk >> 2) ^ (row & 7u)) << 4) | ((kk & 3u) << 2));
 }
+__device__ __forceinline__ float tf32_hi(float v) { return __uint_as_float(__float_as_uint(v) & 0xffffe000u); }
 __device__ __forceinline__ void put_split(uint8_t* hi, uint8_t* lo, uint32_t off, float v) {
-  float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+  float h = tf32_hi(v);
   *reinterpret_cast<float*>(hi + off) = h;
   *reinterpret_cast<float*>(lo + off) = v - h;
 }
@@ -127,9 +145,12 @@ struct TcArgs {
   float* blk_mx;
   float* aggr;
   const float* theta;
+  const float* w_img;
   const PcbDenseBlock* blocks;
+  const PcbDenseImg* imgs;
   int* status;
   uint32_t ld, B, b_per_cta;
+  uint32_t dbg;   // timing experiments only: 1 skip MMAs, 2 skip global loads, 4 skip epilogue, 8 skip smem stores
 };
 
 __device__ __forceinline__ float child_val(const float* __restrict__ mars, uint32_t ld, const PcbDenseBlock& k,
@@ -137,6 +158,192 @@ __device__ __forceinline__ float child_val(const float* __restrict__ mars, uint3
   float v = mars[(size_t)(k.c0 + t) * ld + b];
   if (k.d0 != PCB_NONE) v += mars[(size_t)(k.d0 + t) * ld + b];
   return v;
+}
+
+// ---- exp(theta), split and laid out as operand tiles ------------------------------------------------
+// One block converts a 32 x 32 patch (rows r, columns t) of a dense block's weights and writes it
+// to the FWD image (rows r, K = t) and, transposed through shared memory, to the BWD_CHILD image
+// (rows t, K = r).  Image of a dense block: [column tile][K chunk][hi | lo][rows x 128 bytes].
+__global__ void __launch_bounds__(256) w_image_kernel(const float* __restrict__ theta, float* __restrict__ img,
+                                                      const PcbDenseBlock* __restrict__ blocks,
+                                                      const PcbDenseImg* __restrict__ imgs) {
+  __shared__ float tile[32][33];
+  const PcbDenseBlock k = blocks[blockIdx.z];
+  const PcbDenseImg im = imgs[blockIdx.z];
+  const uint32_t t0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  if (t0 >= k.K || r0 >= k.R) return;
+  const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (uint32_t i = ty; i < 32; i += 8) {
+    uint32_t r = r0 + i, t = t0 + tx;
+    tile[i][tx] = (r < k.R && t < k.K) ? __expf(__ldg(theta + k.pid0 + (size_t)r * k.K + t)) : 0.0f;
+  }
+  __syncthreads();
+  {  // FWD image: row = r, kk = t
+    const uint32_t c = t0 / KCH;
+    for (uint32_t i = ty; i < 32; i += 8) {
+      uint32_t r = r0 + i;
+      if (r >= k.R) continue;
+      uint32_t j = r / TN_MAX, row = r % TN_MAX;
+      float* base = img + im.off_f + ((size_t)(j * im.nch_f + c) * 2) * im.rows_f * 32;
+      float v = tile[i][tx], h = tf32_hi(v);
+      uint32_t o = sw_off(row, tx) / 4;
+      base[o] = h;
+      base[(size_t)im.rows_f * 32 + o] = v - h;
+    }
+  }
+  {  // BWD_CHILD image: row = t, kk = r
+    const uint32_t c = r0 / KCH;
+    for (uint32_t i = ty; i < 32; i += 8) {
+      uint32_t t = t0 + i;
+      if (t >= k.K) continue;
+      uint32_t j = t / TN_MAX, row = t % TN_MAX;
+      float* base = img + im.off_t + ((size_t)(j * im.nch_t + c) * 2) * im.rows_t * 32;
+      float v = tile[tx][i], h = tf32_hi(v);
+      uint32_t o = sw_off(row, tx) / 4;
+      base[o] = h;
+      base[(size_t)im.rows_t * 32 + o] = v - h;
+    }
+  }
+}
+
+// ---- per-example maximum of a dense block's child values ---------------------------------------------
+// grid (example tiles of 128, blocks of the layer); 1024 threads: eight per example, each over an
+// eighth of the children, so a thread has at most two rounds of sixteen loads in flight for K = 256
+__global__ void __launch_bounds__(1024) dense_max_kernel(const float* __restrict__ mars, float* __restrict__ blk_mx,
+                                                         uint32_t ld, const PcbDenseBlock* __restrict__ blocks) {
+  __shared__ float part[8][128];
+  const PcbDenseBlock k = blocks[blockIdx.y];
+  const uint32_t bl = threadIdx.x & 127, sl = threadIdx.x >> 7, b = blockIdx.x * 128 + bl;
+  float mx = -INFINITY;
+  if (b < ld) {
+    uint32_t t = sl;
+    for (; t + 56 < k.K; t += 64) {
+      float v[8];
+#pragma unroll
+      for (uint32_t u = 0; u < 8; ++u) v[u] = child_val(mars, ld, k, t + 8 * u, b);
+#pragma unroll
+      for (uint32_t u = 0; u < 8; ++u) mx = fmaxf(mx, v[u]);
+    }
+    for (; t < k.K; t += 8) mx = fmaxf(mx, child_val(mars, ld, k, t, b));
+  }
+  part[sl][bl] = mx;
+  __syncthreads();
+  if (sl == 0 && b < ld) {
+#pragma unroll
+    for (uint32_t u = 1; u < 8; ++u) mx = fmaxf(mx, part[u][bl]);
+    blk_mx[(size_t)k.mx_row * ld + b] = mx;
+  }
+}
+
+// ---- producer side: one K chunk of the data-dependent operands -----------------------------------
+struct ProdCtx {
+  const float* mars;
+  const float* flows;
+  const float* mxrow;   // per-example max of this dense block
+  const float* mxs;     // the same for the tile's 128 examples, in shared memory (FWD, BWD_CHILD)
+  PcbDenseBlock k;
+  uint32_t tid, ld, m0, n0, k_begin, k_end, nq;
+};
+struct ChunkRegs {
+  float ra[8], rm[8], rb[16];
+  float mx;
+  bool vok;
+};
+
+// Thread -> element maps of the producers.
+//  * "row-contiguous" operands (source contiguous along the tile's row index: A of FWD and
+//    BWD_CHILD): a warp covers 8 rows x 4 K positions per step, so its 32 shared-memory stores
+//    fall into 32 different banks of the swizzled tile and its global loads are four full
+//    32-byte sectors; thread: row = 8*warp + (lane & 7), kk = (lane >> 3) + 4*q, q = 0..7.
+//  * "K-contiguous" operands (BWD_EDGE): a warp covers one whole 128-byte row per step;
+//    thread: kk = lane, row = warp + 16*q.
+__device__ __forceinline__ uint32_t rc_row(uint32_t tid) { return ((tid >> 5) << 3) + (tid & 7u); }
+__device__ __forceinline__ uint32_t rc_kk(uint32_t tid, uint32_t q) { return ((tid & 31u) >> 3) + 4u * q; }
+
+// child value M[t][b] with unconditional loads: invalid positions read a safe address and are
+// replaced afterwards, so a chunk's loads carry no control dependence and issue back to back
+__device__ __forceinline__ float child_val_nb(const float* __restrict__ mars, uint32_t ld, const PcbDenseBlock& k,
+                                              uint32_t t, uint32_t b, bool valid) {
+  const uint32_t tt = valid ? t : 0u, bb = valid ? b : 0u;
+  const bool has_sub = k.d0 != PCB_NONE;
+  float v = mars[(size_t)(k.c0 + tt) * ld + bb];
+  float w = mars[(size_t)((has_sub ? k.d0 : k.c0) + tt) * ld + bb];
+  v += has_sub ? w : 0.0f;
+  return valid ? v : -INFINITY;
+}
+
+// raw global loads of chunk i (nothing depends on shared memory, so they can run chunks ahead)
+template <int MODE>
+__device__ __forceinline__ void load_chunk(const ProdCtx& c, uint32_t i, ChunkRegs& r) {
+  const uint32_t kc = c.k_begin + i * KCH, tid = c.tid, ld = c.ld;
+  if (MODE == MODE_FWD) {
+    const uint32_t row = rc_row(tid), b = c.m0 + row;
+    r.mx = c.mxs[row];
+    r.vok = b < ld && r.mx != -INFINITY;
+#pragma unroll
+    for (uint32_t q = 0; q < 8; ++q) {  // A[m = example][kk = child]
+      uint32_t t = kc + rc_kk(tid, q);
+      r.ra[q] = child_val_nb(c.mars, ld, c.k, t, b, r.vok && t < c.k_end);
+    }
+  } else if (MODE == MODE_BWD_CHILD) {
+    const uint32_t row = rc_row(tid), b = c.m0 + row;
+    r.mx = c.mxs[row];
+    r.vok = b < ld && r.mx != -INFINITY;
+#pragma unroll
+    for (uint32_t q = 0; q < 8; ++q) {  // A[m = example][kk = parent] = G
+      uint32_t rr = kc + rc_kk(tid, q);
+      bool e = r.vok && rr < c.k_end;
+      size_t o = (size_t)(c.k.p0 + (e ? rr : 0)) * ld + (e ? b : 0);
+      float f = c.flows[o], m = c.mars[o];
+      r.ra[q] = e ? f : 0.0f;
+      r.rm[q] = e ? m : 0.0f;
+    }
+  } else {
+    const uint32_t b = kc + (tid & 31);
+    const bool bok = b < c.k_end;
+    float mx = c.mxrow[bok ? b : 0];
+    r.mx = bok ? mx : -INFINITY;
+    r.vok = bok && r.mx != -INFINITY;
+#pragma unroll
+    for (uint32_t q = 0; q < 8; ++q) {  // A[m = parent][kk = example] = G: K contiguous
+      uint32_t rr = c.m0 + (tid >> 5) + 16 * q;
+      bool e = r.vok && rr < c.k.R;
+      size_t o = (size_t)(c.k.p0 + (e ? rr : 0)) * ld + (e ? b : 0);
+      float f = c.flows[o], m = c.mars[o];
+      r.ra[q] = e ? f : 0.0f;
+      r.rm[q] = e ? m : 0.0f;
+    }
+#pragma unroll
+    for (uint32_t q = 0; q < 16; ++q) {  // B[n = child][kk = example] = exp(M - mx)
+      uint32_t t = c.n0 + (tid >> 5) + 16 * q;
+      r.rb[q] = (q < c.nq) ? child_val_nb(c.mars, ld, c.k, t, b, r.vok && t < c.k.K) : -INFINITY;
+    }
+  }
+}
+
+// exp / rescale / split and the swizzled shared-memory stores of a loaded chunk
+template <int MODE>
+__device__ __forceinline__ void store_chunk(const ProdCtx& c, const ChunkRegs& r, uint8_t* a_hi, uint8_t* a_lo,
+                                            uint8_t* b_hi, uint8_t* b_lo) {
+  const uint32_t tid = c.tid;
+  if (MODE == MODE_FWD) {
+    const uint32_t row = rc_row(tid);
+#pragma unroll
+    for (uint32_t q = 0; q < 8; ++q)
+      put_split(a_hi, a_lo, sw_off(row, rc_kk(tid, q)), r.vok ? __expf(r.ra[q] - r.mx) : 0.0f);
+  } else if (MODE == MODE_BWD_CHILD) {
+    const uint32_t row = rc_row(tid);
+#pragma unroll
+    for (uint32_t q = 0; q < 8; ++q)
+      put_split(a_hi, a_lo, sw_off(row, rc_kk(tid, q)), r.vok ? r.ra[q] * __expf(r.mx - r.rm[q]) : 0.0f);
+  } else {
+#pragma unroll
+    for (uint32_t q = 0; q < 8; ++q)
+      put_split(a_hi, a_lo, sw_off((tid >> 5) + 16 * q, tid & 31), r.vok ? r.ra[q] * __expf(r.mx - r.rm[q]) : 0.0f);
+#pragma unroll
+    for (uint32_t q = 0; q < 16; ++q)
+      if (q < c.nq) put_split(b_hi, b_lo, sw_off((tid >> 5) + 16 * q, tid & 31), r.vok ? __expf(r.rb[q] - r.mx) : 0.0f);
+  }
 }
 
 // grid: FWD / BWD_CHILD (example tiles of 128, column tiles of 256, blocks)
@@ -150,188 +357,109 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
   uint64_t* empty = full + STAGES;                            // [STAGES]
   uint64_t* accfull = empty + STAGES;                         // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfull + 1);
-  float* mxs = reinterpret_cast<float*>(ctl + 128);           // [128] (+ [128] scratch)
+  float* mxs = reinterpret_cast<float*>(ctl + 128);           // [128]
 
   const PcbDenseBlock k = a.blocks[blockIdx.z];
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t ld = a.ld;
 
   // ---- tile coordinates ---------------------------------------------------------------------
-  uint32_t m0, n0, n_count, k_begin, k_end;  // rows [m0, m0+128), columns [n0, n0+n_count), K range
+  uint32_t m0, n0, n_count, k_begin, k_end, jn;  // rows [m0, m0+128), columns [n0, n0+n_count), K range
   if (MODE == MODE_FWD) {
-    m0 = blockIdx.x * TM; n0 = blockIdx.y * TN_MAX;
+    m0 = blockIdx.x * TM; jn = blockIdx.y; n0 = jn * TN_MAX;
     if (n0 >= k.R) return;
     n_count = min(TN_MAX, k.R - n0); k_begin = 0; k_end = k.K;
   } else if (MODE == MODE_BWD_CHILD) {
-    m0 = blockIdx.x * TM; n0 = blockIdx.y * TN_MAX;
+    m0 = blockIdx.x * TM; jn = blockIdx.y; n0 = jn * TN_MAX;
     if (n0 >= k.K) return;
     n_count = min(TN_MAX, k.K - n0); k_begin = 0; k_end = k.R;
   } else {
     const uint32_t tiles_n = (k.K + TN_MAX - 1) / TN_MAX;
-    m0 = (blockIdx.y / tiles_n) * TM; n0 = (blockIdx.y % tiles_n) * TN_MAX;
+    m0 = (blockIdx.y / tiles_n) * TM; jn = blockIdx.y % tiles_n; n0 = jn * TN_MAX;
     if (m0 >= k.R) return;
     n_count = min(TN_MAX, k.K - n0);
     k_begin = blockIdx.x * a.b_per_cta; k_end = min(a.B, k_begin + a.b_per_cta);
     if (k_begin >= k_end) return;
   }
-  const uint32_t n_tile = (n_count + 15u) & ~15u;           // UMMA N: multiple of 16
   const uint32_t nchunks = (k_end - k_begin + KCH - 1) / KCH;
   const float* mxrow = a.blk_mx + (size_t)k.mx_row * ld;
+  // B tile rows: the image's row count for the bulk-copied operand, else N rounded up to 16
+  uint32_t n_tile = (n_count + 15u) & ~15u;
+  const float* img_tile = nullptr;   // first K chunk of this column tile in the weight image
+  uint32_t img_rows = 0;
+  if (MODE != MODE_BWD_EDGE) {
+    const PcbDenseImg im = a.imgs[blockIdx.z];
+    img_rows = MODE == MODE_FWD ? im.rows_f : im.rows_t;
+    const uint32_t nch = MODE == MODE_FWD ? im.nch_f : im.nch_t;
+    img_tile = a.w_img + (MODE == MODE_FWD ? im.off_f : im.off_t) + (size_t)jn * nch * 2 * img_rows * 32;
+    n_tile = img_rows;   // rows beyond n_count are zero in the image
+  }
 
   // ---- set-up: barriers, tensor memory, per-example max --------------------------------------
   if (tid == 0) {
-    for (uint32_t s = 0; s < STAGES; ++s) { mbar_init(&full[s], NPROD); mbar_init(&empty[s], 1); }
+    for (uint32_t s = 0; s < STAGES; ++s) { mbar_init(&full[s], NPROD / 32); mbar_init(&empty[s], 1); }
     mbar_init(accfull, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 8) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"(TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  if (MODE == MODE_FWD) {
-    if (tid < NPROD) {  // max over the K children of the tile's 128 examples, two threads per example
-      uint32_t bl = tid & 127, half = tid >> 7, b = m0 + bl;
-      float mx = -INFINITY;
-      if (b < ld) {
-        uint32_t t = half;
-        for (; t + 14 < k.K; t += 16) {  // eight independent loads per round
-          float v[8];
-#pragma unroll
-          for (uint32_t u = 0; u < 8; ++u) v[u] = child_val(a.mars, ld, k, t + 2 * u, b);
-#pragma unroll
-          for (uint32_t u = 0; u < 8; ++u) mx = fmaxf(mx, v[u]);
-        }
-        for (; t < k.K; t += 2) mx = fmaxf(mx, child_val(a.mars, ld, k, t, b));
-      }
-      mxs[half * 128 + bl] = mx;
-    }
-  } else if (MODE == MODE_BWD_CHILD) {
-    if (tid < 128) mxs[tid] = (m0 + tid < ld) ? mxrow[m0 + tid] : -INFINITY;
-  }
+  if (MODE != MODE_BWD_EDGE && tid < 128) mxs[tid] = (m0 + tid < ld) ? mxrow[m0 + tid] : -INFINITY;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (MODE == MODE_FWD) {
-    if (tid < 128) {
-      float mx = fmaxf(mxs[tid], mxs[128 + tid]);
-      mxs[tid] = mx;
-      if (blockIdx.y == 0 && m0 + tid < ld) a.blk_mx[(size_t)k.mx_row * ld + m0 + tid] = mx;
-    }
-    __syncthreads();
-  }
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
 
-  if (warp < 8) {
+  if (warp < MMA_WARP) {
     // =========================== producers ===================================================
-    // Each chunk is produced in two phases so that the global loads of a whole chunk are in
-    // flight together (and overlap the wait for the stage to drain): (1) raw loads into
-    // registers, (2) exp / rescale / split and the swizzled shared-memory stores.
-    const uint32_t nq = n_tile / 8;  // B rows per thread in the K-contiguous pattern
-    for (uint32_t i = 0; i < nchunks && ok; ++i) {
+    // The global loads of chunk i+1 are issued before chunk i is transformed and stored, so
+    // their latency overlaps the exp / split / store work and the wait for the stage.
+    ProdCtx ctx{a.mars, a.flows, mxrow, mxs, k, tid, ld, m0, n0, k_begin, k_end, n_tile / 16};
+    ChunkRegs ra0, ra1;   // two register sets, used alternately: no copies on the loop edge
+    auto process = [&](uint32_t i, const ChunkRegs& cr) -> bool {
       const uint32_t s = i & (STAGES - 1), ph = (i / STAGES) & 1u;
-      const uint32_t kc = k_begin + i * KCH;  // first K index of the chunk
-      float ra[16], rm[16], rb[32];
-      float mx = 0.0f;
-      bool vok = false;
-      // ---- phase 1: loads ----
-      if (MODE == MODE_FWD) {
-        const uint32_t row = tid & 127, b = m0 + row;
-        mx = mxs[row];
-        vok = b < ld && mx != -INFINITY;
-#pragma unroll
-        for (uint32_t q = 0; q < 16; ++q) {  // A[m = example][kk = child]: rows contiguous in the source
-          uint32_t t = kc + (tid >> 7) * 16 + q;
-          ra[q] = (vok && t < k_end) ? child_val(a.mars, ld, k, t, b) : -INFINITY;
-        }
-        const uint32_t t = kc + (tid & 31);
-#pragma unroll
-        for (uint32_t q = 0; q < 32; ++q) {  // B[n = parent][kk = child]: K contiguous in the source
-          uint32_t r = n0 + (tid >> 5) + 8 * q;
-          rb[q] = (q < nq && r < k.R && t < k_end) ? __ldg(a.theta + k.pid0 + (size_t)r * k.K + t) : -INFINITY;
-        }
-      } else if (MODE == MODE_BWD_CHILD) {
-        const uint32_t row = tid & 127, b = m0 + row;
-        mx = mxs[row];
-        vok = b < ld && mx != -INFINITY;
-#pragma unroll
-        for (uint32_t q = 0; q < 16; ++q) {  // A[m = example][kk = parent] = G
-          uint32_t r = kc + (tid >> 7) * 16 + q;
-          bool e = vok && r < k_end;
-          size_t o = (size_t)(k.p0 + (e ? r : 0)) * ld + (e ? b : 0);
-          ra[q] = e ? a.flows[o] : 0.0f;
-          rm[q] = e ? a.mars[o] : 0.0f;
-        }
-        const uint32_t t = n0 + tid;
-#pragma unroll
-        for (uint32_t kk = 0; kk < 32; ++kk) {  // B[n = child][kk = parent] = W[r][t]: rows contiguous
-          uint32_t r = kc + kk;
-          rb[kk] = (tid < n_tile && t < k.K && r < k_end) ? __ldg(a.theta + k.pid0 + (size_t)r * k.K + t) : -INFINITY;
-        }
-      } else {
-        const uint32_t b = kc + (tid & 31);
-        mx = b < k_end ? mxrow[b] : -INFINITY;
-        vok = b < k_end && mx != -INFINITY;
-#pragma unroll
-        for (uint32_t q = 0; q < 16; ++q) {  // A[m = parent][kk = example] = G: K contiguous
-          uint32_t r = m0 + (tid >> 5) + 8 * q;
-          bool e = vok && r < k.R;
-          size_t o = (size_t)(k.p0 + (e ? r : 0)) * ld + (e ? b : 0);
-          ra[q] = e ? a.flows[o] : 0.0f;
-          rm[q] = e ? a.mars[o] : 0.0f;
-        }
-#pragma unroll
-        for (uint32_t q = 0; q < 32; ++q) {  // B[n = child][kk = example] = exp(M - mx)
-          uint32_t t = n0 + (tid >> 5) + 8 * q;
-          rb[q] = (q < nq && vok && t < k.K) ? child_val(a.mars, ld, k, t, b) : -INFINITY;
-        }
-      }
-      // ---- wait for the stage, then phase 2: transform + store ----
-      ok = mbar_wait(&empty[s], ph ^ 1u, a.status);
-      if (!ok) break;
+      // one lane per warp polls; __syncwarp orders the other lanes' stores behind the observed phase
+      bool got = lane != 0 || mbar_wait(&empty[s], ph ^ 1u, a.status);
+      got = __all_sync(0xffffffffu, got);
+      if (!got) return false;
       uint8_t* a_hi = smem + s * STAGE_BYTES;
       uint8_t* a_lo = a_hi + A_BYTES;
       uint8_t* b_hi = a_lo + A_BYTES;
       uint8_t* b_lo = b_hi + B_BYTES;
-      if (MODE == MODE_FWD) {
-        const uint32_t row = tid & 127;
-#pragma unroll
-        for (uint32_t q = 0; q < 16; ++q)
-          put_split(a_hi, a_lo, sw_off(row, (tid >> 7) * 16 + q), vok ? __expf(ra[q] - mx) : 0.0f);
-#pragma unroll
-        for (uint32_t q = 0; q < 32; ++q)
-          if (q < nq) put_split(b_hi, b_lo, sw_off((tid >> 5) + 8 * q, tid & 31), __expf(rb[q]));
-      } else if (MODE == MODE_BWD_CHILD) {
-        const uint32_t row = tid & 127;
-#pragma unroll
-        for (uint32_t q = 0; q < 16; ++q)
-          put_split(a_hi, a_lo, sw_off(row, (tid >> 7) * 16 + q), vok ? ra[q] * __expf(mx - rm[q]) : 0.0f);
-        if (tid < n_tile) {
-#pragma unroll
-          for (uint32_t kk = 0; kk < 32; ++kk) put_split(b_hi, b_lo, sw_off(tid, kk), __expf(rb[kk]));
-        }
-      } else {
-#pragma unroll
-        for (uint32_t q = 0; q < 16; ++q)
-          put_split(a_hi, a_lo, sw_off((tid >> 5) + 8 * q, tid & 31), vok ? ra[q] * __expf(mx - rm[q]) : 0.0f);
-#pragma unroll
-        for (uint32_t q = 0; q < 32; ++q)
-          if (q < nq) put_split(b_hi, b_lo, sw_off((tid >> 5) + 8 * q, tid & 31), vok ? __expf(rb[q] - mx) : 0.0f);
+      if (MODE != MODE_BWD_EDGE && tid == 0) {  // weight tile: hi and lo parts straight from the image
+        const uint32_t bytes = img_rows * 128u;
+        const float* src = img_tile + (size_t)i * 2 * img_rows * 32;
+        mbar_expect_tx(&full[s], 2 * bytes);
+        bulk_g2s(b_hi, src, bytes, &full[s]);
+        bulk_g2s(b_lo, src + (size_t)img_rows * 32, bytes, &full[s]);
       }
+      if (!(a.dbg & 8u)) store_chunk<MODE>(ctx, cr, a_hi, a_lo, b_hi, b_lo);
       fence_proxy_async();   // make the generic-proxy writes visible to the tensor core
-      mbar_arrive(&full[s]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full[s]);   // one arrival per warp: 512 arrivals on one word serialise
+      return true;
+    };
+    load_chunk<MODE>(ctx, 0, ra0);
+    for (uint32_t i = 0; i < nchunks && ok; i += 2) {
+      if (i + 1 < nchunks) load_chunk<MODE>(ctx, i + 1, ra1);
+      ok = process(i, ra0);
+      if (!ok || i + 1 >= nchunks) break;
+      if (i + 2 < nchunks) load_chunk<MODE>(ctx, i + 2, ra0);
+      ok = process(i + 1, ra1);
     }
 
     // =========================== epilogue ====================================================
-    if (ok) ok = mbar_wait(accfull, 0, a.status);
+    if (ok && lane == 0) ok = mbar_wait(accfull, 0, a.status);
     ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
+    if (ok && !(a.dbg & 4u)) {
       tc_fence_after();
-      const uint32_t q4 = warp & 3, half = warp >> 2;
+      const uint32_t q4 = warp & 3, grp = warp >> 2;   // lane quarter, 64-column group
       const uint32_t row = q4 * 32 + lane;
-      const uint32_t c_begin = half * (TN_MAX / 2), c_end = min(n_tile, c_begin + TN_MAX / 2);
+      const uint32_t c_begin = grp * 64, c_end = min(n_tile, c_begin + 64);
       float acc[32];
       for (uint32_t c0 = c_begin; c0 < c_end; c0 += 32) {
         tmem_ld32(tmem_base + ((q4 * 32u) << 16) + c0, acc);
@@ -349,12 +477,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
           uint32_t b = m0 + row;
           float mx = mxs[row];
           if (b < ld) {
+            // all child values first (independent loads), then the products and the stores:
+            // the stores to flows would otherwise order every later load behind them
+            float cv[32];
+#pragma unroll
+            for (uint32_t j = 0; j < 32; ++j) {
+              uint32_t t = n0 + c0 + j;
+              cv[j] = child_val_nb(a.mars, ld, k, t, b, t < k.K && mx != -INFINITY);
+            }
 #pragma unroll
             for (uint32_t j = 0; j < 32; ++j) {
               uint32_t t = n0 + c0 + j;
               if (t < k.K) {
-                float av = mx == -INFINITY ? 0.0f : __expf(child_val(a.mars, ld, k, t, b) - mx);
-                float f = acc[j] * av;
+                float f = acc[j] * __expf(cv[j] - mx);   // exp(-inf) = 0 for masked entries
                 a.flows[(size_t)(k.c0 + t) * ld + b] = f;
                 if (k.d0 != PCB_NONE) a.flows[(size_t)(k.d0 + t) * ld + b] = f;
               }
@@ -363,15 +498,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
         } else {
           uint32_t r = m0 + row;
           if (r < k.R) {
-            const bool whole = gridDim.x == 1;
+            float wv[32];
 #pragma unroll
             for (uint32_t j = 0; j < 32; ++j) {
               uint32_t t = n0 + c0 + j;
-              if (t < k.K) {
-                size_t p = k.pid0 + (size_t)r * k.K + t;
-                float v = __expf(__ldg(a.theta + p)) * acc[j];
-                if (whole) a.aggr[p] += v; else atomicAdd(a.aggr + p, v);
-              }
+              wv[j] = __ldg(a.theta + k.pid0 + (size_t)r * k.K + (t < k.K ? t : 0));
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < 32; ++j) {
+              uint32_t t = n0 + c0 + j;
+              // reduction without a return value: fire-and-forget; one writer per element unless
+              // the examples are sliced over several CTAs
+              if (t < k.K) atomicAdd(a.aggr + k.pid0 + (size_t)r * k.K + t, __expf(wv[j]) * acc[j]);
             }
           }
         }
@@ -389,6 +527,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t d_ahi = make_desc(sa), d_alo = make_desc(sa + A_BYTES);
         const uint64_t d_bhi = make_desc(sa + 2 * A_BYTES), d_blo = make_desc(sa + 2 * A_BYTES + B_BYTES);
+        if (!(a.dbg & 1u))
 #pragma unroll
         for (uint32_t ks = 0; ks < KCH / 8; ++ks) {
           const uint64_t adv = (uint64_t)((ks * 32u) >> 4);  // 8 tf32 = 32 bytes along K
@@ -406,7 +545,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
   // ---- common exit: release tensor memory ---------------------------------------------------------
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
@@ -423,6 +562,11 @@ int32_t launch(dim3 grid, const TcArgs& args, cudaStream_t st) {
   return PCB_OK;
 }
 
+TcArgs make_args(pcb_circuit* c, pcb_workspace* ws, uint32_t o0) {
+  return TcArgs{ws->mars, ws->flows, ws->blk_mx, c->aggr, c->theta, c->w_img, c->dense + o0, c->dense_img + o0,
+                c->status, ws->ld, ws->B, 0, getenv("PCB_TC_DEBUG") ? (uint32_t)atoi(getenv("PCB_TC_DEBUG")) : 0u};
+}
+
 }  // namespace
 
 #define PCB_TRY(expr)              \
@@ -431,11 +575,55 @@ int32_t launch(dim3 grid, const TcArgs& args, cudaStream_t st) {
     if (_s != PCB_OK) return _s;   \
   } while (0)
 
+// Lays out the weight images of every dense block (host side) and allocates them.
+int32_t pcb_dense_tc_prepare(pcb_circuit* c, uint64_t* bytes) {
+  std::vector<PcbDenseImg> imgs(c->h_dense.size());
+  uint64_t off = 0;
+  for (size_t i = 0; i < c->h_dense.size(); ++i) {
+    const PcbDenseBlock& k = c->h_dense[i];
+    PcbDenseImg& im = imgs[i];
+    im.rows_f = std::min<uint32_t>(TN_MAX, pcb_round_up(k.R, 16));
+    im.rows_t = std::min<uint32_t>(TN_MAX, pcb_round_up(k.K, 16));
+    im.nch_f = (k.K + KCH - 1) / KCH;
+    im.nch_t = (k.R + KCH - 1) / KCH;
+    uint64_t tiles_f = (k.R + TN_MAX - 1) / TN_MAX, tiles_t = (k.K + TN_MAX - 1) / TN_MAX;
+    im.off_f = off; off += tiles_f * im.nch_f * 2 * im.rows_f * 32;
+    im.off_t = off; off += tiles_t * im.nch_t * 2 * im.rows_t * 32;
+  }
+  c->w_img_len = off;
+  PCB_CUDA(cudaMalloc((void**)&c->w_img, std::max<uint64_t>(off, 1) * sizeof(float)));
+  PCB_CUDA(cudaMemset(c->w_img, 0, std::max<uint64_t>(off, 1) * sizeof(float)));  // padding rows / columns stay zero
+  PCB_CUDA(cudaMalloc((void**)&c->dense_img, std::max<size_t>(imgs.size(), 1) * sizeof(PcbDenseImg)));
+  if (!imgs.empty())
+    PCB_CUDA(cudaMemcpy(c->dense_img, imgs.data(), imgs.size() * sizeof(PcbDenseImg), cudaMemcpyHostToDevice));
+  *bytes += off * sizeof(float) + imgs.size() * sizeof(PcbDenseImg);
+  c->w_img_valid = false;
+  return PCB_OK;
+}
+
+// Regenerates the weight images if the parameters changed since they were last written.
+int32_t pcb_dense_tc_refresh(pcb_circuit* c, cudaStream_t st) {
+  if (c->w_img_valid || c->n_dense == 0) return PCB_OK;
+  for (uint32_t z0 = 0; z0 < c->n_dense; z0 += 65535) {
+    uint32_t nz = std::min<uint32_t>(65535, c->n_dense - z0);
+    dim3 grid((c->max_dense_K + 31) / 32, (c->max_dense_R + 31) / 32, nz);
+    PcbProfScope ps(c, st, PCB_K_W_IMAGE);
+    w_image_kernel<<<grid, 256, 0, st>>>(c->theta, c->w_img, c->dense + z0, c->dense_img + z0);
+  }
+  c->w_img_valid = true;
+  return PCB_OK;
+}
+
 int32_t pcb_dense_tc_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st) {
   uint32_t o0 = c->h_dense_off[layer], o1 = c->h_dense_off[layer + 1];
   if (o1 == o0) return PCB_OK;
-  TcArgs args{ws->mars, ws->flows, ws->blk_mx, c->aggr, c->theta, c->dense + o0, c->status, ws->ld, ws->B, 0};
-  dim3 grid((pcb_round_up(ws->B, 32) + TM - 1) / TM, (c->max_dense_R + TN_MAX - 1) / TN_MAX, o1 - o0);
+  const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM;
+  {
+    PcbProfScope ps(c, st, PCB_K_DENSE_MAX);
+    dense_max_kernel<<<dim3(bt, o1 - o0), 1024, 0, st>>>(ws->mars, ws->blk_mx, ws->ld, c->dense + o0);
+  }
+  TcArgs args = make_args(c, ws, o0);
+  dim3 grid(bt, (c->max_dense_R + TN_MAX - 1) / TN_MAX, o1 - o0);
   PcbProfScope ps(c, st, PCB_K_DENSE_FWD);
   return launch<MODE_FWD>(grid, args, st);
 }
@@ -443,7 +631,7 @@ int32_t pcb_dense_tc_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, 
 int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st) {
   uint32_t o0 = c->h_dense_off[layer], o1 = c->h_dense_off[layer + 1];
   if (o1 == o0) return PCB_OK;
-  TcArgs args{ws->mars, ws->flows, ws->blk_mx, c->aggr, c->theta, c->dense + o0, c->status, ws->ld, ws->B, 0};
+  TcArgs args = make_args(c, ws, o0);
   {
     dim3 grid((pcb_round_up(ws->B, 32) + TM - 1) / TM, (c->max_dense_K + TN_MAX - 1) / TN_MAX, o1 - o0);
     PcbProfScope ps(c, st, PCB_K_DENSE_BWD_CHILD);

@@ -332,6 +332,7 @@ extern "C" int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   cudaStream_t st = (cudaStream_t)s;
   ws->B = B; ws->data = data_dev; ws->miss = miss_dev; ws->num_rows = num_rows;
   ws->row_ids = row_ids_dev; ws->row_start = row_start; ws->have_forward = false;
+  if (c->use_tc) PCB_TRY(pcb_dense_tc_refresh(c, st));
   if (c->n_inputs) {
     PcbProfScope ps(c, st, PCB_K_LEAF_FWD);
     dim3 grid(c->n_lchunks, (B + LBT - 1) / LBT);
@@ -413,6 +414,7 @@ extern "C" int32_t pcb_em_update(pcb_circuit* c, float pseudocount, float inerti
   if (c->n_inputs)
     { PcbProfScope ps(c, st, PCB_K_UPDATE); em_update_leaf_kernel<<<(c->n_inputs + 7) / 8, 256, 0, st>>>(c->theta, c->aggr, c->n_inputs, c->in_cats,
                                                                  c->in_poff, c->in_foff, pseudocount, inertia); }
+  c->w_img_valid = false;  // the weights changed
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
 }

@@ -39,6 +39,14 @@ struct PcbDenseBlock {
   uint32_t pad;
 };
 
+// Where a dense block's weight images live (floats into w_img): exp(theta) split into TF32 hi/lo
+// and stored as operand tiles [column tile][K chunk][hi | lo][rows x 32 floats, 128-byte swizzle].
+// off_f / rows_f / nch_f: rows = parents, K = children (forward); off_t / ...: the transpose.
+struct PcbDenseImg {
+  uint64_t off_f, off_t;
+  uint32_t rows_f, rows_t, nch_f, nch_t;
+};
+
 // incoming-edge entry of a node (CSR by child, used by every top-down pass)
 struct PcbInEntry {
   uint32_t parent;
@@ -50,7 +58,8 @@ struct PcbInEntry {
 // kernel classes for launch counting and the optional per-class event timing
 enum PcbKernelClass {
   PCB_K_LEAF_FWD = 0, PCB_K_SPARSE_UP, PCB_K_DENSE_FWD, PCB_K_SPARSE_DOWN, PCB_K_DENSE_BWD_CHILD,
-  PCB_K_DENSE_BWD_EDGE, PCB_K_LEAF_FLOW, PCB_K_UPDATE, PCB_K_MISC, PCB_K_ALLREDUCE, PCB_K_COUNT
+  PCB_K_DENSE_BWD_EDGE, PCB_K_LEAF_FLOW, PCB_K_UPDATE, PCB_K_MISC, PCB_K_ALLREDUCE, PCB_K_DENSE_MAX,
+  PCB_K_W_IMAGE, PCB_K_COUNT
 };
 struct PcbProfEvent { int cls; cudaEvent_t e0, e1; };
 struct PcbProf {
@@ -124,6 +133,10 @@ struct pcb_circuit {
 
   // ---- dense-block implementation and the device status word bounded waits report to ----
   bool use_tc = false;
+  float* w_img = nullptr;
+  PcbDenseImg* dense_img = nullptr;
+  uint64_t w_img_len = 0;
+  bool w_img_valid = false;
   int* status = nullptr;
 
   // ---- multi-GPU ----
@@ -198,3 +211,5 @@ int32_t pcb_ws_ensure_sets(pcb_workspace* ws, uint32_t S, bool need_stack);
 int32_t pcb_dense_tc_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
 int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
 int32_t pcb_check_status(pcb_circuit* c);
+int32_t pcb_dense_tc_prepare(pcb_circuit* c, uint64_t* bytes);
+int32_t pcb_dense_tc_refresh(pcb_circuit* c, cudaStream_t st);
