@@ -112,7 +112,9 @@ def algorithmic_work(fc, info, B):
         "leaf_flow": {"bytes": B * n_in * (4.0 + 4.0) + B * fc.num_vars},
         "sparse_up": {"bytes": 4.0 * B * (N - n_in - dense_nodes) * 3},
         "sparse_down": {"bytes": 4.0 * B * (N - 2 * dense_nodes) * 4},
-        "em_update": {"bytes": 4.0 * (4 * Es + 4 * fc.num_inner_params * 0 + 4 * fc.num_input_params)},
+        "em_update": {"bytes": 16.0 * (Es + fc.num_input_params)},
+        "dense_max": {"bytes": 4.0 * B * dense_nodes * 2},
+        "w_image": {"bytes": 20.0 * Ed},
     }
     return work
 
@@ -231,7 +233,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     value = Bg * args.steps / (ms * 1e-3)
-    ll_last = float(ll.item()) / B
+    ll_last = float(ll.item()) / Bg   # the statistics vector (and its log-likelihood slot) is summed over ranks
 
     # ---- per-kernel-class timing (separate pass, events around every launch) -------------------
     m.profile_enable(True)
