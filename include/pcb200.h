@@ -188,6 +188,17 @@ int32_t pcb_adam_step(pcb_circuit* c, float* theta_dev, const float* grad_dev, f
 int32_t pcb_sample_hard(pcb_circuit* c, pcb_workspace* ws, const float* params_dev, uint32_t Sp,
                         const float* u_sum_dev, const float* u_leaf_dev, uint32_t S,
                         int32_t* x_out_dev, pcb_stream s);
+/* Same samples as pcb_sample_hard, for callers that must not see this library allocate: no
+ * workspace argument, no cudaMalloc / cudaFree inside.  Julia's CUDA.jl (and any host that has
+ * given all device memory to its own pool) can be refused memory by a foreign cudaMalloc, which
+ * also synchronises the device under its streams.  The walk stacks live in a static 4 MiB
+ * device array of the library instead, so S * (num_vars + 2) must not exceed 2^20 words
+ * (PCB_ERR_TOO_LARGE otherwise).  The array is shared: calls that overlap on the GPU race.  The
+ * first call on a device looks the array's address up; make that call before starting a stream
+ * capture.  This entry point has no counterpart in the reference. */
+int32_t pcb_sample_hard_static(pcb_circuit* c, const float* params_dev, uint32_t Sp,
+                               const float* u_sum_dev, const float* u_leaf_dev, uint32_t S,
+                               int32_t* x_out_dev, pcb_stream s);
 /* Soft Gumbel-softmax sampling (queries/sample.jl:8-383): u_dev [S, num_inner_params]
  * column-major uniforms or NULL for no_gumbel=true; out_dev is input_aggr_params
  * [S, num_vars, max_num_cats] column-major. */

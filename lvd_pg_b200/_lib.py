@@ -55,6 +55,7 @@ SIGNATURES = {
     "pcb_kld_edge_klds": [_vp, _vp, _vp, _vp, _u32, _vp, _vp],
     "pcb_adam_step": [_vp, _vp, _vp, _vp, _vp, _i32, _f32, _f32, _f32, _f32, _f32, _vp],
     "pcb_sample_hard": [_vp, _vp, _vp, _u32, _vp, _vp, _u32, _vp, _vp],
+    "pcb_sample_hard_static": [_vp, _vp, _u32, _vp, _vp, _u32, _vp, _vp],
     "pcb_sample_soft": [_vp, _vp, _vp, _u32, _vp, _f32, _u32, _vp, _vp],
     "pcb_comm_unique_id": [_vp],
     "pcb_comm_init": [_vp, _vp, _i32, _i32],

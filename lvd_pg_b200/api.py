@@ -390,6 +390,17 @@ def sample(mbpc: CuMetaBitsProbCircuit, params: ArrayLike, u_sum: ArrayLike, u_l
     return x.t()
 
 
+def sample_static(mbpc: CuMetaBitsProbCircuit, params: torch.Tensor, u_sum: torch.Tensor, u_leaf: torch.Tensor,
+                  x_out: torch.Tensor) -> torch.Tensor:
+    """`sample` for callers whose memory pool must stay in charge: every buffer, the output
+    included, is passed in as a CUDA tensor in the layout the C ABI takes (params [P, Sp]
+    contiguous, x_out [V, S] int32) and the library allocates nothing (pcb_sample_hard_static)."""
+    S = int(u_leaf.shape[0])
+    _lib.check(mbpc.lib.pcb_sample_hard_static(mbpc.handle, _ptr(params), int(params.shape[1]), _ptr(u_sum),
+                                               _ptr(u_leaf), S, _ptr(x_out), _stream(mbpc.device)))
+    return x_out.t()
+
+
 def gumbel_sample(mbpc: CuMetaBitsProbCircuit, params: ArrayLike, num_vars: int, par_buffer_size: int,
                   temperature: float, no_gumbel: bool = False, u: Optional[ArrayLike] = None, S: Optional[int] = None):
     """Relaxed top-down sampling: returns input_aggr_params [S, num_vars, par_buffer_size].

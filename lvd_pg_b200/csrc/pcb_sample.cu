@@ -260,3 +260,72 @@ extern "C" int32_t pcb_sample_soft(pcb_circuit* c, pcb_workspace* ws, const floa
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
 }
+
+// ---- hard sampling without any allocation --------------------------------------------------------------
+// Some hosts of this library must not see it allocate device memory.  Julia's CUDA.jl, which is
+// where the reference lives, keeps nearly all free device memory in its own pool, so a
+// cudaMalloc issued behind its back can fail with memory "free" from Julia's point of view, and
+// it synchronises the whole device under the caller's running streams; a serving loop that has
+// already handed every byte to its own arena is in the same position.  pcb_sample_hard needs a
+// workspace and grows it on demand; this variant keeps the per-sample walk stacks (and the
+// status word the bounded walk reports to) in a fixed array that is part of the library image
+// instead, so every GPU that loads the library holds PCB_STATIC_SAMPLE_WORDS * 4 bytes (4 MiB)
+// of it until the process exits.
+//
+// The array is shared by all calls on a device and keeps whatever the last call left in it:
+// stacks are written before they are read and the status word is cleared on the stream at the
+// start of every call, but two calls whose kernels overlap on the GPU (different streams) race.
+#define PCB_STATIC_SAMPLE_WORDS (1u << 20)
+static __device__ __align__(256) uint32_t g_static_sample_scratch[PCB_STATIC_SAMPLE_WORDS + 64];
+
+namespace {
+constexpr int kMaxDevices = 64;
+uint32_t* g_scratch_addr[kMaxDevices] = {nullptr};  // device address of the array, per device
+
+// In host code the array's name is only a handle for the runtime, not a device pointer: the
+// address a kernel may use comes from cudaGetSymbolAddress, asked once per device while that
+// device is current.
+int32_t static_scratch(int device, uint32_t** out) {
+  PCB_REQUIRE(device >= 0 && device < kMaxDevices, "device index beyond the static scratch table");
+  if (!g_scratch_addr[device]) {
+    uint32_t* p = nullptr;
+    PCB_CUDA(cudaGetSymbolAddress((void**)&p, g_static_sample_scratch));
+    g_scratch_addr[device] = p;
+  }
+  *out = g_scratch_addr[device];
+  return PCB_OK;
+}
+}  // namespace
+
+extern "C" int32_t pcb_sample_hard_static(pcb_circuit* c, const float* params_dev, uint32_t Sp,
+                                          const float* u_sum_dev, const float* u_leaf_dev, uint32_t S,
+                                          int32_t* x_out_dev, pcb_stream s) {
+  PCB_REQUIRE(c && params_dev && u_leaf_dev && x_out_dev, "null argument");
+  PCB_REQUIRE(u_sum_dev || c->n_regions == 0, "u_sum missing");
+  PCB_REQUIRE(S >= 1 && (Sp == 1 || Sp == S), "params must hold 1 or S parameter sets");
+  const uint64_t stack_cap = (uint64_t)c->V + 2;
+  if ((uint64_t)S * stack_cap > PCB_STATIC_SAMPLE_WORDS)
+    return pcb_fail(PCB_ERR_TOO_LARGE,
+                    "pcb_sample_hard_static: S * (num_vars + 2) = " + std::to_string((uint64_t)S * stack_cap) +
+                        " exceeds the static scratch of " + std::to_string(PCB_STATIC_SAMPLE_WORDS) +
+                        " words; sample in smaller groups or use pcb_sample_hard");
+  PCB_CUDA(cudaSetDevice(c->device));
+  uint32_t* scratch = nullptr;
+  int32_t st0 = static_scratch(c->device, &scratch);   // first call on a device resolves the symbol
+  if (st0 != PCB_OK) return st0;
+  cudaStream_t st = (cudaStream_t)s;
+  int32_t* status = reinterpret_cast<int32_t*>(scratch + PCB_STATIC_SAMPLE_WORDS);
+  PCB_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
+  const uint32_t warps_per_block = 4;
+  sample_hard_kernel<<<(S + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, st>>>(
+      S, params_dev, Sp, u_sum_dev, u_leaf_dev, c->n_regions, c->max_group, c->max_cats, c->V, c->N, c->kind,
+      c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime, c->e_sub, c->node2input, c->in_var, c->in_cats,
+      c->in_poff, c->P, c->theta, scratch, (uint32_t)stack_cap, x_out_dev, status);
+  PCB_CUDA(cudaGetLastError());
+  int32_t h = 0;
+  PCB_CUDA(cudaMemcpyAsync(&h, status, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  PCB_CUDA(cudaStreamSynchronize(st));
+  if (h == 1) return pcb_fail(PCB_ERR_TOO_LARGE, "sampling walk overflowed its stack (circuit not decomposable?)");
+  if (h == 2) return pcb_fail(PCB_ERR_INVALID, "sampling walk exceeded its iteration limit (malformed circuit)");
+  return PCB_OK;
+}
