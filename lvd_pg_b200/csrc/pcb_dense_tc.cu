@@ -85,6 +85,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   atomicExch(status, 1);
   return false;
 }
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -150,6 +155,7 @@ struct TcArgs {
   const PcbDenseImg* imgs;
   int* status;
   uint32_t ld, B, b_per_cta;
+  unsigned long long* trace;   // timing trace of CTA (0,0,0), or null
   uint32_t dbg;   // timing experiments only: 1 skip MMAs, 2 skip global loads, 4 skip epilogue, 8 skip smem stores
 };
 
@@ -359,6 +365,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfull + 1);
   float* mxs = reinterpret_cast<float*>(ctl + 128);           // [128]
 
+  if (a.trace && threadIdx.x == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[504] = gtime();
   const PcbDenseBlock k = a.blocks[blockIdx.z];
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t ld = a.ld;
@@ -413,6 +420,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
+  if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[503] = gtime();
 
   if (warp < MMA_WARP) {
     // =========================== producers ===================================================
@@ -422,6 +430,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
     ChunkRegs ra0, ra1;   // two register sets, used alternately: no copies on the loop edge
     auto process = [&](uint32_t i, const ChunkRegs& cr) -> bool {
       const uint32_t s = i & (STAGES - 1), ph = (i / STAGES) & 1u;
+      const bool tr = a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && i < 60;
+      if (tr) a.trace[i * 8 + 0] = gtime();
       // one lane per warp polls; __syncwarp orders the other lanes' stores behind the observed phase
       bool got = lane != 0 || mbar_wait(&empty[s], ph ^ 1u, a.status);
       got = __all_sync(0xffffffffu, got);
@@ -430,6 +440,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
       uint8_t* a_lo = a_hi + A_BYTES;
       uint8_t* b_hi = a_lo + A_BYTES;
       uint8_t* b_lo = b_hi + B_BYTES;
+      if (tr) a.trace[i * 8 + 1] = gtime();
       if (MODE != MODE_BWD_EDGE && tid == 0) {  // weight tile: hi and lo parts straight from the image
         const uint32_t bytes = img_rows * 128u;
         const float* src = img_tile + (size_t)i * 2 * img_rows * 32;
@@ -438,9 +449,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
         bulk_g2s(b_lo, src + (size_t)img_rows * 32, bytes, &full[s]);
       }
       if (!(a.dbg & 8u)) store_chunk<MODE>(ctx, cr, a_hi, a_lo, b_hi, b_lo);
+      if (tr) a.trace[i * 8 + 2] = gtime();
       fence_proxy_async();   // make the generic-proxy writes visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(&full[s]);   // one arrival per warp: 512 arrivals on one word serialise
+      if (tr) a.trace[i * 8 + 3] = gtime();
       return true;
     };
     load_chunk<MODE>(ctx, 0, ra0);
@@ -453,8 +466,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
     }
 
     // =========================== epilogue ====================================================
+    if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[500] = gtime();
     if (ok && lane == 0) ok = mbar_wait(accfull, 0, a.status);
     ok = __all_sync(0xffffffffu, ok);
+    if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[501] = gtime();
     if (ok && !(a.dbg & 4u)) {
       tc_fence_after();
       const uint32_t q4 = warp & 3, grp = warp >> 2;   // lane quarter, 64-column group
@@ -496,22 +511,28 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
             }
           }
         } else {
-          uint32_t r = m0 + row;
-          if (r < k.R) {
-            float wv[32];
+          // The accumulator arrives with one tile row per lane; the statistics rows are
+          // contiguous along the column index.  Transpose the 32 x 32 patch through shared memory
+          // (the operand stages are idle once the accumulator is complete) so that a warp reads
+          // theta and issues its reductions as whole 128-byte lines.
+          float* patch = reinterpret_cast<float*>(smem) + warp * (32 * 33);
 #pragma unroll
-            for (uint32_t j = 0; j < 32; ++j) {
-              uint32_t t = n0 + c0 + j;
-              wv[j] = __ldg(a.theta + k.pid0 + (size_t)r * k.K + (t < k.K ? t : 0));
-            }
-#pragma unroll
-            for (uint32_t j = 0; j < 32; ++j) {
-              uint32_t t = n0 + c0 + j;
-              // reduction without a return value: fire-and-forget; one writer per element unless
-              // the examples are sliced over several CTAs
-              if (t < k.K) atomicAdd(a.aggr + k.pid0 + (size_t)r * k.K + t, __expf(wv[j]) * acc[j]);
+          for (uint32_t j = 0; j < 32; ++j) patch[lane * 33 + j] = acc[j];
+          __syncwarp();
+          const uint32_t t = n0 + c0 + lane;
+          if (t < k.K) {
+#pragma unroll 8
+            for (uint32_t rr = 0; rr < 32; ++rr) {
+              const uint32_t r = m0 + q4 * 32 + rr;
+              if (r < k.R) {
+                const size_t p = k.pid0 + (size_t)r * k.K + t;
+                // reduction without a return value: fire-and-forget; one writer per element unless
+                // the examples are sliced over several CTAs
+                atomicAdd(a.aggr + p, __expf(__ldg(a.theta + p)) * patch[rr * 33 + lane]);
+              }
             }
           }
+          __syncwarp();
         }
       }
     }
@@ -521,8 +542,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
       const uint32_t idesc = make_idesc(TM, n_tile);
       for (uint32_t i = 0; i < nchunks && ok; ++i) {
         const uint32_t s = i & (STAGES - 1), ph = (i / STAGES) & 1u;
+        const bool tr = a.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && i < 60;
+        if (tr) a.trace[i * 8 + 4] = gtime();
         ok = mbar_wait(&full[s], ph, a.status);
         if (!ok) break;
+        if (tr) a.trace[i * 8 + 5] = gtime();
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t d_ahi = make_desc(sa), d_alo = make_desc(sa + A_BYTES);
@@ -536,15 +560,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
           umma_tf32(tmem_base, d_ahi + adv, d_blo + adv, idesc, 1u);
         }
         umma_commit(&empty[s]);   // the stage may be refilled once these MMAs have read it
+        if (tr) a.trace[i * 8 + 6] = gtime();
       }
       if (ok) umma_commit(accfull);
     }
     __syncwarp();
   }
 
+  if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[502] = gtime();
   // ---- common exit: release tensor memory ---------------------------------------------------------
   tc_fence_before();
   __syncthreads();
+  if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[505] = gtime();
   if (warp == MMA_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -562,9 +589,15 @@ int32_t launch(dim3 grid, const TcArgs& args, cudaStream_t st) {
   return PCB_OK;
 }
 
+unsigned long long* g_trace = nullptr;   // diagnostic buffer, allocated when PCB_TC_TRACE is set
+
 TcArgs make_args(pcb_circuit* c, pcb_workspace* ws, uint32_t o0) {
+  if (!g_trace && getenv("PCB_TC_TRACE")) {
+    cudaMalloc((void**)&g_trace, 512 * sizeof(unsigned long long));
+    cudaMemset(g_trace, 0, 512 * sizeof(unsigned long long));
+  }
   return TcArgs{ws->mars, ws->flows, ws->blk_mx, c->aggr, c->theta, c->w_img, c->dense + o0, c->dense_img + o0,
-                c->status, ws->ld, ws->B, 0, getenv("PCB_TC_DEBUG") ? (uint32_t)atoi(getenv("PCB_TC_DEBUG")) : 0u};
+                c->status, ws->ld, ws->B, 0, g_trace, getenv("PCB_TC_DEBUG") ? (uint32_t)atoi(getenv("PCB_TC_DEBUG")) : 0u};
 }
 
 }  // namespace
@@ -650,4 +683,11 @@ int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer,
     PCB_TRY(launch<MODE_BWD_EDGE>(grid, args, st));
   }
   return PCB_OK;
+}
+
+// Diagnostic: copies the timing trace of the last traced kernel (PCB_TC_TRACE set) to the host.
+extern "C" int32_t pcb_debug_read_trace(unsigned long long* out) {
+  if (!g_trace) return PCB_ERR_STATE;
+  cudaDeviceSynchronize();
+  return cudaMemcpy(out, g_trace, 512 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? PCB_OK : PCB_ERR_CUDA;
 }
