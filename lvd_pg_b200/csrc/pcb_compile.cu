@@ -354,6 +354,9 @@ void free_circuit(pcb_circuit* c) {
                   c->up_all, c->up_sparse, c->down_all, c->down_sparse, c->in_off, c->in_ent, c->dense,
                   c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status, c->w_img, c->dense_img};
   for (void* p : ptrs) if (p) cudaFree(p);
+  if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+  if (c->ev_join) cudaEventDestroy(c->ev_join);
+  if (c->side) cudaStreamDestroy(c->side);
 }
 
 }  // namespace

@@ -39,7 +39,11 @@ constexpr uint32_t TM = 128;         // tile rows (TMEM lanes)
 constexpr uint32_t TN_MAX = 256;     // tile columns
 constexpr uint32_t KCH = 32;         // K elements per stage (one 128-byte swizzle row of tf32)
 constexpr uint32_t STAGES = 2;
-constexpr uint32_t NPROD = 512;      // producer threads (warps 0..15)
+constexpr uint32_t NPROD = 512;      // producer threads
+constexpr uint32_t PW = NPROD / 32;  // producer warps
+constexpr uint32_t RG = 16 / PW;     // row groups per thread in the row-contiguous map
+constexpr uint32_t QA = 128 / PW;    // A rows per thread in the K-contiguous map
+constexpr uint32_t QB = 256 / PW;    // B rows per thread in the K-contiguous map
 constexpr uint32_t MMA_WARP = NPROD / 32;
 constexpr uint32_t NTHREADS = NPROD + 32;
 constexpr uint32_t A_BYTES = TM * 128;        // one A sub-tile (hi or lo)
@@ -90,6 +94,7 @@ __device__ __forceinline__ unsigned long long gtime() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -251,7 +256,7 @@ struct ProdCtx {
   uint32_t tid, ld, m0, n0, k_begin, k_end, nq;
 };
 struct ChunkRegs {
-  float ra[8], rm[8], rb[16];
+  float ra[QA > 8 * RG ? QA : 8 * RG], rm[QA > 8 * RG ? QA : 8 * RG], rb[QB];
   float mx;
   bool vok;
 };
@@ -260,10 +265,11 @@ struct ChunkRegs {
 //  * "row-contiguous" operands (source contiguous along the tile's row index: A of FWD and
 //    BWD_CHILD): a warp covers 8 rows x 4 K positions per step, so its 32 shared-memory stores
 //    fall into 32 different banks of the swizzled tile and its global loads are four full
-//    32-byte sectors; thread: row = 8*warp + (lane & 7), kk = (lane >> 3) + 4*q, q = 0..7.
+//    32-byte sectors; thread: row = 8*(warp + PW*g) + (lane & 7), kk = (lane >> 3) + 4*q, q = 0..7,
+//    g = 0..RG-1.
 //  * "K-contiguous" operands (BWD_EDGE): a warp covers one whole 128-byte row per step;
-//    thread: kk = lane, row = warp + 16*q.
-__device__ __forceinline__ uint32_t rc_row(uint32_t tid) { return ((tid >> 5) << 3) + (tid & 7u); }
+//    thread: kk = lane, row = warp + PW*q.
+__device__ __forceinline__ uint32_t rc_row(uint32_t tid, uint32_t g = 0) { return (((tid >> 5) + PW * g) << 3) + (tid & 7u); }
 __device__ __forceinline__ uint32_t rc_kk(uint32_t tid, uint32_t q) { return ((tid & 31u) >> 3) + 4u * q; }
 
 // child value M[t][b] with unconditional loads: invalid positions read a safe address and are
@@ -278,77 +284,204 @@ __device__ __forceinline__ float child_val_nb(const float* __restrict__ mars, ui
   return valid ? v : -INFINITY;
 }
 
+// Per-thread quantities that do not change from chunk to chunk.  Rows and examples outside the
+// tile are clamped to a valid address once, here; what they load is masked at store time, so the
+// chunk loop itself is straight-line: affine addresses, unconditional loads.
+struct ProdInv {
+  const float* pc[RG];  // prime-child rows (or the parents' mars rows for G), per row group
+  const float* pd[RG];  // sub-child rows (or the parents' flows rows for G)
+  const float* pb;      // BWD_EDGE: prime-child rows of the B operand
+  const float* pbd;     // BWD_EDGE: sub-child rows of the B operand
+  float mx[RG];         // FWD / BWD_CHILD: the example's max (an infinity masks the whole row)
+  uint32_t rmask;       // BWD_EDGE: bit q set when A row q of this thread is inside the block
+  uint32_t bmask;       // BWD_EDGE: bit q set when B row q of this thread is inside the block
+  bool has_sub;
+  bool full;            // BWD_EDGE: all 128 A rows and all 256 B rows of the tile are inside the block
+};
+
+template <int MODE>
+__device__ __forceinline__ ProdInv make_inv(const ProdCtx& c) {
+  ProdInv v{};
+  const uint32_t tid = c.tid, ld = c.ld;
+  v.has_sub = c.k.d0 != PCB_NONE;
+  if (MODE == MODE_FWD || MODE == MODE_BWD_CHILD) {
+    const uint32_t kk0 = rc_kk(tid, 0);
+#pragma unroll
+    for (uint32_t g = 0; g < RG; ++g) {
+      const uint32_t row = rc_row(tid, g), b = c.m0 + row;
+      const bool bok = b < ld;
+      const float mx = c.mxs[row];
+      const uint32_t bb = bok ? b : 0u;
+      if (MODE == MODE_FWD) {
+        v.mx[g] = (bok && mx != -INFINITY) ? mx : INFINITY;   // exp(x - inf) = 0
+        v.pc[g] = c.mars + (size_t)(c.k.c0 + kk0) * ld + bb;
+        v.pd[g] = c.mars + (size_t)((v.has_sub ? c.k.d0 : c.k.c0) + kk0) * ld + bb;
+      } else {
+        v.mx[g] = (bok && mx != -INFINITY) ? mx : -INFINITY;  // exp(-inf - m) = 0
+        v.pc[g] = c.mars + (size_t)(c.k.p0 + kk0) * ld + bb;
+        v.pd[g] = c.flows + (size_t)(c.k.p0 + kk0) * ld + bb;
+      }
+    }
+  } else {
+    const uint32_t r0 = c.m0 + (tid >> 5), t0 = c.n0 + (tid >> 5), bl = tid & 31;
+    v.pc[0] = c.mars + (size_t)c.k.p0 * ld + bl;
+    v.pd[0] = c.flows + (size_t)c.k.p0 * ld + bl;
+    v.pb = c.mars + (size_t)c.k.c0 * ld + bl;
+    v.pbd = c.mars + (size_t)(v.has_sub ? c.k.d0 : c.k.c0) * ld + bl;
+#pragma unroll
+    for (uint32_t q = 0; q < QA; ++q) v.rmask |= (r0 + PW * q < c.k.R ? 1u : 0u) << q;
+#pragma unroll
+    for (uint32_t q = 0; q < QB; ++q) v.bmask |= ((q < c.nq && t0 + PW * q < c.k.K) ? 1u : 0u) << q;
+    v.full = c.m0 + TM <= c.k.R && c.n0 + TN_MAX <= c.k.K;
+  }
+  return v;
+}
+
 // raw global loads of chunk i (nothing depends on shared memory, so they can run chunks ahead)
 template <int MODE>
-__device__ __forceinline__ void load_chunk(const ProdCtx& c, uint32_t i, ChunkRegs& r) {
+__device__ __forceinline__ void load_chunk(const ProdCtx& c, const ProdInv& v, uint32_t i, ChunkRegs& r) {
   const uint32_t kc = c.k_begin + i * KCH, tid = c.tid, ld = c.ld;
-  if (MODE == MODE_FWD) {
-    const uint32_t row = rc_row(tid), b = c.m0 + row;
-    r.mx = c.mxs[row];
-    r.vok = b < ld && r.mx != -INFINITY;
+  if (MODE == MODE_FWD || MODE == MODE_BWD_CHILD) {
+    // K index of element q: kc + kk0 + 4q; rows past the end of K are clamped and masked
+    const uint32_t kk0 = rc_kk(tid, 0);
+    const uint32_t klast = (c.k_end - 1 - kk0) & ~3u;   // largest valid multiple of 4 for this thread
 #pragma unroll
-    for (uint32_t q = 0; q < 8; ++q) {  // A[m = example][kk = child]
-      uint32_t t = kc + rc_kk(tid, q);
-      r.ra[q] = child_val_nb(c.mars, ld, c.k, t, b, r.vok && t < c.k_end);
-    }
-  } else if (MODE == MODE_BWD_CHILD) {
-    const uint32_t row = rc_row(tid), b = c.m0 + row;
-    r.mx = c.mxs[row];
-    r.vok = b < ld && r.mx != -INFINITY;
+    for (uint32_t q = 0; q < 8; ++q) {
+      const uint32_t kq = kc + 4 * q;
+      const bool ok = kq + kk0 < c.k_end;
+      const size_t o = (size_t)(ok ? kq : klast) * ld;
 #pragma unroll
-    for (uint32_t q = 0; q < 8; ++q) {  // A[m = example][kk = parent] = G
-      uint32_t rr = kc + rc_kk(tid, q);
-      bool e = r.vok && rr < c.k_end;
-      size_t o = (size_t)(c.k.p0 + (e ? rr : 0)) * ld + (e ? b : 0);
-      float f = c.flows[o], m = c.mars[o];
-      r.ra[q] = e ? f : 0.0f;
-      r.rm[q] = e ? m : 0.0f;
+      for (uint32_t g = 0; g < RG; ++g) {
+        float x = v.pc[g][o], y = v.pd[g][o];
+        if (MODE == MODE_FWD) {
+          x += v.has_sub ? y : 0.0f;
+          r.ra[g * 8 + q] = ok ? x : -INFINITY;
+        } else {
+          r.rm[g * 8 + q] = x;                 // mars of the parent
+          r.ra[g * 8 + q] = ok ? y : 0.0f;     // flows of the parent
+        }
+      }
     }
   } else {
     const uint32_t b = kc + (tid & 31);
     const bool bok = b < c.k_end;
-    float mx = c.mxrow[bok ? b : 0];
-    r.mx = bok ? mx : -INFINITY;
-    r.vok = bok && r.mx != -INFINITY;
+    const uint32_t bo = bok ? kc : c.k_end - 1 - (tid & 31);   // clamped example offset (pointers carry the lane)
+    const float mx = c.mxrow[bok ? b : c.k_end - 1];
+    r.vok = bok && mx != -INFINITY;
+    r.mx = mx;
+    const uint32_t r0 = c.m0 + (tid >> 5), t0 = c.n0 + (tid >> 5);
+    // A chunk takes one 128-byte line from each of several hundred rows that lie a whole matrix
+    // row apart, which DRAM serves as that many page misses.  Every fourth chunk, four lanes of
+    // each warp ask L2 for the next 512 bytes of every row (the lines of chunks i+4 .. i+7) in one
+    // go, so DRAM sees four adjacent lines per open page and the later chunk loads hit L2.
+    if ((i & 3u) == 0 && (tid & 31) < 4) {
+      const uint32_t pb0 = kc + 128 + 32 * (tid & 31);   // first example of the line to prefetch
+      if (pb0 < c.k_end) {
+        const size_t po = (size_t)pb0 - (tid & 31);      // the row pointers already carry the lane
 #pragma unroll
-    for (uint32_t q = 0; q < 8; ++q) {  // A[m = parent][kk = example] = G: K contiguous
-      uint32_t rr = c.m0 + (tid >> 5) + 16 * q;
-      bool e = r.vok && rr < c.k.R;
-      size_t o = (size_t)(c.k.p0 + (e ? rr : 0)) * ld + (e ? b : 0);
-      float f = c.flows[o], m = c.mars[o];
-      r.ra[q] = e ? f : 0.0f;
-      r.rm[q] = e ? m : 0.0f;
+        for (uint32_t q = 0; q < QA; ++q) {
+          const size_t o = (size_t)((v.rmask >> q & 1u) ? r0 + PW * q : 0u) * ld + po;
+          prefetch_l2(v.pc[0] + o);
+          prefetch_l2(v.pd[0] + o);
+        }
+#pragma unroll
+        for (uint32_t q = 0; q < QB; ++q) {
+          const size_t o = (size_t)((v.bmask >> q & 1u) ? t0 + PW * q : 0u) * ld + po;
+          prefetch_l2(v.pb + o);
+          if (v.has_sub) prefetch_l2(v.pbd + o);
+        }
+      }
+    }
+    if (v.full) {
+      // every row of the tile lies inside the block: affine addresses, no masks
+      const size_t sa = (size_t)PW * ld;
+      const float* pm = v.pc[0] + (size_t)r0 * ld + bo;
+      const float* pf = v.pd[0] + (size_t)r0 * ld + bo;
+#pragma unroll
+      for (uint32_t q = 0; q < QA; ++q) {
+        r.rm[q] = pm[q * sa];
+        r.ra[q] = pf[q * sa];
+      }
+      const float* pc = v.pb + (size_t)t0 * ld + bo;
+      const float* pd = v.pbd + (size_t)t0 * ld + bo;
+      if (v.has_sub) {
+#pragma unroll
+        for (uint32_t q = 0; q < QB; ++q) r.rb[q] = pc[q * sa] + pd[q * sa];
+      } else {
+#pragma unroll
+        for (uint32_t q = 0; q < QB; ++q) r.rb[q] = pc[q * sa];
+      }
+      return;
     }
 #pragma unroll
-    for (uint32_t q = 0; q < 16; ++q) {  // B[n = child][kk = example] = exp(M - mx)
-      uint32_t t = c.n0 + (tid >> 5) + 16 * q;
-      r.rb[q] = (q < c.nq) ? child_val_nb(c.mars, ld, c.k, t, b, r.vok && t < c.k.K) : -INFINITY;
+    for (uint32_t q = 0; q < QA; ++q) {  // A[m = parent][kk = example] = G: K contiguous
+      const uint32_t rr = (v.rmask >> q & 1u) ? r0 + PW * q : 0u;
+      const size_t o = (size_t)rr * ld + bo;
+      r.rm[q] = v.pc[0][o];
+      r.ra[q] = v.pd[0][o];
+    }
+#pragma unroll
+    for (uint32_t q = 0; q < QB; ++q) {  // B[n = child][kk = example] = exp(M - mx)
+      const uint32_t tt = (v.bmask >> q & 1u) ? t0 + PW * q : 0u;
+      const size_t o = (size_t)tt * ld + bo;
+      float x = v.pb[o], y = v.pbd[o];
+      r.rb[q] = x + (v.has_sub ? y : 0.0f);
     }
   }
 }
 
 // exp / rescale / split and the swizzled shared-memory stores of a loaded chunk
 template <int MODE>
-__device__ __forceinline__ void store_chunk(const ProdCtx& c, const ChunkRegs& r, uint8_t* a_hi, uint8_t* a_lo,
-                                            uint8_t* b_hi, uint8_t* b_lo) {
+__device__ __forceinline__ void store_chunk(const ProdCtx& c, const ProdInv& v, const ChunkRegs& r, uint8_t* a_hi,
+                                            uint8_t* a_lo, uint8_t* b_hi, uint8_t* b_lo,
+                                            unsigned long long* tmark = nullptr) {
   const uint32_t tid = c.tid;
-  if (MODE == MODE_FWD) {
-    const uint32_t row = rc_row(tid);
+  if (MODE == MODE_FWD || MODE == MODE_BWD_CHILD) {
+    // element q sits in 16-byte chunk q of the row (kk >> 2 == q), swizzled with the row index
 #pragma unroll
-    for (uint32_t q = 0; q < 8; ++q)
-      put_split(a_hi, a_lo, sw_off(row, rc_kk(tid, q)), r.vok ? __expf(r.ra[q] - r.mx) : 0.0f);
-  } else if (MODE == MODE_BWD_CHILD) {
-    const uint32_t row = rc_row(tid);
+    for (uint32_t g = 0; g < RG; ++g) {
+      const uint32_t row = rc_row(tid, g);
+      const uint32_t base = row * 128u + (((tid & 31u) >> 3) << 2);
+      const uint32_t r7 = row & 7u;
 #pragma unroll
-    for (uint32_t q = 0; q < 8; ++q)
-      put_split(a_hi, a_lo, sw_off(row, rc_kk(tid, q)), r.vok ? r.ra[q] * __expf(r.mx - r.rm[q]) : 0.0f);
+      for (uint32_t q = 0; q < 8; ++q) {
+        const float val = MODE == MODE_FWD ? __expf(r.ra[g * 8 + q] - v.mx[g])
+                                           : r.ra[g * 8 + q] * __expf(v.mx[g] - r.rm[g * 8 + q]);
+        put_split(a_hi, a_lo, base + ((q ^ r7) << 4), val);
+      }
+    }
   } else {
+    const uint32_t kk = tid & 31, w = tid >> 5;
+    const uint32_t cpos = (kk >> 2), csub = (kk & 3u) << 2;
+    if (v.full) {
+      // PW is a multiple of 8, so the swizzle term (row & 7) == (w & 7) for all of a thread's rows:
+      // one base offset, then a fixed 128 * PW bytes per step; an example outside the batch is
+      // masked through the max (exp(-inf) = 0) instead of per element
+      static_assert(PW % 8 == 0, "row & 7 must not depend on q");
+      const uint32_t base = w * 128u + (((cpos ^ (w & 7u)) << 4) | csub);
+      const float mxa = r.vok ? r.mx : -INFINITY, mxb = r.vok ? r.mx : INFINITY;
 #pragma unroll
-    for (uint32_t q = 0; q < 8; ++q)
-      put_split(a_hi, a_lo, sw_off((tid >> 5) + 16 * q, tid & 31), r.vok ? r.ra[q] * __expf(r.mx - r.rm[q]) : 0.0f);
+      for (uint32_t q = 0; q < QA; ++q) put_split(a_hi, a_lo, base + q * (PW * 128u), r.ra[q] * __expf(mxa - r.rm[q]));
+      if (tmark) *tmark = gtime();
 #pragma unroll
-    for (uint32_t q = 0; q < 16; ++q)
-      if (q < c.nq) put_split(b_hi, b_lo, sw_off((tid >> 5) + 16 * q, tid & 31), r.vok ? __expf(r.rb[q] - r.mx) : 0.0f);
+      for (uint32_t q = 0; q < QB; ++q) put_split(b_hi, b_lo, base + q * (PW * 128u), __expf(r.rb[q] - mxb));
+      return;
+    }
+#pragma unroll
+    for (uint32_t q = 0; q < QA; ++q) {
+      const uint32_t row = w + PW * q;
+      const bool ok = r.vok && (v.rmask >> q & 1u);
+      put_split(a_hi, a_lo, row * 128u + (((cpos ^ (row & 7u)) << 4) | csub), ok ? r.ra[q] * __expf(r.mx - r.rm[q]) : 0.0f);
+    }
+    if (tmark) *tmark = gtime();
+#pragma unroll
+    for (uint32_t q = 0; q < QB; ++q) {
+      if (q < c.nq) {
+        const uint32_t row = w + PW * q;
+        const bool ok = r.vok && (v.bmask >> q & 1u);
+        put_split(b_hi, b_lo, row * 128u + (((cpos ^ (row & 7u)) << 4) | csub), ok ? __expf(r.rb[q] - r.mx) : 0.0f);
+      }
+    }
   }
 }
 
@@ -426,7 +559,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
     // =========================== producers ===================================================
     // The global loads of chunk i+1 are issued before chunk i is transformed and stored, so
     // their latency overlaps the exp / split / store work and the wait for the stage.
-    ProdCtx ctx{a.mars, a.flows, mxrow, mxs, k, tid, ld, m0, n0, k_begin, k_end, n_tile / 16};
+    ProdCtx ctx{a.mars, a.flows, mxrow, mxs, k, tid, ld, m0, n0, k_begin, k_end, n_tile / PW};
+    const ProdInv inv = make_inv<MODE>(ctx);
     ChunkRegs ra0, ra1;   // two register sets, used alternately: no copies on the loop edge
     auto process = [&](uint32_t i, const ChunkRegs& cr) -> bool {
       const uint32_t s = i & (STAGES - 1), ph = (i / STAGES) & 1u;
@@ -448,7 +582,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
         bulk_g2s(b_hi, src, bytes, &full[s]);
         bulk_g2s(b_lo, src + (size_t)img_rows * 32, bytes, &full[s]);
       }
-      if (!(a.dbg & 8u)) store_chunk<MODE>(ctx, cr, a_hi, a_lo, b_hi, b_lo);
+      if (!(a.dbg & 8u)) store_chunk<MODE>(ctx, inv, cr, a_hi, a_lo, b_hi, b_lo, tr ? a.trace + i * 8 + 7 : nullptr);
       if (tr) a.trace[i * 8 + 2] = gtime();
       fence_proxy_async();   // make the generic-proxy writes visible to the tensor core
       __syncwarp();
@@ -456,12 +590,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
       if (tr) a.trace[i * 8 + 3] = gtime();
       return true;
     };
-    load_chunk<MODE>(ctx, 0, ra0);
+    load_chunk<MODE>(ctx, inv, 0, ra0);
     for (uint32_t i = 0; i < nchunks && ok; i += 2) {
-      if (i + 1 < nchunks) load_chunk<MODE>(ctx, i + 1, ra1);
+      if (i + 1 < nchunks) load_chunk<MODE>(ctx, inv, i + 1, ra1);
       ok = process(i, ra0);
       if (!ok || i + 1 >= nchunks) break;
-      if (i + 2 < nchunks) load_chunk<MODE>(ctx, i + 2, ra0);
+      if (i + 2 < nchunks) load_chunk<MODE>(ctx, inv, i + 2, ra0);
       ok = process(i + 1, ra1);
     }
 
@@ -472,9 +606,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
     if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[501] = gtime();
     if (ok && !(a.dbg & 4u)) {
       tc_fence_after();
-      const uint32_t q4 = warp & 3, grp = warp >> 2;   // lane quarter, 64-column group
+      constexpr uint32_t CG = TN_MAX / (PW / 4);       // columns per epilogue warp group
+      const uint32_t q4 = warp & 3, grp = warp >> 2;   // lane quarter, column group
       const uint32_t row = q4 * 32 + lane;
-      const uint32_t c_begin = grp * 64, c_end = min(n_tile, c_begin + 64);
+      const uint32_t c_begin = grp * CG, c_end = min(n_tile, c_begin + CG);
       float acc[32];
       for (uint32_t c0 = c_begin; c0 < c_end; c0 += 32) {
         tmem_ld32(tmem_base + ((q4 * 32u) << 16) + c0, acc);
@@ -631,6 +766,11 @@ int32_t pcb_dense_tc_prepare(pcb_circuit* c, uint64_t* bytes) {
     PCB_CUDA(cudaMemcpy(c->dense_img, imgs.data(), imgs.size() * sizeof(PcbDenseImg), cudaMemcpyHostToDevice));
   *bytes += off * sizeof(float) + imgs.size() * sizeof(PcbDenseImg);
   c->w_img_valid = false;
+  if (!(getenv("PCB_NO_SIDE_STREAM") && atoi(getenv("PCB_NO_SIDE_STREAM")))) {
+    PCB_CUDA(cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking));
+    PCB_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+    PCB_CUDA(cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
+  }
   return PCB_OK;
 }
 
@@ -666,11 +806,6 @@ int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer,
   if (o1 == o0) return PCB_OK;
   TcArgs args = make_args(c, ws, o0);
   {
-    dim3 grid((pcb_round_up(ws->B, 32) + TM - 1) / TM, (c->max_dense_K + TN_MAX - 1) / TN_MAX, o1 - o0);
-    PcbProfScope ps(c, st, PCB_K_DENSE_BWD_CHILD);
-    PCB_TRY(launch<MODE_BWD_CHILD>(grid, args, st));
-  }
-  {
     uint32_t tiles = ((c->max_dense_R + TM - 1) / TM) * ((c->max_dense_K + TN_MAX - 1) / TN_MAX);
     // slice the examples so that small layers still fill the GPU
     uint32_t want = std::max(1u, 148u / std::max(1u, tiles * (o1 - o0)));
@@ -679,9 +814,33 @@ int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer,
     slices = (ws->B + b_per - 1) / b_per;
     args.b_per_cta = b_per;
     dim3 grid(slices, tiles, o1 - o0);
-    PcbProfScope ps(c, st, PCB_K_DENSE_BWD_EDGE);
-    PCB_TRY(launch<MODE_BWD_EDGE>(grid, args, st));
+    // The parents' flows are final when this function is entered and nothing later in the
+    // backward pass reads the statistics, so this kernel goes to the side stream and overlaps the
+    // child-flow kernels of this and the following layers (most layers fill only a few SMs).
+    cudaStream_t es = st;
+    if (c->side) {
+      PCB_CUDA(cudaEventRecord(c->ev_fork, st));
+      PCB_CUDA(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
+      es = c->side;
+      c->side_busy = true;
+    }
+    PcbProfScope ps(c, es, PCB_K_DENSE_BWD_EDGE);
+    PCB_TRY(launch<MODE_BWD_EDGE>(grid, args, es));
   }
+  {
+    dim3 grid((pcb_round_up(ws->B, 32) + TM - 1) / TM, (c->max_dense_K + TN_MAX - 1) / TN_MAX, o1 - o0);
+    PcbProfScope ps(c, st, PCB_K_DENSE_BWD_CHILD);
+    PCB_TRY(launch<MODE_BWD_CHILD>(grid, args, st));
+  }
+  return PCB_OK;
+}
+
+// Makes `st` wait for everything queued on the side stream.
+int32_t pcb_side_join(pcb_circuit* c, cudaStream_t st) {
+  if (!c->side || !c->side_busy) return PCB_OK;
+  PCB_CUDA(cudaEventRecord(c->ev_join, c->side));
+  PCB_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));
+  c->side_busy = false;
   return PCB_OK;
 }
 

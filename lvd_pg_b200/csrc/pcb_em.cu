@@ -370,6 +370,7 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
                                                             c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr); }
     if (lay >= 1) PCB_TRY(pcb_dense_backward(c, ws, (uint32_t)lay, st));
   }
+  PCB_TRY(pcb_side_join(c, st));
   if (c->n_inputs) {
     PcbProfScope ps(c, st, PCB_K_LEAF_FLOW);
     if (c->max_cats <= 1024) {

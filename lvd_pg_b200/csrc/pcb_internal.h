@@ -137,6 +137,11 @@ struct pcb_circuit {
   PcbDenseImg* dense_img = nullptr;
   uint64_t w_img_len = 0;
   bool w_img_valid = false;
+  // edge statistics feed nothing downstream in the backward pass, so their kernels run on a
+  // side stream, forked from and joined to the caller's stream with two reusable events
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  bool side_busy = false;
   int* status = nullptr;
 
   // ---- multi-GPU ----
@@ -213,3 +218,4 @@ int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer,
 int32_t pcb_check_status(pcb_circuit* c);
 int32_t pcb_dense_tc_prepare(pcb_circuit* c, uint64_t* bytes);
 int32_t pcb_dense_tc_refresh(pcb_circuit* c, cudaStream_t st);
+int32_t pcb_side_join(pcb_circuit* c, cudaStream_t st);
