@@ -119,6 +119,21 @@ def algorithmic_work(fc, info, B):
     return work
 
 
+# DRAM bytes per dense block (256 parents x 256 children) at 2048 examples, dram__bytes_read.sum +
+# dram__bytes_write.sum of one ncu capture of the largest launches of the 384-variable cut of the
+# workload (profiles/dense_tc_kernels_cfg5s.md); traffic grows in proportion to blocks x examples.
+NCU_DRAM_BYTES_PER_BLOCK = {"dense_bwd_edge": 594.2e6 / 55, "dense_bwd_child": 719.0e6 / 55, "dense_fwd": 345.0e6 / 55}
+
+
+def measured_traffic(kernel_class, info, B, launches_per_step):
+    """Per-launch DRAM traffic of a dense class scaled from the ncu capture, or None."""
+    per_block = NCU_DRAM_BYTES_PER_BLOCK.get(kernel_class)
+    if per_block is None or int(info.num_dense_blocks) == 0 or not launches_per_step:
+        return None
+    k2 = float(info.num_dense_edges) / float(info.num_dense_blocks)   # edges per block
+    return per_block * (k2 / 65536.0) * (B / 2048.0) * int(info.num_dense_blocks) / launches_per_step
+
+
 def run_cpu_oracle(fc, images_cpu, target_s, rows_hint=None):
     """Time the CPU oracle's EM step on a bounded sample; returns (samples/s, rows, threads, seconds)."""
     from oracle import oracle as orc
@@ -257,6 +272,11 @@ def main():
         achieved = w.get("bytes", 0.0) / (dom_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": None}
+    lps = classes[dom][1] / prof_steps
+    roof["traffic"] = measured_traffic(dom, m.info, B, lps)
+    if roof["traffic"] is not None:
+        roof["traffic_unit"] = "bytes per launch (ncu capture of the reduced workload, scaled by blocks x examples)"
+        roof["algorithmic_bytes_per_launch"] = w.get("bytes", 0.0) / lps
     roof.update({"kernel": dom, "kernel_ms_per_step": dom_ms, "launches_per_step": classes[dom][1] / prof_steps,
                  "peak_source": peaks["which"],
                  "class_ms_per_step": {k: round(v[0] / prof_steps, 4) for k, v in classes.items()},

@@ -771,6 +771,7 @@ int32_t pcb_dense_tc_prepare(pcb_circuit* c, uint64_t* bytes) {
     PCB_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
     PCB_CUDA(cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
   }
+  if (const char* e = getenv("PCB_EDGE_BATCH_TILES")) c->edge_batch_tiles = (uint32_t)std::max(1, atoi(e));
   return PCB_OK;
 }
 
@@ -801,32 +802,54 @@ int32_t pcb_dense_tc_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, 
   return launch<MODE_FWD>(grid, args, st);
 }
 
+// Launches the edge-statistics kernel over the pending block range [edge_lo, edge_hi).
+// The parents' flows of every pending block are final on `st` and nothing later in the backward
+// pass reads the statistics, so the kernel goes to the side stream (when there is one) and overlaps
+// the child-flow kernels that follow on `st`.
+int32_t pcb_dense_tc_flush_edges(pcb_circuit* c, pcb_workspace* ws, cudaStream_t st) {
+  if (c->edge_hi <= c->edge_lo) return PCB_OK;
+  const uint32_t o0 = c->edge_lo, n = c->edge_hi - c->edge_lo;
+  c->edge_lo = c->edge_hi = 0;
+  TcArgs args = make_args(c, ws, o0);
+  uint32_t tiles = ((c->max_dense_R + TM - 1) / TM) * ((c->max_dense_K + TN_MAX - 1) / TN_MAX);
+  // slice the examples so that a short range still fills the GPU
+  uint32_t want = std::max(1u, 148u / std::max(1u, tiles * n));
+  uint32_t slices = std::min(want, (ws->B + 255) / 256);
+  uint32_t b_per = pcb_round_up((ws->B + slices - 1) / slices, KCH);
+  slices = (ws->B + b_per - 1) / b_per;
+  args.b_per_cta = b_per;
+  cudaStream_t es = st;
+  if (c->side) {
+    PCB_CUDA(cudaEventRecord(c->ev_fork, st));
+    PCB_CUDA(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
+    es = c->side;
+    c->side_busy = true;
+  }
+  for (uint32_t z0 = 0; z0 < n; z0 += 65535) {
+    TcArgs a2 = args;
+    a2.blocks = args.blocks + z0;
+    a2.imgs = args.imgs + z0;
+    dim3 grid(slices, tiles, std::min<uint32_t>(65535, n - z0));
+    PcbProfScope ps(c, es, PCB_K_DENSE_BWD_EDGE);
+    PCB_TRY(launch<MODE_BWD_EDGE>(grid, a2, es));
+  }
+  return PCB_OK;
+}
+
 int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st) {
   uint32_t o0 = c->h_dense_off[layer], o1 = c->h_dense_off[layer + 1];
   if (o1 == o0) return PCB_OK;
-  TcArgs args = make_args(c, ws, o0);
+  // Edge statistics: layers are visited top down and their blocks are stored layer after layer, so
+  // consecutive layers extend one block range downwards.  The range is launched once it holds
+  // enough tiles for a few waves of CTAs; most layers alone would fill only a few SMs.
+  if (c->edge_hi > c->edge_lo && c->edge_lo != o1) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
+  if (c->edge_hi <= c->edge_lo) c->edge_hi = o1;
+  c->edge_lo = o0;
   {
     uint32_t tiles = ((c->max_dense_R + TM - 1) / TM) * ((c->max_dense_K + TN_MAX - 1) / TN_MAX);
-    // slice the examples so that small layers still fill the GPU
-    uint32_t want = std::max(1u, 148u / std::max(1u, tiles * (o1 - o0)));
-    uint32_t slices = std::min(want, (ws->B + 255) / 256);
-    uint32_t b_per = pcb_round_up((ws->B + slices - 1) / slices, KCH);
-    slices = (ws->B + b_per - 1) / b_per;
-    args.b_per_cta = b_per;
-    dim3 grid(slices, tiles, o1 - o0);
-    // The parents' flows are final when this function is entered and nothing later in the
-    // backward pass reads the statistics, so this kernel goes to the side stream and overlaps the
-    // child-flow kernels of this and the following layers (most layers fill only a few SMs).
-    cudaStream_t es = st;
-    if (c->side) {
-      PCB_CUDA(cudaEventRecord(c->ev_fork, st));
-      PCB_CUDA(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
-      es = c->side;
-      c->side_busy = true;
-    }
-    PcbProfScope ps(c, es, PCB_K_DENSE_BWD_EDGE);
-    PCB_TRY(launch<MODE_BWD_EDGE>(grid, args, es));
+    if (!c->side || (c->edge_hi - c->edge_lo) * tiles >= c->edge_batch_tiles) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
   }
+  TcArgs args = make_args(c, ws, o0);
   {
     dim3 grid((pcb_round_up(ws->B, 32) + TM - 1) / TM, (c->max_dense_K + TN_MAX - 1) / TN_MAX, o1 - o0);
     PcbProfScope ps(c, st, PCB_K_DENSE_BWD_CHILD);

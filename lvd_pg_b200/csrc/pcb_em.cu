@@ -363,6 +363,7 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
   PCB_CUDA(cudaSetDevice(c->device));
   cudaStream_t st = (cudaStream_t)s;
   const uint32_t B = ws->B;
+  c->edge_lo = c->edge_hi = 0;
   for (int64_t lay = c->L; lay >= 0; --lay) {
     uint32_t o0 = c->h_down_sparse_off[lay], o1 = c->h_down_sparse_off[lay + 1];
     if (o1 > o0)
@@ -370,7 +371,7 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
                                                             c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr); }
     if (lay >= 1) PCB_TRY(pcb_dense_backward(c, ws, (uint32_t)lay, st));
   }
-  PCB_TRY(pcb_side_join(c, st));
+  if (c->use_tc) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
   if (c->n_inputs) {
     PcbProfScope ps(c, st, PCB_K_LEAF_FLOW);
     if (c->max_cats <= 1024) {
@@ -385,6 +386,7 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
                                                               ws->num_rows, ws->row_ids, ws->row_start, weights_dev);
     }
   }
+  PCB_TRY(pcb_side_join(c, st));  // the leaf statistics above overlap the last edge-statistics kernels
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
 }

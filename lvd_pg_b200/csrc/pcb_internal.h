@@ -142,6 +142,9 @@ struct pcb_circuit {
   cudaStream_t side = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   bool side_busy = false;
+  // dense blocks [edge_lo, edge_hi) whose edge statistics are still to be launched, and the number
+  // of tiles at which the range is launched
+  uint32_t edge_lo = 0, edge_hi = 0, edge_batch_tiles = 592;
   int* status = nullptr;
 
   // ---- multi-GPU ----
@@ -219,3 +222,4 @@ int32_t pcb_check_status(pcb_circuit* c);
 int32_t pcb_dense_tc_prepare(pcb_circuit* c, uint64_t* bytes);
 int32_t pcb_dense_tc_refresh(pcb_circuit* c, cudaStream_t st);
 int32_t pcb_side_join(pcb_circuit* c, cudaStream_t st);
+int32_t pcb_dense_tc_flush_edges(pcb_circuit* c, pcb_workspace* ws, cudaStream_t st);
