@@ -414,6 +414,10 @@ extern "C" int32_t pcb_workspace_create(pcb_circuit* c, uint32_t max_batch, int3
     delete ws;
     return pcb_fail(PCB_ERR_CUDA, std::string("workspace allocation: ") + cudaGetErrorString(e3));
   }
+  {
+    int32_t st = pcb_dense_edge_prepare_ws(ws);
+    if (st != PCB_OK) { pcb_workspace_destroy(ws); return st; }
+  }
   if (sets) {
     int32_t st = pcb_ws_ensure_sets(ws, max_batch, true);
     if (st != PCB_OK) { pcb_workspace_destroy(ws); return st; }

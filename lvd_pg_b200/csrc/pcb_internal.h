@@ -158,6 +158,9 @@ struct pcb_workspace {
   float* mars = nullptr;    // [N][ld]
   float* flows = nullptr;   // [N][ld]
   float* blk_mx = nullptr;  // [n_dense][ld] per-example max of a dense block's children
+  // tensor maps over mars / flows for the copy-fed edge-statistics kernel (128-byte opaque objects)
+  alignas(64) unsigned char tm[3][128];
+  bool have_tm = false;
   // state of the last forward
   uint32_t B = 0;
   const uint8_t* data = nullptr;
@@ -222,4 +225,7 @@ int32_t pcb_check_status(pcb_circuit* c);
 int32_t pcb_dense_tc_prepare(pcb_circuit* c, uint64_t* bytes);
 int32_t pcb_dense_tc_refresh(pcb_circuit* c, cudaStream_t st);
 int32_t pcb_side_join(pcb_circuit* c, cudaStream_t st);
+int32_t pcb_dense_edge_prepare_ws(pcb_workspace* ws);
+int32_t pcb_dense_edge_launch(pcb_circuit* c, pcb_workspace* ws, uint32_t o0, uint32_t n, uint32_t slices,
+                              uint32_t b_per, cudaStream_t st);
 int32_t pcb_dense_tc_flush_edges(pcb_circuit* c, pcb_workspace* ws, cudaStream_t st);
