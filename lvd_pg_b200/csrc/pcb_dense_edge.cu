@@ -51,12 +51,19 @@ struct EdgeArgs {
   const PcbDenseBlock* blocks;
   int* status;
   uint32_t ld, B, b_per_cta;
+  unsigned long long* trace;   // timing trace of CTA (0,0,0), or null
+  uint32_t dbg;                // timing experiments only: 1 skip MMAs, 2 copies re-read the first chunk, 4 skip conversion
 };
 
 __device__ __forceinline__ float4 split_hi(float4 v) {
   return make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
 }
 __device__ __forceinline__ float4 sub4(float4 a, float4 b) { return make_float4(a.x - b.x, a.y - b.y, a.z - b.z, a.w - b.w); }
+
+#define EDGE_TRACE(slot)                                                            \
+  do {                                                                              \
+    if (a.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[slot] = gtime(); \
+  } while (0)
 
 // grid: (example slices, row tiles x column tiles, blocks)
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -105,6 +112,7 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
+  if (tid == 0) EDGE_TRACE(503);
 
   if (warp < CW) {
     // =========================== converters ==================================================
@@ -120,6 +128,20 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
       const uint32_t s = i & (STAGES - 1), ph = (i / STAGES) & 1u;
       const float4 mx = mxn;
       if (i + 1 < nchunks) mxn = load_mx(i + 1);
+      if (i + 4 == nchunks || (nchunks < 4 && i == 0)) {
+        // the epilogue reads theta and reduces into aggr over this tile's 128 rows x 1 KB: ask L2
+        // for those lines a few chunks ahead (earlier, the operand stream would evict them again)
+#pragma unroll
+        for (uint32_t j = 0; j < 2; ++j) {
+          const uint32_t lid = tid + CW * 32u * j;          // 1024 lines per array
+          const uint32_t r = m0 + (lid >> 3), t = n0 + ((lid & 7u) << 5);
+          if (r < k.R && t < k.K) {
+            const size_t p = k.pid0 + (size_t)r * k.K + t;
+            prefetch_l2(a.theta + p);
+            prefetch_l2(a.aggr + p);
+          }
+        }
+      }
       const uint32_t b0 = k_begin + i * KCH + 4u * kk4;
       const bool v0 = b0 < k_end && mx.x != -INFINITY, v1 = b0 + 1 < k_end && mx.y != -INFINITY,
                  v2 = b0 + 2 < k_end && mx.z != -INFINITY, v3 = b0 + 3 < k_end && mx.w != -INFINITY;
@@ -128,7 +150,9 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
       bool got = lane != 0 || mbar_wait(&raw_full[s], ph, a.status);
       got = __all_sync(0xffffffffu, got);
       if (!got) { ok = false; break; }
+      if (tid == 0 && i < 60) EDGE_TRACE(i * 8 + 2);
       uint8_t* st = smem + s * STAGE_BYTES + off0;
+      if (!(a.dbg & 4u)) {
 #pragma unroll
       for (uint32_t q = 0; q < TM / 64; ++q) {   // G = flows * exp(mx - mars), exponent clamped: inf * 0 stays out
         uint8_t* p = st + q * 8192u;
@@ -164,14 +188,18 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
           *reinterpret_cast<float4*>(p + B_BYTES) = sub4(e, h);
         }
       }
+      }
       fence_proxy_async();   // generic-proxy writes -> visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(&conv_full[s]);
+      if (tid == 0 && i < 60) EDGE_TRACE(i * 8 + 3);
     }
+    if (tid == 0) EDGE_TRACE(500);
 
     // =========================== epilogue ====================================================
     if (ok && lane == 0) ok = mbar_wait(accfull, 0, a.status);
     ok = __all_sync(0xffffffffu, ok);
+    if (tid == 0) EDGE_TRACE(501);
     if (ok) {
       tc_fence_after();
       constexpr uint32_t CG = TN / (CW / 4);           // columns per epilogue warp group
@@ -189,7 +217,7 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
         __syncwarp();
         const uint32_t t = n0 + c0 + lane;
         if (t < k.K) {
-#pragma unroll 8
+#pragma unroll 16
           for (uint32_t rr = 0; rr < 32; ++rr) {
             const uint32_t r = m0 + q4 * 32 + rr;
             if (r < k.R) {
@@ -209,10 +237,12 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
         const uint32_t s = i & (STAGES - 1), ph = (i / STAGES) & 1u;
         ok = mbar_wait(&conv_full[s], ph, a.status);
         if (!ok) break;
+        if (i < 60) EDGE_TRACE(i * 8 + 4);
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t d_ahi = make_desc(sa), d_alo = make_desc(sa + A_BYTES);
         const uint64_t d_bhi = make_desc(sa + 2 * A_BYTES), d_blo = make_desc(sa + 2 * A_BYTES + B_BYTES);
+        if (!(a.dbg & 1u))
 #pragma unroll
         for (uint32_t ks = 0; ks < KCH / 8; ++ks) {
           const uint64_t adv = (uint64_t)((ks * 32u) >> 4);  // 8 tf32 = 32 bytes along K
@@ -221,6 +251,7 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
           umma_tf32(tmem_base, d_ahi + adv, d_blo + adv, idesc, 1u);
         }
         umma_commit(&empty[s]);
+        if (i < 60) EDGE_TRACE(i * 8 + 5);
       }
       if (ok) umma_commit(accfull);
     }
@@ -231,9 +262,11 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
       uint32_t issued = 0;
       for (uint32_t i = 0; i < nchunks; ++i) {
         const uint32_t s = i & (STAGES - 1), ph = (i / STAGES) & 1u;
+        if (i < 60) EDGE_TRACE(i * 8 + 0);
         if (!mbar_wait(&empty[s], ph ^ 1u, a.status)) break;
+        if (i < 60) EDGE_TRACE(i * 8 + 1);
         uint8_t* st = smem + s * STAGE_BYTES;
-        const int32_t x = (int32_t)(k_begin + i * KCH);
+        const int32_t x = (int32_t)(k_begin + ((a.dbg & 2u) ? 0u : i * KCH));
         mbar_arrive_expect_tx(&raw_full[s], has_sub ? RAW_BYTES + B_BYTES : RAW_BYTES);
         tma_load_2d(st, &tm_mars_a, x, (int32_t)(k.p0 + m0), &raw_full[s]);
         tma_load_2d(st + A_BYTES, &tm_flows_a, x, (int32_t)(k.p0 + m0), &raw_full[s]);
@@ -250,6 +283,7 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
     __syncwarp();
   }
 
+  if (tid == 0) EDGE_TRACE(502);
   // ---- common exit: release tensor memory -------------------------------------------------------
   tc_fence_before();
   __syncthreads();
@@ -258,6 +292,8 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
+
+unsigned long long* g_edge_trace = nullptr;   // diagnostic buffer, allocated when PCB_TC_TRACE is set
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -320,16 +356,28 @@ int32_t pcb_dense_edge_launch(pcb_circuit* c, pcb_workspace* ws, uint32_t o0, ui
     PCB_CUDA(cudaFuncSetAttribute(dense_edge_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     configured = true;
   }
+  if (!g_edge_trace && getenv("PCB_TC_TRACE")) {
+    cudaMalloc((void**)&g_edge_trace, 512 * sizeof(unsigned long long));
+    cudaMemset(g_edge_trace, 0, 512 * sizeof(unsigned long long));
+  }
   alignas(64) CUtensorMap ma, fa, mb;
   memcpy(&ma, ws->tm[0], sizeof(ma));
   memcpy(&fa, ws->tm[1], sizeof(fa));
   memcpy(&mb, ws->tm[2], sizeof(mb));
   const uint32_t tiles = ((c->max_dense_R + TM - 1) / TM) * ((c->max_dense_K + TN - 1) / TN);
   for (uint32_t z0 = 0; z0 < n; z0 += 65535) {
-    EdgeArgs args{ws->blk_mx, c->aggr, c->theta, c->dense + o0 + z0, c->status, ws->ld, ws->B, b_per};
+    EdgeArgs args{ws->blk_mx, c->aggr, c->theta, c->dense + o0 + z0, c->status, ws->ld, ws->B, b_per, g_edge_trace,
+                  getenv("PCB_TC_DEBUG") ? (uint32_t)atoi(getenv("PCB_TC_DEBUG")) : 0u};
     dim3 grid(slices, tiles, std::min<uint32_t>(65535, n - z0));
     PcbProfScope ps(c, st, PCB_K_DENSE_BWD_EDGE);
     dense_edge_tma_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(ma, fa, mb, args);
   }
   return PCB_OK;
+}
+
+// Diagnostic: copies the timing trace of the last traced edge-statistics kernel (PCB_TC_TRACE set) to the host.
+extern "C" int32_t pcb_debug_read_edge_trace(unsigned long long* out) {
+  if (!g_edge_trace) return PCB_ERR_STATE;
+  cudaDeviceSynchronize();
+  return cudaMemcpy(out, g_edge_trace, 512 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? PCB_OK : PCB_ERR_CUDA;
 }

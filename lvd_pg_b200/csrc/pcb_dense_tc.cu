@@ -66,6 +66,7 @@ struct TcArgs {
   const PcbDenseImg* imgs;
   int* status;
   uint32_t ld, B, b_per_cta;
+  uint32_t nsplit;   // FWD / BWD_CHILD: CTAs sharing one 256-column tile (1, 2 or 4), each taking 256 / nsplit columns
   unsigned long long* trace;   // timing trace of CTA (0,0,0), or null
   uint32_t dbg;   // timing experiments only: 1 skip MMAs, 2 skip global loads, 4 skip epilogue, 8 skip smem stores
 };
@@ -411,14 +412,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
 
   // ---- tile coordinates ---------------------------------------------------------------------
   uint32_t m0, n0, n_count, k_begin, k_end, jn;  // rows [m0, m0+128), columns [n0, n0+n_count), K range
-  if (MODE == MODE_FWD) {
-    m0 = blockIdx.x * TM; jn = blockIdx.y; n0 = jn * TN_MAX;
-    if (n0 >= k.R) return;
-    n_count = min(TN_MAX, k.R - n0); k_begin = 0; k_end = k.K;
-  } else if (MODE == MODE_BWD_CHILD) {
-    m0 = blockIdx.x * TM; jn = blockIdx.y; n0 = jn * TN_MAX;
-    if (n0 >= k.K) return;
-    n_count = min(TN_MAX, k.K - n0); k_begin = 0; k_end = k.R;
+  uint32_t part0 = 0;                            // first column of this CTA inside its 256-column tile
+  if (MODE == MODE_FWD || MODE == MODE_BWD_CHILD) {
+    const uint32_t ncols = MODE == MODE_FWD ? k.R : k.K, sw = TN_MAX / a.nsplit;
+    m0 = blockIdx.x * TM; jn = blockIdx.y / a.nsplit; part0 = (blockIdx.y % a.nsplit) * sw;
+    n0 = jn * TN_MAX + part0;
+    if (n0 >= ncols) return;
+    n_count = min(sw, ncols - n0); k_begin = 0; k_end = MODE == MODE_FWD ? k.K : k.R;
   } else {
     const uint32_t tiles_n = (k.K + TN_MAX - 1) / TN_MAX;
     m0 = (blockIdx.y / tiles_n) * TM; jn = blockIdx.y % tiles_n; n0 = jn * TN_MAX;
@@ -437,8 +437,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
     const PcbDenseImg im = a.imgs[blockIdx.z];
     img_rows = MODE == MODE_FWD ? im.rows_f : im.rows_t;
     const uint32_t nch = MODE == MODE_FWD ? im.nch_f : im.nch_t;
-    img_tile = a.w_img + (MODE == MODE_FWD ? im.off_f : im.off_t) + (size_t)jn * nch * 2 * img_rows * 32;
-    n_tile = img_rows;   // rows beyond n_count are zero in the image
+    img_tile = a.w_img + (MODE == MODE_FWD ? im.off_f : im.off_t) + (size_t)jn * nch * 2 * img_rows * 32 + part0 * 32;
+    n_tile = min(TN_MAX / a.nsplit, img_rows - part0);   // rows beyond n_count are zero in the image
   }
 
   // ---- set-up: barriers, tensor memory, per-example max --------------------------------------
@@ -482,7 +482,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
       uint8_t* b_lo = b_hi + B_BYTES;
       if (tr) a.trace[i * 8 + 1] = gtime();
       if (MODE != MODE_BWD_EDGE && tid == 0) {  // weight tile: hi and lo parts straight from the image
-        const uint32_t bytes = img_rows * 128u;
+        const uint32_t bytes = n_tile * 128u;
         const float* src = img_tile + (size_t)i * 2 * img_rows * 32;
         mbar_expect_tx(&full[s], 2 * bytes);
         bulk_g2s(b_hi, src, bytes, &full[s]);
@@ -496,12 +496,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
       if (tr) a.trace[i * 8 + 3] = gtime();
       return true;
     };
+    // BWD_CHILD: the epilogue reads the children's value rows (prime and sub) for this tile's 128
+    // examples: 2 x 256 rows x 512 bytes.  Each producer thread asks L2 for four of those lines
+    // while the K loop runs, so the epilogue's loads do not start from DRAM latency.
+    auto prefetch_children = [&](uint32_t j) {
+      if (MODE != MODE_BWD_CHILD) return;
+      const uint32_t lid = tid + NPROD * j;            // 2048 lines: (prime | sub) x 256 rows x 4 segments
+      const uint32_t row = (lid >> 2) & 255u, seg = lid & 3u;
+      const bool sub = lid >= 1024u;
+      if (row < n_count && m0 + seg * 32u < ld && (!sub || k.d0 != PCB_NONE))
+        prefetch_l2(a.mars + (size_t)((sub ? k.d0 : k.c0) + n0 + row) * ld + m0 + seg * 32u);
+    };
     load_chunk<MODE>(ctx, inv, 0, ra0);
     for (uint32_t i = 0; i < nchunks && ok; i += 2) {
       if (i + 1 < nchunks) load_chunk<MODE>(ctx, inv, i + 1, ra1);
+      const bool pf = i + 4 == nchunks || i + 5 == nchunks || (nchunks < 4 && i == 0);
+      if (pf) { prefetch_children(0); prefetch_children(1); }
       ok = process(i, ra0);
       if (!ok || i + 1 >= nchunks) break;
       if (i + 2 < nchunks) load_chunk<MODE>(ctx, inv, i + 2, ra0);
+      if (pf) { prefetch_children(2); prefetch_children(3); }
       ok = process(i + 1, ra1);
     }
 
@@ -512,7 +526,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
     if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[501] = gtime();
     if (ok && !(a.dbg & 4u)) {
       tc_fence_after();
-      constexpr uint32_t CG = TN_MAX / (PW / 4);       // columns per epilogue warp group
+      const uint32_t CG = max(32u, ((n_tile + 127u) >> 7) << 5);   // columns per epilogue warp group (4 groups)
       const uint32_t q4 = warp & 3, grp = warp >> 2;   // lane quarter, column group
       const uint32_t row = q4 * 32 + lane;
       const uint32_t c_begin = grp * CG, c_end = min(n_tile, c_begin + CG);
@@ -638,7 +652,19 @@ TcArgs make_args(pcb_circuit* c, pcb_workspace* ws, uint32_t o0) {
     cudaMemset(g_trace, 0, 512 * sizeof(unsigned long long));
   }
   return TcArgs{ws->mars, ws->flows, ws->blk_mx, c->aggr, c->theta, c->w_img, c->dense + o0, c->dense_img + o0,
-                c->status, ws->ld, ws->B, 0, g_trace, getenv("PCB_TC_DEBUG") ? (uint32_t)atoi(getenv("PCB_TC_DEBUG")) : 0u};
+                c->status, ws->ld, ws->B, 0, 1, g_trace, getenv("PCB_TC_DEBUG") ? (uint32_t)atoi(getenv("PCB_TC_DEBUG")) : 0u};
+}
+
+// A layer that would not fill the GPU with 256-column tiles is cut into narrower tiles: the CTAs
+// of one tile then repeat the production of the data-dependent operand, but each has half (a
+// quarter) of the weight tile to fetch, of the MMAs to wait for and of the epilogue, and a layer's
+// latency is what a chain of small layers pays.
+uint32_t pick_nsplit(uint32_t ctas, uint32_t max_cols) {
+  static const int forced = getenv("PCB_TC_NSPLIT") ? atoi(getenv("PCB_TC_NSPLIT")) : 0;
+  if (forced == 1 || forced == 2 || forced == 4) return (uint32_t)forced;
+  uint32_t n = 1;
+  while (n < 4 && ctas * n * 2 <= 160 && max_cols > TN_MAX / (2 * n)) n *= 2;
+  return n;
 }
 
 }  // namespace
@@ -703,7 +729,9 @@ int32_t pcb_dense_tc_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, 
     dense_max_kernel<<<dim3(bt, o1 - o0), 1024, 0, st>>>(ws->mars, ws->blk_mx, ws->ld, c->dense + o0);
   }
   TcArgs args = make_args(c, ws, o0);
-  dim3 grid(bt, (c->max_dense_R + TN_MAX - 1) / TN_MAX, o1 - o0);
+  const uint32_t ct = (c->max_dense_R + TN_MAX - 1) / TN_MAX;
+  args.nsplit = pick_nsplit(bt * ct * (o1 - o0), c->max_dense_R);
+  dim3 grid(bt, ct * args.nsplit, o1 - o0);
   PcbProfScope ps(c, st, PCB_K_DENSE_FWD);
   return launch<MODE_FWD>(grid, args, st);
 }
@@ -758,7 +786,9 @@ int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer,
   }
   TcArgs args = make_args(c, ws, o0);
   {
-    dim3 grid((pcb_round_up(ws->B, 32) + TM - 1) / TM, (c->max_dense_K + TN_MAX - 1) / TN_MAX, o1 - o0);
+    const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM, ct = (c->max_dense_K + TN_MAX - 1) / TN_MAX;
+    args.nsplit = pick_nsplit(bt * ct * (o1 - o0), c->max_dense_K);
+    dim3 grid(bt, ct * args.nsplit, o1 - o0);
     PcbProfScope ps(c, st, PCB_K_DENSE_BWD_CHILD);
     PCB_TRY(launch<MODE_BWD_CHILD>(grid, args, st));
   }
