@@ -4,13 +4,13 @@
 //   aggr[edge(r, t)] += exp(theta[edge(r, t)]) * D[r][t]
 //
 // Both operands are K-major in the work matrices as they lie in memory (K = the example index, which is
-// contiguous), so a 2-D tensor-map copy with the 128-byte swizzle drops a [rows][32 examples] box
-// into shared memory in exactly the layout tcgen05.mma reads.  Per 32-example chunk one elected
-// thread issues the copies (parents' mars, parents' flows, prime children's mars and, where edges
-// carry a sub child, the sub children's mars: 64 or 96 KB), sixteen
-// converter warps turn the raw boxes into the TF32 hi / lo operand tiles IN PLACE with 16-byte
-// shared-memory accesses (hi(G) over the mars box, lo(G) over the flows box, hi(E) over the
-// prime children's box, lo(E) over the sub children's box), and one thread issues the MMAs (hi*hi + lo*hi + hi*lo) into a
+// contiguous), so a 2-D tensor-map copy with a swizzle as wide as its rows drops a
+// [rows][KCH examples] box into shared memory in exactly the layout tcgen05.mma reads.  Per chunk of
+// KCH examples one elected thread issues the copies (parents' mars, parents' flows, prime
+// children's mars and, where edges carry a sub child, the sub children's mars), sixteen converter
+// warps turn the raw boxes into the TF32 hi / lo operand tiles IN PLACE with 16-byte shared-memory
+// accesses (hi(G) over the mars box, lo(G) over the flows box, hi(E) over the prime children's
+// box, lo(E) over the sub children's box), and one thread issues the MMAs (hi*hi + lo*hi + hi*lo) into a
 // 128 x 256 fp32 accumulator in tensor memory.  A stage cycles through
 //   empty -> (copies) -> raw_full -> (convert) -> conv_full -> (MMA, commit) -> empty.
 // Every wait is bounded; on expiry the thread raises the circuit's status word and all roles
@@ -32,12 +32,20 @@ using namespace pcbtc;
 
 constexpr uint32_t TM = 128;          // parents per tile (TMEM lanes)
 constexpr uint32_t TN = 256;          // children per tile (TMEM columns)
-constexpr uint32_t KCH = 32;          // examples per stage: one 128-byte swizzle row of fp32
+// Examples per stage (32: 128-byte rows and swizzle, two stages; 16: 64-byte rows and swizzle, four
+// stages).  Both run at the same speed: per 32 examples the stage memory sees 96 KB written by the
+// copies, 96 KB read and 96 KB written by the conversion and 144 KB read by the MMAs, which is the
+// shared-memory bandwidth of an SM over the ~1.9 us a chunk takes; 32 keeps whole 128-byte lines
+// per row in each copy.
+constexpr uint32_t KCH = 32;
 constexpr uint32_t STAGES = 2;
+constexpr uint32_t ROWB = KCH * 4;    // bytes per operand row in a stage
+constexpr uint32_t SLOTS = ROWB / 16; // 16-byte slots per row
+static_assert(KCH == 16 || KCH == 32, "one swizzle row per stage row");
 constexpr uint32_t CW = 16;           // converter warps
 constexpr uint32_t MMA_WARP = CW;   // warp CW + 1 issues the copies
 constexpr uint32_t NTHREADS = (CW + 2) * 32;
-constexpr uint32_t A_BYTES = TM * 128, B_BYTES = TN * 128;
+constexpr uint32_t A_BYTES = TM * ROWB, B_BYTES = TN * ROWB;
 constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
 constexpr uint32_t RAW_BYTES = 2 * A_BYTES + B_BYTES;   // what the copies of one chunk deliver
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 1024 /*barriers*/;
@@ -64,6 +72,19 @@ __device__ __forceinline__ float4 sub4(float4 a, float4 b) { return make_float4(
   do {                                                                              \
     if (a.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[slot] = gtime(); \
   } while (0)
+
+// K-major operand descriptor for this kernel's row width: 8-row groups ROWB * 8 bytes apart, swizzle
+// span = row width (layout code 2: 128-byte swizzle, 4: 64-byte swizzle)
+__device__ __forceinline__ uint64_t edge_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)((ROWB * 8u) >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)(KCH == 32 ? 2 : 4) << 61;
+  return d;
+}
+// swizzle term of a row: the 16-byte slot index is XORed with it
+__device__ __forceinline__ uint32_t row_swz(uint32_t row) { return KCH == 32 ? (row & 7u) : ((row >> 1) & 3u); }
 
 // grid: (example slices, row tiles x column tiles, blocks)
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -120,15 +141,17 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
     // thread, rows advance by 64, so the swizzled byte offset is one base plus a constant step and
     // the thread's four per-example maxima are the same for all of its rows.  The eight lanes of a
     // quarter warp cover the eight slots of one row: every 16-byte access is conflict-free.
-    const uint32_t kk4 = tid & 7u, rbase = tid >> 3;
-    const uint32_t off0 = rbase * 128u + ((kk4 ^ (rbase & 7u)) << 4);
+    constexpr uint32_t RP = CW * 32 / SLOTS;          // rows per pass of the 512 threads
+    const uint32_t kk4 = tid % SLOTS, rbase = tid / SLOTS;
+    const uint32_t off0 = rbase * ROWB + ((kk4 ^ row_swz(rbase)) << 4);
+    static_assert(RP % 8 == 0, "the swizzle term must not change from pass to pass");
     auto load_mx = [&](uint32_t i) { return *reinterpret_cast<const float4*>(mxrow + k_begin + i * KCH + 4u * kk4); };
     float4 mxn = load_mx(0);
     for (uint32_t i = 0; i < nchunks; ++i) {
       const uint32_t s = i & (STAGES - 1), ph = (i / STAGES) & 1u;
       const float4 mx = mxn;
       if (i + 1 < nchunks) mxn = load_mx(i + 1);
-      if (i + 4 == nchunks || (nchunks < 4 && i == 0)) {
+      if (i + 8 == nchunks || (nchunks < 8 && i == 0)) {
         // the epilogue reads theta and reduces into aggr over this tile's 128 rows x 1 KB: ask L2
         // for those lines a few chunks ahead (earlier, the operand stream would evict them again)
 #pragma unroll
@@ -154,8 +177,8 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
       uint8_t* st = smem + s * STAGE_BYTES + off0;
       if (!(a.dbg & 4u)) {
 #pragma unroll
-      for (uint32_t q = 0; q < TM / 64; ++q) {   // G = flows * exp(mx - mars), exponent clamped: inf * 0 stays out
-        uint8_t* p = st + q * 8192u;
+      for (uint32_t q = 0; q < TM / RP; ++q) {   // G = flows * exp(mx - mars), exponent clamped: inf * 0 stays out
+        uint8_t* p = st + q * (RP * ROWB);
         const float4 m = *reinterpret_cast<const float4*>(p);
         const float4 f = *reinterpret_cast<const float4*>(p + A_BYTES);
         float4 g;
@@ -169,9 +192,9 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
         *reinterpret_cast<float4*>(p + A_BYTES) = sub4(g, h);
       }
 #pragma unroll
-      for (uint32_t q = 0; q < TN / 64; ++q) {   // E = exp(mars_child - mx) <= 1
-        if (rbase + 64u * q < n_tile) {
-          uint8_t* p = st + 2 * A_BYTES + q * 8192u;
+      for (uint32_t q = 0; q < TN / RP; ++q) {   // E = exp(mars_child - mx) <= 1
+        if (rbase + RP * q < n_tile) {
+          uint8_t* p = st + 2 * A_BYTES + q * (RP * ROWB);
           float4 c = *reinterpret_cast<const float4*>(p);
           if (has_sub) {   // child value = prime row + sub row (the sub box lies where lo(E) goes)
             const float4 d = *reinterpret_cast<const float4*>(p + B_BYTES);
@@ -240,8 +263,8 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
         if (i < 60) EDGE_TRACE(i * 8 + 4);
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-        const uint64_t d_ahi = make_desc(sa), d_alo = make_desc(sa + A_BYTES);
-        const uint64_t d_bhi = make_desc(sa + 2 * A_BYTES), d_blo = make_desc(sa + 2 * A_BYTES + B_BYTES);
+        const uint64_t d_ahi = edge_desc(sa), d_alo = edge_desc(sa + A_BYTES);
+        const uint64_t d_bhi = edge_desc(sa + 2 * A_BYTES), d_blo = edge_desc(sa + 2 * A_BYTES + B_BYTES);
         if (!(a.dbg & 1u))
 #pragma unroll
         for (uint32_t ks = 0; ks < KCH / 8; ++ks) {
@@ -324,7 +347,7 @@ bool encode_rows_map(void* out, float* base, uint32_t ld, uint64_t n_rows, uint3
   cuuint32_t box[2] = {KCH, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  KCH == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (getenv("PCB_DEBUG_TM")) fprintf(stderr, "pcb: tensor map encode (ld %u rows %llu box %u) -> %d\n", ld, (unsigned long long)n_rows, box_rows, (int)r);
   if (r != CUDA_SUCCESS) return false;
   static_assert(sizeof(CUtensorMap) == 128, "tensor map size");

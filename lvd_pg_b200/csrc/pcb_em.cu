@@ -183,13 +183,25 @@ __global__ void __launch_bounds__(LTH) leaf_forward_chunk_kernel(
   const uint32_t nb = min((uint32_t)LBT, B - b0);
   stage_values(xs, b0, nb, lchunk_var[chunk], data, miss, num_rows, row_ids, row_start);
   __syncthreads();
+  // a thread's examples are the same for every leaf of the chunk: fetch their values once
+  constexpr uint32_t U = LBT / LTH;
+  uint16_t xv[U];
+#pragma unroll
+  for (uint32_t u = 0; u < U; ++u) {
+    const uint32_t b = threadIdx.x + LTH * u;
+    xv[u] = b < nb ? xs[b] : (uint16_t)0xffff;
+  }
   for (uint32_t li = lchunk_off[chunk]; li < lchunk_off[chunk + 1]; ++li) {
     uint32_t i = lchunk_inputs[li];
     const float* tab = theta + in_poff[i];
     float* out = mars + (size_t)in_node[i] * ld + b0;
-    for (uint32_t b = threadIdx.x; b < nb; b += LTH) {
-      uint16_t x = xs[b];
-      out[b] = x == 0xffff ? 0.0f : __ldg(tab + x);
+    float v[U];
+#pragma unroll
+    for (uint32_t u = 0; u < U; ++u) v[u] = xv[u] == 0xffff ? 0.0f : __ldg(tab + xv[u]);
+#pragma unroll
+    for (uint32_t u = 0; u < U; ++u) {
+      const uint32_t b = threadIdx.x + LTH * u;
+      if (b < nb) out[b] = v[u];
     }
   }
 }
@@ -211,19 +223,33 @@ __global__ void __launch_bounds__(LTH) leaf_flow_chunk_kernel(
   for (uint32_t x = threadIdx.x; x < nl * hstride; x += LTH) hist[x] = 0.0f;
   stage_values(xs, b0, nb, lchunk_var[chunk], data, miss, num_rows, row_ids, row_start);
   __syncthreads();
+  // a thread's examples (and their values and weights) are the same for every leaf of the chunk;
+  // per leaf all of the thread's flow loads are issued before the first histogram update
+  constexpr uint32_t U = LBT / LTH;
+  uint16_t xv[U];
+  float wv[U];
+#pragma unroll
+  for (uint32_t u = 0; u < U; ++u) {
+    const uint32_t b = threadIdx.x + LTH * u;
+    xv[u] = b < nb ? xs[b] : (uint16_t)0xfffe;   // 0xfffe: no example
+    wv[u] = (weights && b < nb) ? weights[data_row(row_ids, row_start, b0 + b)] : 1.0f;
+  }
   for (uint32_t l = 0; l < nl; ++l) {
     uint32_t i = lchunk_inputs[l0 + l];
     if (in_foff[i] == ~0ull) continue;  // fixed leaf
     const uint32_t C = in_cats[i];
     const float* f = flows + (size_t)in_node[i] * ld + b0;
     float* h = hist + l * hstride;
-    for (uint32_t b = threadIdx.x; b < nb; b += LTH) {
-      uint16_t x = xs[b];
-      uint32_t slot = x == 0xffff ? C : (uint32_t)x;
-      if (slot > C) continue;  // value outside the leaf's categories
-      float v = f[b];
-      if (weights) v *= weights[data_row(row_ids, row_start, b0 + b)];
-      atomicAdd(h + slot, v);
+    float v[U];
+#pragma unroll
+    for (uint32_t u = 0; u < U; ++u) {
+      const uint32_t b = threadIdx.x + LTH * u;
+      v[u] = f[b < nb ? b : 0u];
+    }
+#pragma unroll
+    for (uint32_t u = 0; u < U; ++u) {
+      const uint32_t slot = xv[u] == 0xffff ? C : (uint32_t)xv[u];   // missing value -> the extra slot
+      if (xv[u] != 0xfffe && slot <= C) atomicAdd(h + slot, v[u] * wv[u]);
     }
   }
   __syncthreads();
