@@ -330,6 +330,7 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
     PCB_CUDA(cudaGetDeviceProperties(&prop, c->device));
     const char* impl = getenv("PCB_DENSE_IMPL");
     c->use_tc = prop.major == 10 && !(impl && std::string(impl) == "simt");
+    c->graph_enabled = !(getenv("PCB_NO_GRAPH") && atoi(getenv("PCB_NO_GRAPH")) != 0);
     if (c->use_tc) PCB_TRY(pcb_dense_tc_prepare(c, &bytes));
   }
   c->device_bytes = bytes;
@@ -354,6 +355,9 @@ void free_circuit(pcb_circuit* c) {
                   c->up_all, c->up_sparse, c->down_all, c->down_sparse, c->in_off, c->in_ent, c->dense,
                   c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status, c->w_img, c->dense_img};
   for (void* p : ptrs) if (p) cudaFree(p);
+  if (c->ev_g0) cudaEventDestroy(c->ev_g0);
+  if (c->ev_g1) cudaEventDestroy(c->ev_g1);
+  if (c->gstream) cudaStreamDestroy(c->gstream);
   if (c->ev_fork) cudaEventDestroy(c->ev_fork);
   if (c->ev_join) cudaEventDestroy(c->ev_join);
   if (c->side) cudaStreamDestroy(c->side);
@@ -414,6 +418,10 @@ extern "C" int32_t pcb_workspace_create(pcb_circuit* c, uint32_t max_batch, int3
     delete ws;
     return pcb_fail(PCB_ERR_CUDA, std::string("workspace allocation: ") + cudaGetErrorString(e3));
   }
+  if (cudaMalloc((void**)&ws->ids_stage, (size_t)max_batch * sizeof(int32_t)) != cudaSuccess) {
+    pcb_workspace_destroy(ws);
+    return pcb_fail(PCB_ERR_CUDA, "workspace allocation: row id staging");
+  }
   {
     int32_t st = pcb_dense_edge_prepare_ws(ws);
     if (st != PCB_OK) { pcb_workspace_destroy(ws); return st; }
@@ -451,8 +459,9 @@ int32_t pcb_ws_ensure_sets(pcb_workspace* ws, uint32_t S, bool need_stack) {
 extern "C" int32_t pcb_workspace_destroy(pcb_workspace* ws) {
   if (!ws) return PCB_OK;
   cudaSetDevice(ws->c->device);
+  if (ws->step_exec) cudaGraphExecDestroy(ws->step_exec);
   for (void* p : {(void*)ws->mars, (void*)ws->flows, (void*)ws->blk_mx, (void*)ws->klds, (void*)ws->grads,
-                  (void*)ws->eprob, (void*)ws->cum, (void*)ws->stack})
+                  (void*)ws->eprob, (void*)ws->cum, (void*)ws->stack, (void*)ws->ids_stage})
     if (p) cudaFree(p);
   delete ws;
   return PCB_OK;

@@ -18,6 +18,8 @@
 // one atomic per warp and edge).
 #include <algorithm>
 
+#include <cstring>
+
 #include "pcb_internal.h"
 
 namespace {
@@ -448,12 +450,12 @@ extern "C" int32_t pcb_em_update(pcb_circuit* c, float pseudocount, float inerti
   return PCB_OK;
 }
 
-extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev,
-                               const uint8_t* miss_dev, uint64_t num_rows, const int32_t* row_ids_dev,
-                               uint32_t row_start, uint32_t B, const float* weights_dev, float clear_rate,
-                               float pseudocount, float inertia, float* ll_sum_dev, pcb_stream s) {
-  PCB_REQUIRE(c && ws, "null argument");
-  cudaStream_t st = (cudaStream_t)s;
+// clear, forward, backward, (all-reduce,) update: the launches of one EM step on stream st
+static int32_t em_step_body(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev, const uint8_t* miss_dev,
+                            uint64_t num_rows, const int32_t* row_ids_dev, uint32_t row_start, uint32_t B,
+                            const float* weights_dev, float clear_rate, float pseudocount, float inertia,
+                            float* ll_sum_dev, cudaStream_t st) {
+  pcb_stream s = (pcb_stream)st;
   PCB_TRY(pcb_clear_flows(c, clear_rate, s));
   PCB_TRY(pcb_forward(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, nullptr, s));
   PCB_TRY(pcb_backward(c, ws, weights_dev, s));
@@ -464,6 +466,108 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
     PCB_CUDA(cudaMemcpyAsync(ll_sum_dev, c->aggr + c->aggr_len - 1, sizeof(float), cudaMemcpyDeviceToDevice, st));
   PCB_TRY(pcb_em_update(c, pseudocount, inertia, s));
   PCB_CUDA(cudaGetLastError());
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev,
+                               const uint8_t* miss_dev, uint64_t num_rows, const int32_t* row_ids_dev,
+                               uint32_t row_start, uint32_t B, const float* weights_dev, float clear_rate,
+                               float pseudocount, float inertia, float* ll_sum_dev, pcb_stream s) {
+  PCB_REQUIRE(c && ws, "null argument");
+  PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
+  PCB_REQUIRE(B >= 1 && B <= ws->max_batch, "batch size exceeds the workspace");
+  PCB_CUDA(cudaSetDevice(c->device));
+  cudaStream_t st = (cudaStream_t)s;
+  // the step reads the row ids from the workspace's own buffer, so a replayed graph sees the ids
+  // of the current call
+  if (row_ids_dev) {
+    PCB_CUDA(cudaMemcpyAsync(ws->ids_stage, row_ids_dev, (size_t)B * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
+    row_ids_dev = ws->ids_stage;
+  }
+  if (!c->graph_enabled || c->prof.on)
+    return em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
+                        pseudocount, inertia, ll_sum_dev, st);
+
+  pcb_workspace::StepKey key;
+  memset(&key, 0, sizeof(key));
+  key.data = data_dev; key.miss = miss_dev; key.weights = weights_dev; key.ll = ll_sum_dev; key.comm = c->comm;
+  key.stream = (void*)st; key.num_rows = num_rows; key.row_start = row_start; key.B = B;
+  key.clear_rate = clear_rate; key.pseudocount = pseudocount; key.inertia = inertia;
+  key.has_ids = row_ids_dev != nullptr; key.w_valid = c->w_img_valid;
+
+  // the legacy default stream cannot be captured: graphs run on a stream of the circuit's own,
+  // ordered after and before the caller's stream with two events
+  cudaStream_t gs = st;
+  const bool legacy = st == nullptr || st == cudaStreamLegacy;
+  if (legacy) {
+    if (!c->gstream) {
+      PCB_CUDA(cudaStreamCreateWithFlags(&c->gstream, cudaStreamNonBlocking));
+      PCB_CUDA(cudaEventCreateWithFlags(&c->ev_g0, cudaEventDisableTiming));
+      PCB_CUDA(cudaEventCreateWithFlags(&c->ev_g1, cudaEventDisableTiming));
+    }
+    gs = c->gstream;
+  }
+  auto enter = [&]() -> int32_t {
+    if (legacy) { PCB_CUDA(cudaEventRecord(c->ev_g0, st)); PCB_CUDA(cudaStreamWaitEvent(gs, c->ev_g0, 0)); }
+    return PCB_OK;
+  };
+  auto leave = [&]() -> int32_t {
+    if (legacy) { PCB_CUDA(cudaEventRecord(c->ev_g1, gs)); PCB_CUDA(cudaStreamWaitEvent(st, c->ev_g1, 0)); }
+    return PCB_OK;
+  };
+
+  if (ws->step_exec && !memcmp(&key, &ws->exec_key, sizeof(key))) {
+    // replay; the host-side state is what the captured run left behind
+    PCB_TRY(enter());
+    PCB_CUDA(cudaGraphLaunch(ws->step_exec, gs));
+    PCB_TRY(leave());
+    for (int k = 0; k < PCB_K_COUNT; ++k) c->prof.launches[k] += ws->step_launches[k];
+    ws->B = B; ws->data = data_dev; ws->miss = miss_dev; ws->num_rows = num_rows;
+    ws->row_ids = row_ids_dev; ws->row_start = row_start; ws->have_forward = true;
+    c->w_img_valid = false;
+    return PCB_OK;
+  }
+  const bool capture = ws->have_key && !memcmp(&key, &ws->last_key, sizeof(key));
+  ws->last_key = key;
+  ws->have_key = true;
+  if (!capture)
+    return em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
+                        pseudocount, inertia, ll_sum_dev, st);
+
+  if (ws->step_exec) { cudaGraphExecDestroy(ws->step_exec); ws->step_exec = nullptr; }
+  uint64_t before[PCB_K_COUNT];
+  for (int k = 0; k < PCB_K_COUNT; ++k) before[k] = c->prof.launches[k];
+  PCB_TRY(enter());
+  PCB_CUDA(cudaStreamBeginCapture(gs, cudaStreamCaptureModeRelaxed));
+  int32_t body = em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
+                              pseudocount, inertia, ll_sum_dev, gs);
+  cudaGraph_t graph = nullptr;
+  cudaError_t ce = cudaStreamEndCapture(gs, &graph);
+  if (body != PCB_OK || ce != cudaSuccess || !graph) {
+    if (graph) cudaGraphDestroy(graph);
+    cudaGetLastError();
+    c->graph_enabled = false;   // this circuit's step does not capture: stay with plain launches
+    if (body != PCB_OK) return body;
+    for (int k = 0; k < PCB_K_COUNT; ++k) c->prof.launches[k] = before[k];
+    c->w_img_valid = key.w_valid != 0;
+    return em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
+                        pseudocount, inertia, ll_sum_dev, st);
+  }
+  ce = cudaGraphInstantiate(&ws->step_exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (ce != cudaSuccess) {
+    ws->step_exec = nullptr;
+    c->graph_enabled = false;
+    for (int k = 0; k < PCB_K_COUNT; ++k) c->prof.launches[k] = before[k];
+    c->w_img_valid = key.w_valid != 0;
+    cudaGetLastError();
+    return em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
+                        pseudocount, inertia, ll_sum_dev, st);
+  }
+  for (int k = 0; k < PCB_K_COUNT; ++k) ws->step_launches[k] = c->prof.launches[k] - before[k];
+  ws->exec_key = key;
+  PCB_CUDA(cudaGraphLaunch(ws->step_exec, gs));
+  PCB_TRY(leave());
   return PCB_OK;
 }
 

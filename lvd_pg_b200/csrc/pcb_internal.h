@@ -142,6 +142,9 @@ struct pcb_circuit {
   cudaStream_t side = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   bool side_busy = false;
+  cudaStream_t gstream = nullptr;   // stands in for the legacy default stream, which cannot be captured
+  cudaEvent_t ev_g0 = nullptr, ev_g1 = nullptr;
+  bool graph_enabled = true;
   // dense blocks [edge_lo, edge_hi) whose edge statistics are still to be launched, and the number
   // of tiles at which the range is launched
   uint32_t edge_lo = 0, edge_hi = 0, edge_batch_tiles = 592;
@@ -158,6 +161,21 @@ struct pcb_workspace {
   float* mars = nullptr;    // [N][ld]
   float* flows = nullptr;   // [N][ld]
   float* blk_mx = nullptr;  // [n_dense][ld] per-example max of a dense block's children
+  // One EM step as a CUDA graph: a step called twice in a row with the same arguments is captured
+  // on the second call and replayed from then on (the row ids are staged in ids_stage so that
+  // their address does not change from step to step).
+  struct StepKey {
+    const void* data; const void* miss; const void* weights; void* ll; void* comm; void* stream;
+    uint64_t num_rows;
+    uint32_t row_start, B;
+    float clear_rate, pseudocount, inertia;
+    uint32_t has_ids, w_valid;
+  };
+  StepKey last_key{}, exec_key{};
+  bool have_key = false;
+  cudaGraphExec_t step_exec = nullptr;
+  uint64_t step_launches[PCB_K_COUNT] = {0};   // launches of one replay, per kernel class
+  int32_t* ids_stage = nullptr;                 // [max_batch]
   // tensor maps over mars / flows for the copy-fed edge-statistics kernel (128-byte opaque objects)
   alignas(64) unsigned char tm[3][128];
   bool have_tm = false;
