@@ -19,7 +19,9 @@
 //     w_image_kernel writes exp(theta), already split and already in the swizzled tile layout,
 //     to two images (W for FWD, W^T for BWD_CHILD); the GEMM kernels fetch a tile of an image
 //     with two cp.async.bulk copies that complete on the stage's mbarrier.
-//   * the per-example maximum mx is computed by a small full-occupancy kernel per layer.
+//   * the per-example maximum mx is computed by the FWD kernel's producers in a first pass over
+//     the child rows (which the K loop then re-reads from L2) and kept in blk_mx for the backward
+//     kernels.
 //
 // Synchronisation: a two-stage ring of shared-memory tiles guarded by mbarriers
 // (full: one arrival per producer warp + the bulk copies' byte count, empty: one tcgen05.commit), one
@@ -71,13 +73,6 @@ struct TcArgs {
   uint32_t dbg;   // timing experiments only: 1 skip MMAs, 2 skip global loads, 4 skip epilogue, 8 skip smem stores
 };
 
-__device__ __forceinline__ float child_val(const float* __restrict__ mars, uint32_t ld, const PcbDenseBlock& k,
-                                           uint32_t t, uint32_t b) {
-  float v = mars[(size_t)(k.c0 + t) * ld + b];
-  if (k.d0 != PCB_NONE) v += mars[(size_t)(k.d0 + t) * ld + b];
-  return v;
-}
-
 // ---- exp(theta), split and laid out as operand tiles ------------------------------------------------
 // One block converts a 32 x 32 patch (rows r, columns t) of a dense block's weights and writes it
 // to the FWD image (rows r, K = t) and, transposed through shared memory, to the BWD_CHILD image
@@ -121,35 +116,6 @@ __global__ void __launch_bounds__(256) w_image_kernel(const float* __restrict__ 
       base[o] = h;
       base[(size_t)im.rows_t * 32 + o] = v - h;
     }
-  }
-}
-
-// ---- per-example maximum of a dense block's child values ---------------------------------------------
-// grid (example tiles of 128, blocks of the layer); 1024 threads: eight per example, each over an
-// eighth of the children, so a thread has at most two rounds of sixteen loads in flight for K = 256
-__global__ void __launch_bounds__(1024) dense_max_kernel(const float* __restrict__ mars, float* __restrict__ blk_mx,
-                                                         uint32_t ld, const PcbDenseBlock* __restrict__ blocks) {
-  __shared__ float part[8][128];
-  const PcbDenseBlock k = blocks[blockIdx.y];
-  const uint32_t bl = threadIdx.x & 127, sl = threadIdx.x >> 7, b = blockIdx.x * 128 + bl;
-  float mx = -INFINITY;
-  if (b < ld) {
-    uint32_t t = sl;
-    for (; t + 56 < k.K; t += 64) {
-      float v[8];
-#pragma unroll
-      for (uint32_t u = 0; u < 8; ++u) v[u] = child_val(mars, ld, k, t + 8 * u, b);
-#pragma unroll
-      for (uint32_t u = 0; u < 8; ++u) mx = fmaxf(mx, v[u]);
-    }
-    for (; t < k.K; t += 8) mx = fmaxf(mx, child_val(mars, ld, k, t, b));
-  }
-  part[sl][bl] = mx;
-  __syncthreads();
-  if (sl == 0 && b < ld) {
-#pragma unroll
-    for (uint32_t u = 1; u < 8; ++u) mx = fmaxf(mx, part[u][bl]);
-    blk_mx[(size_t)k.mx_row * ld + b] = mx;
   }
 }
 
@@ -453,7 +419,42 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  if (MODE != MODE_BWD_EDGE && tid < 128) mxs[tid] = (m0 + tid < ld) ? mxrow[m0 + tid] : -INFINITY;
+  if (MODE == MODE_BWD_CHILD && tid < 128) mxs[tid] = (m0 + tid < ld) ? mxrow[m0 + tid] : -INFINITY;
+  if (MODE == MODE_FWD && warp < MMA_WARP) {
+    // Per-example maximum of the block's child values, over all K children: the producers' own
+    // thread -> (example, child) map, sixteen children per thread and round with all loads of a
+    // round in flight together, then a reduction over the four lanes that share an example.  The
+    // rows are read again by the K loop, from L2.  The maxima also go to blk_mx for the backward
+    // kernels (one CTA per example tile writes them).
+    const uint32_t row = rc_row(tid), b = m0 + row, kk0 = rc_kk(tid, 0);
+    const bool bok = b < ld, has_sub = k.d0 != PCB_NONE;
+    const float* pc = a.mars + (size_t)(k.c0 + kk0) * ld + (bok ? b : 0u);
+    const float* pd = a.mars + (size_t)((has_sub ? k.d0 : k.c0) + kk0) * ld + (bok ? b : 0u);
+    float mx = -INFINITY;
+    for (uint32_t kc = 0; kc < k.K; kc += 64) {
+      float x[16];
+#pragma unroll
+      for (uint32_t q = 0; q < 16; ++q) {
+        const bool in = kc + 4 * q + kk0 < k.K;
+        x[q] = pc[(size_t)(in ? kc + 4 * q : 0u) * ld];
+      }
+      if (has_sub) {
+#pragma unroll
+        for (uint32_t q = 0; q < 16; ++q) {
+          const bool in = kc + 4 * q + kk0 < k.K;
+          x[q] += pd[(size_t)(in ? kc + 4 * q : 0u) * ld];
+        }
+      }
+#pragma unroll
+      for (uint32_t q = 0; q < 16; ++q) mx = fmaxf(mx, kc + 4 * q + kk0 < k.K ? x[q] : -INFINITY);
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+    if ((lane >> 3) == 0) {
+      mxs[row] = bok ? mx : -INFINITY;
+      if (bok && blockIdx.y == 0) a.blk_mx[(size_t)k.mx_row * ld + b] = mx;
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -724,10 +725,6 @@ int32_t pcb_dense_tc_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, 
   uint32_t o0 = c->h_dense_off[layer], o1 = c->h_dense_off[layer + 1];
   if (o1 == o0) return PCB_OK;
   const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM;
-  {
-    PcbProfScope ps(c, st, PCB_K_DENSE_MAX);
-    dense_max_kernel<<<dim3(bt, o1 - o0), 1024, 0, st>>>(ws->mars, ws->blk_mx, ws->ld, c->dense + o0);
-  }
   TcArgs args = make_args(c, ws, o0);
   const uint32_t ct = (c->max_dense_R + TN_MAX - 1) / TN_MAX;
   args.nsplit = pick_nsplit(bt * ct * (o1 - o0), c->max_dense_R);

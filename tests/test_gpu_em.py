@@ -108,7 +108,9 @@ def test_em_steps_track_oracle_with_row_ids(oracle):
     dd = api.DeviceData(data, m.device)
     rng = np.random.default_rng(0)
     ll_dev = torch.zeros(1, device=m.device)
-    for step in range(3):
+    # the second identical call captures the step as a CUDA graph, later ones replay it: every step
+    # brings its own row ids
+    for step in range(5):
         ids = (rng.permutation(300)[:128] + 1).astype(np.int32)
         ll_ref, _ = oracle.em_step(ref, data, row_ids=ids, pseudocount=0.1, inertia=0.9)
         api.em_step(m, dd, torch.from_numpy(ids).to(m.device), pseudocount=0.1, inertia=0.9, ll_sum=ll_dev)
