@@ -72,7 +72,7 @@ def lib():
         if not os.path.exists(LIB_PATH):
             raise PcbError(-1, f"{LIB_PATH} is missing: build it with `python -m lvd_pg_b200.build` "
                                "(there is no CPU fallback)")
-        _lib = C.CDLL(LIB_PATH)
+        _lib = C.CDLL(os.environ.get("PCB200_LIBRARY", LIB_PATH))   # override: a differently tuned build of the same sources
         _lib.pcb_last_error.restype = C.c_char_p
         for name, args in SIGNATURES.items():
             fn = getattr(_lib, name)

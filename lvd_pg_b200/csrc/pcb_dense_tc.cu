@@ -42,8 +42,13 @@ enum { MODE_FWD = 0, MODE_BWD_CHILD = 1, MODE_BWD_EDGE = 2 };
 constexpr uint32_t TM = 128;         // tile rows (TMEM lanes)
 constexpr uint32_t TN_MAX = 256;     // tile columns
 constexpr uint32_t KCH = 32;         // K elements per stage (one 128-byte swizzle row of tf32)
-constexpr uint32_t STAGES = 2;
-constexpr uint32_t NPROD = 512;      // producer threads
+#ifndef PCB_TC_STAGES
+#define PCB_TC_STAGES 2
+#define PCB_TC_NPROD 512
+#define PCB_TC_CTAS 1
+#endif
+constexpr uint32_t STAGES = PCB_TC_STAGES;
+constexpr uint32_t NPROD = PCB_TC_NPROD;      // producer threads
 constexpr uint32_t PW = NPROD / 32;  // producer warps
 constexpr uint32_t RG = 16 / PW;     // row groups per thread in the row-contiguous map
 constexpr uint32_t QA = 128 / PW;    // A rows per thread in the K-contiguous map
@@ -70,7 +75,8 @@ struct TcArgs {
   uint32_t ld, B, b_per_cta;
   uint32_t nsplit;   // FWD / BWD_CHILD: CTAs sharing one 256-column tile (1, 2 or 4), each taking 256 / nsplit columns
   unsigned long long* trace;   // timing trace of CTA (0,0,0), or null
-  uint32_t dbg;   // timing experiments only: 1 skip MMAs, 2 skip global loads, 4 skip epilogue, 8 skip smem stores
+  uint32_t dbg;   // timing experiments only: 1 skip MMAs, 2 skip global loads, 4 skip epilogue, 8 skip smem stores,
+                  // 16 skip the child-flow stores, 32 skip the child-value loads of the child-flow epilogue
 };
 
 // ---- exp(theta), split and laid out as operand tiles ------------------------------------------------
@@ -151,8 +157,8 @@ __device__ __forceinline__ float child_val_nb(const float* __restrict__ mars, ui
                                               uint32_t t, uint32_t b, bool valid) {
   const uint32_t tt = valid ? t : 0u, bb = valid ? b : 0u;
   const bool has_sub = k.d0 != PCB_NONE;
-  float v = mars[(size_t)(k.c0 + tt) * ld + bb];
-  float w = mars[(size_t)((has_sub ? k.d0 : k.c0) + tt) * ld + bb];
+  float v = __ldcg(mars + (size_t)(k.c0 + tt) * ld + bb);
+  float w = __ldcg(mars + (size_t)((has_sub ? k.d0 : k.c0) + tt) * ld + bb);
   v += has_sub ? w : 0.0f;
   return valid ? v : -INFINITY;
 }
@@ -361,7 +367,7 @@ __device__ __forceinline__ void store_chunk(const ProdCtx& c, const ProdInv& v, 
 // grid: FWD / BWD_CHILD (example tiles of 128, column tiles of 256, blocks)
 //       BWD_EDGE        (example slices, row tiles x column tiles, blocks)
 template <int MODE>
-__global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
+__global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* ctl = smem + STAGES * STAGE_BYTES;
@@ -369,6 +375,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
   uint64_t* empty = full + STAGES;                            // [STAGES]
   uint64_t* accfull = empty + STAGES;                         // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfull + 1);
+  uint64_t* ebar = reinterpret_cast<uint64_t*>(ctl + 64);     // [3] child-value copies of the BWD_CHILD epilogue
+  uint32_t* epi_fail = reinterpret_cast<uint32_t*>(ctl + 96); // a producer warp lost a wait
   float* mxs = reinterpret_cast<float*>(ctl + 128);           // [128]
 
   if (a.trace && threadIdx.x == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[504] = gtime();
@@ -411,6 +419,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
   if (tid == 0) {
     for (uint32_t s = 0; s < STAGES; ++s) { mbar_init(&full[s], NPROD / 32); mbar_init(&empty[s], 1); }
     mbar_init(accfull, 1);
+    for (uint32_t j = 0; j < 3; ++j) mbar_init(&ebar[j], 1);
+    *epi_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) {
@@ -426,33 +436,38 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
     // round in flight together, then a reduction over the four lanes that share an example.  The
     // rows are read again by the K loop, from L2.  The maxima also go to blk_mx for the backward
     // kernels (one CTA per example tile writes them).
-    const uint32_t row = rc_row(tid), b = m0 + row, kk0 = rc_kk(tid, 0);
-    const bool bok = b < ld, has_sub = k.d0 != PCB_NONE;
-    const float* pc = a.mars + (size_t)(k.c0 + kk0) * ld + (bok ? b : 0u);
-    const float* pd = a.mars + (size_t)((has_sub ? k.d0 : k.c0) + kk0) * ld + (bok ? b : 0u);
-    float mx = -INFINITY;
-    for (uint32_t kc = 0; kc < k.K; kc += 64) {
-      float x[16];
+    const uint32_t kk0 = rc_kk(tid, 0);
+    const bool has_sub = k.d0 != PCB_NONE;
 #pragma unroll
-      for (uint32_t q = 0; q < 16; ++q) {
-        const bool in = kc + 4 * q + kk0 < k.K;
-        x[q] = pc[(size_t)(in ? kc + 4 * q : 0u) * ld];
-      }
-      if (has_sub) {
+    for (uint32_t g = 0; g < RG; ++g) {
+      const uint32_t row = rc_row(tid, g), b = m0 + row;
+      const bool bok = b < ld;
+      const float* pc = a.mars + (size_t)(k.c0 + kk0) * ld + (bok ? b : 0u);
+      const float* pd = a.mars + (size_t)((has_sub ? k.d0 : k.c0) + kk0) * ld + (bok ? b : 0u);
+      float mx = -INFINITY;
+      for (uint32_t kc = 0; kc < k.K; kc += 64) {
+        float x[16];
 #pragma unroll
         for (uint32_t q = 0; q < 16; ++q) {
           const bool in = kc + 4 * q + kk0 < k.K;
-          x[q] += pd[(size_t)(in ? kc + 4 * q : 0u) * ld];
+          x[q] = pc[(size_t)(in ? kc + 4 * q : 0u) * ld];
         }
-      }
+        if (has_sub) {
 #pragma unroll
-      for (uint32_t q = 0; q < 16; ++q) mx = fmaxf(mx, kc + 4 * q + kk0 < k.K ? x[q] : -INFINITY);
-    }
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-    if ((lane >> 3) == 0) {
-      mxs[row] = bok ? mx : -INFINITY;
-      if (bok && blockIdx.y == 0) a.blk_mx[(size_t)k.mx_row * ld + b] = mx;
+          for (uint32_t q = 0; q < 16; ++q) {
+            const bool in = kc + 4 * q + kk0 < k.K;
+            x[q] += pd[(size_t)(in ? kc + 4 * q : 0u) * ld];
+          }
+        }
+#pragma unroll
+        for (uint32_t q = 0; q < 16; ++q) mx = fmaxf(mx, kc + 4 * q + kk0 < k.K ? x[q] : -INFINITY);
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      if ((lane >> 3) == 0) {
+        mxs[row] = bok ? mx : -INFINITY;
+        if (bok && blockIdx.y == 0) a.blk_mx[(size_t)k.mx_row * ld + b] = mx;
+      }
     }
   }
   tc_fence_before();
@@ -512,11 +527,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
     for (uint32_t i = 0; i < nchunks && ok; i += 2) {
       if (i + 1 < nchunks) load_chunk<MODE>(ctx, inv, i + 1, ra1);
       const bool pf = i + 4 == nchunks || i + 5 == nchunks || (nchunks < 4 && i == 0);
-      if (pf) { prefetch_children(0); prefetch_children(1); }
+      constexpr uint32_t NPF = 2048 / NPROD;   // lines per thread
+      if (pf) for (uint32_t j = 0; j < NPF / 2; ++j) prefetch_children(j);
       ok = process(i, ra0);
       if (!ok || i + 1 >= nchunks) break;
       if (i + 2 < nchunks) load_chunk<MODE>(ctx, inv, i + 2, ra0);
-      if (pf) { prefetch_children(2); prefetch_children(3); }
+      if (pf) for (uint32_t j = NPF / 2; j < NPF; ++j) prefetch_children(j);
       ok = process(i + 1, ra1);
     }
 
@@ -525,9 +541,81 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
     if (ok && lane == 0) ok = mbar_wait(accfull, 0, a.status);
     ok = __all_sync(0xffffffffu, ok);
     if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[501] = gtime();
-    if (ok && !(a.dbg & 4u)) {
+    constexpr bool COPY_EPI = MODE == MODE_BWD_CHILD && PW == 16;
+    if (COPY_EPI) {
+      // Child flows  f[t][b] = acc[b][t] * exp(M[t][b] - mx[b])  need the children's value rows for
+      // the tile's examples: up to 2 x 256 rows of 512 bytes.  Plain loads of that shape (every
+      // request a line of another row) run at a fraction of what the copy engine delivers, so the
+      // rows are fetched with one bulk copy each into the operand stages, idle by now: slot c of
+      // 1 KB holds column c's prime row and sub row.  192 slots fit; columns 192..255 reuse slots
+      // 0..63 once the first round has read them.  Round r, warp group g: columns 128 r + 32 g ...
+      if (!ok) *reinterpret_cast<volatile uint32_t*>(epi_fail) = 1u;
+      const uint32_t ex = min(TM, ld - m0);              // examples of this tile (ld is a multiple of 32)
+      const uint32_t rowb = ex * 4u;
+      const bool has_sub = k.d0 != PCB_NONE;
+      const uint32_t per = has_sub ? 2u : 1u;
+      const uint32_t cnt0 = min(n_count, 128u), cnt1 = n_count > 128u ? min(n_count - 128u, 64u) : 0u,
+                     cnt2 = n_count > 192u ? n_count - 192u : 0u;
+      if (tid == 0) {
+        mbar_arrive_expect_tx(&ebar[0], cnt0 * rowb * per);
+        mbar_arrive_expect_tx(&ebar[1], cnt1 * rowb * per);
+        mbar_arrive_expect_tx(&ebar[2], cnt2 * rowb * per);
+      }
+      // every producer warp is past the accumulator wait (the stages are idle) and the byte counts
+      // are posted before the first copy is issued
+      asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");
+      const bool go = *reinterpret_cast<volatile uint32_t*>(epi_fail) == 0u && !(a.dbg & 4u);
+      if (go) {
+        tc_fence_after();
+        auto issue = [&](uint32_t c, uint32_t which, uint64_t* bar) {
+          const uint32_t slot = c < 192u ? c : c - 192u;
+          const float* src = a.mars + (size_t)((which ? k.d0 : k.c0) + n0 + c) * ld + m0;
+          bulk_g2s(smem + slot * 1024u + which * 512u, src, rowb, bar);
+        };
+        if (tid < 384u) {
+          const uint32_t c = tid % 192u, which = tid / 192u;
+          if (c < n_count && (which == 0u || has_sub)) issue(c, which, c < 128u ? &ebar[0] : &ebar[1]);
+        }
+        const uint32_t q4 = warp & 3, grp = warp >> 2, row = q4 * 32 + lane, b = m0 + row;
+        const float mx = mxs[row];
+        auto round = [&](uint32_t c0, uint64_t* bar) {   // 32 columns from c0, warp-uniform
+          if (c0 >= n_tile) return;
+          bool got = lane != 0 || mbar_wait(bar, 0, a.status);
+          got = __all_sync(0xffffffffu, got);
+          float acc[32];
+          tmem_ld32(tmem_base + ((q4 * 32u) << 16) + c0, acc);
+          if (got && b < ld) {
+#pragma unroll
+            for (uint32_t j = 0; j < 32; ++j) {
+              const uint32_t c = c0 + j, t = n0 + c;
+              if (t < k.K) {
+                const float* sp = reinterpret_cast<const float*>(smem + (c < 192u ? c : c - 192u) * 1024u) + row;
+                float cv = sp[0];
+                if (has_sub) cv += sp[128];
+                const float f = mx == -INFINITY ? 0.0f : acc[j] * __expf(cv - mx);
+                a.flows[(size_t)(k.c0 + t) * ld + b] = f;
+                if (has_sub) a.flows[(size_t)(k.d0 + t) * ld + b] = f;
+              }
+            }
+          }
+        };
+        round(32u * grp, &ebar[0]);
+        if (n_tile > 128u) {
+          asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");   // slots 0..63 have been read
+          if (tid < 128u) {
+            const uint32_t c = 192u + (tid & 63u), which = tid >> 6;
+            if (c < n_count && (which == 0u || has_sub)) {
+              fence_proxy_async();
+              issue(c, which, &ebar[2]);
+            }
+          }
+          round(128u + 32u * grp, grp < 2u ? &ebar[1] : &ebar[2]);
+        }
+      }
+    } else if (ok && !(a.dbg & 4u)) {
       tc_fence_after();
-      const uint32_t CG = max(32u, ((n_tile + 127u) >> 7) << 5);   // columns per epilogue warp group (4 groups)
+      constexpr uint32_t NG = PW / 4;                                             // epilogue warp groups
+      const uint32_t CG = max(32u, ((n_tile + 32u * NG - 1u) / (32u * NG)) * 32u);   // columns per group
       const uint32_t q4 = warp & 3, grp = warp >> 2;   // lane quarter, column group
       const uint32_t row = q4 * 32 + lane;
       const uint32_t c_begin = grp * CG, c_end = min(n_tile, c_begin + CG);
@@ -554,13 +642,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) dense_tc_kernel(TcArgs a) {
 #pragma unroll
             for (uint32_t j = 0; j < 32; ++j) {
               uint32_t t = n0 + c0 + j;
-              cv[j] = child_val_nb(a.mars, ld, k, t, b, t < k.K && mx != -INFINITY);
+              cv[j] = (a.dbg & 32u) ? mx : child_val_nb(a.mars, ld, k, t, b, t < k.K && mx != -INFINITY);
             }
 #pragma unroll
             for (uint32_t j = 0; j < 32; ++j) {
               uint32_t t = n0 + c0 + j;
               if (t < k.K) {
                 float f = acc[j] * __expf(cv[j] - mx);   // exp(-inf) = 0 for masked entries
+                if ((a.dbg & 16u) && f != 12345.0f) continue;
                 a.flows[(size_t)(k.c0 + t) * ld + b] = f;
                 if (k.d0 != PCB_NONE) a.flows[(size_t)(k.d0 + t) * ld + b] = f;
               }
