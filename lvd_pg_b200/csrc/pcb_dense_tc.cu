@@ -58,7 +58,7 @@ constexpr uint32_t NTHREADS = NPROD + 32;
 constexpr uint32_t A_BYTES = TM * 128;        // one A sub-tile (hi or lo)
 constexpr uint32_t B_BYTES = TN_MAX * 128;    // one B sub-tile (hi or lo)
 constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 1024 /*barriers, mx*/;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 1024 /*barriers, mx*/ + 2048 /*partial maxima*/;
 constexpr uint32_t TMEM_COLS = 256;
 
 
@@ -431,44 +431,68 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
   }
   if (MODE == MODE_BWD_CHILD && tid < 128) mxs[tid] = (m0 + tid < ld) ? mxrow[m0 + tid] : -INFINITY;
   if (MODE == MODE_FWD && warp < MMA_WARP) {
-    // Per-example maximum of the block's child values, over all K children: the producers' own
-    // thread -> (example, child) map, sixteen children per thread and round with all loads of a
-    // round in flight together, then a reduction over the four lanes that share an example.  The
-    // rows are read again by the K loop, from L2.  The maxima also go to blk_mx for the backward
-    // kernels (one CTA per example tile writes them).
-    const uint32_t kk0 = rc_kk(tid, 0);
+    // Per-example maximum of the block's child values over all K children.  The child rows for
+    // the tile's examples (512 bytes each, prime and sub) come in by bulk copies, 96 children per
+    // batch, into two buffers carved from the operand stages (idle before the K loop): slot c of
+    // 1 KB = [prime row | sub row].  Thread (example e, part q) scans its share of a batch's slots;
+    // batch j + 2 is requested as soon as batch j has been read.  The K loop reads the rows again,
+    // from L2.  The maxima also go to blk_mx for the backward kernels (one CTA per example tile).
+    constexpr uint32_t NQ = NPROD / 128, BATCH = 96, PER_Q = BATCH / NQ;
     const bool has_sub = k.d0 != PCB_NONE;
-#pragma unroll
-    for (uint32_t g = 0; g < RG; ++g) {
-      const uint32_t row = rc_row(tid, g), b = m0 + row;
-      const bool bok = b < ld;
-      const float* pc = a.mars + (size_t)(k.c0 + kk0) * ld + (bok ? b : 0u);
-      const float* pd = a.mars + (size_t)((has_sub ? k.d0 : k.c0) + kk0) * ld + (bok ? b : 0u);
-      float mx = -INFINITY;
-      for (uint32_t kc = 0; kc < k.K; kc += 64) {
-        float x[16];
-#pragma unroll
-        for (uint32_t q = 0; q < 16; ++q) {
-          const bool in = kc + 4 * q + kk0 < k.K;
-          x[q] = pc[(size_t)(in ? kc + 4 * q : 0u) * ld];
-        }
-        if (has_sub) {
-#pragma unroll
-          for (uint32_t q = 0; q < 16; ++q) {
-            const bool in = kc + 4 * q + kk0 < k.K;
-            x[q] += pd[(size_t)(in ? kc + 4 * q : 0u) * ld];
-          }
-        }
-#pragma unroll
-        for (uint32_t q = 0; q < 16; ++q) mx = fmaxf(mx, kc + 4 * q + kk0 < k.K ? x[q] : -INFINITY);
+    const uint32_t ex = min(TM, ld - m0), rowb = ex * 4u, per = has_sub ? 2u : 1u;
+    const uint32_t nbatch = (k.K + BATCH - 1) / BATCH;
+    const uint32_t e = tid & 127u, q = tid >> 7;
+    float* part = reinterpret_cast<float*>(ctl + 1024);   // [NQ][128]
+    auto rows_of = [&](uint32_t j) { return min(BATCH, k.K - j * BATCH); };
+    auto issue_batch = [&](uint32_t j) {
+      if (tid < 2 * BATCH) {
+        const uint32_t c = tid % BATCH, which = tid / BATCH;
+        if (c < rows_of(j) && (which == 0u || has_sub))
+          bulk_g2s(smem + ((j & 1u) * BATCH + c) * 1024u + which * 512u,
+                   a.mars + (size_t)((which ? k.d0 : k.c0) + j * BATCH + c) * ld + m0, rowb, &ebar[j & 1u]);
       }
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-      if ((lane >> 3) == 0) {
-        mxs[row] = bok ? mx : -INFINITY;
-        if (bok && blockIdx.y == 0) a.blk_mx[(size_t)k.mx_row * ld + b] = mx;
+    };
+    if (tid == 0) {
+      mbar_arrive_expect_tx(&ebar[0], rows_of(0) * rowb * per);
+      if (nbatch > 1) mbar_arrive_expect_tx(&ebar[1], rows_of(1) * rowb * per);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");   // byte counts posted before the first copy
+    issue_batch(0);
+    if (nbatch > 1) issue_batch(1);
+    float mx = -INFINITY;
+    bool got = true;
+    for (uint32_t j = 0; j < nbatch; ++j) {
+      bool g1 = lane != 0 || mbar_wait(&ebar[j & 1u], (j >> 1) & 1u, a.status);
+      got = __all_sync(0xffffffffu, g1) && got;
+      const uint32_t nr = rows_of(j);
+      const float* base = reinterpret_cast<const float*>(smem + (j & 1u) * BATCH * 1024u) + e;
+      if (got && e < ex) {
+#pragma unroll 8
+        for (uint32_t c = q * PER_Q; c < min(nr, (q + 1) * PER_Q); ++c) {
+          float v = base[c * 256u];
+          if (has_sub) v += base[c * 256u + 128u];
+          mx = fmaxf(mx, v);
+        }
+      }
+      if (j + 2 < nbatch) {   // CTA-uniform
+        asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");   // the buffer has been read by everyone
+        if (tid == 0) mbar_arrive_expect_tx(&ebar[j & 1u], rows_of(j + 2) * rowb * per);
+        asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");
+        fence_proxy_async();
+        issue_batch(j + 2);
       }
     }
+    if (!got) *reinterpret_cast<volatile uint32_t*>(epi_fail) = 1u;
+    part[q * 128u + e] = mx;
+    asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");
+    if (tid < 128u) {
+#pragma unroll
+      for (uint32_t u = 1; u < NQ; ++u) mx = fmaxf(mx, part[u * 128u + tid]);
+      const bool bok = tid < ex;
+      mxs[tid] = bok ? mx : -INFINITY;
+      if (bok && blockIdx.y == 0) a.blk_mx[(size_t)k.mx_row * ld + m0 + tid] = mx;
+    }
+    fence_proxy_async();   // the K loop's copies and MMAs touch the same memory next
   }
   tc_fence_before();
   __syncthreads();
