@@ -331,6 +331,7 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
     const char* impl = getenv("PCB_DENSE_IMPL");
     c->use_tc = prop.major == 10 && !(impl && std::string(impl) == "simt");
     c->graph_enabled = !(getenv("PCB_NO_GRAPH") && atoi(getenv("PCB_NO_GRAPH")) != 0);
+    c->pdl = !(getenv("PCB_NO_PDL") && atoi(getenv("PCB_NO_PDL")) != 0);
     if (c->use_tc) PCB_TRY(pcb_dense_tc_prepare(c, &bytes));
   }
   c->device_bytes = bytes;

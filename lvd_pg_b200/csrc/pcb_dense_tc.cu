@@ -380,6 +380,7 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
   float* mxs = reinterpret_cast<float*>(ctl + 128);           // [128]
 
   if (a.trace && threadIdx.x == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[504] = gtime();
+  pcb_grid_dep_launch();
   const PcbDenseBlock k = a.blocks[blockIdx.z];
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t ld = a.ld;
@@ -429,6 +430,9 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // Up to here only static circuit data was read: a launch with programmatic stream serialization
+  // may have come this far while the previous kernel of the stream was still running.
+  pcb_grid_dep_wait();
   if (MODE == MODE_BWD_CHILD && tid < 128) mxs[tid] = (m0 + tid < ld) ? mxrow[m0 + tid] : -INFINITY;
   if (MODE == MODE_FWD && warp < MMA_WARP) {
     // Per-example maximum of the block's child values over all K children.  The child rows for
@@ -536,27 +540,12 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
       if (tr) a.trace[i * 8 + 3] = gtime();
       return true;
     };
-    // BWD_CHILD: the epilogue reads the children's value rows (prime and sub) for this tile's 128
-    // examples: 2 x 256 rows x 512 bytes.  Each producer thread asks L2 for four of those lines
-    // while the K loop runs, so the epilogue's loads do not start from DRAM latency.
-    auto prefetch_children = [&](uint32_t j) {
-      if (MODE != MODE_BWD_CHILD) return;
-      const uint32_t lid = tid + NPROD * j;            // 2048 lines: (prime | sub) x 256 rows x 4 segments
-      const uint32_t row = (lid >> 2) & 255u, seg = lid & 3u;
-      const bool sub = lid >= 1024u;
-      if (row < n_count && m0 + seg * 32u < ld && (!sub || k.d0 != PCB_NONE))
-        prefetch_l2(a.mars + (size_t)((sub ? k.d0 : k.c0) + n0 + row) * ld + m0 + seg * 32u);
-    };
     load_chunk<MODE>(ctx, inv, 0, ra0);
     for (uint32_t i = 0; i < nchunks && ok; i += 2) {
       if (i + 1 < nchunks) load_chunk<MODE>(ctx, inv, i + 1, ra1);
-      const bool pf = i + 4 == nchunks || i + 5 == nchunks || (nchunks < 4 && i == 0);
-      constexpr uint32_t NPF = 2048 / NPROD;   // lines per thread
-      if (pf) for (uint32_t j = 0; j < NPF / 2; ++j) prefetch_children(j);
       ok = process(i, ra0);
       if (!ok || i + 1 >= nchunks) break;
       if (i + 2 < nchunks) load_chunk<MODE>(ctx, inv, i + 2, ra0);
-      if (pf) for (uint32_t j = NPF / 2; j < NPF; ++j) prefetch_children(j);
       ok = process(i + 1, ra1);
     }
 
@@ -748,13 +737,13 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
 }
 
 template <int MODE>
-int32_t launch(dim3 grid, const TcArgs& args, cudaStream_t st) {
+int32_t launch(dim3 grid, const TcArgs& args, cudaStream_t st, bool pdl = false) {
   static bool configured = false;
   if (!configured) {
     PCB_CUDA(cudaFuncSetAttribute(dense_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     configured = true;
   }
-  dense_tc_kernel<MODE><<<grid, NTHREADS, SMEM_BYTES, st>>>(args);
+  PCB_CUDA(pcb_launch_pdl(dense_tc_kernel<MODE>, grid, dim3(NTHREADS), SMEM_BYTES, st, pdl, args));
   return PCB_OK;
 }
 
@@ -843,7 +832,7 @@ int32_t pcb_dense_tc_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, 
   args.nsplit = pick_nsplit(bt * ct * (o1 - o0), c->max_dense_R);
   dim3 grid(bt, ct * args.nsplit, o1 - o0);
   PcbProfScope ps(c, st, PCB_K_DENSE_FWD);
-  return launch<MODE_FWD>(grid, args, st);
+  return launch<MODE_FWD>(grid, args, st, c->pdl);
 }
 
 // Launches the edge-statistics kernel over the pending block range [edge_lo, edge_hi).
@@ -900,7 +889,7 @@ int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer,
     args.nsplit = pick_nsplit(bt * ct * (o1 - o0), c->max_dense_K);
     dim3 grid(bt, ct * args.nsplit, o1 - o0);
     PcbProfScope ps(c, st, PCB_K_DENSE_BWD_CHILD);
-    PCB_TRY(launch<MODE_BWD_CHILD>(grid, args, st));
+    PCB_TRY(launch<MODE_BWD_CHILD>(grid, args, st, c->pdl));
   }
   return PCB_OK;
 }

@@ -43,10 +43,12 @@ __global__ void sparse_up_kernel(float* __restrict__ mars, uint32_t ld, uint32_t
                                  const uint32_t* __restrict__ n_estart, const uint32_t* __restrict__ n_ecount,
                                  const uint32_t* __restrict__ n_pid0, const uint32_t* __restrict__ e_prime,
                                  const uint32_t* __restrict__ e_sub, const float* __restrict__ theta) {
+  pcb_grid_dep_launch();
   uint32_t n = nodes[blockIdx.x];
   uint32_t b = blockIdx.y * blockDim.x + threadIdx.x;
   if (b >= B) return;
   uint32_t e0 = n_estart[n], cnt = n_ecount[n];
+  pcb_grid_dep_wait();   // everything above is static circuit data
   float out;
   if (kind[n] == PCB_SUM) {
     const float* w = theta + n_pid0[n];
@@ -89,11 +91,13 @@ __global__ void sparse_down_kernel(float* __restrict__ flows, const float* __res
                                    uint32_t B, const uint32_t* __restrict__ nodes, uint32_t root,
                                    const uint32_t* __restrict__ in_off, const PcbInEntry* __restrict__ in_ent,
                                    const float* __restrict__ theta, float* __restrict__ aggr) {
+  pcb_grid_dep_launch();
   uint32_t n = nodes[blockIdx.x];
   uint32_t b = blockIdx.y * blockDim.x + threadIdx.x;
   bool active = b < B;
   uint32_t bb = active ? b : 0;
   uint32_t i0 = in_off[n], i1 = in_off[n + 1];
+  pcb_grid_dep_wait();   // everything above is static circuit data
   float acc = (i0 == i1 && n == root) ? 1.0f : 0.0f;
   float my = mars[(size_t)n * ld + bb];
   for (uint32_t i = i0; i < i1; ++i) {
@@ -371,7 +375,7 @@ extern "C" int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   for (uint32_t lay = 1; lay <= c->L; ++lay) {
     uint32_t o0 = c->h_up_sparse_off[lay - 1], o1 = c->h_up_sparse_off[lay];
     if (o1 > o0)
-      { PcbProfScope ps(c, st, PCB_K_SPARSE_UP); sparse_up_kernel<<<grid2(o1 - o0, B), TPB, 0, st>>>(ws->mars, ws->ld, B, c->up_sparse + o0, c->kind,
+      { PcbProfScope ps(c, st, PCB_K_SPARSE_UP); pcb_launch_pdl(sparse_up_kernel, grid2(o1 - o0, B), dim3(TPB), 0, st, c->pdl, ws->mars, ws->ld, B, c->up_sparse + o0, c->kind,
                                                           c->n_estart, c->n_ecount, c->n_pid0, c->e_prime,
                                                           c->e_sub, c->theta); }
     PCB_TRY(pcb_dense_forward(c, ws, lay, st));
@@ -395,7 +399,7 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
   for (int64_t lay = c->L; lay >= 0; --lay) {
     uint32_t o0 = c->h_down_sparse_off[lay], o1 = c->h_down_sparse_off[lay + 1];
     if (o1 > o0)
-      { PcbProfScope ps(c, st, PCB_K_SPARSE_DOWN); sparse_down_kernel<<<grid2(o1 - o0, B), TPB, 0, st>>>(ws->flows, ws->mars, ws->ld, B, c->down_sparse + o0,
+      { PcbProfScope ps(c, st, PCB_K_SPARSE_DOWN); pcb_launch_pdl(sparse_down_kernel, grid2(o1 - o0, B), dim3(TPB), 0, st, c->pdl, ws->flows, ws->mars, ws->ld, B, c->down_sparse + o0,
                                                             c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr); }
     if (lay >= 1) PCB_TRY(pcb_dense_backward(c, ws, (uint32_t)lay, st));
   }

@@ -145,6 +145,7 @@ struct pcb_circuit {
   cudaStream_t gstream = nullptr;   // stands in for the legacy default stream, which cannot be captured
   cudaEvent_t ev_g0 = nullptr, ev_g1 = nullptr;
   bool graph_enabled = true;
+  bool pdl = true;   // chain kernels are launched with programmatic stream serialization
   // dense blocks [edge_lo, edge_hi) whose edge statistics are still to be launched, and the number
   // of tiles at which the range is launched
   uint32_t edge_lo = 0, edge_hi = 0, edge_batch_tiles = 592;
@@ -231,6 +232,26 @@ struct PcbProfScope {
   }
   ~PcbProfScope() { if (e1) cudaEventRecord(e1, st); }
 };
+
+// Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor
+// in the stream is still running, so its set-up (barrier initialisation, tensor-memory allocation)
+// overlaps the predecessor's tail.  Such a kernel executes pcb_grid_dep_wait() before it touches
+// global memory that an earlier kernel writes or reads, and pcb_grid_dep_launch() on entry.
+template <typename... KArgs, typename... Args>
+inline cudaError_t pcb_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  bool pdl, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1u : 0u;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pcb_grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pcb_grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 // entry points implemented across translation units and used by pcb_em_step
 int32_t pcb_allreduce_aggr(pcb_circuit* c, cudaStream_t st);
