@@ -555,7 +555,7 @@ extern "C" int32_t pcb_get_sum_regions(pcb_circuit* c, uint32_t* out, uint64_t n
 // ---- launch counters and per-class event timing ----------------------------------------------
 static const char* kClassNames[PCB_K_COUNT] = {"leaf_forward", "sparse_up", "dense_fwd", "sparse_down",
                                                "dense_bwd_child", "dense_bwd_edge", "leaf_flow", "em_update",
-                                               "misc", "allreduce", "dense_max", "w_image"};
+                                               "misc", "allreduce", "dense_max", "w_image", "kld_adam", "sampling"};
 extern "C" int32_t pcb_profile_num_classes(void) { return PCB_K_COUNT; }
 extern "C" const char* pcb_profile_class_name(int32_t i) { return (i >= 0 && i < PCB_K_COUNT) ? kClassNames[i] : ""; }
 extern "C" int32_t pcb_profile_enable(pcb_circuit* c, int32_t on) {

@@ -852,7 +852,7 @@ int32_t pcb_dense_tc_flush_edges(pcb_circuit* c, pcb_workspace* ws, cudaStream_t
   slices = (ws->B + b_per - 1) / b_per;
   args.b_per_cta = b_per;
   cudaStream_t es = st;
-  if (c->side) {
+  if (c->side && !c->prof.on) {   // per-class timing wants every class alone on the GPU
     PCB_CUDA(cudaEventRecord(c->ev_fork, st));
     PCB_CUDA(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
     es = c->side;

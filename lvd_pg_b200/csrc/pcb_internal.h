@@ -59,7 +59,7 @@ struct PcbInEntry {
 enum PcbKernelClass {
   PCB_K_LEAF_FWD = 0, PCB_K_SPARSE_UP, PCB_K_DENSE_FWD, PCB_K_SPARSE_DOWN, PCB_K_DENSE_BWD_CHILD,
   PCB_K_DENSE_BWD_EDGE, PCB_K_LEAF_FLOW, PCB_K_UPDATE, PCB_K_MISC, PCB_K_ALLREDUCE, PCB_K_DENSE_MAX,
-  PCB_K_W_IMAGE, PCB_K_COUNT
+  PCB_K_W_IMAGE, PCB_K_KLD, PCB_K_SAMPLE, PCB_K_COUNT
 };
 struct PcbProfEvent { int cls; cudaEvent_t e0, e1; };
 struct PcbProf {

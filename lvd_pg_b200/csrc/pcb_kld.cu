@@ -226,6 +226,7 @@ extern "C" int32_t pcb_kld(pcb_circuit* c, pcb_workspace* ws, const float* param
   const uint32_t ld = ws->ldS;
   if (c->n_inputs) {
     Shape2 sh = shape_for(S, c->n_inputs);
+    ++c->prof.launches[PCB_K_KLD];
     kld_leaf_kernel<<<sh.grid, sh.block, 0, st>>>(ws->klds, ld, S, params1_dev, params2_dev, c->n_inputs, c->P,
                                                   c->in_node, c->in_cats, c->in_poff);
   }
@@ -233,11 +234,12 @@ extern "C" int32_t pcb_kld(pcb_circuit* c, pcb_workspace* ws, const float* param
     uint32_t o0 = c->h_up_all_off[lay - 1], o1 = c->h_up_all_off[lay];
     if (o1 == o0) continue;
     Shape2 sh = shape_for(S, o1 - o0);
+    ++c->prof.launches[PCB_K_KLD];
     kld_up_kernel<<<sh.grid, sh.block, 0, st>>>(ws->klds, ld, S, params1_dev, params2_dev, c->up_all + o0, o1 - o0,
                                                 c->kind, c->n_estart, c->n_ecount, c->n_pid0, c->e_prime, c->e_sub);
   }
   if (kld_out_dev)
-    copy_root_kernel<<<(S + 127) / 128, 128, 0, st>>>(ws->klds + (size_t)(c->N - 1) * ld, S, kld_out_dev);
+    ++c->prof.launches[PCB_K_KLD], copy_root_kernel<<<(S + 127) / 128, 128, 0, st>>>(ws->klds + (size_t)(c->N - 1) * ld, S, kld_out_dev);
   PCB_CUDA(cudaGetLastError());
   ws->have_kld = true;
   ws->kld_S = S;
@@ -258,12 +260,14 @@ extern "C" int32_t pcb_kld_backward(pcb_circuit* c, pcb_workspace* ws, const flo
     uint32_t o0 = c->h_down_all_off[lay], o1 = c->h_down_all_off[lay + 1];
     if (o1 == o0) continue;
     Shape2 sh = shape_for(S, o1 - o0);
+    ++c->prof.launches[PCB_K_KLD];
     kld_down_kernel<<<sh.grid, sh.block, 0, st>>>(ws->grads, ws->klds, ld, S, params1_dev, params2_dev,
                                                   c->down_all + o0, o1 - o0, c->N - 1, c->in_off, c->in_ent,
                                                   grads1_dev, grads2_dev);
   }
   if (c->n_inputs) {
     Shape2 sh = shape_for(S, c->n_inputs);
+    ++c->prof.launches[PCB_K_KLD];
     kld_leaf_grad_kernel<<<sh.grid, sh.block, 0, st>>>(ws->grads, ld, S, params1_dev, params2_dev, c->n_inputs, c->P,
                                                        c->in_node, c->in_cats, c->in_poff, grads1_dev, grads2_dev);
   }
@@ -291,6 +295,7 @@ extern "C" int32_t pcb_kld_edge_klds(pcb_circuit* c, pcb_workspace* ws, const fl
   uint32_t total = c->h_up_all_off[c->L];
   if (total) {
     Shape2 sh = shape_for(S, total);
+    ++c->prof.launches[PCB_K_KLD];
     kld_edge_kernel<<<sh.grid, sh.block, 0, st>>>(ws->klds, ws->ldS, S, params1_dev, params2_dev, c->up_all, total,
                                                   c->kind, c->n_estart, c->n_ecount, c->n_pid0, c->e_prime, c->e_sub,
                                                   edge_klds_dev);
@@ -308,8 +313,10 @@ extern "C" int32_t pcb_adam_step(pcb_circuit* c, float* theta_dev, const float* 
   float c1 = 1.0f - powf(beta1, (float)t), c2 = 1.0f - powf(beta2, (float)t);
   if (c->P) {
     uint32_t blocks = (uint32_t)std::min<uint64_t>((c->P + 255) / 256, 148 * 16);
+    ++c->prof.launches[PCB_K_KLD];
     adam_kernel<<<blocks, 256, 0, st>>>(theta_dev, grad_dev, m_dev, v_dev, c->P, lr, beta1, beta2, eps, c1, c2, sign);
     uint32_t warps = c->n_groups + c->n_inputs;
+    ++c->prof.launches[PCB_K_KLD];
     renorm_kernel<<<(warps + 7) / 8, 256, 0, st>>>(theta_dev, c->n_groups, c->grp_node, c->n_pid0, c->n_ecount,
                                                    c->n_inputs, c->P, c->in_cats, c->in_poff);
   }

@@ -212,6 +212,7 @@ extern "C" int32_t pcb_sample_hard(pcb_circuit* c, pcb_workspace* ws, const floa
   int32_t* status = reinterpret_cast<int32_t*>(ws->cum);  // scratch word
   PCB_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
   uint32_t warps_per_block = 4;
+  ++c->prof.launches[PCB_K_SAMPLE];
   sample_hard_kernel<<<(S + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, st>>>(
       S, params_dev, Sp, u_sum_dev, u_leaf_dev, c->n_regions, c->max_group, c->max_cats, c->V, c->N, c->kind,
       c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime, c->e_sub, c->node2input, c->in_var, c->in_cats,
@@ -242,6 +243,7 @@ extern "C" int32_t pcb_sample_soft(pcb_circuit* c, pcb_workspace* ws, const floa
   PCB_CUDA(cudaMemsetAsync(out_dev, 0, (size_t)S * c->V * c->max_cats * sizeof(float), st));
   if (c->n_groups) {
     Shape2 sh = shape_for(S, c->n_groups);
+    ++c->prof.launches[PCB_K_SAMPLE];
     soft_params_kernel<<<sh.grid, sh.block, 0, st>>>(ws->eprob, cum, ld, S, params_dev, Sp, u_dev, temperature,
                                                      c->grp_node, c->n_groups, c->n_pid0, c->n_ecount);
   }
@@ -249,11 +251,13 @@ extern "C" int32_t pcb_sample_soft(pcb_circuit* c, pcb_workspace* ws, const floa
     uint32_t o0 = c->h_down_all_off[lay], o1 = c->h_down_all_off[lay + 1];
     if (o1 == o0) continue;
     Shape2 sh = shape_for(S, o1 - o0);
+    ++c->prof.launches[PCB_K_SAMPLE];
     soft_down_kernel<<<sh.grid, sh.block, 0, st>>>(td, ld, S, ws->eprob, cum, c->down_all + o0, o1 - o0, c->N - 1,
                                                    c->in_off, c->in_ent);
   }
   if (c->n_inputs) {
     Shape2 sh = shape_for(S, c->n_inputs);
+    ++c->prof.launches[PCB_K_SAMPLE];
     soft_leaf_kernel<<<sh.grid, sh.block, 0, st>>>(td, ld, S, params_dev, Sp, c->n_inputs, c->V, c->in_node, c->in_var,
                                                    c->in_cats, c->in_poff, c->P, c->theta, out_dev);
   }
@@ -317,6 +321,7 @@ extern "C" int32_t pcb_sample_hard_static(pcb_circuit* c, const float* params_de
   int32_t* status = reinterpret_cast<int32_t*>(scratch + PCB_STATIC_SAMPLE_WORDS);
   PCB_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
   const uint32_t warps_per_block = 4;
+  ++c->prof.launches[PCB_K_SAMPLE];
   sample_hard_kernel<<<(S + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, st>>>(
       S, params_dev, Sp, u_sum_dev, u_leaf_dev, c->n_regions, c->max_group, c->max_cats, c->V, c->N, c->kind,
       c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime, c->e_sub, c->node2input, c->in_var, c->in_cats,
