@@ -121,7 +121,7 @@ def algorithmic_work(fc, info, B):
 # DRAM bytes per dense block (256 parents x 256 children) at 2048 examples, dram__bytes_read.sum +
 # dram__bytes_write.sum of one ncu capture of the largest launches of the 384-variable cut of the
 # workload (profiles/dense_tc_kernels_cfg5s.md); traffic grows in proportion to blocks x examples.
-NCU_DRAM_BYTES_PER_BLOCK = {"dense_bwd_edge": 594.2e6 / 55, "dense_bwd_child": 719.0e6 / 55, "dense_fwd": 345.0e6 / 55}
+NCU_DRAM_BYTES_PER_BLOCK = {"dense_bwd_edge": 2444.6e6 / 287, "dense_bwd_child": 690.4e6 / 55, "dense_fwd": 345.6e6 / 55}
 
 
 def measured_traffic(kernel_class, info, B, launches_per_step):
@@ -244,6 +244,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="strong: the config's global batch is split over the GPUs (config 5 as stated); "
+                         "weak: every GPU takes the config's batch")
     args = ap.parse_args()
     if args.config == "cfg4":
         if int(os.environ.get("RANK", "0")) == 0:
@@ -253,7 +256,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    Bg = cfg["batch"]
+    Bg = cfg["batch"] * (int(os.environ.get("WORLD_SIZE", "1")) if args.scaling == "weak" else 1)
 
     if args.impl == "reference":
         # The reference has no CPU implementation of this path and Julia is not installed: the
@@ -419,7 +422,7 @@ def main():
         n_edges = fc.num_edges
         line = {"metric": "samples/sec fwd+bwd+EM", "value": value, "unit": "samples/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-                "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": cfg["desc"], "bench_config": args.config, "global_batch": Bg,
                            "parallelism": f"dp{world}", "l2": "inputs (mars+flows) larger than L2" if
                            fc.num_nodes * B * 8 > 126e6 else "working set below L2",
