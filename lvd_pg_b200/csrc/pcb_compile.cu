@@ -322,6 +322,15 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
     PCB_TRY(upload(&c->lchunk_var, lvar, &bytes));
     PCB_TRY(upload(&c->lchunk_off, loff, &bytes));
     PCB_TRY(upload(&c->lchunk_inputs, order, &bytes));
+    std::vector<uint32_t> gvar, goff;
+    for (uint32_t i = 0; i < NI; ++i) {
+      bool cut = i == 0 || in_var[order[i]] != in_var[order[i - 1]] || (i - goff.back()) >= PCB_LEAF_GROUP;
+      if (cut) { gvar.push_back(in_var[order[i]]); goff.push_back(i); }
+    }
+    goff.push_back(NI);
+    c->n_lgrps = (uint32_t)gvar.size();
+    PCB_TRY(upload(&c->lgrp_var, gvar, &bytes));
+    PCB_TRY(upload(&c->lgrp_off, goff, &bytes));
   }
   PCB_CUDA(cudaMalloc((void**)&c->status, sizeof(int)));
   PCB_CUDA(cudaMemset(c->status, 0, sizeof(int)));
@@ -354,7 +363,8 @@ void free_circuit(pcb_circuit* c) {
   void* ptrs[] = {c->theta, c->aggr, c->kind, c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime,
                   c->e_sub, c->in_node, c->in_var, c->in_cats, c->in_poff, c->in_foff, c->node2input,
                   c->up_all, c->up_sparse, c->down_all, c->down_sparse, c->in_off, c->in_ent, c->dense,
-                  c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status, c->w_img, c->dense_img};
+                  c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status, c->w_img, c->dense_img,
+                  c->lgrp_var, c->lgrp_off};
   for (void* p : ptrs) if (p) cudaFree(p);
   if (c->ev_g0) cudaEventDestroy(c->ev_g0);
   if (c->ev_g1) cudaEventDestroy(c->ev_g1);

@@ -21,6 +21,7 @@
 #include <cstring>
 
 #include "pcb_internal.h"
+#include "pcb_tc.cuh"
 
 namespace {
 
@@ -271,6 +272,114 @@ __global__ void __launch_bounds__(LTH) leaf_flow_chunk_kernel(
   }
 }
 
+// Leaf statistics without atomics on the histogram: the examples of the block's slice are sorted
+// by the variable's value once (counting sort in shared memory: `perm` lists the examples value by
+// value, `binoff` delimits each value's segment), then every leaf row of the group streams through
+// a three-deep ring of shared-memory buffers (one bulk copy per row) and thread x sums its
+// segment  sum_j row[perm[j]]  and adds it to slot x of the leaf.  A missing value sorts into the
+// extra segment C.  The group's leaves share one variable, so one sort serves up to 64 rows.
+constexpr int LSB = 2048;   // examples per block slice
+constexpr int LST = 256;    // threads; also the number of value segments a pass of the block covers
+constexpr int LSR = 3;      // row buffers
+constexpr int LSC = 508;    // most categories of a variable (static + dynamic shared memory stay under 48 KB)
+__global__ void __launch_bounds__(LST) leaf_flow_sorted_kernel(
+    const float* __restrict__ flows, uint32_t ld, uint32_t B, float* __restrict__ aggr,
+    const uint32_t* __restrict__ in_node, const uint32_t* __restrict__ in_cats, const uint64_t* __restrict__ in_foff,
+    const uint32_t* __restrict__ lgrp_var, const uint32_t* __restrict__ lgrp_off,
+    const uint32_t* __restrict__ linputs, uint32_t max_cats, const uint8_t* __restrict__ data,
+    const uint8_t* __restrict__ miss, uint64_t num_rows, const int32_t* __restrict__ row_ids, uint32_t row_start,
+    const float* __restrict__ weights, int* __restrict__ status) {
+  __shared__ __align__(128) float rowbuf[LSR][LSB];
+  __shared__ uint16_t xs[LSB];
+  __shared__ uint16_t perm[LSB];
+  __shared__ uint32_t binoff[LSC + 4];   // segment starts and the end
+  __shared__ uint32_t cursor[LSC + 4];
+  __shared__ __align__(8) uint64_t bar[LSR];
+  extern __shared__ float wsm[];          // [LSB] example weights, only when weights are given
+  const uint32_t grp = blockIdx.x, b0 = blockIdx.y * LSB, tid = threadIdx.x;
+  const uint32_t nb = min((uint32_t)LSB, B - b0);
+  const uint32_t l0 = lgrp_off[grp], nl = lgrp_off[grp + 1] - l0;
+  // segments: values 0 .. max_cats (a value equal to a leaf's category count lands in that leaf's
+  // extra slot, larger ones are dropped, as in the atomic kernel), then the missing-value segment
+  const uint32_t miss_bin = max_cats + 1, nbins = max_cats + 2;
+  if (tid == 0) {
+    for (int r = 0; r < LSR; ++r) pcbtc::mbar_init(&bar[r], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (uint32_t x = tid; x <= nbins; x += LST) { binoff[x] = 0; }
+  stage_values(xs, b0, nb, lgrp_var[grp], data, miss, num_rows, row_ids, row_start);
+  if (weights) for (uint32_t b = tid; b < nb; b += LST) wsm[b] = weights[data_row(row_ids, row_start, b0 + b)];
+  __syncthreads();
+  // rows are requested as early as possible: the sort below hides their latency
+  const uint32_t rowbytes = ((nb + 3u) & ~3u) * 4u;   // the pitch is a multiple of 32 floats: stays inside the row
+  auto request = [&](uint32_t l) {
+    const uint32_t i = linputs[l0 + l];
+    pcbtc::mbar_arrive_expect_tx(&bar[l % LSR], rowbytes);
+    pcbtc::bulk_g2s(rowbuf[l % LSR], flows + (size_t)in_node[i] * ld + b0, rowbytes, &bar[l % LSR]);
+  };
+  if (tid == 0) for (uint32_t l = 0; l < min(nl, (uint32_t)LSR); ++l) request(l);
+  // counting sort of the examples by value
+  for (uint32_t b = tid; b < nb; b += LST) {
+    const uint32_t x = xs[b] == 0xffff ? miss_bin : (uint32_t)xs[b];
+    if (x <= miss_bin) atomicAdd(&binoff[x + 1], 1u);
+  }
+  __syncthreads();
+  if (tid < 32) {   // inclusive scan of the counts, one warp
+    uint32_t carry = 0;
+    for (uint32_t base = 0; base <= nbins; base += 32) {
+      const uint32_t idx = base + tid;
+      uint32_t v = idx <= nbins ? binoff[idx] : 0u;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t u = __shfl_up_sync(0xffffffffu, v, d);
+        if ((int)tid >= d) v += u;
+      }
+      v += carry;
+      if (idx <= nbins) binoff[idx] = v;
+      carry = __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+  for (uint32_t x = tid; x < nbins; x += LST) cursor[x] = binoff[x];
+  __syncthreads();
+  for (uint32_t b = tid; b < nb; b += LST) {
+    const uint32_t x = xs[b] == 0xffff ? miss_bin : (uint32_t)xs[b];
+    if (x <= miss_bin) perm[atomicAdd(&cursor[x], 1u)] = (uint16_t)b;
+  }
+  __syncthreads();
+  const bool whole = gridDim.y == 1;
+  bool ok = true;
+  for (uint32_t l = 0; l < nl; ++l) {
+    const uint32_t i = linputs[l0 + l];
+    const uint64_t fo = in_foff[i];
+    const uint32_t C = in_cats[i];
+    ok = ok && pcbtc::mbar_wait(&bar[l % LSR], (l / LSR) & 1u, status);
+    const float* row = rowbuf[l % LSR];
+    if (ok && fo != ~0ull) {
+      for (uint32_t x = tid; x < nbins; x += LST) {
+        // leaf slot: value x <= C -> x, missing -> C; values beyond the leaf's categories are dropped
+        const uint32_t slot = x == miss_bin ? C : x;
+        if (slot > C) continue;
+        float acc = 0.0f;
+        const uint32_t j1 = binoff[x + 1];
+        if (weights) for (uint32_t j = binoff[x]; j < j1; ++j) acc += row[perm[j]] * wsm[perm[j]];
+        else         for (uint32_t j = binoff[x]; j < j1; ++j) acc += row[perm[j]];
+        if (acc != 0.0f) {
+          if (whole) aggr[fo + slot] += acc; else atomicAdd(aggr + fo + slot, acc);
+        }
+      }
+    }
+    __syncthreads();   // the buffer has been read by everyone
+    if (tid == 0 && ok && l + LSR < nl) {
+      pcbtc::fence_proxy_async();
+      request(l + LSR);
+    }
+  }
+  if (!ok && tid == 0) {   // a wait was lost: let the copies in flight land before the block ends
+    for (int r = 0; r < LSR; ++r) pcbtc::mbar_wait(&bar[r], 0, status);
+  }
+}
+
 __global__ void scale_kernel(float* __restrict__ x, uint64_t n, float rate) {
   uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
@@ -406,7 +515,17 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
   if (c->use_tc) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
   if (c->n_inputs) {
     PcbProfScope ps(c, st, PCB_K_LEAF_FLOW);
-    if (c->max_cats <= 1024) {
+    // sorted segments pay off once a variable has enough values to keep a block's threads busy;
+    // PCB_LEAF_FLOW_IMPL=atomic / sorted forces one of the two kernels
+    const char* impl = getenv("PCB_LEAF_FLOW_IMPL");
+    const bool want_sorted = impl ? !strcmp(impl, "sorted") : c->max_cats >= 16;
+    if (c->max_cats <= LSC && want_sorted) {
+      dim3 grid(c->n_lgrps, (B + LSB - 1) / LSB);
+      leaf_flow_sorted_kernel<<<grid, LST, weights_dev ? LSB * sizeof(float) : 0, st>>>(
+          ws->flows, ws->ld, B, c->aggr, c->in_node, c->in_cats, c->in_foff, c->lgrp_var, c->lgrp_off,
+          c->lchunk_inputs, c->max_cats, ws->data, ws->miss, ws->num_rows, ws->row_ids, ws->row_start, weights_dev,
+          c->status);
+    } else if (c->max_cats <= 1024) {
       uint32_t hstride = c->max_cats + 1;
       dim3 grid(c->n_lchunks, (B + LBT - 1) / LBT);
       leaf_flow_chunk_kernel<<<grid, LTH, PCB_LEAF_CHUNK * hstride * sizeof(float), st>>>(

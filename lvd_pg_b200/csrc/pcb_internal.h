@@ -27,6 +27,7 @@
 
 #define PCB_NONE 0xffffffffu
 #define PCB_LEAF_CHUNK 8
+#define PCB_LEAF_GROUP 64
 
 struct PcbDenseBlock {
   uint32_t p0;    // first parent node
@@ -104,6 +105,10 @@ struct pcb_circuit {
   uint32_t* lchunk_off = nullptr;   // [n_lchunks + 1] range into lchunk_inputs
   uint32_t* lchunk_inputs = nullptr; // [n_inputs] input indices sorted by variable
   uint32_t n_lchunks = 0;
+  // the same order cut into groups of at most PCB_LEAF_GROUP leaves of one variable (leaf statistics)
+  uint32_t* lgrp_var = nullptr;
+  uint32_t* lgrp_off = nullptr;
+  uint32_t n_lgrps = 0;
   // layer lists: all inner nodes by layer / only those outside dense blocks
   uint32_t* up_all = nullptr;     // [n_inner_nodes]
   uint32_t* up_sparse = nullptr;

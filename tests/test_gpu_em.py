@@ -119,6 +119,30 @@ def test_em_steps_track_oracle_with_row_ids(oracle):
         assert np.abs(np.exp(p) - np.exp(p_ref)).max() <= TOL
 
 
+@pytest.mark.parametrize("impl", ["atomic", "sorted"])
+@pytest.mark.parametrize("cats,rows,missing", [(3, 77, 0.3), (40, 300, 0.0), (256, 2500, 0.1)])
+def test_leaf_statistics_kernels_agree_with_oracle(oracle, monkeypatch, impl, cats, rows, missing):
+    """Both leaf-statistics kernels (shared-memory histogram with atomics, sorted segments) against the
+    oracle: few and many categories, missing values, more rows than one block slice, example weights."""
+    torch, api = _cuda()
+    monkeypatch.setenv("PCB_LEAF_FLOW_IMPL", impl)
+    fc = random_hclt(5, 16, cats, 21)
+    data, miss = random_data(rows, fc.num_vars, cats, 4, missing)
+    w = np.random.default_rng(8).uniform(0.5, 1.5, rows).astype(np.float32)
+    for weights in (None, w):
+        m = api.CuMetaBitsProbCircuit(fc.copy())
+        dd = api.DeviceData(data, m.device, miss)
+        ws, B = api.forward(m, dd)
+        api.backward(m, ws, None if weights is None else torch.from_numpy(weights).to(m.device))
+        heap = m.heap()
+        ref = fc.copy()
+        mars = oracle.forward(ref, data, miss=miss)
+        flows, _ = oracle.backward(ref, mars)
+        oracle.input_flows(ref, flows, data, miss=miss, weights=weights)
+        scale = max(1e-6, float(np.abs(ref.heap).max()))
+        assert np.abs(heap - ref.heap).max() <= TOL * scale
+
+
 def test_params_roundtrip_and_errors(oracle):
     torch, api = _cuda()
     from lvd_pg_b200._lib import PcbError
