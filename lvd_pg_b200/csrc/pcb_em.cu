@@ -37,8 +37,19 @@ __device__ __forceinline__ int64_t data_row(const int32_t* row_ids, uint32_t row
   return row_ids ? (int64_t)row_ids[b] - 1 : (int64_t)row_start - 1 + b;
 }
 
-// One thread per (example, node).  Sum nodes: two passes over the children (max, then
-// sum of exp), which needs one exp per edge instead of the exp+log of a binary fold.
+// One thread per (node, four consecutive examples): every row access is a 16-byte load, so a warp
+// keeps 512 bytes per request in flight (the chain node -> edge list -> child row is four dependent
+// loads deep; with one example per thread it ran at a third of the memory roof).  Sum nodes: two
+// passes over the children (max, then sum of exp), one exp per edge instead of the exp + log of a
+// binary fold.  The last thread of a row may cover padding examples: the row pitch is a multiple
+// of 32, and whatever lands in the padding is never read as a result.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float4 adds4(float4 a, float s) { return make_float4(a.x + s, a.y + s, a.z + s, a.w + s); }
+__device__ __forceinline__ float4 max4(float4 a, float4 b) {
+  return make_float4(fmaxf(a.x, b.x), fmaxf(a.y, b.y), fmaxf(a.z, b.z), fmaxf(a.w, b.w));
+}
+
 __global__ void sparse_up_kernel(float* __restrict__ mars, uint32_t ld, uint32_t B,
                                  const uint32_t* __restrict__ nodes, const uint8_t* __restrict__ kind,
                                  const uint32_t* __restrict__ n_estart, const uint32_t* __restrict__ n_ecount,
@@ -46,43 +57,36 @@ __global__ void sparse_up_kernel(float* __restrict__ mars, uint32_t ld, uint32_t
                                  const uint32_t* __restrict__ e_sub, const float* __restrict__ theta) {
   pcb_grid_dep_launch();
   uint32_t n = nodes[blockIdx.x];
-  uint32_t b = blockIdx.y * blockDim.x + threadIdx.x;
+  uint32_t b = (blockIdx.y * blockDim.x + threadIdx.x) * 4u;
   if (b >= B) return;
   uint32_t e0 = n_estart[n], cnt = n_ecount[n];
   pcb_grid_dep_wait();   // everything above is static circuit data
-  float out;
+  auto child = [&](uint32_t j) {
+    float4 v = ld4(mars + (size_t)e_prime[e0 + j] * ld + b);
+    uint32_t sb = e_sub[e0 + j];
+    if (sb != PCB_NONE) v = add4(v, ld4(mars + (size_t)sb * ld + b));
+    return v;
+  };
+  float4 out;
   if (kind[n] == PCB_SUM) {
     const float* w = theta + n_pid0[n];
-    float mx = -INFINITY;
+    float4 mx = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    for (uint32_t j = 0; j < cnt; ++j) mx = max4(mx, adds4(child(j), __ldg(w + j)));
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (uint32_t j = 0; j < cnt; ++j) {
-      float v = mars[(size_t)e_prime[e0 + j] * ld + b];
-      uint32_t sb = e_sub[e0 + j];
-      if (sb != PCB_NONE) v += mars[(size_t)sb * ld + b];
-      v += __ldg(w + j);
-      mx = fmaxf(mx, v);
+      const float4 v = adds4(child(j), __ldg(w + j));
+      // a maximum of -inf (every child impossible) gives exp(nan): masked below
+      acc.x += __expf(v.x - mx.x); acc.y += __expf(v.y - mx.y); acc.z += __expf(v.z - mx.z); acc.w += __expf(v.w - mx.w);
     }
-    if (mx == -INFINITY) {
-      out = -INFINITY;
-    } else {
-      float acc = 0.0f;
-      for (uint32_t j = 0; j < cnt; ++j) {
-        float v = mars[(size_t)e_prime[e0 + j] * ld + b];
-        uint32_t sb = e_sub[e0 + j];
-        if (sb != PCB_NONE) v += mars[(size_t)sb * ld + b];
-        v += __ldg(w + j);
-        acc += __expf(v - mx);
-      }
-      out = mx + __logf(acc);
-    }
+    out.x = mx.x == -INFINITY ? -INFINITY : mx.x + __logf(acc.x);
+    out.y = mx.y == -INFINITY ? -INFINITY : mx.y + __logf(acc.y);
+    out.z = mx.z == -INFINITY ? -INFINITY : mx.z + __logf(acc.z);
+    out.w = mx.w == -INFINITY ? -INFINITY : mx.w + __logf(acc.w);
   } else {
-    out = 0.0f;
-    for (uint32_t j = 0; j < cnt; ++j) {
-      out += mars[(size_t)e_prime[e0 + j] * ld + b];
-      uint32_t sb = e_sub[e0 + j];
-      if (sb != PCB_NONE) out += mars[(size_t)sb * ld + b];
-    }
+    out = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t j = 0; j < cnt; ++j) out = add4(out, child(j));
   }
-  mars[(size_t)n * ld + b] = out;
+  *reinterpret_cast<float4*>(mars + (size_t)n * ld + b) = out;
 }
 
 // Pull-based top-down pass: flows[n][b] = sum over incoming edges of the edge flow
@@ -94,36 +98,39 @@ __global__ void sparse_down_kernel(float* __restrict__ flows, const float* __res
                                    const float* __restrict__ theta, float* __restrict__ aggr) {
   pcb_grid_dep_launch();
   uint32_t n = nodes[blockIdx.x];
-  uint32_t b = blockIdx.y * blockDim.x + threadIdx.x;
-  bool active = b < B;
-  uint32_t bb = active ? b : 0;
+  uint32_t b = (blockIdx.y * blockDim.x + threadIdx.x) * 4u;
+  const bool any = b < B;                      // examples b .. b+3, those below B count
+  const uint32_t bb = any ? b : 0;
+  const bool a0 = b < B, a1 = b + 1 < B, a2 = b + 2 < B, a3 = b + 3 < B;
   uint32_t i0 = in_off[n], i1 = in_off[n + 1];
   pcb_grid_dep_wait();   // everything above is static circuit data
-  float acc = (i0 == i1 && n == root) ? 1.0f : 0.0f;
-  float my = mars[(size_t)n * ld + bb];
+  const float init = (i0 == i1 && n == root) ? 1.0f : 0.0f;
+  float4 acc = make_float4(init, init, init, init);
+  const float4 my = ld4(mars + (size_t)n * ld + bb);
   for (uint32_t i = i0; i < i1; ++i) {
     PcbInEntry en = in_ent[i];
-    float f = flows[(size_t)en.parent * ld + bb];
+    float4 f = ld4(flows + (size_t)en.parent * ld + bb);
     if (en.pid != PCB_NONE) {
-      float pm = mars[(size_t)en.parent * ld + bb];
-      float lp = __ldg(theta + en.pid);
+      const float4 pm = ld4(mars + (size_t)en.parent * ld + bb);
+      const float lp = __ldg(theta + en.pid);
       // order of additions as in flow.jl:55-58: prime + logp, then + sub
-      float child;
+      float4 child;
       if (en.sib == PCB_NONE) {
-        child = my + lp;
+        child = adds4(my, lp);
       } else {
-        float sv = mars[(size_t)en.sib * ld + bb];
-        child = (en.flags & 1u) ? (my + lp) + sv : (sv + lp) + my;
+        const float4 sv = ld4(mars + (size_t)en.sib * ld + bb);
+        child = (en.flags & 1u) ? add4(adds4(my, lp), sv) : add4(adds4(sv, lp), my);
       }
-      f = f * __expf(child - pm);
+      f.x *= __expf(child.x - pm.x); f.y *= __expf(child.y - pm.y);
+      f.z *= __expf(child.z - pm.z); f.w *= __expf(child.w - pm.w);
       if (en.flags & 1u) {
-        float s = warp_sum(active ? f : 0.0f);
+        float s = warp_sum((a0 ? f.x : 0.0f) + (a1 ? f.y : 0.0f) + (a2 ? f.z : 0.0f) + (a3 ? f.w : 0.0f));
         if ((threadIdx.x & 31) == 0) atomicAdd(aggr + en.pid, s);
       }
     }
-    acc += f;
+    acc = add4(acc, f);
   }
-  if (active) flows[(size_t)n * ld + b] = acc;
+  if (any) *reinterpret_cast<float4*>(flows + (size_t)n * ld + b) = acc;
 }
 
 // leaf statistics: aggr[foff + x_b] += flows[leaf][b] * w_b ; missing -> slot C
@@ -453,6 +460,8 @@ __global__ void ll_sum_kernel(const float* __restrict__ root_mars, uint32_t B, f
 }
 
 dim3 grid2(uint32_t items, uint32_t B) { return dim3(items, (B + TPB - 1) / TPB, 1); }
+// grid of the kernels that take four examples per thread
+dim3 grid2v(uint32_t items, uint32_t B) { return dim3(items, (B + 4 * TPB - 1) / (4 * TPB), 1); }
 
 }  // namespace
 
@@ -484,7 +493,7 @@ extern "C" int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   for (uint32_t lay = 1; lay <= c->L; ++lay) {
     uint32_t o0 = c->h_up_sparse_off[lay - 1], o1 = c->h_up_sparse_off[lay];
     if (o1 > o0)
-      { PcbProfScope ps(c, st, PCB_K_SPARSE_UP); pcb_launch_pdl(sparse_up_kernel, grid2(o1 - o0, B), dim3(TPB), 0, st, c->pdl, ws->mars, ws->ld, B, c->up_sparse + o0, c->kind,
+      { PcbProfScope ps(c, st, PCB_K_SPARSE_UP); pcb_launch_pdl(sparse_up_kernel, grid2v(o1 - o0, B), dim3(TPB), 0, st, c->pdl, ws->mars, ws->ld, B, c->up_sparse + o0, c->kind,
                                                           c->n_estart, c->n_ecount, c->n_pid0, c->e_prime,
                                                           c->e_sub, c->theta); }
     PCB_TRY(pcb_dense_forward(c, ws, lay, st));
@@ -508,7 +517,7 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
   for (int64_t lay = c->L; lay >= 0; --lay) {
     uint32_t o0 = c->h_down_sparse_off[lay], o1 = c->h_down_sparse_off[lay + 1];
     if (o1 > o0)
-      { PcbProfScope ps(c, st, PCB_K_SPARSE_DOWN); pcb_launch_pdl(sparse_down_kernel, grid2(o1 - o0, B), dim3(TPB), 0, st, c->pdl, ws->flows, ws->mars, ws->ld, B, c->down_sparse + o0,
+      { PcbProfScope ps(c, st, PCB_K_SPARSE_DOWN); pcb_launch_pdl(sparse_down_kernel, grid2v(o1 - o0, B), dim3(TPB), 0, st, c->pdl, ws->flows, ws->mars, ws->ld, B, c->down_sparse + o0,
                                                             c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr); }
     if (lay >= 1) PCB_TRY(pcb_dense_backward(c, ws, (uint32_t)lay, st));
   }
