@@ -192,30 +192,35 @@ __global__ void __launch_bounds__(LTH) leaf_forward_chunk_kernel(
     const uint32_t* __restrict__ lchunk_var, const uint32_t* __restrict__ lchunk_off,
     const uint32_t* __restrict__ lchunk_inputs, const uint8_t* __restrict__ data,
     const uint8_t* __restrict__ miss, uint64_t num_rows, const int32_t* __restrict__ row_ids, uint32_t row_start) {
-  __shared__ uint16_t xs[LBT];
+  __shared__ __align__(8) uint16_t xs[LBT];
   const uint32_t chunk = blockIdx.x, b0 = blockIdx.y * LBT;
   const uint32_t nb = min((uint32_t)LBT, B - b0);
   stage_values(xs, b0, nb, lchunk_var[chunk], data, miss, num_rows, row_ids, row_start);
   __syncthreads();
-  // a thread's examples are the same for every leaf of the chunk: fetch their values once
-  constexpr uint32_t U = LBT / LTH;
-  uint16_t xv[U];
+  // A thread takes four consecutive examples per pass (one 16-byte store per leaf and pass); its
+  // examples are the same for every leaf of the group, so their values are fetched once.  The last
+  // store of a row may reach into the padding of the row pitch (a multiple of 32).
+  constexpr uint32_t U = LBT / (4 * LTH);
+  uint16_t xv[U][4];
 #pragma unroll
   for (uint32_t u = 0; u < U; ++u) {
-    const uint32_t b = threadIdx.x + LTH * u;
-    xv[u] = b < nb ? xs[b] : (uint16_t)0xffff;
+    const uint32_t b = 4 * threadIdx.x + 4 * LTH * u;
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j) xv[u][j] = b + j < nb ? xs[b + j] : (uint16_t)0xffff;
   }
   for (uint32_t li = lchunk_off[chunk]; li < lchunk_off[chunk + 1]; ++li) {
     uint32_t i = lchunk_inputs[li];
     const float* tab = theta + in_poff[i];
     float* out = mars + (size_t)in_node[i] * ld + b0;
-    float v[U];
+    float v[U][4];
 #pragma unroll
-    for (uint32_t u = 0; u < U; ++u) v[u] = xv[u] == 0xffff ? 0.0f : __ldg(tab + xv[u]);
+    for (uint32_t u = 0; u < U; ++u)
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) v[u][j] = xv[u][j] == 0xffff ? 0.0f : __ldg(tab + xv[u][j]);
 #pragma unroll
     for (uint32_t u = 0; u < U; ++u) {
-      const uint32_t b = threadIdx.x + LTH * u;
-      if (b < nb) out[b] = v[u];
+      const uint32_t b = 4 * threadIdx.x + 4 * LTH * u;
+      if (b < nb) *reinterpret_cast<float4*>(out + b) = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
     }
   }
 }
@@ -485,9 +490,9 @@ extern "C" int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   if (c->use_tc) PCB_TRY(pcb_dense_tc_refresh(c, st));
   if (c->n_inputs) {
     PcbProfScope ps(c, st, PCB_K_LEAF_FWD);
-    dim3 grid(c->n_lchunks, (B + LBT - 1) / LBT);
+    dim3 grid(c->n_lgrps, (B + LBT - 1) / LBT);   // groups of up to 64 leaves of one variable share the staged values
     leaf_forward_chunk_kernel<<<grid, LTH, 0, st>>>(ws->mars, ws->ld, B, c->theta, c->in_node, c->in_poff,
-                                                    c->lchunk_var, c->lchunk_off, c->lchunk_inputs, data_dev,
+                                                    c->lgrp_var, c->lgrp_off, c->lchunk_inputs, data_dev,
                                                     miss_dev, num_rows, row_ids_dev, row_start);
   }
   for (uint32_t lay = 1; lay <= c->L; ++lay) {
