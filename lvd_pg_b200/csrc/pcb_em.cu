@@ -410,6 +410,42 @@ __global__ void em_update_sum_kernel(float* __restrict__ theta, float* __restric
   uint32_t p0 = n_pid0[n], cnt = n_ecount[n];
   float pc = pseudocount / (float)cnt;
   float tot = 0.0f;
+  if ((cnt & 3u) == 0 && (p0 & 3u) == 0 && cnt <= 1024 && cnt > 1) {
+    // aligned group of up to 1024 edges (every dense block): 16-byte accesses, statistics and
+    // parameters loaded together and kept in registers between the two passes
+    float4 a[8], th[8];
+#pragma unroll
+    for (uint32_t u = 0; u < 8; ++u) {
+      const uint32_t j = 4u * lane + 128u * u;
+      if (j < cnt) {
+        a[u] = *reinterpret_cast<const float4*>(aggr + p0 + j);
+        th[u] = *reinterpret_cast<const float4*>(theta + p0 + j);
+      }
+    }
+#pragma unroll
+    for (uint32_t u = 0; u < 8; ++u) {
+      const uint32_t j = 4u * lane + 128u * u;
+      if (j < cnt) {
+        a[u].x += pc; a[u].y += pc; a[u].z += pc; a[u].w += pc;
+        *reinterpret_cast<float4*>(aggr + p0 + j) = a[u];   // the reference keeps the pseudocount in edge_aggr
+        tot += (a[u].x + a[u].y) + (a[u].z + a[u].w);
+      }
+    }
+    tot = warp_sum(tot);
+#pragma unroll
+    for (uint32_t u = 0; u < 8; ++u) {
+      const uint32_t j = 4u * lane + 128u * u;
+      if (j < cnt) {
+        float4 o;
+        o.x = logf(inertia * expf(th[u].x) + (1.0f - inertia) * a[u].x / tot);
+        o.y = logf(inertia * expf(th[u].y) + (1.0f - inertia) * a[u].y / tot);
+        o.z = logf(inertia * expf(th[u].z) + (1.0f - inertia) * a[u].z / tot);
+        o.w = logf(inertia * expf(th[u].w) + (1.0f - inertia) * a[u].w / tot);
+        *reinterpret_cast<float4*>(theta + p0 + j) = o;
+      }
+    }
+    return;
+  }
   for (uint32_t j = lane; j < cnt; j += 32) {
     float a = aggr[p0 + j] + pc;
     aggr[p0 + j] = a;  // the reference keeps the pseudocount in edge_aggr
@@ -436,6 +472,32 @@ __global__ void em_update_leaf_kernel(float* __restrict__ theta, const float* __
   if (fo == ~0ull) return;
   uint32_t C = in_cats[i];
   uint64_t po = in_poff[i];
+  if (C <= 256) {
+    // statistics and parameters of the leaf loaded together and kept in registers between the passes
+    float a[8], th[8];
+    float s = 0.0f;
+#pragma unroll
+    for (uint32_t u = 0; u < 8; ++u) {
+      const uint32_t k = lane + 32u * u;
+      if (k < C) { a[u] = aggr[fo + k]; th[u] = theta[po + k]; }
+    }
+    const float missing_flow = aggr[fo + C];
+#pragma unroll
+    for (uint32_t u = 0; u < 8; ++u) if (lane + 32u * u < C) s += a[u];
+    s = warp_sum(s);
+    const float node_flow = s + (missing_flow + pseudocount);
+    const float cat_pc = pseudocount / (float)C;
+#pragma unroll
+    for (uint32_t u = 0; u < 8; ++u) {
+      const uint32_t k = lane + 32u * u;
+      if (k < C) {
+        const float oldp = expf(th[u]);
+        const float newv = (1.0f - inertia) * (a[u] + cat_pc + missing_flow * oldp) / node_flow;
+        theta[po + k] = logf(inertia * oldp + newv);
+      }
+    }
+    return;
+  }
   float s = 0.0f;
   for (uint32_t k = lane; k < C; k += 32) s += aggr[fo + k];
   s = warp_sum(s);
@@ -448,6 +510,11 @@ __global__ void em_update_leaf_kernel(float* __restrict__ theta, const float* __
     float newv = (1.0f - inertia) * (aggr[fo + k] + cat_pc + missing_flow * oldp) / node_flow;
     theta[po + k] = logf(oldv + newv);
   }
+}
+
+__global__ void iota_ids_kernel(int32_t* __restrict__ ids, int32_t first, uint32_t n) {
+  uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) ids[i] = first + (int32_t)i;
 }
 
 __global__ void ll_sum_kernel(const float* __restrict__ root_mars, uint32_t B, float* __restrict__ out) {
@@ -619,8 +686,13 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   // of the current call
   if (row_ids_dev) {
     PCB_CUDA(cudaMemcpyAsync(ws->ids_stage, row_ids_dev, (size_t)B * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
-    row_ids_dev = ws->ids_stage;
+  } else {
+    // a row range becomes staged ids too, so that consecutive batches of an epoch replay one graph
+    PCB_REQUIRE(row_start >= 1 && (uint64_t)row_start - 1 + B <= num_rows, "row range out of bounds");
+    iota_ids_kernel<<<(B + 255) / 256, 256, 0, st>>>(ws->ids_stage, (int32_t)row_start, B);
+    row_start = 1;
   }
+  row_ids_dev = ws->ids_stage;
   if (!c->graph_enabled || c->prof.on)
     return em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
                         pseudocount, inertia, ll_sum_dev, st);
