@@ -226,6 +226,15 @@ const char* pcb_profile_class_name(int32_t i);
 int32_t pcb_profile_enable(pcb_circuit* c, int32_t on);
 int32_t pcb_profile_read(pcb_circuit* c, double* ms_out, uint64_t* launches_out, int32_t reset);
 
+/* ---- diagnostics -------------------------------------------------------------------------- */
+/* With PCB_TC_TRACE set in the environment, CTA (0,0,0) of every tensor-core dense kernel writes
+ * %globaltimer stamps of its pipeline events into a 512-word device buffer; these calls synchronise
+ * the device and copy the buffer of the last traced launch (forward / child-flow kernels, or the
+ * edge-statistics kernel) to `out` (512 words).  PCB_ERR_STATE when tracing is off.  No counterpart in
+ * the reference. */
+int32_t pcb_debug_read_trace(unsigned long long* out);
+int32_t pcb_debug_read_edge_trace(unsigned long long* out);
+
 #ifdef __cplusplus
 }
 #endif
