@@ -150,6 +150,16 @@ struct ChunkRegs {
 //    thread: kk = lane, row = warp + PW*q.
 __device__ __forceinline__ uint32_t rc_row(uint32_t tid, uint32_t g = 0) { return (((tid >> 5) + PW * g) << 3) + (tid & 7u); }
 __device__ __forceinline__ uint32_t rc_kk(uint32_t tid, uint32_t q) { return ((tid & 31u) >> 3) + 4u * q; }
+//  * 16-byte variant of the row-contiguous map (sixteen producer warps): a thread loads four
+//    consecutive examples of one K position; warp w covers examples 8w .. 8w+7 (lane & 1 picks the
+//    half) and sixteen K positions (lane >> 1), two passes per chunk.  A quarter of the load
+//    instructions of the 4-byte map for the same sectors; the four stores of a load go to rows
+//    r .. r+3, and over a warp (two row halves x sixteen K positions) they still fall into 32 banks.
+//    Used by BWD_CHILD (two source matrices per element: K loop 15 -> 13 us per tile); FWD measured
+//    slower with it and keeps the 4-byte map.
+constexpr bool VEC_MAP = PW == 16;
+__device__ __forceinline__ uint32_t v4_row(uint32_t tid) { return ((tid >> 5) << 3) + ((tid & 1u) << 2); }
+__device__ __forceinline__ uint32_t v4_kk(uint32_t tid, uint32_t q) { return ((tid & 31u) >> 1) + 16u * q; }
 
 // child value M[t][b] with unconditional loads: invalid positions read a safe address and are
 // replaced afterwards, so a chunk's loads carry no control dependence and issue back to back
@@ -172,6 +182,7 @@ struct ProdInv {
   const float* pb;      // BWD_EDGE: prime-child rows of the B operand
   const float* pbd;     // BWD_EDGE: sub-child rows of the B operand
   float mx[RG];         // FWD / BWD_CHILD: the example's max (an infinity masks the whole row)
+  float mx4[4];         // the same for the four examples of the 16-byte map
   uint32_t rmask;       // BWD_EDGE: bit q set when A row q of this thread is inside the block
   uint32_t bmask;       // BWD_EDGE: bit q set when B row q of this thread is inside the block
   bool has_sub;
@@ -183,7 +194,25 @@ __device__ __forceinline__ ProdInv make_inv(const ProdCtx& c) {
   ProdInv v{};
   const uint32_t tid = c.tid, ld = c.ld;
   v.has_sub = c.k.d0 != PCB_NONE;
-  if (MODE == MODE_FWD || MODE == MODE_BWD_CHILD) {
+  if (MODE == MODE_BWD_CHILD && VEC_MAP) {
+    // 16-byte map: four consecutive examples (rows v4_row .. +3) of one K position per load
+    const uint32_t row = v4_row(tid), b = c.m0 + row, kk0 = v4_kk(tid, 0);
+    const bool bok = b < ld;                  // the pitch is a multiple of 4: a group is inside or outside as a whole
+    const uint32_t bb = bok ? b : 0u;
+#pragma unroll
+    for (uint32_t j = 0; j < 4; ++j) {
+      const float mx = c.mxs[row + j];
+      if (MODE == MODE_FWD) v.mx4[j] = (bok && mx != -INFINITY) ? mx : INFINITY;     // exp(x - inf) = 0
+      else                  v.mx4[j] = (bok && mx != -INFINITY) ? mx : -INFINITY;    // exp(-inf - m) = 0
+    }
+    if (MODE == MODE_FWD) {
+      v.pc[0] = c.mars + (size_t)(c.k.c0 + kk0) * ld + bb;
+      v.pd[0] = c.mars + (size_t)((v.has_sub ? c.k.d0 : c.k.c0) + kk0) * ld + bb;
+    } else {
+      v.pc[0] = c.mars + (size_t)(c.k.p0 + kk0) * ld + bb;
+      v.pd[0] = c.flows + (size_t)(c.k.p0 + kk0) * ld + bb;
+    }
+  } else if (MODE == MODE_FWD || MODE == MODE_BWD_CHILD) {
     const uint32_t kk0 = rc_kk(tid, 0);
 #pragma unroll
     for (uint32_t g = 0; g < RG; ++g) {
@@ -220,7 +249,28 @@ __device__ __forceinline__ ProdInv make_inv(const ProdCtx& c) {
 template <int MODE>
 __device__ __forceinline__ void load_chunk(const ProdCtx& c, const ProdInv& v, uint32_t i, ChunkRegs& r) {
   const uint32_t kc = c.k_begin + i * KCH, tid = c.tid, ld = c.ld;
-  if (MODE == MODE_FWD || MODE == MODE_BWD_CHILD) {
+  if (MODE == MODE_BWD_CHILD && VEC_MAP) {
+    const uint32_t kk0 = v4_kk(tid, 0);
+    const uint32_t klast = (c.k_end - 1 - kk0) & ~15u;   // a valid row of this thread's K phase (K >= 16)
+#pragma unroll
+    for (uint32_t q = 0; q < 2; ++q) {
+      const uint32_t kq = kc + 16 * q;
+      const bool ok = kq + kk0 < c.k_end;
+      const size_t o = (size_t)(ok ? kq : klast) * ld;
+      const float4 x = *reinterpret_cast<const float4*>(v.pc[0] + o);
+      const float4 y = *reinterpret_cast<const float4*>(v.pd[0] + o);
+      if (MODE == MODE_FWD) {
+        r.ra[q * 4 + 0] = ok ? x.x + (v.has_sub ? y.x : 0.0f) : -INFINITY;
+        r.ra[q * 4 + 1] = ok ? x.y + (v.has_sub ? y.y : 0.0f) : -INFINITY;
+        r.ra[q * 4 + 2] = ok ? x.z + (v.has_sub ? y.z : 0.0f) : -INFINITY;
+        r.ra[q * 4 + 3] = ok ? x.w + (v.has_sub ? y.w : 0.0f) : -INFINITY;
+      } else {
+        r.rm[q * 4 + 0] = x.x; r.rm[q * 4 + 1] = x.y; r.rm[q * 4 + 2] = x.z; r.rm[q * 4 + 3] = x.w;   // mars of the parent
+        r.ra[q * 4 + 0] = ok ? y.x : 0.0f; r.ra[q * 4 + 1] = ok ? y.y : 0.0f;                       // flows of the parent
+        r.ra[q * 4 + 2] = ok ? y.z : 0.0f; r.ra[q * 4 + 3] = ok ? y.w : 0.0f;
+      }
+    }
+  } else if (MODE == MODE_FWD || MODE == MODE_BWD_CHILD) {
     // K index of element q: kc + kk0 + 4q; rows past the end of K are clamped and masked
     const uint32_t kk0 = rc_kk(tid, 0);
     const uint32_t klast = (c.k_end - 1 - kk0) & ~3u;   // largest valid multiple of 4 for this thread
@@ -315,7 +365,19 @@ __device__ __forceinline__ void store_chunk(const ProdCtx& c, const ProdInv& v, 
                                             uint8_t* a_lo, uint8_t* b_hi, uint8_t* b_lo,
                                             unsigned long long* tmark = nullptr) {
   const uint32_t tid = c.tid;
-  if (MODE == MODE_FWD || MODE == MODE_BWD_CHILD) {
+  if (MODE == MODE_BWD_CHILD && VEC_MAP) {
+    const uint32_t row0 = v4_row(tid);
+#pragma unroll
+    for (uint32_t q = 0; q < 2; ++q) {
+      const uint32_t kk = v4_kk(tid, q);
+#pragma unroll
+      for (uint32_t j = 0; j < 4; ++j) {
+        const float val = MODE == MODE_FWD ? __expf(r.ra[q * 4 + j] - v.mx4[j])
+                                           : r.ra[q * 4 + j] * __expf(v.mx4[j] - r.rm[q * 4 + j]);
+        put_split(a_hi, a_lo, sw_off(row0 + j, kk), val);
+      }
+    }
+  } else if (MODE == MODE_FWD || MODE == MODE_BWD_CHILD) {
     // element q sits in 16-byte chunk q of the row (kk >> 2 == q), swizzled with the row index
 #pragma unroll
     for (uint32_t g = 0; g < RG; ++g) {
