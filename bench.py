@@ -234,6 +234,74 @@ def run_cfg4(args):
     print(json.dumps(line))
 
 
+def run_cfg3(args):
+    """Config 3 (patch model): forward + backward + EM on 64 independent HCLTs (192 variables,
+    128 latents, 256 categories), batch 256 images per circuit, all circuits of a step in flight
+    together on their own streams.  With N GPUs the circuits are dealt out 64 / N per rank, no
+    collective.  Prints its own JSON line."""
+    import torch
+    import torch.distributed as dist
+    from lvd_pg_b200 import api, synth
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B = 256
+    parts = synth.config3(device=dev)
+    mine = parts[rank::world]
+    circuits = [(api.CuMetaBitsProbCircuit(fc, dev.index), api.DeviceData(data, dev)) for data, fc in mine]
+    streams = [torch.cuda.Stream(device=dev) for _ in circuits]
+    rng = np.random.default_rng(7)
+    n_total = args.warmup + args.steps
+    ids = [[torch.from_numpy((rng.permutation(20000)[:B] + 1).astype(np.int32)).to(dev) for _ in circuits] for _ in range(n_total)]
+    lls = [torch.zeros(1, device=dev) for _ in circuits]
+
+    def step(i):
+        cur = torch.cuda.current_stream(dev)
+        for j, (m, dd) in enumerate(circuits):
+            streams[j].wait_stream(cur)
+            with torch.cuda.stream(streams[j]):
+                api.em_step(m, dd, ids[i][j], 1, B, PSEUDOCOUNT, INERTIA, 0.0, None, lls[j])
+        for st_ in streams:
+            cur.wait_stream(st_)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(dev.index) as clocks:
+        e0.record()
+        for i in range(args.warmup, n_total):
+            step(i)
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    launches = sum(sum(v[1] for v in m.profile_read(reset=True).values()) for m, _ in circuits)
+    if rank == 0:
+        fc0 = mine[0][1]
+        line = {"metric": "samples/sec fwd+bwd+EM", "value": 64 * B * args.steps / (ms * 1e-3), "unit": "samples/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "config 3: 64 patch HCLTs (192 vars x 256 cats, 128 latents), B=256 images per circuit, all circuits per step",
+                           "circuits": 64, "circuits_per_rank": len(mine), "nodes_per_circuit": fc0.num_nodes,
+                           "edges_per_circuit": fc0.num_edges, "parallelism": f"circuits over {world} rank(s), no collective"},
+                "train_ll_circuit0": float(lls[0].item()) / B, "clocks": clocks.summary(), "gpu_launches": int(launches)}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -248,6 +316,9 @@ def main():
                     help="strong: the config's global batch is split over the GPUs (config 5 as stated); "
                          "weak: every GPU takes the config's batch")
     args = ap.parse_args()
+    if args.config == "cfg3":
+        run_cfg3(args)
+        return
     if args.config == "cfg4":
         if int(os.environ.get("RANK", "0")) == 0:
             run_cfg4(args)

@@ -104,3 +104,18 @@ def image_hclt(k: int, rows: int, side: int = 32, sigma: float = 2.0, seed: int 
     parent = image_clt(images, clt_rows)
     fc = st.hclt_flat(parent, 256, k, seed=seed + 1)
     return images, fc
+
+
+def config3(rows: int = 20000, k: int = 128, seed: int = 3, device="cpu", patches: int = 64):
+    """Config 3: 64x64x3 images (sigma = 4 px) cut into 64 non-overlapping 8x8x3 patches of 192
+    variables; one HCLT (k latents, 256 categories) per patch position.  Returns a list of
+    (patch data [rows, 192] uint8, FlatCircuit)."""
+    images = blurred_noise_images(rows, 64, 4.0, seed, device)
+    img = images.view(rows, 64, 64, 3)
+    out = []
+    for p in range(patches):
+        py, px = divmod(p, 8)
+        data = img[:, 8 * py:8 * py + 8, 8 * px:8 * px + 8, :].reshape(rows, 192).contiguous()
+        parent = image_clt(data, 4096)
+        out.append((data, st.hclt_flat(parent, 256, k, seed=seed + 1 + p)))
+    return out
