@@ -82,6 +82,36 @@ __global__ void kld_up_kernel(float* __restrict__ klds, uint32_t ld, uint32_t S,
   klds[(size_t)n * ld + s] = acc;
 }
 
+// The same with one warp per (node, set): lanes over the node's edges.  With a handful of parameter
+// sets the (set, node) layout above leaves every thread a serial loop over up to k edges; a layer
+// of a single-set call then takes tens of microseconds instead of a few.
+__global__ void kld_up_warp_kernel(float* __restrict__ klds, uint32_t ld, uint32_t S, const float* __restrict__ p1,
+                                   const float* __restrict__ p2, const uint32_t* __restrict__ nodes, uint32_t count,
+                                   const uint8_t* __restrict__ kind, const uint32_t* __restrict__ n_estart,
+                                   const uint32_t* __restrict__ n_ecount, const uint32_t* __restrict__ n_pid0,
+                                   const uint32_t* __restrict__ e_prime, const uint32_t* __restrict__ e_sub) {
+  const uint32_t w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= count * S) return;
+  const uint32_t i = w / S, s = w % S;
+  const uint32_t n = nodes[i];
+  const uint32_t e0 = n_estart[n], cnt = n_ecount[n];
+  const bool issum = kind[n] == PCB_SUM;
+  const uint32_t pid0 = n_pid0[n];
+  float acc = 0.0f;
+  for (uint32_t j = lane; j < cnt; j += 32) {
+    float k = klds[(size_t)e_prime[e0 + j] * ld + s];
+    uint32_t sb = e_sub[e0 + j];
+    if (sb != PCB_NONE) k += klds[(size_t)sb * ld + s];
+    if (issum) {
+      float a = p1[s + (size_t)S * (pid0 + j)], b = p2[s + (size_t)S * (pid0 + j)];
+      k = expf(a) * (k + a - b);
+    }
+    acc += k;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) klds[(size_t)n * ld + s] = acc;
+}
+
 // edge_klds of sum and product edges in up-edge order, [E][ldS]-free: written straight to a
 // [S, E] column-major buffer (parity accessor only)
 __global__ void kld_edge_kernel(const float* __restrict__ klds, uint32_t ld, uint32_t S, const float* __restrict__ p1,
@@ -141,6 +171,41 @@ __global__ void kld_down_kernel(float* __restrict__ grads, const float* __restri
     acc += eg;
   }
   grads[(size_t)n * ld + s] = acc;
+}
+
+// one warp per (node, set): lanes over the node's incoming edges
+__global__ void kld_down_warp_kernel(float* __restrict__ grads, const float* __restrict__ klds, uint32_t ld,
+                                     uint32_t S, const float* __restrict__ p1, const float* __restrict__ p2,
+                                     const uint32_t* __restrict__ nodes, uint32_t count, uint32_t root,
+                                     const uint32_t* __restrict__ in_off, const PcbInEntry* __restrict__ in_ent,
+                                     float* __restrict__ g1, float* __restrict__ g2) {
+  const uint32_t w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= count * S) return;
+  const uint32_t i = w / S, s = w % S;
+  const uint32_t n = nodes[i];
+  const uint32_t i0 = in_off[n], i1 = in_off[n + 1];
+  const float myk = klds[(size_t)n * ld + s];
+  float acc = 0.0f;
+  for (uint32_t x = i0 + lane; x < i1; x += 32) {
+    PcbInEntry en = in_ent[x];
+    float pg = grads[(size_t)en.parent * ld + s];
+    float eg = pg;
+    if (en.pid != PCB_NONE) {
+      float a = p1[s + (size_t)S * en.pid];
+      float ea = expf(a);
+      eg = pg * ea;
+      if (en.flags & 1u) {
+        float b = p2[s + (size_t)S * en.pid];
+        float ck = myk + (en.sib != PCB_NONE ? klds[(size_t)en.sib * ld + s] : 0.0f);
+        float edge_kld = ea * (ck + a - b);
+        g1[s + (size_t)S * en.pid] = pg * (edge_kld + ea);
+        g2[s + (size_t)S * en.pid] = -pg * ea;
+      }
+    }
+    acc += eg;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) grads[(size_t)n * ld + s] = acc + ((i0 == i1 && n == root) ? 1.0f : 0.0f);
 }
 
 __global__ void kld_leaf_grad_kernel(const float* __restrict__ grads, uint32_t ld, uint32_t S,
@@ -235,6 +300,12 @@ extern "C" int32_t pcb_kld(pcb_circuit* c, pcb_workspace* ws, const float* param
     if (o1 == o0) continue;
     Shape2 sh = shape_for(S, o1 - o0);
     ++c->prof.launches[PCB_K_KLD];
+    if (S <= 8) {
+      kld_up_warp_kernel<<<(uint32_t)(((uint64_t)(o1 - o0) * S + 7) / 8), 256, 0, st>>>(
+          ws->klds, ld, S, params1_dev, params2_dev, c->up_all + o0, o1 - o0, c->kind, c->n_estart, c->n_ecount,
+          c->n_pid0, c->e_prime, c->e_sub);
+      continue;
+    }
     kld_up_kernel<<<sh.grid, sh.block, 0, st>>>(ws->klds, ld, S, params1_dev, params2_dev, c->up_all + o0, o1 - o0,
                                                 c->kind, c->n_estart, c->n_ecount, c->n_pid0, c->e_prime, c->e_sub);
   }
@@ -261,6 +332,12 @@ extern "C" int32_t pcb_kld_backward(pcb_circuit* c, pcb_workspace* ws, const flo
     if (o1 == o0) continue;
     Shape2 sh = shape_for(S, o1 - o0);
     ++c->prof.launches[PCB_K_KLD];
+    if (S <= 8) {
+      kld_down_warp_kernel<<<(uint32_t)(((uint64_t)(o1 - o0) * S + 7) / 8), 256, 0, st>>>(
+          ws->grads, ws->klds, ld, S, params1_dev, params2_dev, c->down_all + o0, o1 - o0, c->N - 1, c->in_off,
+          c->in_ent, grads1_dev, grads2_dev);
+      continue;
+    }
     kld_down_kernel<<<sh.grid, sh.block, 0, st>>>(ws->grads, ws->klds, ld, S, params1_dev, params2_dev,
                                                   c->down_all + o0, o1 - o0, c->N - 1, c->in_off, c->in_ent,
                                                   grads1_dev, grads2_dev);
