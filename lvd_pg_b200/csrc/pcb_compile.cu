@@ -293,6 +293,18 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
   PCB_TRY(upload(&c->n_ecount, ecount, &bytes));
   PCB_TRY(upload(&c->n_pid0, n_pid0, &bytes));
   PCB_TRY(upload(&c->n_region, region, &bytes));
+  {
+    std::vector<uint4> sn(N), sl(NI);
+    for (uint32_t n = 0; n < N; ++n) {
+      const uint32_t third = kind[n] == PCB_INPUT ? node2input[n] : n_pid0[n];
+      const uint32_t reg = region[n] == PCB_NONE ? 0x3fffffffu : region[n];
+      sn[n] = make_uint4(estart[n], ecount[n], third, (uint32_t)kind[n] | (reg << 2));
+    }
+    for (uint32_t i = 0; i < NI; ++i)
+      sl[i] = make_uint4((uint32_t)(in_poff[i] & 0xffffffffu), (uint32_t)(in_poff[i] >> 32), in_cats[i], in_var[i]);
+    PCB_TRY(upload(&c->s_node, sn, &bytes));
+    PCB_TRY(upload(&c->s_leaf, sl, &bytes));
+  }
   PCB_TRY(upload(&c->e_prime, e_prime, &bytes));
   PCB_TRY(upload(&c->e_sub, e_sub, &bytes));
   PCB_TRY(upload(&c->in_node, in_node, &bytes));
@@ -364,7 +376,7 @@ void free_circuit(pcb_circuit* c) {
                   c->e_sub, c->in_node, c->in_var, c->in_cats, c->in_poff, c->in_foff, c->node2input,
                   c->up_all, c->up_sparse, c->down_all, c->down_sparse, c->in_off, c->in_ent, c->dense,
                   c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status, c->w_img, c->dense_img,
-                  c->lgrp_var, c->lgrp_off};
+                  c->lgrp_var, c->lgrp_off, c->s_node, c->s_leaf};
   for (void* p : ptrs) if (p) cudaFree(p);
   if (c->ev_g0) cudaEventDestroy(c->ev_g0);
   if (c->ev_g1) cudaEventDestroy(c->ev_g1);

@@ -99,6 +99,11 @@ struct pcb_circuit {
   uint64_t* in_poff = nullptr;    // [n_inputs] offset of the log-probs in theta
   uint64_t* in_foff = nullptr;    // [n_inputs] offset of the flow slots in aggr, ~0 for fixed
   uint32_t* node2input = nullptr; // [N] input index or PCB_NONE
+  // packed per-node and per-leaf records for the sampling walk (one 16-byte load per visited node):
+  // node: {first edge, edge count, first parameter id (sum) or input index (leaf), kind | region << 2}
+  // leaf: {parameter offset lo, hi, categories, variable}
+  uint4* s_node = nullptr;        // [N]
+  uint4* s_leaf = nullptr;        // [n_inputs]
   // leaves grouped by variable and cut into chunks of at most PCB_LEAF_CHUNK: one thread block
   // stages the variable's observed values once and serves every leaf of the chunk
   uint32_t* lchunk_var = nullptr;   // [n_lchunks] variable of the chunk

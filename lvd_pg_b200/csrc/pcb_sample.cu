@@ -52,12 +52,17 @@ __global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params,
                                    const uint32_t* __restrict__ in_var, const uint32_t* __restrict__ in_cats,
                                    const uint64_t* __restrict__ in_poff, uint64_t P,
                                    const float* __restrict__ theta, uint32_t* __restrict__ stack_all,
-                                   uint32_t stack_cap, int32_t* __restrict__ x_out, int32_t* __restrict__ status) {
+                                   uint32_t stack_cap, int32_t* __restrict__ x_out, int32_t* __restrict__ status,
+                                   uint32_t smem_stack, const uint4* __restrict__ s_node,
+                                   const uint4* __restrict__ s_leaf) {
+  extern __shared__ uint32_t sstack[];   // [warps per block][stack_cap] when smem_stack is set
   const uint32_t s = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t lane = threadIdx.x & 31;
   if (s >= S) return;
   const size_t ps = Sp == 1 ? 0 : s, pld = Sp;
-  uint32_t* stack = stack_all + (size_t)s * stack_cap;
+  // the walk pops and pushes once per visited node: with the stack in shared memory those are not
+  // global round trips on the walk's dependent chain
+  uint32_t* stack = smem_stack ? sstack + (size_t)(threadIdx.x >> 5) * stack_cap : stack_all + (size_t)s * stack_cap;
   for (uint32_t v = lane; v < V; v += 32) x_out[s + (size_t)S * v] = -1;
   uint32_t sp = 1;
   if (lane == 0) stack[0] = N - 1;
@@ -70,11 +75,12 @@ __global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params,
     }
     uint32_t n = stack[--sp];
     __syncwarp();
-    uint8_t kd = kind[n];
+    const uint4 nm = s_node[n];             // one load instead of kind / edge range / parameter id / region
+    const uint8_t kd = (uint8_t)(nm.w & 3u);
     if (kd == PCB_INPUT) {
-      uint32_t i = node2input[n];
-      uint32_t C = in_cats[i], var = in_var[i];
-      uint64_t off = in_poff[i];
+      const uint4 lm = s_leaf[nm.z];
+      uint32_t C = lm.z, var = lm.w;
+      uint64_t off = (uint64_t)lm.x | ((uint64_t)lm.y << 32);
       const float* us = u_leaf + ((size_t)s * V + var) * cmax;
       double best = 0.0;
       uint32_t bi = 0xffffffffu;
@@ -87,7 +93,7 @@ __global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params,
       warp_argmax(best, bi);
       if (lane == 0) x_out[s + (size_t)S * var] = (int32_t)bi;
     } else if (kd == PCB_PRODUCT) {
-      uint32_t e0 = n_estart[n], cnt = n_ecount[n];
+      uint32_t e0 = nm.x, cnt = nm.y;
       // count pushes first so that every lane keeps the same stack pointer
       uint32_t pushes = 0;
       for (uint32_t j = lane; j < cnt; j += 32) pushes += e_sub[e0 + j] != PCB_NONE ? 2 : 1;
@@ -108,8 +114,8 @@ __global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params,
       sp += pushes;
       __syncwarp();
     } else {
-      uint32_t e0 = n_estart[n], cnt = n_ecount[n], pid0 = n_pid0[n];
-      const float* us = u_sum + ((size_t)s * R + n_region[n]) * kmax;
+      uint32_t e0 = nm.x, cnt = nm.y, pid0 = nm.z;
+      const float* us = u_sum + ((size_t)s * R + (nm.w >> 2)) * kmax;
       double best = 0.0;
       uint32_t bi = 0xffffffffu;
       for (uint32_t j = lane; j < cnt; j += 32) {
@@ -212,11 +218,14 @@ extern "C" int32_t pcb_sample_hard(pcb_circuit* c, pcb_workspace* ws, const floa
   int32_t* status = reinterpret_cast<int32_t*>(ws->cum);  // scratch word
   PCB_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
   uint32_t warps_per_block = 4;
+  while (warps_per_block > 1 && (size_t)warps_per_block * ws->stack_cap * 4 > 48 * 1024) warps_per_block /= 2;
+  const size_t sm = (size_t)warps_per_block * ws->stack_cap * 4;
+  const uint32_t smem_stack = sm <= 48 * 1024 ? 1u : 0u;
   ++c->prof.launches[PCB_K_SAMPLE];
-  sample_hard_kernel<<<(S + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, st>>>(
+  sample_hard_kernel<<<(S + warps_per_block - 1) / warps_per_block, warps_per_block * 32, smem_stack ? sm : 0, st>>>(
       S, params_dev, Sp, u_sum_dev, u_leaf_dev, c->n_regions, c->max_group, c->max_cats, c->V, c->N, c->kind,
       c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime, c->e_sub, c->node2input, c->in_var, c->in_cats,
-      c->in_poff, c->P, c->theta, ws->stack, ws->stack_cap, x_out_dev, status);
+      c->in_poff, c->P, c->theta, ws->stack, ws->stack_cap, x_out_dev, status, smem_stack, c->s_node, c->s_leaf);
   PCB_CUDA(cudaGetLastError());
   int32_t h = 0;
   PCB_CUDA(cudaMemcpyAsync(&h, status, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
@@ -320,12 +329,15 @@ extern "C" int32_t pcb_sample_hard_static(pcb_circuit* c, const float* params_de
   cudaStream_t st = (cudaStream_t)s;
   int32_t* status = reinterpret_cast<int32_t*>(scratch + PCB_STATIC_SAMPLE_WORDS);
   PCB_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
-  const uint32_t warps_per_block = 4;
+  uint32_t warps_per_block = 4;
+  while (warps_per_block > 1 && (size_t)warps_per_block * stack_cap * 4 > 48 * 1024) warps_per_block /= 2;
+  const size_t sm = (size_t)warps_per_block * stack_cap * 4;
+  const uint32_t smem_stack = sm <= 48 * 1024 ? 1u : 0u;   // else the walk stacks stay in the static scratch
   ++c->prof.launches[PCB_K_SAMPLE];
-  sample_hard_kernel<<<(S + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, st>>>(
+  sample_hard_kernel<<<(S + warps_per_block - 1) / warps_per_block, warps_per_block * 32, smem_stack ? sm : 0, st>>>(
       S, params_dev, Sp, u_sum_dev, u_leaf_dev, c->n_regions, c->max_group, c->max_cats, c->V, c->N, c->kind,
       c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime, c->e_sub, c->node2input, c->in_var, c->in_cats,
-      c->in_poff, c->P, c->theta, scratch, (uint32_t)stack_cap, x_out_dev, status);
+      c->in_poff, c->P, c->theta, scratch, (uint32_t)stack_cap, x_out_dev, status, smem_stack, c->s_node, c->s_leaf);
   PCB_CUDA(cudaGetLastError());
   int32_t h = 0;
   PCB_CUDA(cudaMemcpyAsync(&h, status, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
