@@ -108,8 +108,10 @@ def algorithmic_work(fc, info, B):
         "dense_fwd": {"flops": 2.0 * B * Ed, "bytes": 4.0 * (B * dense_nodes * 3 + Ed)},
         "dense_bwd_child": {"flops": 2.0 * B * Ed, "bytes": 4.0 * (B * dense_nodes * 6 + Ed)},
         "dense_bwd_edge": {"flops": 2.0 * B * Ed, "bytes": 4.0 * (B * dense_nodes * 4 + 3 * Ed)},
-        "leaf_forward": {"bytes": B * n_in * (4.0 + 4.0) + B * fc.num_vars},
-        "leaf_flow": {"bytes": B * n_in * (4.0 + 4.0) + B * fc.num_vars},
+        # leaf values written / leaf flows read once; the parameter tables and the data bytes are small
+        # beside them; the leaf statistics are read-modify-written once per step
+        "leaf_forward": {"bytes": 4.0 * B * n_in + B * fc.num_vars},
+        "leaf_flow": {"bytes": 4.0 * B * n_in + B * fc.num_vars + 8.0 * (fc.num_input_params + n_in)},
         "sparse_up": {"bytes": 4.0 * B * (N - n_in - dense_nodes) * 3},
         "sparse_down": {"bytes": 4.0 * B * (N - 2 * dense_nodes) * 4},
         "em_update": {"bytes": 16.0 * (Es + fc.num_input_params)},
@@ -449,6 +451,9 @@ def main():
     if roof["traffic"] is not None:
         roof["traffic_unit"] = "bytes per launch (ncu capture of the reduced workload, scaled by blocks x examples)"
         roof["algorithmic_bytes_per_launch"] = w.get("bytes", 0.0) / lps
+    # every class against the HBM roof, from its algorithmic bytes and its own event time
+    roof["class_hbm_frac"] = {kk: round(work[kk]["bytes"] / (classes[kk][0] / prof_steps * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+                              for kk in classes if kk in work and classes[kk][0] > 0}
     roof.update({"kernel": dom, "kernel_ms_per_step": dom_ms, "launches_per_step": classes[dom][1] / prof_steps,
                  "peak_source": peaks["which"],
                  "class_ms_per_step": {k: round(v[0] / prof_steps, 4) for k, v in classes.items()},
