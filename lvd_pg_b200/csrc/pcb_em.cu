@@ -562,13 +562,28 @@ extern "C" int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
                                                     c->lgrp_var, c->lgrp_off, c->lchunk_inputs, data_dev,
                                                     miss_dev, num_rows, row_ids_dev, row_start);
   }
+  const bool fwd_split = !(getenv("PCB_NO_FWD_SPLIT") && atoi(getenv("PCB_NO_FWD_SPLIT")));
   for (uint32_t lay = 1; lay <= c->L; ++lay) {
     uint32_t o0 = c->h_up_sparse_off[lay - 1], o1 = c->h_up_sparse_off[lay];
+    // The sparse nodes and the dense blocks of one layer do not depend on each other (both read
+    // lower layers only): with a side stream the two kernels of a layer run side by side.
+    const bool has_dense = c->h_dense_off[lay + 1] > c->h_dense_off[lay];
+    const bool split = c->side && !c->prof.on && fwd_split && o1 > o0 && has_dense;
+    cudaStream_t ss = st;
+    if (split) {
+      PCB_CUDA(cudaEventRecord(c->ev_fork, st));
+      PCB_CUDA(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
+      ss = c->side;
+    }
     if (o1 > o0)
-      { PcbProfScope ps(c, st, PCB_K_SPARSE_UP); pcb_launch_pdl(sparse_up_kernel, grid2v(o1 - o0, B), dim3(TPB), 0, st, c->pdl, ws->mars, ws->ld, B, c->up_sparse + o0, c->kind,
+      { PcbProfScope ps(c, ss, PCB_K_SPARSE_UP); pcb_launch_pdl(sparse_up_kernel, grid2v(o1 - o0, B), dim3(TPB), 0, ss, c->pdl && !split, ws->mars, ws->ld, B, c->up_sparse + o0, c->kind,
                                                           c->n_estart, c->n_ecount, c->n_pid0, c->e_prime,
                                                           c->e_sub, c->theta); }
     PCB_TRY(pcb_dense_forward(c, ws, lay, st));
+    if (split) {
+      PCB_CUDA(cudaEventRecord(c->ev_join, c->side));
+      PCB_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));
+    }
   }
   if (ll_out_dev)
     PCB_CUDA(cudaMemcpyAsync(ll_out_dev, ws->mars + (size_t)(c->N - 1) * ws->ld, B * sizeof(float),
