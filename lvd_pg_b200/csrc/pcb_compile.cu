@@ -381,6 +381,9 @@ void free_circuit(pcb_circuit* c) {
   if (c->ev_g0) cudaEventDestroy(c->ev_g0);
   if (c->ev_g1) cudaEventDestroy(c->ev_g1);
   if (c->gstream) cudaStreamDestroy(c->gstream);
+  if (c->ev_fork2) cudaEventDestroy(c->ev_fork2);
+  if (c->ev_join2) cudaEventDestroy(c->ev_join2);
+  if (c->side2) cudaStreamDestroy(c->side2);
   if (c->ev_fork) cudaEventDestroy(c->ev_fork);
   if (c->ev_join) cudaEventDestroy(c->ev_join);
   if (c->side) cudaStreamDestroy(c->side);

@@ -867,6 +867,9 @@ int32_t pcb_dense_tc_prepare(pcb_circuit* c, uint64_t* bytes) {
     PCB_CUDA(cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking));
     PCB_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
     PCB_CUDA(cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
+    PCB_CUDA(cudaStreamCreateWithFlags(&c->side2, cudaStreamNonBlocking));
+    PCB_CUDA(cudaEventCreateWithFlags(&c->ev_fork2, cudaEventDisableTiming));
+    PCB_CUDA(cudaEventCreateWithFlags(&c->ev_join2, cudaEventDisableTiming));
   }
   if (const char* e = getenv("PCB_EDGE_BATCH_TILES")) c->edge_batch_tiles = (uint32_t)std::max(1, atoi(e));
   return PCB_OK;

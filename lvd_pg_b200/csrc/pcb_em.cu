@@ -601,12 +601,34 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
   cudaStream_t st = (cudaStream_t)s;
   const uint32_t B = ws->B;
   c->edge_lo = c->edge_hi = 0;
-  for (int64_t lay = c->L; lay >= 0; --lay) {
+  auto sparse_down = [&](int64_t lay, cudaStream_t ss, bool pdl) -> int32_t {
     uint32_t o0 = c->h_down_sparse_off[lay], o1 = c->h_down_sparse_off[lay + 1];
-    if (o1 > o0)
-      { PcbProfScope ps(c, st, PCB_K_SPARSE_DOWN); pcb_launch_pdl(sparse_down_kernel, grid2v(o1 - o0, B), dim3(TPB), 0, st, c->pdl, ws->flows, ws->mars, ws->ld, B, c->down_sparse + o0,
-                                                            c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr); }
-    if (lay >= 1) PCB_TRY(pcb_dense_backward(c, ws, (uint32_t)lay, st));
+    if (o1 > o0) {
+      PcbProfScope ps(c, ss, PCB_K_SPARSE_DOWN);
+      PCB_CUDA(pcb_launch_pdl(sparse_down_kernel, grid2v(o1 - o0, B), dim3(TPB), 0, ss, pdl, ws->flows, ws->mars, ws->ld,
+                              B, c->down_sparse + o0, c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr));
+    }
+    return PCB_OK;
+  };
+  // Layer l: its sparse nodes pull their flows, then its dense blocks push flows to their children.
+  // The sparse nodes of layer l-1 read parents of layers >= l that are never children of a layer-l
+  // block, so they do not wait for the layer-l blocks: with a second side stream they run beside them.
+  const bool split = c->side2 && !c->prof.on && !(getenv("PCB_NO_BWD_SPLIT") && atoi(getenv("PCB_NO_BWD_SPLIT")));
+  PCB_TRY(sparse_down(c->L, st, c->pdl));
+  for (int64_t lay = c->L; lay >= 1; --lay) {
+    const bool has_dense = c->h_dense_off[lay + 1] > c->h_dense_off[lay];
+    const bool has_sparse = c->h_down_sparse_off[lay] > c->h_down_sparse_off[lay - 1];
+    if (split && has_dense && has_sparse) {
+      PCB_CUDA(cudaEventRecord(c->ev_fork2, st));
+      PCB_CUDA(cudaStreamWaitEvent(c->side2, c->ev_fork2, 0));
+      PCB_TRY(sparse_down(lay - 1, c->side2, false));
+      PCB_TRY(pcb_dense_backward(c, ws, (uint32_t)lay, st));
+      PCB_CUDA(cudaEventRecord(c->ev_join2, c->side2));
+      PCB_CUDA(cudaStreamWaitEvent(st, c->ev_join2, 0));
+    } else {
+      PCB_TRY(pcb_dense_backward(c, ws, (uint32_t)lay, st));
+      PCB_TRY(sparse_down(lay - 1, st, c->pdl));
+    }
   }
   if (c->use_tc) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
   if (c->n_inputs) {

@@ -152,6 +152,9 @@ struct pcb_circuit {
   cudaStream_t side = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   bool side_busy = false;
+  // second side stream: the sparse nodes of layer l-1 take their flows while the dense blocks of layer l run
+  cudaStream_t side2 = nullptr;
+  cudaEvent_t ev_fork2 = nullptr, ev_join2 = nullptr;
   cudaStream_t gstream = nullptr;   // stands in for the legacy default stream, which cannot be captured
   cudaEvent_t ev_g0 = nullptr, ev_g1 = nullptr;
   bool graph_enabled = true;
