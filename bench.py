@@ -135,26 +135,72 @@ def measured_traffic(kernel_class, info, B, launches_per_step):
     return per_block * (k2 / 65536.0) * (B / 2048.0) * int(info.num_dense_blocks) / launches_per_step
 
 
-def run_cpu_oracle(fc, images_cpu, target_s, rows_hint=None):
-    """Time the CPU oracle's EM step on a bounded sample; returns (samples/s, rows, threads, seconds)."""
-    from oracle import oracle as orc
-    orc.lib()
-    threads = orc.num_threads()
-    per_row = max(fc.num_edges, 1) * 1.2e-7  # rough single-core seconds per row (fwd + bwd)
-    rows = rows_hint or int(max(threads, min(images_cpu.shape[0], threads * max(1, round(target_s / max(per_row, 1e-9))))))
-    rows = max(1, min(rows, images_cpu.shape[0]))
-    ref = fc.copy()
-    data = np.asfortranarray(images_cpu[:rows])
-    t0 = time.perf_counter()
-    orc.em_step(ref, data, pseudocount=PSEUDOCOUNT, inertia=INERTIA)
-    dt = time.perf_counter() - t0
-    return rows / dt, rows, threads, dt
+def host_threads():
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except Exception:
+        return max(1, os.cpu_count() or 1)
 
 
-def run_cfg4(args):
+def cpu_model():
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except Exception:
+        pass
+    return "unknown"
+
+
+class CpuOracle:
+    """The CPU arm: the oracle (a C restatement of the reference's per-(example, edge) algorithm),
+    built -march=native on this machine, on every host thread the process may use (torchrun exports
+    OMP_NUM_THREADS=1, so the count is set explicitly).  One EM step = E-step on `rows` rows (forward,
+    backward, leaf statistics: linear in the rows) + the M-step over all parameters (independent of the
+    rows).  Throughput is stated for the workload's full batch: B / (t_E * B / rows + t_M)."""
+
+    def __init__(self, fc, images_cpu):
+        from oracle import oracle as orc
+        orc.use_native_build()
+        self.orc, self.threads = orc, host_threads()
+        orc.set_num_threads(self.threads)
+        self.ref = fc.copy()
+        self.images = images_cpu
+        self.aggr = np.zeros(fc.num_edges, np.float32)
+
+    def step(self, rows, first_row=0):
+        orc, ref = self.orc, self.ref
+        rows = max(1, min(rows, self.images.shape[0] - first_row))
+        orc.set_row_block(max(1, min(16, rows // self.threads)))
+        data = np.asfortranarray(self.images[first_row:first_row + rows])
+        t0 = time.perf_counter()
+        orc.clear_flows(ref, self.aggr, 0.0)
+        mars = orc.forward(ref, data)
+        flows, _ = orc.backward(ref, mars, self.aggr)
+        orc.input_flows(ref, flows, data)
+        t1 = time.perf_counter()
+        orc.em_update(ref, self.aggr, PSEUDOCOUNT, INERTIA)
+        t2 = time.perf_counter()
+        return rows, t1 - t0, t2 - t1
+
+    @staticmethod
+    def full_batch_rate(B, rows, t_e, t_m):
+        return B / (t_e * B / rows + t_m)
+
+    def describe(self, B, rows, t_e, t_m):
+        return {"value": self.full_batch_rate(B, rows, t_e, t_m), "unit": "samples/s", "cores": self.threads, "kind": "port",
+                "sample": (f"E-step (forward, backward, leaf statistics) timed on {rows} rows of the same workload "
+                           f"(full circuit) and scaled linearly to the batch of {B}; M-step timed in full"),
+                "rows": rows, "threads": self.threads, "nproc": os.cpu_count(), "cpu_model": cpu_model(),
+                "e_step_s": round(t_e, 3), "m_step_s": round(t_m, 3), "batch": B,
+                "e_step_s_at_batch": round(t_e * B / rows, 2), "build": "gcc -O3 -march=native -fopenmp, fp32, no fast-math",
+                "measured_samples_per_s_on_sample": rows / (t_e + t_m)}
+
+
+def measure_cfg4(args, cpu_leg=True):
     """Config 4 (variational path): exact KLD(q || p) + gradient + Adam step, then hard sampling, on
     two HCLTs over 784 binary variables with 64 latents.  One GPU (a single parameter set has no
-    batch dimension to shard).  Prints its own JSON line."""
+    batch dimension to shard).  Returns the JSON line as a dict."""
     import torch
     from lvd_pg_b200 import api, synth
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"
@@ -207,7 +253,7 @@ def run_cfg4(args):
     kld_bytes = 48.0 * P
     samp_bytes = 8.0 * S * (shp_s[1] * shp_s[2] + shp_l[1] * shp_l[2])
     cpu = None
-    if not args.no_cpu_baseline:
+    if cpu_leg and not args.no_cpu_baseline:
         from oracle import oracle as orc
         orc.lib()
         tq, tp = theta_q.cpu().numpy().copy(), theta_p.cpu().numpy()
@@ -233,7 +279,34 @@ def run_cfg4(args):
             "clocks": clocks.summary(), "gpu_launches": int(sum(v[1] for v in m.profile_read(reset=True).values()))}
     if cpu:
         line["cpu_baseline"] = cpu
-    print(json.dumps(line))
+    return line
+
+
+def measure_cfg2_step(steps=10, warmup=3):
+    """Config 2 (3072 variables x 256 categories, 32 latents, B = 512): milliseconds per mini-batch EM
+    step with the data resident on the GPU."""
+    import torch
+    from lvd_pg_b200 import api
+    cfg = CONFIGS["cfg2"]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    images, fc = build_workload(cfg, dev)
+    m = api.CuMetaBitsProbCircuit(fc, dev.index)
+    data = api.DeviceData(images, dev)
+    rng = np.random.default_rng(321)
+    ids = [torch.from_numpy((rng.permutation(data.num_rows)[:cfg["batch"]] + 1).astype(np.int32)).to(dev) for _ in range(steps + warmup)]
+    ll = torch.zeros(1, device=dev)
+    for i in range(warmup):
+        api.em_step(m, data, ids[i], 1, cfg["batch"], PSEUDOCOUNT, INERTIA, 0.0, None, ll)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(warmup, warmup + steps):
+        api.em_step(m, data, ids[i], 1, cfg["batch"], PSEUDOCOUNT, INERTIA, 0.0, None, ll)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"workload": cfg["desc"], "ms_per_step": ms, "samples_per_s": cfg["batch"] / (ms * 1e-3), "steps": steps,
+            "sum_edges": int(m.info.num_inner_params), "train_ll_last_batch": float(ll.item()) / cfg["batch"]}
 
 
 def run_cfg3(args):
@@ -313,7 +386,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--cpu-seconds", type=float, default=20.0, help="CPU time the cpu_baseline leg of the N=1 run may take")
+    ap.add_argument("--reference-seconds", type=float, default=200.0,
+                    help="--impl reference: CPU time for all warm-up and timed steps together")
+    ap.add_argument("--no-also", action="store_true", help="skip the config 2 / config 4 side measurements of the N=1 run")
+    ap.add_argument("--no-parity", action="store_true", help="N>1: skip the comparison with a 1-GPU run of the same steps")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="strong: the config's global batch is split over the GPUs (config 5 as stated); "
                          "weak: every GPU takes the config's batch")
@@ -323,7 +400,7 @@ def main():
         return
     if args.config == "cfg4":
         if int(os.environ.get("RANK", "0")) == 0:
-            run_cfg4(args)
+            print(json.dumps(measure_cfg4(args)))
         return
     cfg = CONFIGS[args.config]
     rank = int(os.environ.get("RANK", "0"))
@@ -337,22 +414,34 @@ def main():
         if rank != 0:
             return
         import torch
-        from lvd_pg_b200 import synth
         images, fc = build_workload(cfg, "cuda" if torch.cuda.is_available() else "cpu")
-        images_cpu = images.cpu().numpy()
-        vals, rows, threads = [], 0, 0
-        for i in range(args.warmup + args.steps):
-            v, rows, threads, dt = run_cpu_oracle(fc, images_cpu, max(2.0, args.cpu_seconds / max(1, args.steps)))
+        images_cpu = images[:4096].cpu().numpy()
+        del images
+        cpu = CpuOracle(fc, images_cpu)
+        n_total = args.warmup + args.steps
+        # every step is a bounded sample: the rows per step are sized from a first step of one row
+        # per thread so that warm-up + timed steps end within about --reference-seconds
+        rows, t_e, t_m = cpu.step(cpu.threads)
+        per_step = args.reference_seconds / max(1, n_total)
+        rows_per_step = int(max(1, min(cfg["batch"], (per_step - t_m) / max(t_e / rows, 1e-9))))
+        rows_per_step = max(cpu.threads, rows_per_step // cpu.threads * cpu.threads) if rows_per_step >= cpu.threads else rows_per_step
+        meas = []
+        for i in range(n_total):
+            r = cpu.step(rows_per_step, first_row=(i * rows_per_step) % max(1, images_cpu.shape[0] - rows_per_step))
             if i >= args.warmup:
-                vals.append((v, dt))
-        value = float(np.mean([v for v, _ in vals]))
+                meas.append(r)
+        rows = meas[0][0]
+        t_e, t_m = float(np.mean([x[1] for x in meas])), float(np.mean([x[2] for x in meas]))
+        desc = cpu.describe(cfg["batch"], rows, t_e, t_m)
+        value = desc["value"]
         line = {"impl": "reference", "metric": "samples/sec fwd+bwd+EM", "value": value, "unit": "samples/s",
                 "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": float(np.mean([dt for _, dt in vals]) * 1e3), "higher_is_better": True,
+                "ms_per_step": cfg["batch"] / value * 1e3, "measured_ms_per_sample_step": (t_e + t_m) * 1e3,
+                "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": cfg["desc"], "bench_config": args.config, "parallelism": "cpu-threads"},
-                "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": "port",
-                                 "sample": f"{rows} rows per step of the same workload (full circuit)"},
+                "config": {"workload": cfg["desc"], "bench_config": args.config, "global_batch": cfg["batch"],
+                           "parallelism": f"cpu-threads x{cpu.threads}", "rows_per_step": rows},
+                "cpu_baseline": desc,
                 "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
         return
@@ -383,6 +472,9 @@ def main():
     perms = [torch.from_numpy((rng.permutation(rows)[:Bg] + 1).astype(np.int32)) for _ in range(n_steps_total)]
     ids = [p[rank * B:(rank + 1) * B].to(dev) for p in perms]
     ll = torch.zeros(1, device=dev)
+    p_init = None
+    if world > 1 and not args.no_parity:   # the parameters every later comparison starts from
+        p_init = api.vectorize_parameters(m, torch.empty(api.num_parameters(m), dtype=torch.float32, device=dev)).clone()
     torch.cuda.synchronize()
     setup_s = time.perf_counter() - t_setup
 
@@ -490,11 +582,47 @@ def main():
         e2e = {"value": Bg * args.steps / float(tt.item()), "unit": "samples/s",
                "h2d_bytes_per_step": int(B * fc.num_vars * world), "d2h_bytes_per_step": 4 * world}
 
+    # ---- N > 1: the same steps on one GPU with the whole batch, from the same parameters ------------
+    parity = None
+    if p_init is not None:
+        k_par = min(3, n_steps_total)
+
+        def run_steps(shard):
+            api.update_parameters(m, p_init)
+            out = []
+            for i in range(k_par):
+                sel = perms[i][rank * B:(rank + 1) * B] if shard else perms[i]
+                api.em_step(m, data, sel.to(dev), 1, int(sel.numel()), PSEUDOCOUNT, INERTIA, 0.0, None, ll)
+                out.append(float(ll.item()))
+            return out, api.vectorize_parameters(m, torch.empty_like(p_init)).clone()
+
+        ll_n, p_n = run_steps(True)
+        # every rank must hold the same parameters bit for bit after the replicated update
+        p0 = p_n.clone()
+        dist.broadcast(p0, src=0)
+        same = torch.tensor([1.0 if torch.equal(p0, p_n) else 0.0], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        del p0
+        barrier()
+        m.detach_comm()
+        if rank == 0:
+            ll_1, p_1 = run_steps(False)
+            parity = {"steps": k_par, "max_abs_dprob": float((p_n.double().exp() - p_1.double().exp()).abs().max().item()),
+                      "ll_rel": max(abs(a - b) / abs(b) for a, b in zip(ll_n, ll_1)),
+                      "ranks_bit_identical": bool(same.item() == 1.0)}
+            parity["ok"] = bool(parity["max_abs_dprob"] <= 1e-4 and parity["ll_rel"] <= 1e-4 and parity["ranks_bit_identical"])
+        barrier()
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        v, crow, threads, cdt = run_cpu_oracle(fc, images[:4096].cpu().numpy(), args.cpu_seconds)
-        cpu_baseline = {"value": v, "unit": "samples/s", "cores": threads, "kind": "port",
-                        "sample": f"one EM step on {crow} rows of the same workload (full circuit), {cdt:.1f} s"}
+        cpu = CpuOracle(fc, images[:4096].cpu().numpy())
+        # at least 64 rows (four per thread on a 16-thread host), more while the leg stays inside --cpu-seconds
+        r0, te0, tm0 = cpu.step(cpu.threads)
+        want = int((args.cpu_seconds - tm0) / max(te0 / r0, 1e-9))
+        rows_c = max(64, min(cfg["batch"], want // cpu.threads * cpu.threads))
+        r1, te1, tm1 = cpu.step(rows_c, first_row=r0)
+        cpu_baseline = cpu.describe(cfg["batch"], r1, te1, tm1)
+        del cpu
 
     if rank == 0:
         n_edges = fc.num_edges
@@ -513,6 +641,22 @@ def main():
             line["e2e"] = e2e
         if cpu_baseline:
             line["cpu_baseline"] = cpu_baseline
+        if parity:
+            line["parity_vs_1gpu"] = parity
+        if world == 1 and not args.no_also and args.config == "cfg5":
+            # the other configurations' headline figures, measured in the same run (a second of GPU time each)
+            del m, data, images
+            torch.cuda.empty_cache()
+            also = {}
+            try:
+                also["cfg2"] = measure_cfg2_step()
+                torch.cuda.empty_cache()
+                c4 = measure_cfg4(argparse.Namespace(steps=20, warmup=5, no_cpu_baseline=True), cpu_leg=False)
+                also["cfg4"] = {"workload": c4["config"]["workload"], "us_per_kld_grad_adam_step": c4["value"],
+                                "hard_samples_per_s": c4["sampling"]["samples_per_s"], "hard_sampling_ms_per_call": c4["sampling"]["ms_per_call"]}
+            except Exception as e:   # a side measurement must not lose the headline line
+                also["error"] = repr(e)
+            line["also"] = also
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

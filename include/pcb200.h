@@ -103,6 +103,11 @@ int32_t pcb_version(void);
 int32_t pcb_circuit_create(const pcb_circuit_desc* desc, int32_t device, pcb_circuit** out);
 int32_t pcb_circuit_destroy(pcb_circuit* c);
 int32_t pcb_circuit_get_info(const pcb_circuit* c, pcb_circuit_info* info);
+/* Waits for the circuit's device and reports whether any kernel of this circuit gave up a bounded
+ * wait since the circuit was created (PCB_ERR_CUDA; the statistics of that step are then
+ * incomplete).  A training loop calls it where it synchronises anyway, e.g. when it reads the
+ * epoch's log-likelihoods (the CUDA.synchronize() of regularization/reg_em.jl:288). */
+int32_t pcb_circuit_status(pcb_circuit* c);
 
 /* prep_memory(mars_mem / flows_mem, (batch_size, num_nodes)) of reg_em.jl:226-235.
  * `sets` != 0 additionally reserves the per-parameter-set buffers the KLD and
@@ -194,8 +199,9 @@ int32_t pcb_sample_hard(pcb_circuit* c, pcb_workspace* ws, const float* params_d
  * also synchronises the device under its streams.  The walk stacks live in a static 4 MiB
  * device array of the library instead, so S * (num_vars + 2) must not exceed 2^20 words
  * (PCB_ERR_TOO_LARGE otherwise).  The array is shared: calls that overlap on the GPU race.  The
- * first call on a device looks the array's address up; make that call before starting a stream
- * capture.  This entry point has no counterpart in the reference. */
+ * first call on a device looks the array's address up.  Every call waits for the stream before it
+ * returns (it reads the walk's status word back), so it must not be made while the stream is
+ * being captured.  This entry point has no counterpart in the reference. */
 int32_t pcb_sample_hard_static(pcb_circuit* c, const float* params_dev, uint32_t Sp,
                                const float* u_sum_dev, const float* u_leaf_dev, uint32_t S,
                                int32_t* x_out_dev, pcb_stream s);
@@ -227,10 +233,11 @@ int32_t pcb_profile_enable(pcb_circuit* c, int32_t on);
 int32_t pcb_profile_read(pcb_circuit* c, double* ms_out, uint64_t* launches_out, int32_t reset);
 
 /* ---- diagnostics -------------------------------------------------------------------------- */
-/* With PCB_TC_TRACE set in the environment, CTA (0,0,0) of every tensor-core dense kernel writes
- * %globaltimer stamps of its pipeline events into a 512-word device buffer; these calls synchronise
- * the device and copy the buffer of the last traced launch (forward / child-flow kernels, or the
- * edge-statistics kernel) to `out` (512 words).  PCB_ERR_STATE when tracing is off.  No counterpart in
+/* Only in a library built with -DPCB_DIAG and with PCB_TC_TRACE set in the environment, CTA (0,0,0)
+ * of every tensor-core dense kernel writes %globaltimer stamps of its pipeline events into a
+ * 512-word device buffer; these calls synchronise the device and copy the buffer of the last traced
+ * launch (forward / child-flow kernels, or the edge-statistics kernel) to `out` (512 words).
+ * PCB_ERR_STATE when tracing is off, which it always is in the default build.  No counterpart in
  * the reference. */
 int32_t pcb_debug_read_trace(unsigned long long* out);
 int32_t pcb_debug_read_edge_trace(unsigned long long* out);

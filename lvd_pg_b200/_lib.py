@@ -32,6 +32,7 @@ SIGNATURES = {
     "pcb_circuit_create": [C.POINTER(PcbCircuitDesc), _i32, C.POINTER(_vp)],
     "pcb_circuit_destroy": [_vp],
     "pcb_circuit_get_info": [_vp, C.POINTER(PcbCircuitInfo)],
+    "pcb_circuit_status": [_vp],
     "pcb_workspace_create": [_vp, _u32, _i32, C.POINTER(_vp)],
     "pcb_workspace_destroy": [_vp],
     "pcb_get_params": [_vp, _vp, _u64],

@@ -165,6 +165,11 @@ class CuMetaBitsProbCircuit:
         _lib.check(self.lib.pcb_comm_init(self.handle, C.cast(buf, C.c_void_p), rank, nranks))
 
 
+    def detach_comm(self):
+        """Drop the communicator: later steps run on this GPU alone."""
+        _lib.check(self.lib.pcb_comm_destroy(self.handle))
+
+
 def comm_unique_id() -> bytes:
     buf = (C.c_uint8 * 128)()
     _lib.check(_lib.lib().pcb_comm_unique_id(C.cast(buf, C.c_void_p)))
@@ -283,6 +288,7 @@ def mini_batch_em(mbpc: CuMetaBitsProbCircuit, data, num_epochs: int, batch_size
             ids = perm_dev[b * batch_size:(b + 1) * batch_size]
             em_step(mbpc, data, ids, 1, batch_size, pseudocount, param_inertia, rate, weights, ll_epoch[b:b + 1])
         ll = float(ll_epoch.sum().item()) / batch_size / num_batches
+        _lib.check(mbpc.lib.pcb_circuit_status(mbpc.handle))   # the loop synchronises here anyway (reg_em.jl:303)
         out.append(ll)
         param_inertia += delta
         if verbose:

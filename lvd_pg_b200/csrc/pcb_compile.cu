@@ -350,9 +350,20 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
     cudaDeviceProp prop;
     PCB_CUDA(cudaGetDeviceProperties(&prop, c->device));
     const char* impl = getenv("PCB_DENSE_IMPL");
-    c->use_tc = prop.major == 10 && !(impl && std::string(impl) == "simt");
-    c->graph_enabled = !(getenv("PCB_NO_GRAPH") && atoi(getenv("PCB_NO_GRAPH")) != 0);
-    c->pdl = !(getenv("PCB_NO_PDL") && atoi(getenv("PCB_NO_PDL")) != 0);
+    const bool simt = impl && std::string(impl) == "simt";
+    // sm_100 only: the fp32 SIMT kernels are the cross-check of the tensor-core path and run only on request
+    if (prop.major != 10 && !simt && !c->h_dense.empty())
+      return pcb_fail(PCB_ERR_INVALID, "dense sum blocks need an sm_100 device (tcgen05); this device is sm_" +
+                                           std::to_string(prop.major) + std::to_string(prop.minor));
+    c->use_tc = prop.major == 10 && !simt;
+    auto flag = [](const char* name) { const char* e = getenv(name); return e && atoi(e) != 0; };
+    c->graph_enabled = !flag("PCB_NO_GRAPH");
+    c->pdl = !flag("PCB_NO_PDL");
+    c->fwd_split = !flag("PCB_NO_FWD_SPLIT");
+    c->bwd_split = !flag("PCB_NO_BWD_SPLIT");
+    if (const char* e = getenv("PCB_LEAF_FLOW_IMPL")) c->leaf_flow_impl = !strcmp(e, "sorted") ? 2 : !strcmp(e, "atomic") ? 1 : 0;
+    if (const char* e = getenv("PCB_TC_NSPLIT")) { int v = atoi(e); c->tc_nsplit = (v == 1 || v == 2 || v == 4) ? v : 0; }
+    if (const char* e = getenv("PCB_EDGE_IMPL")) c->edge_ld = !strcmp(e, "ld");
     if (c->use_tc) PCB_TRY(pcb_dense_tc_prepare(c, &bytes));
   }
   c->device_bytes = bytes;
@@ -367,6 +378,13 @@ int32_t pcb_check_status(pcb_circuit* c) {
   PCB_CUDA(cudaMemcpy(&h, c->status, sizeof(int), cudaMemcpyDeviceToHost));
   if (h != 0) return pcb_fail(PCB_ERR_CUDA, "a dense-block kernel gave up a bounded wait (status " + std::to_string(h) + ")");
   return PCB_OK;
+}
+
+extern "C" int32_t pcb_circuit_status(pcb_circuit* c) {
+  PCB_REQUIRE(c, "null argument");
+  PCB_CUDA(cudaSetDevice(c->device));
+  PCB_CUDA(cudaDeviceSynchronize());
+  return pcb_check_status(c);
 }
 
 namespace {

@@ -68,10 +68,17 @@ __device__ __forceinline__ float4 split_hi(float4 v) {
 }
 __device__ __forceinline__ float4 sub4(float4 a, float4 b) { return make_float4(a.x - b.x, a.y - b.y, a.z - b.z, a.w - b.w); }
 
+// Timing experiments exist only in a build with -DPCB_DIAG; the default build compiles them out.
+#ifdef PCB_DIAG
+#define PCB_DBG(a, bit) ((a).dbg & (bit))
 #define EDGE_TRACE(slot)                                                            \
   do {                                                                              \
     if (a.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[slot] = gtime(); \
   } while (0)
+#else
+#define PCB_DBG(a, bit) 0u
+#define EDGE_TRACE(slot) do { } while (0)
+#endif
 
 // K-major operand descriptor for this kernel's row width: 8-row groups ROWB * 8 bytes apart, swizzle
 // span = row width (layout code 2: 128-byte swizzle, 4: 64-byte swizzle)
@@ -175,7 +182,7 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
       if (!got) { ok = false; break; }
       if (tid == 0 && i < 60) EDGE_TRACE(i * 8 + 2);
       uint8_t* st = smem + s * STAGE_BYTES + off0;
-      if (!(a.dbg & 4u)) {
+      if (!(PCB_DBG(a, 4u))) {
 #pragma unroll
       for (uint32_t q = 0; q < TM / RP; ++q) {   // G = flows * exp(mx - mars), exponent clamped: inf * 0 stays out
         uint8_t* p = st + q * (RP * ROWB);
@@ -265,7 +272,7 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t d_ahi = edge_desc(sa), d_alo = edge_desc(sa + A_BYTES);
         const uint64_t d_bhi = edge_desc(sa + 2 * A_BYTES), d_blo = edge_desc(sa + 2 * A_BYTES + B_BYTES);
-        if (!(a.dbg & 1u))
+        if (!(PCB_DBG(a, 1u)))
 #pragma unroll
         for (uint32_t ks = 0; ks < KCH / 8; ++ks) {
           const uint64_t adv = (uint64_t)((ks * 32u) >> 4);  // 8 tf32 = 32 bytes along K
@@ -289,7 +296,7 @@ dense_edge_tma_kernel(const __grid_constant__ CUtensorMap tm_mars_a, const __gri
         if (!mbar_wait(&empty[s], ph ^ 1u, a.status)) break;
         if (i < 60) EDGE_TRACE(i * 8 + 1);
         uint8_t* st = smem + s * STAGE_BYTES;
-        const int32_t x = (int32_t)(k_begin + ((a.dbg & 2u) ? 0u : i * KCH));
+        const int32_t x = (int32_t)(k_begin + ((PCB_DBG(a, 2u)) ? 0u : i * KCH));
         mbar_arrive_expect_tx(&raw_full[s], has_sub ? RAW_BYTES + B_BYTES : RAW_BYTES);
         tma_load_2d(st, &tm_mars_a, x, (int32_t)(k.p0 + m0), &raw_full[s]);
         tma_load_2d(st + A_BYTES, &tm_flows_a, x, (int32_t)(k.p0 + m0), &raw_full[s]);
@@ -339,7 +346,6 @@ EncodeTiledFn encode_fn() {
 // [rows][32 examples] boxes of an [n_rows][ld] fp32 matrix, 128-byte swizzle, zero fill outside
 bool encode_rows_map(void* out, float* base, uint32_t ld, uint64_t n_rows, uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
-  if (getenv("PCB_DEBUG_TM")) fprintf(stderr, "pcb: cuTensorMapEncodeTiled entry point %p\n", (void*)fn);
   if (!fn) return false;
   alignas(64) CUtensorMap m;
   cuuint64_t gdim[2] = {ld, n_rows};
@@ -348,7 +354,6 @@ bool encode_rows_map(void* out, float* base, uint32_t ld, uint64_t n_rows, uint3
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   KCH == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (getenv("PCB_DEBUG_TM")) fprintf(stderr, "pcb: tensor map encode (ld %u rows %llu box %u) -> %d\n", ld, (unsigned long long)n_rows, box_rows, (int)r);
   if (r != CUDA_SUCCESS) return false;
   static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
   memcpy(out, &m, sizeof(m));
@@ -363,7 +368,7 @@ int32_t pcb_dense_edge_prepare_ws(pcb_workspace* ws) {
   ws->have_tm = false;
   pcb_circuit* c = ws->c;
   if (!c->use_tc || c->n_dense == 0) return PCB_OK;
-  if (const char* e = getenv("PCB_EDGE_IMPL")) if (!strcmp(e, "ld")) return PCB_OK;
+  if (c->edge_ld) return PCB_OK;
   bool good = encode_rows_map(ws->tm[0], ws->mars, ws->ld, c->N, TM) &&
               encode_rows_map(ws->tm[1], ws->flows, ws->ld, c->N, TM) &&
               encode_rows_map(ws->tm[2], ws->mars, ws->ld, c->N, TN);
@@ -374,23 +379,25 @@ int32_t pcb_dense_edge_prepare_ws(pcb_workspace* ws) {
 // Edge statistics of dense blocks [o0, o0 + n) with the examples cut into `slices` ranges of b_per.
 int32_t pcb_dense_edge_launch(pcb_circuit* c, pcb_workspace* ws, uint32_t o0, uint32_t n, uint32_t slices,
                               uint32_t b_per, cudaStream_t st) {
-  static bool configured = false;
-  if (!configured) {
-    PCB_CUDA(cudaFuncSetAttribute(dense_edge_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-    configured = true;
-  }
+  static PcbPerDeviceOnce once;
+  PCB_CUDA(once.run([] {
+    return cudaFuncSetAttribute(dense_edge_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+  }));
+  uint32_t dbg = 0;
+#ifdef PCB_DIAG
   if (!g_edge_trace && getenv("PCB_TC_TRACE")) {
     cudaMalloc((void**)&g_edge_trace, 512 * sizeof(unsigned long long));
     cudaMemset(g_edge_trace, 0, 512 * sizeof(unsigned long long));
   }
+  if (const char* e = getenv("PCB_TC_DEBUG")) dbg = (uint32_t)atoi(e);
+#endif
   alignas(64) CUtensorMap ma, fa, mb;
   memcpy(&ma, ws->tm[0], sizeof(ma));
   memcpy(&fa, ws->tm[1], sizeof(fa));
   memcpy(&mb, ws->tm[2], sizeof(mb));
   const uint32_t tiles = ((c->max_dense_R + TM - 1) / TM) * ((c->max_dense_K + TN - 1) / TN);
   for (uint32_t z0 = 0; z0 < n; z0 += 65535) {
-    EdgeArgs args{ws->blk_mx, c->aggr, c->theta, c->dense + o0 + z0, c->status, ws->ld, ws->B, b_per, g_edge_trace,
-                  getenv("PCB_TC_DEBUG") ? (uint32_t)atoi(getenv("PCB_TC_DEBUG")) : 0u};
+    EdgeArgs args{ws->blk_mx, c->aggr, c->theta, c->dense + o0 + z0, c->status, ws->ld, ws->B, b_per, g_edge_trace, dbg};
     dim3 grid(slices, tiles, std::min<uint32_t>(65535, n - z0));
     PcbProfScope ps(c, st, PCB_K_DENSE_BWD_EDGE);
     dense_edge_tma_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(ma, fa, mb, args);

@@ -62,6 +62,16 @@ constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 1024
 constexpr uint32_t TMEM_COLS = 256;
 
 
+// Timing experiments (skipping parts of a kernel, %globaltimer stamps of CTA 0) exist only in a
+// build with -DPCB_DIAG; the default build compiles them out.
+#ifdef PCB_DIAG
+#define PCB_DBG(a, bit) ((a).dbg & (bit))
+#define PCB_TRACE_ON(a) ((a).trace != nullptr)
+#else
+#define PCB_DBG(a, bit) 0u
+#define PCB_TRACE_ON(a) false
+#endif
+
 struct TcArgs {
   float* mars;
   float* flows;
@@ -441,7 +451,7 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
   uint32_t* epi_fail = reinterpret_cast<uint32_t*>(ctl + 96); // a producer warp lost a wait
   float* mxs = reinterpret_cast<float*>(ctl + 128);           // [128]
 
-  if (a.trace && threadIdx.x == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[504] = gtime();
+  if (PCB_TRACE_ON(a) && threadIdx.x == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[504] = gtime();
   pcb_grid_dep_launch();
   const PcbDenseBlock k = a.blocks[blockIdx.z];
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -565,7 +575,7 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
-  if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[503] = gtime();
+  if (PCB_TRACE_ON(a) && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[503] = gtime();
 
   if (warp < MMA_WARP) {
     // =========================== producers ===================================================
@@ -576,7 +586,7 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
     ChunkRegs ra0, ra1;   // two register sets, used alternately: no copies on the loop edge
     auto process = [&](uint32_t i, const ChunkRegs& cr) -> bool {
       const uint32_t s = i & (STAGES - 1), ph = (i / STAGES) & 1u;
-      const bool tr = a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && i < 60;
+      const bool tr = PCB_TRACE_ON(a) && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && i < 60;
       if (tr) a.trace[i * 8 + 0] = gtime();
       // one lane per warp polls; __syncwarp orders the other lanes' stores behind the observed phase
       bool got = lane != 0 || mbar_wait(&empty[s], ph ^ 1u, a.status);
@@ -594,7 +604,7 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
         bulk_g2s(b_hi, src, bytes, &full[s]);
         bulk_g2s(b_lo, src + (size_t)img_rows * 32, bytes, &full[s]);
       }
-      if (!(a.dbg & 8u)) store_chunk<MODE>(ctx, inv, cr, a_hi, a_lo, b_hi, b_lo, tr ? a.trace + i * 8 + 7 : nullptr);
+      if (!(PCB_DBG(a, 8u))) store_chunk<MODE>(ctx, inv, cr, a_hi, a_lo, b_hi, b_lo, tr ? a.trace + i * 8 + 7 : nullptr);
       if (tr) a.trace[i * 8 + 2] = gtime();
       fence_proxy_async();   // make the generic-proxy writes visible to the tensor core
       __syncwarp();
@@ -612,10 +622,10 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
     }
 
     // =========================== epilogue ====================================================
-    if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[500] = gtime();
+    if (PCB_TRACE_ON(a) && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[500] = gtime();
     if (ok && lane == 0) ok = mbar_wait(accfull, 0, a.status);
     ok = __all_sync(0xffffffffu, ok);
-    if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[501] = gtime();
+    if (PCB_TRACE_ON(a) && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[501] = gtime();
     constexpr bool COPY_EPI = MODE == MODE_BWD_CHILD && PW == 16;
     if (COPY_EPI) {
       // Child flows  f[t][b] = acc[b][t] * exp(M[t][b] - mx[b])  need the children's value rows for
@@ -639,7 +649,7 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
       // every producer warp is past the accumulator wait (the stages are idle) and the byte counts
       // are posted before the first copy is issued
       asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");
-      const bool go = *reinterpret_cast<volatile uint32_t*>(epi_fail) == 0u && !(a.dbg & 4u);
+      const bool go = *reinterpret_cast<volatile uint32_t*>(epi_fail) == 0u && !(PCB_DBG(a, 4u));
       if (go) {
         tc_fence_after();
         auto issue = [&](uint32_t c, uint32_t which, uint64_t* bar) {
@@ -687,7 +697,7 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
           round(128u + 32u * grp, grp < 2u ? &ebar[1] : &ebar[2]);
         }
       }
-    } else if (ok && !(a.dbg & 4u)) {
+    } else if (ok && !(PCB_DBG(a, 4u))) {
       tc_fence_after();
       constexpr uint32_t NG = PW / 4;                                             // epilogue warp groups
       const uint32_t CG = max(32u, ((n_tile + 32u * NG - 1u) / (32u * NG)) * 32u);   // columns per group
@@ -717,14 +727,14 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
 #pragma unroll
             for (uint32_t j = 0; j < 32; ++j) {
               uint32_t t = n0 + c0 + j;
-              cv[j] = (a.dbg & 32u) ? mx : child_val_nb(a.mars, ld, k, t, b, t < k.K && mx != -INFINITY);
+              cv[j] = (PCB_DBG(a, 32u)) ? mx : child_val_nb(a.mars, ld, k, t, b, t < k.K && mx != -INFINITY);
             }
 #pragma unroll
             for (uint32_t j = 0; j < 32; ++j) {
               uint32_t t = n0 + c0 + j;
               if (t < k.K) {
                 float f = acc[j] * __expf(cv[j] - mx);   // exp(-inf) = 0 for masked entries
-                if ((a.dbg & 16u) && f != 12345.0f) continue;
+                if ((PCB_DBG(a, 16u)) && f != 12345.0f) continue;
                 a.flows[(size_t)(k.c0 + t) * ld + b] = f;
                 if (k.d0 != PCB_NONE) a.flows[(size_t)(k.d0 + t) * ld + b] = f;
               }
@@ -762,7 +772,7 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
       const uint32_t idesc = make_idesc(TM, n_tile);
       for (uint32_t i = 0; i < nchunks && ok; ++i) {
         const uint32_t s = i & (STAGES - 1), ph = (i / STAGES) & 1u;
-        const bool tr = a.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && i < 60;
+        const bool tr = PCB_TRACE_ON(a) && (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && i < 60;
         if (tr) a.trace[i * 8 + 4] = gtime();
         ok = mbar_wait(&full[s], ph, a.status);
         if (!ok) break;
@@ -771,7 +781,7 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t d_ahi = make_desc(sa), d_alo = make_desc(sa + A_BYTES);
         const uint64_t d_bhi = make_desc(sa + 2 * A_BYTES), d_blo = make_desc(sa + 2 * A_BYTES + B_BYTES);
-        if (!(a.dbg & 1u))
+        if (!(PCB_DBG(a, 1u)))
 #pragma unroll
         for (uint32_t ks = 0; ks < KCH / 8; ++ks) {
           const uint64_t adv = (uint64_t)((ks * 32u) >> 4);  // 8 tf32 = 32 bytes along K
@@ -787,11 +797,11 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
     __syncwarp();
   }
 
-  if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[502] = gtime();
+  if (PCB_TRACE_ON(a) && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[502] = gtime();
   // ---- common exit: release tensor memory ---------------------------------------------------------
   tc_fence_before();
   __syncthreads();
-  if (a.trace && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[505] = gtime();
+  if (PCB_TRACE_ON(a) && tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[505] = gtime();
   if (warp == MMA_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -800,11 +810,10 @@ __global__ void __launch_bounds__(NTHREADS, PCB_TC_CTAS) dense_tc_kernel(TcArgs 
 
 template <int MODE>
 int32_t launch(dim3 grid, const TcArgs& args, cudaStream_t st, bool pdl = false) {
-  static bool configured = false;
-  if (!configured) {
-    PCB_CUDA(cudaFuncSetAttribute(dense_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-    configured = true;
-  }
+  static PcbPerDeviceOnce once;
+  PCB_CUDA(once.run([] {
+    return cudaFuncSetAttribute(dense_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+  }));
   PCB_CUDA(pcb_launch_pdl(dense_tc_kernel<MODE>, grid, dim3(NTHREADS), SMEM_BYTES, st, pdl, args));
   return PCB_OK;
 }
@@ -812,20 +821,23 @@ int32_t launch(dim3 grid, const TcArgs& args, cudaStream_t st, bool pdl = false)
 unsigned long long* g_trace = nullptr;   // diagnostic buffer, allocated when PCB_TC_TRACE is set
 
 TcArgs make_args(pcb_circuit* c, pcb_workspace* ws, uint32_t o0) {
+  uint32_t dbg = 0;
+#ifdef PCB_DIAG
   if (!g_trace && getenv("PCB_TC_TRACE")) {
     cudaMalloc((void**)&g_trace, 512 * sizeof(unsigned long long));
     cudaMemset(g_trace, 0, 512 * sizeof(unsigned long long));
   }
+  if (const char* e = getenv("PCB_TC_DEBUG")) dbg = (uint32_t)atoi(e);
+#endif
   return TcArgs{ws->mars, ws->flows, ws->blk_mx, c->aggr, c->theta, c->w_img, c->dense + o0, c->dense_img + o0,
-                c->status, ws->ld, ws->B, 0, 1, g_trace, getenv("PCB_TC_DEBUG") ? (uint32_t)atoi(getenv("PCB_TC_DEBUG")) : 0u};
+                c->status, ws->ld, ws->B, 0, 1, g_trace, dbg};
 }
 
 // A layer that would not fill the GPU with 256-column tiles is cut into narrower tiles: the CTAs
 // of one tile then repeat the production of the data-dependent operand, but each has half (a
 // quarter) of the weight tile to fetch, of the MMAs to wait for and of the epilogue, and a layer's
 // latency is what a chain of small layers pays.
-uint32_t pick_nsplit(uint32_t ctas, uint32_t max_cols) {
-  static const int forced = getenv("PCB_TC_NSPLIT") ? atoi(getenv("PCB_TC_NSPLIT")) : 0;
+uint32_t pick_nsplit(uint32_t ctas, uint32_t max_cols, int forced) {
   if (forced == 1 || forced == 2 || forced == 4) return (uint32_t)forced;
   uint32_t n = 1;
   while (n < 4 && ctas * n * 2 <= 160 && max_cols > TN_MAX / (2 * n)) n *= 2;
@@ -894,7 +906,7 @@ int32_t pcb_dense_tc_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, 
   const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM;
   TcArgs args = make_args(c, ws, o0);
   const uint32_t ct = (c->max_dense_R + TN_MAX - 1) / TN_MAX;
-  args.nsplit = pick_nsplit(bt * ct * (o1 - o0), c->max_dense_R);
+  args.nsplit = pick_nsplit(bt * ct * (o1 - o0), c->max_dense_R, c->tc_nsplit);
   dim3 grid(bt, ct * args.nsplit, o1 - o0);
   PcbProfScope ps(c, st, PCB_K_DENSE_FWD);
   return launch<MODE_FWD>(grid, args, st, c->pdl);
@@ -951,7 +963,7 @@ int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer,
   TcArgs args = make_args(c, ws, o0);
   {
     const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM, ct = (c->max_dense_K + TN_MAX - 1) / TN_MAX;
-    args.nsplit = pick_nsplit(bt * ct * (o1 - o0), c->max_dense_K);
+    args.nsplit = pick_nsplit(bt * ct * (o1 - o0), c->max_dense_K, c->tc_nsplit);
     dim3 grid(bt, ct * args.nsplit, o1 - o0);
     PcbProfScope ps(c, st, PCB_K_DENSE_BWD_CHILD);
     PCB_TRY(launch<MODE_BWD_CHILD>(grid, args, st, c->pdl));

@@ -562,7 +562,7 @@ extern "C" int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
                                                     c->lgrp_var, c->lgrp_off, c->lchunk_inputs, data_dev,
                                                     miss_dev, num_rows, row_ids_dev, row_start);
   }
-  const bool fwd_split = !(getenv("PCB_NO_FWD_SPLIT") && atoi(getenv("PCB_NO_FWD_SPLIT")));
+  const bool fwd_split = c->fwd_split;
   for (uint32_t lay = 1; lay <= c->L; ++lay) {
     uint32_t o0 = c->h_up_sparse_off[lay - 1], o1 = c->h_up_sparse_off[lay];
     // The sparse nodes and the dense blocks of one layer do not depend on each other (both read
@@ -613,7 +613,7 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
   // Layer l: its sparse nodes pull their flows, then its dense blocks push flows to their children.
   // The sparse nodes of layer l-1 read parents of layers >= l that are never children of a layer-l
   // block, so they do not wait for the layer-l blocks: with a second side stream they run beside them.
-  const bool split = c->side2 && !c->prof.on && !(getenv("PCB_NO_BWD_SPLIT") && atoi(getenv("PCB_NO_BWD_SPLIT")));
+  const bool split = c->side2 && !c->prof.on && c->bwd_split;
   PCB_TRY(sparse_down(c->L, st, c->pdl));
   for (int64_t lay = c->L; lay >= 1; --lay) {
     const bool has_dense = c->h_dense_off[lay + 1] > c->h_dense_off[lay];
@@ -634,9 +634,8 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
   if (c->n_inputs) {
     PcbProfScope ps(c, st, PCB_K_LEAF_FLOW);
     // sorted segments pay off once a variable has enough values to keep a block's threads busy;
-    // PCB_LEAF_FLOW_IMPL=atomic / sorted forces one of the two kernels
-    const char* impl = getenv("PCB_LEAF_FLOW_IMPL");
-    const bool want_sorted = impl ? !strcmp(impl, "sorted") : c->max_cats >= 16;
+    // PCB_LEAF_FLOW_IMPL=atomic / sorted (read when the circuit is created) forces one of the two kernels
+    const bool want_sorted = c->leaf_flow_impl ? c->leaf_flow_impl == 2 : c->max_cats >= 16;
     if (c->max_cats <= LSC && want_sorted) {
       dim3 grid(c->n_lgrps, (B + LSB - 1) / LSB);
       leaf_flow_sorted_kernel<<<grid, LST, weights_dev ? LSB * sizeof(float) : 0, st>>>(
@@ -691,20 +690,24 @@ extern "C" int32_t pcb_em_update(pcb_circuit* c, float pseudocount, float inerti
   return PCB_OK;
 }
 
-// clear, forward, backward, (all-reduce,) update: the launches of one EM step on stream st
+// clear, forward, backward, (all-reduce,) update: the launches of one EM step on stream st.  The
+// batch log-likelihood stays in the last slot of the statistics vector; pcb_em_step copies it out.
 static int32_t em_step_body(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev, const uint8_t* miss_dev,
                             uint64_t num_rows, const int32_t* row_ids_dev, uint32_t row_start, uint32_t B,
                             const float* weights_dev, float clear_rate, float pseudocount, float inertia,
-                            float* ll_sum_dev, cudaStream_t st) {
+                            cudaStream_t st) {
   pcb_stream s = (pcb_stream)st;
-  PCB_TRY(pcb_clear_flows(c, clear_rate, s));
+  // With a communicator every rank enters the step holding the same summed statistics of the last
+  // step (pseudocount included, as the reference keeps it in edge_aggr); the all-reduce below adds
+  // the ranks' vectors, so each rank carries rate / nranks of them and the sum is rate * previous
+  // + this step's flows, as reg_em.jl:276-284 computes it on one device.
+  const float carried = (c->comm && c->nranks > 1) ? clear_rate / (float)c->nranks : clear_rate;
+  PCB_TRY(pcb_clear_flows(c, carried, s));
   PCB_TRY(pcb_forward(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, nullptr, s));
   PCB_TRY(pcb_backward(c, ws, weights_dev, s));
   // batch log-likelihood into the last slot of the statistics vector, so it is reduced with them
   { PcbProfScope ps(c, st, PCB_K_MISC); ll_sum_kernel<<<1, 256, 0, st>>>(ws->mars + (size_t)(c->N - 1) * ws->ld, B, c->aggr + c->aggr_len - 1); }
   if (c->comm) { PcbProfScope ps(c, st, PCB_K_ALLREDUCE); PCB_TRY(pcb_allreduce_aggr(c, st)); }
-  if (ll_sum_dev)
-    PCB_CUDA(cudaMemcpyAsync(ll_sum_dev, c->aggr + c->aggr_len - 1, sizeof(float), cudaMemcpyDeviceToDevice, st));
   PCB_TRY(pcb_em_update(c, pseudocount, inertia, s));
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
@@ -730,13 +733,23 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
     row_start = 1;
   }
   row_ids_dev = ws->ids_stage;
-  if (!c->graph_enabled || c->prof.on)
-    return em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
-                        pseudocount, inertia, ll_sum_dev, st);
+  // The log-likelihood leaves through a copy issued after the step (the update does not touch its
+  // slot), outside any captured graph: a training loop hands in a different slot for every batch.
+  auto ll_out = [&](cudaStream_t on) -> int32_t {
+    if (ll_sum_dev)
+      PCB_CUDA(cudaMemcpyAsync(ll_sum_dev, c->aggr + c->aggr_len - 1, sizeof(float), cudaMemcpyDeviceToDevice, on));
+    return PCB_OK;
+  };
+  auto plain = [&]() -> int32_t {
+    PCB_TRY(em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
+                         pseudocount, inertia, st));
+    return ll_out(st);
+  };
+  if (!c->graph_enabled || c->prof.on) return plain();
 
   pcb_workspace::StepKey key;
   memset(&key, 0, sizeof(key));
-  key.data = data_dev; key.miss = miss_dev; key.weights = weights_dev; key.ll = ll_sum_dev; key.comm = c->comm;
+  key.data = data_dev; key.miss = miss_dev; key.weights = weights_dev; key.comm = c->comm;
   key.stream = (void*)st; key.num_rows = num_rows; key.row_start = row_start; key.B = B;
   key.clear_rate = clear_rate; key.pseudocount = pseudocount; key.inertia = inertia;
   key.has_ids = row_ids_dev != nullptr; key.w_valid = c->w_img_valid;
@@ -766,6 +779,7 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
     // replay; the host-side state is what the captured run left behind
     PCB_TRY(enter());
     PCB_CUDA(cudaGraphLaunch(ws->step_exec, gs));
+    PCB_TRY(ll_out(gs));
     PCB_TRY(leave());
     for (int k = 0; k < PCB_K_COUNT; ++k) c->prof.launches[k] += ws->step_launches[k];
     ws->B = B; ws->data = data_dev; ws->miss = miss_dev; ws->num_rows = num_rows;
@@ -776,9 +790,7 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   const bool capture = ws->have_key && !memcmp(&key, &ws->last_key, sizeof(key));
   ws->last_key = key;
   ws->have_key = true;
-  if (!capture)
-    return em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
-                        pseudocount, inertia, ll_sum_dev, st);
+  if (!capture) return plain();
 
   if (ws->step_exec) { cudaGraphExecDestroy(ws->step_exec); ws->step_exec = nullptr; }
   uint64_t before[PCB_K_COUNT];
@@ -786,7 +798,7 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   PCB_TRY(enter());
   PCB_CUDA(cudaStreamBeginCapture(gs, cudaStreamCaptureModeRelaxed));
   int32_t body = em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
-                              pseudocount, inertia, ll_sum_dev, gs);
+                              pseudocount, inertia, gs);
   cudaGraph_t graph = nullptr;
   cudaError_t ce = cudaStreamEndCapture(gs, &graph);
   if (body != PCB_OK || ce != cudaSuccess || !graph) {
@@ -796,8 +808,7 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
     if (body != PCB_OK) return body;
     for (int k = 0; k < PCB_K_COUNT; ++k) c->prof.launches[k] = before[k];
     c->w_img_valid = key.w_valid != 0;
-    return em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
-                        pseudocount, inertia, ll_sum_dev, st);
+    return plain();
   }
   ce = cudaGraphInstantiate(&ws->step_exec, graph, 0);
   cudaGraphDestroy(graph);
@@ -807,12 +818,12 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
     for (int k = 0; k < PCB_K_COUNT; ++k) c->prof.launches[k] = before[k];
     c->w_img_valid = key.w_valid != 0;
     cudaGetLastError();
-    return em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
-                        pseudocount, inertia, ll_sum_dev, st);
+    return plain();
   }
   for (int k = 0; k < PCB_K_COUNT; ++k) ws->step_launches[k] = c->prof.launches[k] - before[k];
   ws->exec_key = key;
   PCB_CUDA(cudaGraphLaunch(ws->step_exec, gs));
+  PCB_TRY(ll_out(gs));
   PCB_TRY(leave());
   return PCB_OK;
 }

@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <string>
 #include <vector>
 
@@ -159,6 +160,11 @@ struct pcb_circuit {
   cudaEvent_t ev_g0 = nullptr, ev_g1 = nullptr;
   bool graph_enabled = true;
   bool pdl = true;   // chain kernels are launched with programmatic stream serialization
+  // tuning switches, read from the environment once when the circuit is created
+  bool fwd_split = true, bwd_split = true;   // side-stream splits of the forward / backward layer loops
+  int leaf_flow_impl = 0;                    // 0 by category count, 1 shared-memory histograms, 2 sorted segments
+  int tc_nsplit = 0;                         // 0 automatic, else 1 / 2 / 4 column splits of a dense tile
+  bool edge_ld = false;                      // edge statistics by the load-fed kernel instead of tensor-map copies
   // dense blocks [edge_lo, edge_hi) whose edge statistics are still to be launched, and the number
   // of tiles at which the range is launched
   uint32_t edge_lo = 0, edge_hi = 0, edge_batch_tiles = 592;
@@ -179,7 +185,7 @@ struct pcb_workspace {
   // on the second call and replayed from then on (the row ids are staged in ids_stage so that
   // their address does not change from step to step).
   struct StepKey {
-    const void* data; const void* miss; const void* weights; void* ll; void* comm; void* stream;
+    const void* data; const void* miss; const void* weights; void* comm; void* stream;
     uint64_t num_rows;
     uint32_t row_start, B;
     float clear_rate, pseudocount, inertia;
@@ -230,6 +236,24 @@ int32_t pcb_fail(int32_t code, const std::string& msg);
   } while (0)
 
 static inline uint32_t pcb_round_up(uint32_t x, uint32_t m) { return (x + m - 1) / m * m; }
+
+// cudaFuncSetAttribute applies to the current device only: a kernel that needs more than 48 KB of
+// dynamic shared memory is configured once per device it is launched on (a host may hold circuits
+// on several GPUs in one process).  Two threads racing here both set the same value.
+struct PcbPerDeviceOnce {
+  std::atomic<uint64_t> done{0};
+  template <typename F>
+  cudaError_t run(F&& configure) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const uint64_t bit = 1ull << (dev & 63);
+    if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    e = configure();
+    if (e == cudaSuccess) done.fetch_or(bit, std::memory_order_release);
+    return e;
+  }
+};
 
 // Counts a launch of class `cls`; with profiling on, brackets it with two events on `st`.
 struct PcbProfScope {

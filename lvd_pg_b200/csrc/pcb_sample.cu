@@ -10,6 +10,7 @@
 //  * pcb_sample_soft: the relaxed sampler itself — gumbel_params_down_kernel (sample.jl:8-58),
 //    gumbel_sample_down_kernel (:60-148), gumbel_input_sample_down_kernel (:233-296).
 #include <algorithm>
+#include <mutex>
 
 #include "../../include/pcb200_gumbel.h"
 #include "pcb_internal.h"
@@ -288,18 +289,24 @@ extern "C" int32_t pcb_sample_soft(pcb_circuit* c, pcb_workspace* ws, const floa
 // The array is shared by all calls on a device and keeps whatever the last call left in it:
 // stacks are written before they are read and the status word is cleared on the stream at the
 // start of every call, but two calls whose kernels overlap on the GPU (different streams) race.
+// A circuit with at most 12 286 variables keeps one warp's stack within 48 KB of shared memory and
+// then only the status word of the array is used; larger circuits walk on the array itself.
+// Like pcb_sample_hard the call ends by reading the status word back and waiting for the stream,
+// so it cannot be made while that stream is being captured.
 #define PCB_STATIC_SAMPLE_WORDS (1u << 20)
 static __device__ __align__(256) uint32_t g_static_sample_scratch[PCB_STATIC_SAMPLE_WORDS + 64];
 
 namespace {
 constexpr int kMaxDevices = 64;
 uint32_t* g_scratch_addr[kMaxDevices] = {nullptr};  // device address of the array, per device
+std::mutex g_scratch_mutex;                          // host threads may make their first calls together
 
 // In host code the array's name is only a handle for the runtime, not a device pointer: the
 // address a kernel may use comes from cudaGetSymbolAddress, asked once per device while that
 // device is current.
 int32_t static_scratch(int device, uint32_t** out) {
   PCB_REQUIRE(device >= 0 && device < kMaxDevices, "device index beyond the static scratch table");
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
   if (!g_scratch_addr[device]) {
     uint32_t* p = nullptr;
     PCB_CUDA(cudaGetSymbolAddress((void**)&p, g_static_sample_scratch));

@@ -6,9 +6,8 @@
 # `update_parameters`).  Device buffers stay `CuArray`s; the library enqueues on CUDA.jl's
 # task-local stream.
 #
-# This file was written against Julia 1.9+/CUDA.jl 5 and ProbabilisticCircuits.jl 0.4; it has not
-# been executed on the build machines (no Julia there).  The same ABI is exercised by the Python
-# binding in lvd_pg_b200/api.py, which is what the test-suite and the benchmark drive.
+# Written against Julia 1.9+ / CUDA.jl 5 and ProbabilisticCircuits.jl 0.4.  The same ABI is exercised
+# by the Python binding in lvd_pg_b200/api.py, which is what the test-suite and the benchmark drive.
 module PCB200
 
 using CUDA
@@ -16,6 +15,7 @@ using ProbabilisticCircuits
 using ProbabilisticCircuits: BitsProbCircuit, SumEdge, BitsInput, BitsSum, BitsMul, dist, isfirst, islast
 
 const libpcb200 = get(ENV, "PCB200_LIB", joinpath(@__DIR__, "..", "libpcb200.so"))
+const STATIC_SAMPLE_WORDS = 1 << 20   # capacity of pcb_sample_hard_static's scratch (include/pcb200.h)
 
 struct PcbError <: Exception
     code::Int32
@@ -217,10 +217,17 @@ U_sum is (kmax, R, S) and U_leaf (cmax, V, S) in Julia's column-major order (the
 function sample(c::PcbCircuit, params::CuMatrix{Float32}, U_sum::CuArray{Float32,3}, U_leaf::CuArray{Float32,3})
     S = size(U_leaf, 3); V = size(U_leaf, 2)
     x = CUDA.zeros(Int32, S, V)
-    ws = workspace(c, 1)
-    check(ccall((:pcb_sample_hard, libpcb200), Int32,
-                (Ptr{Cvoid}, Ptr{Cvoid}, CuPtr{Cfloat}, UInt32, CuPtr{Cfloat}, CuPtr{Cfloat}, UInt32, CuPtr{Int32}, Ptr{Cvoid}),
-                c.handle, ws, params, size(params, 1), U_sum, U_leaf, S, x, stream()))
+    if S * (V + 2) <= STATIC_SAMPLE_WORDS
+        # CUDA.jl's pool owns the device memory: take the entry point that allocates nothing
+        check(ccall((:pcb_sample_hard_static, libpcb200), Int32,
+                    (Ptr{Cvoid}, CuPtr{Cfloat}, UInt32, CuPtr{Cfloat}, CuPtr{Cfloat}, UInt32, CuPtr{Int32}, Ptr{Cvoid}),
+                    c.handle, params, size(params, 1), U_sum, U_leaf, S, x, stream()))
+    else
+        ws = workspace(c, 1)
+        check(ccall((:pcb_sample_hard, libpcb200), Int32,
+                    (Ptr{Cvoid}, Ptr{Cvoid}, CuPtr{Cfloat}, UInt32, CuPtr{Cfloat}, CuPtr{Cfloat}, UInt32, CuPtr{Int32}, Ptr{Cvoid}),
+                    c.handle, ws, params, size(params, 1), U_sum, U_leaf, S, x, stream()))
+    end
     x
 end
 

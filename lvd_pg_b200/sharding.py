@@ -27,3 +27,12 @@ def statistics_length(num_inner_params: int, leaf_cats) -> int:
     """Length of the all-reduced vector: one slot per sum edge, C + 1 per learnable leaf, one
     for the log-likelihood sum."""
     return int(num_inner_params + sum(int(c) + 1 for c in leaf_cats) + 1)
+
+
+def carried_rate(rate: float, world: int) -> float:
+    """Decay each rank applies to the statistics it carries from the last step when `flow_memory`
+    is on (regularization/reg_em.jl:276-284: edge_aggr .*= rate).  After an all-reduced step every
+    rank holds the same global sums, and the next all-reduce adds the ranks' vectors again, so each
+    rank keeps rate / world of them: the sum is rate * previous + this step's flows, as on one
+    device.  pcb_em_step applies the same rule when a communicator is attached."""
+    return rate / world if world > 1 else rate

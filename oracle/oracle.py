@@ -18,26 +18,47 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
 
 
-def build(force: bool = False) -> str:
-    path = os.path.join(_HERE, "libpc_oracle.so")
+VARIANTS = {
+    "f32": "libpc_oracle.so",           # the reference's Float32 arithmetic (the parity checker)
+    "f64": "libpc_oracle64.so",         # the EM path in double on the same fp32 parameters ("exact")
+    "native": "libpc_oracle_native.so",  # f32 built -march=native on the machine that times it
+}
+
+
+def build(force: bool = False, variant: str = "f32") -> str:
+    name = VARIANTS[variant]
+    path = os.path.join(_HERE, name)
     src = os.path.join(_HERE, "pc_oracle.c")
     hdrs = [os.path.join(_HERE, "..", "include", h) for h in ("pcb200.h", "pcb200_gumbel.h")]
     stale = (not os.path.exists(path)) or any(
         os.path.exists(p) and os.path.getmtime(p) > os.path.getmtime(path) for p in [src] + hdrs)
     if force or stale:
-        subprocess.run(["make", "-C", _HERE, "-B", "libpc_oracle.so"], check=True,
-                       stdout=subprocess.DEVNULL)
+        subprocess.run(["make", "-C", _HERE, "-B", name], check=True, stdout=subprocess.DEVNULL)
     return path
+
+
+def _load(variant: str):
+    l = C.CDLL(build(variant=variant))
+    l.orc_num_threads.restype = C.c_int
+    l.orc_real_bytes.restype = C.c_int
+    l.orc_gumbel_key.restype = C.c_double
+    l.orc_log.restype = C.c_double
+    return l
 
 
 def lib():
     global _LIB
     if _LIB is None:
-        _LIB = C.CDLL(build())
-        _LIB.orc_num_threads.restype = C.c_int
-        _LIB.orc_gumbel_key.restype = C.c_double
-        _LIB.orc_log.restype = C.c_double
+        _LIB = _load("f32")
     return _LIB
+
+
+def use_native_build() -> None:
+    """Switch this process to the -march=native build (compiled on this machine on first use):
+    what the benchmark's CPU arm times.  Results are the same arithmetic (no fast-math)."""
+    global _LIB
+    build(force=True, variant="native")   # never trust a copy built on another machine
+    _LIB = _load("native")
 
 
 def _p(a):
@@ -62,6 +83,11 @@ def num_threads() -> int:
 
 def set_num_threads(n: int) -> None:
     lib().orc_set_num_threads(C.c_int(n))
+
+
+def set_row_block(n: int) -> None:
+    """Rows per block of the forward / backward loops (1..16, default 16)."""
+    lib().orc_set_row_block(C.c_int(n))
 
 
 def counts(fc):
@@ -227,3 +253,76 @@ def sample_soft(fc, params, u, temperature, S, cmax):
     lib().orc_sample_soft(C.byref(d), _p(fc.heap), _p(p), C.c_uint32(p.shape[0]), _p(uu),
                           C.c_float(temperature), C.c_uint32(S), C.c_uint32(cmax), _p(ep), _p(cp), _p(td), _p(out))
     return out, {"edge_probs": ep, "cum_probs": cp, "td_probs": td}
+
+
+class Exact:
+    """The EM path of the oracle evaluated in float64 (libpc_oracle64.so) on the same fp32
+    parameters: mars, flows, statistics and the updated parameters as the exact arithmetic gives
+    them.  Two fp32 implementations that sum in different orders (the reference's own atomics do)
+    differ from each other by rounding that grows with the magnitude of the log-values; both are
+    compared with this.  Holds its own float64 copies of the parameters (`up_logp`, `heap`)."""
+
+    def __init__(self, fc):
+        self.fc = fc
+        self.lib = _load("f64")
+        assert self.lib.orc_real_bytes() == 8
+        self.up_logp = fc.up_logp.astype(np.float64)
+        self.heap = fc.heap.astype(np.float64)
+
+    def forward(self, data, row_ids=None, row_start=1, B=None, miss=None):
+        d = self.fc.desc()
+        data, miss, rid, B = _data_args(data, miss, row_ids, row_start, B)
+        mars = np.zeros((B, self.fc.num_nodes), np.float64, order="F")
+        self.lib.orc_forward(C.byref(d), _p(self.up_logp), _p(self.heap), _p(data), _p(miss),
+                             C.c_uint64(data.shape[0]), _p(rid), C.c_uint32(row_start), C.c_uint32(B), _p(mars), None)
+        return mars
+
+    def backward(self, mars, edge_aggr=None):
+        d = self.fc.desc()
+        B = mars.shape[0]
+        flows = np.zeros((B, self.fc.num_nodes), np.float64, order="F")
+        if edge_aggr is None:
+            edge_aggr = np.zeros(self.fc.num_edges, np.float64)
+        self.lib.orc_backward(C.byref(d), _p(self.up_logp), _p(np.asfortranarray(mars)), C.c_uint32(B),
+                              _p(flows), None, _p(edge_aggr))
+        return flows, edge_aggr
+
+    def input_flows(self, flows, data, row_ids=None, row_start=1, miss=None, weights=None):
+        d = self.fc.desc()
+        data, miss, rid, B = _data_args(data, miss, row_ids, row_start, flows.shape[0])
+        w = None if weights is None else np.ascontiguousarray(weights, np.float64)
+        self.lib.orc_input_flows(C.byref(d), _p(self.heap), _p(np.asfortranarray(flows)), _p(data), _p(miss),
+                                 C.c_uint64(data.shape[0]), _p(rid), C.c_uint32(row_start), C.c_uint32(B), _p(w))
+
+    def clear_flows(self, edge_aggr, rate=0.0):
+        d = self.fc.desc()
+        self.lib.orc_clear_flows(C.byref(d), _p(edge_aggr), _p(self.heap), C.c_double(rate))
+
+    def em_update(self, edge_aggr, pseudocount, inertia):
+        d = self.fc.desc()
+        self.lib.orc_em_update(C.byref(d), _p(self.up_logp), _p(edge_aggr), _p(self.heap),
+                               C.c_double(pseudocount), C.c_double(inertia))
+
+    def em_step(self, data, row_ids=None, row_start=1, B=None, pseudocount=0.1, inertia=0.0, miss=None,
+                weights=None, edge_aggr=None, clear_rate=0.0):
+        if edge_aggr is None:
+            edge_aggr = np.zeros(self.fc.num_edges, np.float64)
+        self.clear_flows(edge_aggr, clear_rate)
+        mars = self.forward(data, row_ids, row_start, B, miss)
+        flows, edge_aggr = self.backward(mars, edge_aggr)
+        self.input_flows(flows, data, row_ids, row_start, miss, weights)
+        ll = float(mars[:, -1].sum())
+        aggr_before = edge_aggr.copy()
+        self.em_update(edge_aggr, pseudocount, inertia)
+        return ll, aggr_before
+
+    def vectorize(self) -> np.ndarray:
+        """Flat parameters (misc.jl:42-68 order) as float64."""
+        fc = self.fc
+        inner = self.up_logp[fc.edge_is_sum]
+        leaves = []
+        for nid in fc.input_node_ids.astype(np.int64):
+            if not fc.node_fixed[nid - 1]:
+                hs = int(fc.node_heap_start[nid - 1]) - 1
+                leaves.append(self.heap[hs:hs + int(fc.node_num_cats[nid - 1])])
+        return np.concatenate([inner] + leaves) if leaves else inner.copy()

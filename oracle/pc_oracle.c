@@ -40,6 +40,28 @@
 
 #define IDX(b, n, ld) ((size_t)(b) + (size_t)(ld) * (size_t)(n))
 
+/* The EM path (forward, backward, leaf statistics, clear, M-step) is written over `real`.  The
+ * default build has real = float and follows the reference's Float32 arithmetic; a second build
+ * with -DORC_F64 has real = double and takes every matrix, the statistics and the parameter
+ * arrays as double (the caller converts the same fp32 parameters), which gives the exact answer
+ * that two fp32 implementations with different summation orders are both compared with. */
+#ifdef ORC_F64
+typedef double real;
+#define REXP exp
+#define RLOG log
+#define RLOG1P log1p
+#define RMAX fmax
+#define RABS fabs
+#else
+typedef float real;
+#define REXP expf
+#define RLOG logf
+#define RLOG1P log1pf
+#define RMAX fmaxf
+#define RABS fabsf
+#endif
+int orc_real_bytes(void) { return (int)sizeof(real); }
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
@@ -60,9 +82,9 @@ double orc_log(double x) { return pcb_log(x); }
 
 /* ProbabilisticCircuits.logsumexp(x::Float32, y::Float32), the sum_agg_func of
  * queries/likelihood.jl:101-102. */
-static inline float lse2(float x, float y) {
-  if (isfinite(x) && isfinite(y)) return fmaxf(x, y) + log1pf(expf(-fabsf(x - y)));
-  return fmaxf(x, y);
+static inline real lse2(real x, real y) {
+  if (isfinite(x) && isfinite(y)) return RMAX(x, y) + RLOG1P(REXP(-RABS(x - y)));
+  return RMAX(x, y);
 }
 
 /* ------------------------------------------------------------------------------------ */
@@ -140,38 +162,62 @@ static inline int64_t data_row(const int32_t* row_ids, uint32_t row_start, uint3
 }
 
 /* mars [B, N] column-major (ld = B); edge_mars [B, E] or NULL */
-void orc_forward(const pcb_circuit_desc* d, const float* up_logp, const float* heap,
+/* Examples are processed in blocks of ORC_RB consecutive rows: the loop over the rows of a block is
+ * the innermost one, so an edge's indices are read once per block and the rows of a node are
+ * contiguous in memory.  Per example the sequence of operations is exactly the reference's
+ * per-edge loop in edge order. */
+#define ORC_RB 16
+static uint32_t g_row_block = ORC_RB;
+/* rows per block, 1 .. ORC_RB: a short batch timed on many threads takes smaller blocks */
+void orc_set_row_block(int n) { g_row_block = n < 1 ? 1u : (n > ORC_RB ? (uint32_t)ORC_RB : (uint32_t)n); }
+
+void orc_forward(const pcb_circuit_desc* d, const real* up_logp, const real* heap,
                  const uint8_t* data, const uint8_t* miss, uint64_t num_rows,
-                 const int32_t* row_ids, uint32_t row_start, uint32_t B, float* mars,
-                 float* edge_mars) {
-  const uint32_t N = d->num_nodes, E = d->num_edges;
-#pragma omp parallel for schedule(static)
-  for (int64_t b = 0; b < (int64_t)B; ++b) {
-    int64_t row = data_row(row_ids, row_start, (uint32_t)b);
+                 const int32_t* row_ids, uint32_t row_start, uint32_t B, real* mars,
+                 real* edge_mars) {
+  const uint32_t N = d->num_nodes, E = d->num_edges, RB = g_row_block;
+  const int64_t nblk = ((int64_t)B + RB - 1) / RB;
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int64_t blk = 0; blk < nblk; ++blk) {
+    const uint32_t b0 = (uint32_t)(blk * RB);
+    const uint32_t nb = B - b0 < RB ? B - b0 : RB;
+    int64_t rows[ORC_RB];
+    for (uint32_t j = 0; j < nb; ++j) rows[j] = data_row(row_ids, row_start, b0 + j);
     /* reg_likelihood.jl:26-46 (soft_reg = 0: the plain lookup) */
     for (uint32_t n = 0; n < N; ++n) {
-      float v;
-      if (d->node_kind[n] == PCB_SUM) v = -INFINITY;
-      else if (d->node_kind[n] == PCB_PRODUCT) v = 0.0f;
+      real* out = mars + IDX(b0, n, B);
+      if (d->node_kind[n] == PCB_SUM) { for (uint32_t j = 0; j < nb; ++j) out[j] = -(real)INFINITY; }
+      else if (d->node_kind[n] == PCB_PRODUCT) { for (uint32_t j = 0; j < nb; ++j) out[j] = (real)0; }
       else {
-        size_t di = (size_t)row + (size_t)num_rows * (d->node_var[n] - 1);
-        if (miss && miss[di]) v = 0.0f;
-        else v = heap[d->node_heap_start[n] - 1 + data[di]];
+        const size_t col = (size_t)num_rows * (d->node_var[n] - 1);
+        const real* tab = heap + d->node_heap_start[n] - 1;
+        for (uint32_t j = 0; j < nb; ++j) {
+          size_t di = (size_t)rows[j] + col;
+          out[j] = (miss && miss[di]) ? (real)0 : tab[data[di]];
+        }
       }
-      mars[IDX(b, n, B)] = v;
     }
     /* likelihood.jl:18-64, one thread owning every edge of the node */
-    float acc = 0.0f;
+    real acc[ORC_RB];
+    for (uint32_t j = 0; j < ORC_RB; ++j) acc[j] = (real)0;
     for (uint32_t e = 0; e < E; ++e) {
-      int issum = edge_is_sum(d, e);
-      float child = mars[IDX(b, d->up_prime[e] - 1, B)];
-      if (d->up_sub[e] != 0) child += mars[IDX(b, d->up_sub[e] - 1, B)];
-      if (issum) child += up_logp[e];
-      if (edge_mars) edge_mars[IDX(b, e, B)] = child;
-      if (edge_first(d, e)) acc = child;
-      else if (issum) acc = lse2(acc, child);
-      else acc += child;
-      if (edge_last(d, e)) mars[IDX(b, d->up_parent[e] - 1, B)] = acc;
+      const int issum = edge_is_sum(d, e), first = edge_first(d, e);
+      const real* pv = mars + IDX(b0, d->up_prime[e] - 1, B);
+      const real* sv = d->up_sub[e] != 0 ? mars + IDX(b0, d->up_sub[e] - 1, B) : NULL;
+      const real lp = issum ? up_logp[e] : (real)0;
+      for (uint32_t j = 0; j < nb; ++j) {
+        real child = pv[j];
+        if (sv) child += sv[j];
+        if (issum) child += lp;
+        if (edge_mars) edge_mars[IDX(b0 + j, e, B)] = child;
+        if (first) acc[j] = child;
+        else if (issum) acc[j] = lse2(acc[j], child);
+        else acc[j] += child;
+      }
+      if (edge_last(d, e)) {
+        real* out = mars + IDX(b0, d->up_parent[e] - 1, B);
+        for (uint32_t j = 0; j < nb; ++j) out[j] = acc[j];
+      }
     }
   }
 }
@@ -180,56 +226,64 @@ void orc_forward(const pcb_circuit_desc* d, const float* up_logp, const float* h
 /* backward: flows_circuit / reg_flows_circuit                                            */
 /* ------------------------------------------------------------------------------------ */
 /* flows [B, N]; edge_flows [B, E] in up-edge order or NULL (flow.jl:70-71);
- * edge_aggr [E] in down-edge order, accumulated into (flow.jl:75-81), may be NULL. */
-void orc_backward(const pcb_circuit_desc* d, const float* up_logp, const float* mars, uint32_t B,
-                  float* flows, float* edge_flows, float* edge_aggr) {
+ * edge_aggr [E] in down-edge order, accumulated into (flow.jl:75-81), may be NULL.  The sum over
+ * the examples of an edge is collected in one double per edge shared by all threads (one atomic
+ * add per edge and block of rows) and rounded once at the end. */
+void orc_backward(const pcb_circuit_desc* d, const real* up_logp, const real* mars, uint32_t B,
+                  real* flows, real* edge_flows, real* edge_aggr) {
   const uint32_t N = d->num_nodes, E = d->num_edges;
-  int nt = orc_num_threads();
-  double* part = edge_aggr ? (double*)calloc((size_t)nt * E, sizeof(double)) : NULL;
-#pragma omp parallel
-  {
-#ifdef _OPENMP
-    int tid = omp_get_thread_num();
-#else
-    int tid = 0;
-#endif
-    double* my = part ? part + (size_t)tid * E : NULL;
-#pragma omp for schedule(static)
-    for (int64_t b = 0; b < (int64_t)B; ++b) {
-      for (uint32_t n = 0; n < N; ++n) flows[IDX(b, n, B)] = 0.0f; /* flow.jl:140-143 */
-      flows[IDX(b, N - 1, B)] = 1.0f;
-      for (uint32_t de = 0; de < E; ++de) {
-        uint32_t e = d->down2up[de] - 1;
-        uint32_t parent = d->up_parent[e] - 1, prime = d->up_prime[e] - 1, sub = d->up_sub[e];
-        float ef = flows[IDX(b, parent, B)];
-        if (edge_is_sum(d, e)) { /* flow.jl:53-60 */
-          float parent_mar = mars[IDX(b, parent, B)];
-          float child = mars[IDX(b, prime, B)] + up_logp[e];
-          if (sub != 0) child += mars[IDX(b, sub - 1, B)];
-          ef = ef * expf(child - parent_mar);
+  double* part = edge_aggr ? (double*)calloc((size_t)E, sizeof(double)) : NULL;
+  const uint32_t RB = g_row_block;
+  const int64_t nblk = ((int64_t)B + RB - 1) / RB;
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int64_t blk = 0; blk < nblk; ++blk) {
+    const uint32_t b0 = (uint32_t)(blk * RB);
+    const uint32_t nb = B - b0 < RB ? B - b0 : RB;
+    for (uint32_t n = 0; n < N; ++n) { /* flow.jl:140-143 */
+      real* f = flows + IDX(b0, n, B);
+      const real init = n == N - 1 ? (real)1 : (real)0;
+      for (uint32_t j = 0; j < nb; ++j) f[j] = init;
+    }
+    for (uint32_t de = 0; de < E; ++de) {
+      const uint32_t e = d->down2up[de] - 1;
+      const uint32_t parent = d->up_parent[e] - 1, prime = d->up_prime[e] - 1, sub = d->up_sub[e];
+      const int issum = edge_is_sum(d, e);
+      const real* fp = flows + IDX(b0, parent, B);
+      const real* mp = mars + IDX(b0, parent, B);
+      const real* mc = mars + IDX(b0, prime, B);
+      const real* ms = sub != 0 ? mars + IDX(b0, sub - 1, B) : NULL;
+      real* fc = flows + IDX(b0, prime, B);
+      real* fs = sub != 0 ? flows + IDX(b0, sub - 1, B) : NULL;
+      double tot = 0.0;
+      for (uint32_t j = 0; j < nb; ++j) {
+        real ef = fp[j];
+        if (issum) { /* flow.jl:53-60 */
+          real child = mc[j] + up_logp[e];
+          if (ms) child += ms[j];
+          ef = ef * REXP(child - mp[j]);
         }
-        if (sub != 0) flows[IDX(b, sub - 1, B)] += ef;
-        if (edge_flows) edge_flows[IDX(b, e, B)] = ef;
-        if (my) my[de] += (double)ef;
-        flows[IDX(b, prime, B)] += ef;
+        if (fs) fs[j] += ef;
+        if (edge_flows) edge_flows[IDX(b0 + j, e, B)] = ef;
+        tot += (double)ef;
+        fc[j] += ef;
+      }
+      if (part) {
+#pragma omp atomic
+        part[de] += tot;
       }
     }
   }
   if (edge_aggr) {
-    for (uint32_t de = 0; de < E; ++de) {
-      double s = 0.0;
-      for (int t = 0; t < nt; ++t) s += part[(size_t)t * E + de];
-      edge_aggr[de] = (float)((double)edge_aggr[de] + s);
-    }
+    for (uint32_t de = 0; de < E; ++de) edge_aggr[de] = (real)((double)edge_aggr[de] + part[de]);
     free(part);
   }
 }
 
 /* input_flows_circuit_with_reg_kernel (reg_flow.jl:24-48) with soft_reg = 0, i.e. the plain
  * flow() of fixable_categorical_dist.jl:121-130.  weights is per data row or NULL. */
-void orc_input_flows(const pcb_circuit_desc* d, float* heap, const float* flows,
+void orc_input_flows(const pcb_circuit_desc* d, real* heap, const real* flows,
                      const uint8_t* data, const uint8_t* miss, uint64_t num_rows,
-                     const int32_t* row_ids, uint32_t row_start, uint32_t B, const float* weights) {
+                     const int32_t* row_ids, uint32_t row_start, uint32_t B, const real* weights) {
 #pragma omp parallel for schedule(dynamic, 16)
   for (int64_t i = 0; i < (int64_t)d->num_input_nodes; ++i) {
     uint32_t n = d->input_node_ids[i] - 1;
@@ -239,78 +293,85 @@ void orc_input_flows(const pcb_circuit_desc* d, float* heap, const float* flows,
     double* acc = (double*)calloc(C + 1, sizeof(double));
     for (uint32_t b = 0; b < B; ++b) {
       int64_t row = data_row(row_ids, row_start, b);
-      float f = flows[IDX(b, n, B)];
+      real f = flows[IDX(b, n, B)];
       if (weights) f *= weights[row];
       size_t di = (size_t)row + (size_t)num_rows * (d->node_var[n] - 1);
       if (miss && miss[di]) acc[C] += (double)f;
       else acc[data[di]] += (double)f;
     }
-    for (uint32_t c = 0; c <= C; ++c) heap[hs + C + c] = (float)((double)heap[hs + C + c] + acc[c]);
+    for (uint32_t c = 0; c <= C; ++c) heap[hs + C + c] = (real)((double)heap[hs + C + c] + acc[c]);
     free(acc);
   }
 }
 
 /* edge_aggr .*= rate ; clear_memory(d, heap, rate) (fixable_categorical_dist.jl:250-260) */
-void orc_clear_flows(const pcb_circuit_desc* d, float* edge_aggr, float* heap, float rate) {
-  if (edge_aggr) for (uint32_t e = 0; e < d->num_edges; ++e) edge_aggr[e] = (rate == 0.0f) ? 0.0f : edge_aggr[e] * rate;
+void orc_clear_flows(const pcb_circuit_desc* d, real* edge_aggr, real* heap, real rate) {
+  if (edge_aggr) for (uint32_t e = 0; e < d->num_edges; ++e) edge_aggr[e] = (rate == (real)0) ? (real)0 : edge_aggr[e] * rate;
   for (uint32_t i = 0; i < d->num_input_nodes; ++i) {
     uint32_t n = d->input_node_ids[i] - 1;
     if (d->node_fixed[n]) continue;
     uint32_t C = d->node_num_cats[n];
     size_t hs = d->node_heap_start[n] - 1;
-    for (uint32_t c = 0; c <= C; ++c) heap[hs + C + c] = (rate == 0.0f) ? 0.0f : heap[hs + C + c] * rate;
+    for (uint32_t c = 0; c <= C; ++c) heap[hs + C + c] = (rate == (real)0) ? (real)0 : heap[hs + C + c] * rate;
   }
 }
 
 /* M-step.  edge_aggr is in down-edge order and is modified (pseudocount added), as the
  * reference does.  up_logp is updated in place (the reference writes both edge copies). */
-void orc_em_update(const pcb_circuit_desc* d, float* up_logp, float* edge_aggr, float* heap,
-                   float pseudocount, float inertia) {
+void orc_em_update(const pcb_circuit_desc* d, real* up_logp, real* edge_aggr, real* heap,
+                   real pseudocount, real inertia) {
   const uint32_t N = d->num_nodes, E = d->num_edges;
-  float* node_aggr = (float*)calloc(N, sizeof(float));
+  real* node_aggr = (real*)calloc(N, sizeof(real));
   /* count_siblings + add_pseudocount (mini_batch_warmup.jl:4-23, gate removed) */
   for (uint32_t e = 0; e < E; ++e)
-    if (edge_is_sum(d, e)) node_aggr[d->up_parent[e] - 1] += 1.0f;
-  for (uint32_t de = 0; de < E; ++de) {
+    if (edge_is_sum(d, e)) node_aggr[d->up_parent[e] - 1] += (real)1;
+#pragma omp parallel for schedule(static)
+  for (int64_t de = 0; de < (int64_t)E; ++de) {
     uint32_t e = d->down2up[de] - 1;
     if (edge_is_sum(d, e)) edge_aggr[de] += pseudocount / node_aggr[d->up_parent[e] - 1];
   }
   /* aggr_node_flows (adam.jl:30-36) */
-  memset(node_aggr, 0, N * sizeof(float));
+  memset(node_aggr, 0, N * sizeof(real));
   {
     double* na = (double*)calloc(N, sizeof(double));
-    for (uint32_t de = 0; de < E; ++de) {
+#pragma omp parallel for schedule(static)
+    for (int64_t de = 0; de < (int64_t)E; ++de) {
       uint32_t e = d->down2up[de] - 1;
-      if (edge_is_sum(d, e)) na[d->up_parent[e] - 1] += (double)edge_aggr[de];
+      if (edge_is_sum(d, e)) {
+#pragma omp atomic
+        na[d->up_parent[e] - 1] += (double)edge_aggr[de];
+      }
     }
-    for (uint32_t n = 0; n < N; ++n) node_aggr[n] = (float)na[n];
+    for (uint32_t n = 0; n < N; ++n) node_aggr[n] = (real)na[n];
     free(na);
   }
   /* update_params (reg_em.jl:136-168 / mini_batch_warmup.jl:39-76 without the gate) */
-  for (uint32_t de = 0; de < E; ++de) {
+#pragma omp parallel for schedule(static)
+  for (int64_t de = 0; de < (int64_t)E; ++de) {
     uint32_t e = d->down2up[de] - 1;
     if (!edge_is_sum(d, e)) continue;
     if (edge_first(d, e) && edge_last(d, e)) continue;
-    float oldv = inertia * expf(up_logp[e]);
-    float newv = (1.0f - inertia) * edge_aggr[de] / node_aggr[d->up_parent[e] - 1];
-    up_logp[e] = logf(oldv + newv);
+    real oldv = inertia * REXP(up_logp[e]);
+    real newv = ((real)1 - inertia) * edge_aggr[de] / node_aggr[d->up_parent[e] - 1];
+    up_logp[e] = RLOG(oldv + newv);
   }
   free(node_aggr);
   /* update_input_node_params (fixable_categorical_dist.jl:223-248) */
-  for (uint32_t i = 0; i < d->num_input_nodes; ++i) {
+#pragma omp parallel for schedule(dynamic, 64)
+  for (int64_t i = 0; i < (int64_t)d->num_input_nodes; ++i) {
     uint32_t n = d->input_node_ids[i] - 1;
     if (d->node_fixed[n]) continue;
     uint32_t C = d->node_num_cats[n];
     size_t hs = d->node_heap_start[n] - 1;
-    float node_flow = 0.0f, cat_pc = pseudocount / (float)C;
+    real node_flow = (real)0, cat_pc = pseudocount / (real)C;
     for (uint32_t c = 0; c < C; ++c) node_flow += heap[hs + C + c];
-    float missing_flow = heap[hs + 2 * C];
+    real missing_flow = heap[hs + 2 * C];
     node_flow += missing_flow + pseudocount;
     for (uint32_t c = 0; c < C; ++c) {
-      float oldp = expf(heap[hs + c]);
-      float oldv = inertia * oldp;
-      float newv = (1.0f - inertia) * (heap[hs + C + c] + cat_pc + missing_flow * oldp) / node_flow;
-      heap[hs + c] = logf(oldv + newv);
+      real oldp = REXP(heap[hs + c]);
+      real oldv = inertia * oldp;
+      real newv = ((real)1 - inertia) * (heap[hs + C + c] + cat_pc + missing_flow * oldp) / node_flow;
+      heap[hs + c] = RLOG(oldv + newv);
     }
   }
 }

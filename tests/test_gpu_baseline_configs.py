@@ -1,0 +1,156 @@
+"""CUDA path vs the CPU oracle on the benchmark configurations at their stated sizes, through the
+reference-named entry points (api.loglikelihoods / full_batch_em / mini_batch_em / kld /
+kld_backward / Adam / sample), and at the block shape of the headline workload.
+
+  config 1  10 000 x 64 binary rows, HCLT k = 16 on their Chow-Liu tree: LL of rows 1..1024, then one
+            full-batch EM step over all rows (pseudocount 0.1)
+  config 4  two HCLTs over 784 binary variables, k = 64: KLD(q || p), its gradient, one Adam step,
+            4096 hard samples bit-exact
+  headline  the 96-variable cut of the 3072-variable image HCLT with 256 latents and 256
+            categories, 256 rows (two 128-row tiles): LL, the root block's edge statistics, the
+            parameters after one mini-batch step
+"""
+import numpy as np
+import pytest
+
+from tests.helpers import random_data, random_hclt, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4   # relative, fp32: the tolerance the workload definition states
+
+
+def _cuda():
+    import torch
+    from lvd_pg_b200 import api
+    assert torch.cuda.is_available()
+    return torch, api
+
+
+def test_config1_loglikelihoods_and_full_batch_em(oracle):
+    torch, api = _cuda()
+    from lvd_pg_b200 import synth
+    data, fc = synth.config1()
+    assert data.shape == (10000, 64) and fc.meta.get("k") == 16
+    ref = fc.copy()
+    m = api.CuMetaBitsProbCircuit(fc)
+    dd = api.DeviceData(data, m.device)
+    # log-likelihood of rows 1..1024 in batches of 512 (reg_likelihood.jl:139-162)
+    ll = api.loglikelihoods(m, api.DeviceData(data[:1024], m.device), batch_size=512).cpu().numpy()
+    ll_ref = oracle.forward(ref, data[:1024])[:, -1]
+    assert rel_err(ll, ll_ref) <= TOL
+    # one full-batch EM step over the 10 000 rows: statistics gathered over 4 batches, one update, inertia 0
+    out = api.full_batch_em(m, dd, 1, batch_size=2500, pseudocount=0.1)
+    aggr_ref = np.zeros(ref.num_edges, np.float32)
+    ll_all, _ = oracle.em_step(ref, data, pseudocount=0.1, inertia=0.0, edge_aggr=aggr_ref)   # aggr_ref: after the update
+    assert abs(out[0] - ll_all / 10000) <= TOL * abs(ll_all / 10000)
+    p, p_ref = api.vectorize_parameters(m), oracle.vectorize(ref)
+    assert np.abs(np.exp(p) - np.exp(p_ref)).max() <= TOL
+    assert np.abs(p - p_ref).max() <= TOL * max(1.0, np.abs(p_ref).max())
+    sum_edges = ref.edge_is_sum[ref.down2up.astype(np.int64) - 1]
+    # edge_aggr keeps the pseudocount after the update, as the reference's does
+    assert rel_err(m.edge_aggr()[sum_edges], aggr_ref[sum_edges]) <= TOL
+
+
+def test_config4_kld_gradient_adam_and_sampling(oracle):
+    torch, api = _cuda()
+    from lvd_pg_b200 import synth
+    q, p = synth.config4()
+    assert q.num_vars == 784 and q.meta.get("k") == 64
+    m = api.CuMetaBitsProbCircuit(q)
+    tq, tp = oracle.vectorize(q), oracle.vectorize(p)
+    theta = torch.from_numpy(tq.copy()).to(m.device)
+    k, reuse = api.kld(m, theta, tp)
+    klds_ref, ek_ref = oracle.kld(q, tq, tp)
+    assert rel_err(k.cpu().numpy(), klds_ref[:, -1]) <= TOL
+    g1, g2 = api.kld_backward(m, reuse=reuse)
+    ref = oracle.kld_backward(q, tq, tp, klds_ref, ek_ref)
+    assert rel_err(g1.cpu().numpy(), ref["param_grads1"], 1e-2) <= TOL
+    assert rel_err(g2.cpu().numpy(), ref["param_grads2"]) <= TOL
+    # one Adam step (lr 1e-2, beta 0.9 / 0.999) on q's parameters, then re-normalisation
+    opt = api.Adam(m, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8)
+    opt.step(theta, g1, sign=-1.0)
+    th_ref, m_ref, v_ref = tq.copy(), np.zeros_like(tq), np.zeros_like(tq)
+    oracle.adam_step(q, th_ref, ref["param_grads1"][0], m_ref, v_ref, 1, lr=1e-2, sign=-1.0)
+    assert np.abs(np.exp(theta.cpu().numpy()) - np.exp(th_ref)).max() <= TOL
+    # 4096 hard samples from q, same uniform buffers (seed 5) on both sides: bit-exact
+    S = 4096
+    shp = api.noise_shapes(m, S)
+    rng = np.random.default_rng(5)
+    u_sum, u_leaf = rng.random(shp[0], dtype=np.float32), rng.random(shp[1], dtype=np.float32)
+    x = api.sample(m, tq, u_sum, u_leaf).cpu().numpy()
+    x_ref = oracle.sample_hard(q, tq, u_sum, u_leaf, S)
+    assert np.array_equal(x, x_ref)
+
+
+def test_headline_block_shape_against_oracle(oracle):
+    torch, api = _cuda()
+    from lvd_pg_b200 import synth
+    images, fc = synth.image_hclt(256, 4096, 32, 2.0, 3, "cuda", num_vars=96)
+    data = images[:256].cpu().numpy()
+    ref = fc.copy()
+    m = api.CuMetaBitsProbCircuit(fc, 0)
+    assert m.info.num_dense_blocks > 0 and m.info.max_group_size == 256
+    ll_dev = torch.zeros(1, device=m.device)
+    api.em_step(m, data, pseudocount=0.1, inertia=0.9, ll_sum=ll_dev)
+    aggr_ref = np.zeros(ref.num_edges, np.float32)
+    ll_ref, _ = oracle.em_step(ref, data, pseudocount=0.1, inertia=0.9, edge_aggr=aggr_ref)   # aggr_ref: after the update
+    assert abs(ll_dev.item() - ll_ref) <= TOL * abs(ll_ref)
+    # the root block's edge statistics (first down-edges are the root's, misc_tests.jl:27-30)
+    root_edges = np.nonzero(ref.up_parent[ref.down2up.astype(np.int64) - 1] == ref.num_nodes)[0]
+    assert len(root_edges) == 256
+    assert rel_err(m.edge_aggr()[root_edges], aggr_ref[root_edges]) <= TOL
+    p, p_ref = api.vectorize_parameters(m), oracle.vectorize(ref)
+    assert np.abs(np.exp(p) - np.exp(p_ref)).max() <= TOL
+
+
+def test_flow_memory_steps_track_oracle(oracle):
+    """clear_rate > 0: the statistics of earlier batches decay instead of being cleared
+    (flow_memory of reg_em.jl:276-284; clear_memory of fixable_categorical_dist.jl:250-260)."""
+    torch, api = _cuda()
+    fc = random_hclt(10, 16, 3, 5)
+    data, _ = random_data(300, fc.num_vars, 3, 9)
+    ref = fc.copy()
+    m = api.CuMetaBitsProbCircuit(fc)
+    dd = api.DeviceData(data, m.device)
+    rng = np.random.default_rng(1)
+    ll_dev = torch.zeros(1, device=m.device)
+    aggr = np.zeros(ref.num_edges, np.float32)
+    sum_edges = ref.edge_is_sum[ref.down2up.astype(np.int64) - 1]
+    for step in range(4):
+        ids = (rng.permutation(300)[:96] + 1).astype(np.int32)
+        ll_ref, _ = oracle.em_step(ref, data, row_ids=ids, pseudocount=0.1, inertia=0.8, edge_aggr=aggr, clear_rate=0.6)
+        api.em_step(m, dd, torch.from_numpy(ids).to(m.device), pseudocount=0.1, inertia=0.8, clear_rate=0.6, ll_sum=ll_dev)
+        assert abs(ll_dev.item() - ll_ref) <= TOL * abs(ll_ref)
+        assert rel_err(m.edge_aggr()[sum_edges], aggr[sum_edges]) <= TOL, step
+        assert rel_err(m.heap(), ref.heap) <= TOL, step
+        p, p_ref = api.vectorize_parameters(m), oracle.vectorize(ref)
+        assert np.abs(np.exp(p) - np.exp(p_ref)).max() <= TOL
+
+
+def test_mini_batch_em_loop_matches_an_oracle_loop(oracle):
+    """api.mini_batch_em as a whole (reg_em.jl:208-336): shuffled batches, dropped last batch,
+    inertia schedule over the epochs, flow memory, per-epoch mean log-likelihood."""
+    torch, api = _cuda()
+    fc = random_hclt(9, 8, 4, 13)
+    data, _ = random_data(230, fc.num_vars, 4, 6)
+    ref = fc.copy()
+    m = api.CuMetaBitsProbCircuit(fc)
+    epochs, bs, pc, i0, i1, fm = 3, 64, 0.1, 0.9, 0.5, 150.0
+    got = api.mini_batch_em(m, data, epochs, bs, pc, i0, i1, flow_memory=fm, seed=77)
+    rng = np.random.default_rng(77)
+    nb = 230 // bs
+    rate = max(0.0, 1.0 - (bs + pc) / fm)
+    aggr = np.zeros(ref.num_edges, np.float32)
+    inertia, want = i0, []
+    for _ in range(epochs):
+        perm = (rng.permutation(230) + 1).astype(np.int32)
+        lls = []
+        for b in range(nb):
+            ll, _ = oracle.em_step(ref, data, row_ids=perm[b * bs:(b + 1) * bs], pseudocount=pc, inertia=inertia,
+                                   edge_aggr=aggr, clear_rate=rate)
+            lls.append(ll)
+        want.append(sum(lls) / bs / nb)
+        inertia += (i1 - i0) / epochs
+    assert np.allclose(got, want, rtol=TOL)
+    p, p_ref = api.vectorize_parameters(m), oracle.vectorize(ref)
+    assert np.abs(np.exp(p) - np.exp(p_ref)).max() <= TOL
