@@ -393,7 +393,7 @@ void free_circuit(pcb_circuit* c) {
   void* ptrs[] = {c->theta, c->aggr, c->kind, c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime,
                   c->e_sub, c->in_node, c->in_var, c->in_cats, c->in_poff, c->in_foff, c->node2input,
                   c->up_all, c->up_sparse, c->down_all, c->down_sparse, c->in_off, c->in_ent, c->dense,
-                  c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status, c->w_img, c->dense_img,
+                  c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status, c->w_img, c->dense_img, c->w_img16, c->dense_img16,
                   c->lgrp_var, c->lgrp_off, c->s_node, c->s_leaf};
   for (void* p : ptrs) if (p) cudaFree(p);
   if (c->ev_g0) cudaEventDestroy(c->ev_g0);

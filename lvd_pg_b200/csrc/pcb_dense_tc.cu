@@ -854,9 +854,11 @@ uint32_t pick_nsplit(uint32_t ctas, uint32_t max_cols, int forced) {
 
 // Lays out the weight images of every dense block (host side) and allocates them.
 int32_t pcb_dense_tc_prepare(pcb_circuit* c, uint64_t* bytes) {
-  std::vector<PcbDenseImg> imgs(c->h_dense.size());
+  if (const char* e = getenv("PCB_TC_IMPL")) c->tc_mn = std::string(e) != "km";   // km: the K-major staging kernels of this file
+  if (c->tc_mn) PCB_TRY(pcb_dense_mn_prepare(c, bytes));
+  std::vector<PcbDenseImg> imgs(c->tc_mn ? 0 : c->h_dense.size());
   uint64_t off = 0;
-  for (size_t i = 0; i < c->h_dense.size(); ++i) {
+  for (size_t i = 0; i < imgs.size(); ++i) {
     const PcbDenseBlock& k = c->h_dense[i];
     PcbDenseImg& im = imgs[i];
     im.rows_f = std::min<uint32_t>(TN_MAX, pcb_round_up(k.R, 16));
@@ -890,6 +892,11 @@ int32_t pcb_dense_tc_prepare(pcb_circuit* c, uint64_t* bytes) {
 // Regenerates the weight images if the parameters changed since they were last written.
 int32_t pcb_dense_tc_refresh(pcb_circuit* c, cudaStream_t st) {
   if (c->w_img_valid || c->n_dense == 0) return PCB_OK;
+  if (c->tc_mn) {
+    PCB_TRY(pcb_dense_mn_refresh(c, st));
+    c->w_img_valid = true;
+    return PCB_OK;
+  }
   for (uint32_t z0 = 0; z0 < c->n_dense; z0 += 65535) {
     uint32_t nz = std::min<uint32_t>(65535, c->n_dense - z0);
     dim3 grid((c->max_dense_K + 31) / 32, (c->max_dense_R + 31) / 32, nz);
@@ -903,6 +910,7 @@ int32_t pcb_dense_tc_refresh(pcb_circuit* c, cudaStream_t st) {
 int32_t pcb_dense_tc_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st) {
   uint32_t o0 = c->h_dense_off[layer], o1 = c->h_dense_off[layer + 1];
   if (o1 == o0) return PCB_OK;
+  if (c->tc_mn) return pcb_dense_mn_forward(c, ws, layer, st);
   const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM;
   TcArgs args = make_args(c, ws, o0);
   const uint32_t ct = (c->max_dense_R + TN_MAX - 1) / TN_MAX;
@@ -960,6 +968,7 @@ int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer,
     uint32_t tiles = ((c->max_dense_R + TM - 1) / TM) * ((c->max_dense_K + TN_MAX - 1) / TN_MAX);
     if (!c->side || (c->edge_hi - c->edge_lo) * tiles >= c->edge_batch_tiles) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
   }
+  if (c->tc_mn) return pcb_dense_mn_backward_child(c, ws, layer, st);
   TcArgs args = make_args(c, ws, o0);
   {
     const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM, ct = (c->max_dense_K + TN_MAX - 1) / TN_MAX;

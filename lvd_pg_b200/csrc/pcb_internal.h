@@ -148,6 +148,12 @@ struct pcb_circuit {
   PcbDenseImg* dense_img = nullptr;
   uint64_t w_img_len = 0;
   bool w_img_valid = false;
+  // 16-deep weight images of the kernels that read the data-dependent operand example-major
+  // (pcb_dense_mn.cu); tc_mn selects those kernels for values and child flows
+  bool tc_mn = true;
+  float* w_img16 = nullptr;
+  PcbDenseImg* dense_img16 = nullptr;
+  uint64_t w_img16_len = 0;
   // edge statistics feed nothing downstream in the backward pass, so their kernels run on a
   // side stream, forked from and joined to the caller's stream with two reusable events
   cudaStream_t side = nullptr;
@@ -305,3 +311,7 @@ int32_t pcb_dense_edge_prepare_ws(pcb_workspace* ws);
 int32_t pcb_dense_edge_launch(pcb_circuit* c, pcb_workspace* ws, uint32_t o0, uint32_t n, uint32_t slices,
                               uint32_t b_per, cudaStream_t st);
 int32_t pcb_dense_tc_flush_edges(pcb_circuit* c, pcb_workspace* ws, cudaStream_t st);
+int32_t pcb_dense_mn_prepare(pcb_circuit* c, uint64_t* bytes);
+int32_t pcb_dense_mn_refresh(pcb_circuit* c, cudaStream_t st);
+int32_t pcb_dense_mn_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
+int32_t pcb_dense_mn_backward_child(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);

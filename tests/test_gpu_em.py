@@ -51,10 +51,10 @@ def test_forward_backward_update(oracle, name, make, c, rows, missing):
     m.lib.pcb_clear_flows(m.handle, 0.0, None)
     api.backward(m, ws)
     flows = m.flows(ws, B)
-    assert rel_err(flows, flows_ref) <= 2 * TOL
+    assert rel_err(flows, flows_ref) <= TOL
     sum_edges = ref.edge_is_sum[ref.down2up.astype(np.int64) - 1]
-    assert rel_err(m.edge_aggr()[sum_edges], aggr_ref[sum_edges]) <= 2 * TOL
-    assert rel_err(m.heap(), ref.heap) <= 2 * TOL
+    assert rel_err(m.edge_aggr()[sum_edges], aggr_ref[sum_edges]) <= TOL
+    assert rel_err(m.heap(), ref.heap) <= TOL
 
     # M-step
     oracle.em_update(ref, aggr_ref, 0.1, 0.3)
@@ -79,7 +79,7 @@ def test_dense_and_sparse_paths_agree(oracle, monkeypatch):
         api.em_step(m, data, pseudocount=0.1, inertia=0.5)
         outs.append((api.vectorize_parameters(m), m.edge_aggr()))
     assert np.abs(outs[0][0] - outs[1][0]).max() <= TOL
-    assert rel_err(outs[0][1], outs[1][1]) <= 2 * TOL
+    assert rel_err(outs[0][1], outs[1][1]) <= TOL
 
 
 def test_tensor_core_and_simt_dense_kernels_agree(monkeypatch):
@@ -97,6 +97,29 @@ def test_tensor_core_and_simt_dense_kernels_agree(monkeypatch):
     assert abs(outs[0][2] - outs[1][2]) <= 1e-5 * abs(outs[1][2])
     assert np.abs(outs[0][0] - outs[1][0]).max() <= TOL
     assert rel_err(outs[0][1], outs[1][1]) <= TOL
+
+
+def test_example_major_and_k_major_tensor_core_kernels_agree(monkeypatch):
+    """The kernels that read the data-dependent operand example-major (pcb_dense_mn.cu, the default)
+    against the K-major staging kernels of pcb_dense_tc.cu (PCB_TC_IMPL=km), ragged and full tiles,
+    with and without column splits."""
+    torch, api = _cuda()
+    for fc, rows in ((random_hclt(6, 256, 3, 31), 300), (random_hclt(9, 80, 4, 32), 77)):
+        data, _ = random_data(rows, fc.num_vars, int(fc.meta["num_cats"]), 5)
+        outs = []
+        for impl, nsplit in (("mn", "0"), ("km", "0"), ("mn", "1"), ("mn", "4")):
+            monkeypatch.setenv("PCB_TC_IMPL", impl)
+            monkeypatch.setenv("PCB_TC_NSPLIT", nsplit)
+            m = api.CuMetaBitsProbCircuit(fc.copy())
+            assert m.info.num_dense_blocks > 0
+            ll = torch.zeros(1, device=m.device)
+            ws = api.em_step(m, data, pseudocount=0.1, inertia=0.5, ll_sum=ll)
+            outs.append((api.vectorize_parameters(m), m.edge_aggr(), ll.item(), m.flows(ws, rows)))
+        for o in outs[1:]:
+            assert abs(o[2] - outs[0][2]) <= 1e-5 * abs(outs[0][2])
+            assert np.abs(np.exp(o[0]) - np.exp(outs[0][0])).max() <= TOL
+            assert rel_err(o[1], outs[0][1]) <= TOL
+            assert rel_err(o[3], outs[0][3]) <= TOL
 
 
 def test_em_steps_track_oracle_with_row_ids(oracle):
