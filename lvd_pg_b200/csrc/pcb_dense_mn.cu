@@ -12,7 +12,7 @@
 // The work matrices are node-major with the example index contiguous, so the rows a tile needs are
 // [K rows][128 examples] slabs: 512 contiguous bytes per row.  That is an M-major ("MN-major") A
 // operand for a 128 (examples) x N x K tile, and tcgen05 reads such an operand from shared memory
-// directly: 128-byte rows of 32 examples, eight K rows per 1 KB swizzle atom.  A producer warp
+// directly: 128-byte rows of 32 examples, four K rows per 512-byte swizzle atom.  A producer warp
 // therefore loads one K row of the tile with a single fully coalesced 16-byte-per-lane request,
 // applies exp / rescale, splits into TF32 hi / lo and stores 16 bytes per lane — no transposition
 // through registers, a quarter of the instructions of a K-major staging.
@@ -44,7 +44,7 @@ constexpr uint32_t STAGES = 2;
 constexpr uint32_t PW = 8;              // producer warps
 constexpr uint32_t NPROD = PW * 32;
 constexpr uint32_t NTHREADS = NPROD + 32;
-constexpr uint32_t A_BYTES = TM * KC * 4;       // one A part (hi or lo): 8 swizzle atoms of 1 KB
+constexpr uint32_t A_BYTES = TM * KC * 4;       // one A part (hi or lo): 16 swizzle atoms of 512 bytes
 constexpr uint32_t B_BYTES = TN * KC * 4;       // one W part (hi or lo): 256 rows x 64 bytes
 constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // 48 KB
 constexpr uint32_t CTL_BYTES = 4096;            // barriers, per-example maxima, partial maxima
@@ -76,16 +76,19 @@ __device__ __forceinline__ uint64_t desc_k64(uint32_t smem_addr) {
   d |= (uint64_t)4 << 61;               // SWIZZLE_64B
   return d;
 }
-// M-major operand descriptor for a 128 x 8 slice of the A tile: 128-byte swizzle atoms of
-// [8 K rows][32 examples]; the four atoms of the slice lie 1 KB apart (leading byte offset), the
-// next group of 8 K rows 4 KB further (stride byte offset)
+// M-major operand descriptor for a 128 x 8 slice of the A tile.  For 32-bit operands the M-major
+// layout tcgen05 reads is the 128-byte swizzle with 32-byte atoms: rows of 128 bytes (32 examples)
+// per K value, atoms of [4 K rows][32 examples] = 512 bytes, inside an atom the four 32-byte units
+// of a row are XORed with the row index (address bits [5,7) ^= bits [7,9)).  The four atoms along
+// the examples lie 512 bytes apart (leading byte offset), the next group of 4 K rows 2 KB further
+// (stride byte offset); a K step of 8 takes two such groups.
 __device__ __forceinline__ uint64_t desc_mn128(uint32_t smem_addr) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
-  d |= (uint64_t)(1024u >> 4) << 16;    // leading byte offset: next 32 examples
-  d |= (uint64_t)(4096u >> 4) << 32;    // stride byte offset: next 8 K rows
+  d |= (uint64_t)(512u >> 4) << 16;     // leading byte offset: next 32 examples
+  d |= (uint64_t)(2048u >> 4) << 32;    // stride byte offset: next 4 K rows
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;               // SWIZZLE_128B
+  d |= (uint64_t)1 << 61;               // SWIZZLE_128B with 32-byte atoms
   return d;
 }
 // instruction descriptor: D fp32, A/B tf32, A M-major (bit 15), B K-major, M x N
@@ -274,9 +277,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(MnArgs a) {
     if (!bok || mx4.y == -INFINITY) mx4.y = dead;
     if (!bok || mx4.z == -INFINITY) mx4.z = dead;
     if (!bok || mx4.w == -INFINITY) mx4.w = dead;
-    // byte offset of this thread's 16 bytes inside an A part: atom (pass, lane / 8), row w of the atom,
-    // slot (lane % 8) ^ w
-    const uint32_t aoff = (lane >> 3) * 1024u + warp * 128u + (((lane & 7u) ^ warp) << 4);
+    // byte offset of this thread's 16 bytes inside an A part: K row kr = 8 * pass + warp lies in row
+    // kr % 4 of the atom (kr / 4, lane / 8); the lane's 32-byte unit (lane % 8) / 2 is XORed with the row
+    const uint32_t r4 = warp & 3u;
+    const uint32_t aoff = ((warp >> 2) * 4u + (lane >> 3)) * 512u + r4 * 128u + (((((lane & 7u) >> 1) ^ r4)) << 5) +
+                          ((lane & 1u) << 4);
     struct Regs { float4 x[2], y[2]; };
     auto load = [&](uint32_t i, Regs& r) {
 #pragma unroll
@@ -390,7 +395,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(MnArgs a) {
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
 #pragma unroll
         for (uint32_t ks = 0; ks < KC / 8; ++ks) {
-          // A: the next 8 K rows are the next four atoms (4 KB); W: 8 tf32 = 32 bytes along the row
+          // A: the next 8 K rows are the next eight atoms (4 KB); W: 8 tf32 = 32 bytes along the row
           const uint64_t d_ahi = desc_mn128(sa + ks * 4096u), d_alo = desc_mn128(sa + A_BYTES + ks * 4096u);
           const uint64_t d_bhi = desc_k64(sa + 2 * A_BYTES) + (uint64_t)((ks * 32u) >> 4);
           const uint64_t d_blo = desc_k64(sa + 2 * A_BYTES + B_BYTES) + (uint64_t)((ks * 32u) >> 4);

@@ -115,6 +115,7 @@ def test_example_major_and_k_major_tensor_core_kernels_agree(monkeypatch):
             ll = torch.zeros(1, device=m.device)
             ws = api.em_step(m, data, pseudocount=0.1, inertia=0.5, ll_sum=ll)
             outs.append((api.vectorize_parameters(m), m.edge_aggr(), ll.item(), m.flows(ws, rows)))
+        assert np.isfinite(outs[0][2]) and np.isfinite(outs[0][0]).all()
         for o in outs[1:]:
             assert abs(o[2] - outs[0][2]) <= 1e-5 * abs(outs[0][2])
             assert np.abs(np.exp(o[0]) - np.exp(outs[0][0])).max() <= TOL
