@@ -343,21 +343,27 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [rows][32 examples] boxes of an [n_rows][ld] fp32 matrix, 128-byte swizzle, zero fill outside
-bool encode_rows_map(void* out, float* base, uint32_t ld, uint64_t n_rows, uint32_t box_rows) {
+// [box_rows][box_cols examples] boxes of an [n_rows][ld] fp32 matrix, zero fill outside; swizzled
+// as wide as the box's rows (box_cols = KCH) or not at all (row slabs)
+bool encode_map(void* out, float* base, uint32_t ld, uint64_t n_rows, uint32_t box_cols, uint32_t box_rows, bool swizzle) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   alignas(64) CUtensorMap m;
   cuuint64_t gdim[2] = {ld, n_rows};
   cuuint64_t gstride[1] = {(cuuint64_t)ld * sizeof(float)};
-  cuuint32_t box[2] = {KCH, box_rows};
+  cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = !swizzle ? CU_TENSOR_MAP_SWIZZLE_NONE : (KCH == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
   CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  KCH == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return false;
   static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
   memcpy(out, &m, sizeof(m));
   return true;
+}
+
+bool encode_rows_map(void* out, float* base, uint32_t ld, uint64_t n_rows, uint32_t box_rows) {
+  return encode_map(out, base, ld, n_rows, KCH, box_rows, true);
 }
 
 }  // namespace
@@ -366,8 +372,11 @@ bool encode_rows_map(void* out, float* base, uint32_t ld, uint64_t n_rows, uint3
 // boxes of 256 rows over mars).  Leaves have_tm false when the driver entry point is missing.
 int32_t pcb_dense_edge_prepare_ws(pcb_workspace* ws) {
   ws->have_tm = false;
+  ws->have_tm_rows = false;
   pcb_circuit* c = ws->c;
   if (!c->use_tc || c->n_dense == 0) return PCB_OK;
+  // row slabs [16 rows][128 examples] of mars, as they lie in memory (pcb_dense_mn.cu)
+  ws->have_tm_rows = encode_map(ws->tm_rows, ws->mars, ws->ld, c->N, 128, 16, false);
   if (c->edge_ld) return PCB_OK;
   bool good = encode_rows_map(ws->tm[0], ws->mars, ws->ld, c->N, TM) &&
               encode_rows_map(ws->tm[1], ws->flows, ws->ld, c->N, TM) &&

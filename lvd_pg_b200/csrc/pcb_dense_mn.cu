@@ -27,7 +27,11 @@
 // tensor-pipe bound) the other runs its max pass or its epilogue (memory bound).
 // Every mbarrier wait is bounded; on expiry the status word is raised and all roles drain to the
 // common exit where tensor memory is released.
+#include <cuda.h>
+
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 #include "pcb_internal.h"
 #include "pcb_tc.cuh"
@@ -39,17 +43,23 @@ enum { MN_FWD = 0, MN_BWD_CHILD = 1 };
 
 constexpr uint32_t TM = 128;            // examples per tile (TMEM lanes)
 constexpr uint32_t TN = 256;            // columns per tile (TMEM columns)
-constexpr uint32_t KC = 16;             // K values per stage
-constexpr uint32_t STAGES = 2;
-constexpr uint32_t PW = 8;              // producer warps
+constexpr uint32_t KC = 16;             // K values per chunk
+constexpr uint32_t PW = 8;              // producer warps: warp w owns K rows w and w + 8 of every chunk
 constexpr uint32_t NPROD = PW * 32;
-constexpr uint32_t NTHREADS = NPROD + 32;
-constexpr uint32_t A_BYTES = TM * KC * 4;       // one A part (hi or lo): 16 swizzle atoms of 512 bytes
-constexpr uint32_t B_BYTES = TN * KC * 4;       // one W part (hi or lo): 256 rows x 64 bytes
-constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;   // 48 KB
+constexpr uint32_t MMA_WARP = PW, COPY_WARP = PW + 1;
+constexpr uint32_t NTHREADS = NPROD + 64;
+constexpr uint32_t ROW_BYTES = TM * 4;          // one row of a tile: 128 examples
+constexpr uint32_t A_BYTES = KC * ROW_BYTES;    // one A part (hi or lo): 16 swizzle atoms of 512 bytes
+constexpr uint32_t A_STAGE = 2 * A_BYTES;       // hi | lo
+constexpr uint32_t A_STAGES = 2;
+constexpr uint32_t W_RING = 64 * 1024;          // weight chunks [hi | lo] of n_tile rows x 64 bytes: 2 chunks of a 256-column
+constexpr uint32_t W_MAX_STAGES = 16;           // tile, 8 of a 64-column tile
+constexpr uint32_t BUF_BYTES = A_STAGES * A_STAGE + W_RING;   // 96 KB: also the staging area of the row copies
 constexpr uint32_t CTL_BYTES = 4096;            // barriers, per-example maxima, partial maxima
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + CTL_BYTES;
+constexpr uint32_t SMEM_BYTES = BUF_BYTES + 1024 /*alignment*/ + CTL_BYTES;
 constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t MAXP_CHUNKS = 3;             // FWD maximum pass: chunks of rows per copy round, two rounds in flight
+constexpr uint32_t EPI_COLS = 32;               // BWD epilogue: child rows of 32 columns per round, three rounds in flight
 
 struct MnArgs {
   float* mars;
@@ -61,7 +71,18 @@ struct MnArgs {
   int* status;
   uint32_t ld;
   uint32_t nsplit;   // CTAs sharing one 256-column tile (1, 2 or 4), each taking 256 / nsplit columns
+  unsigned long long* trace;   // -DPCB_DIAG builds: %globaltimer stamps of CTA (0,0,0), else null
 };
+
+// Timing stamps exist only in a build with -DPCB_DIAG; the default build compiles them out.
+#ifdef PCB_DIAG
+#define MN_TRACE(slot)                                                                                   \
+  do {                                                                                                   \
+    if (a.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[(MODE == MN_FWD ? 0 : 256) + (slot)] = gtime(); \
+  } while (0)
+#else
+#define MN_TRACE(slot) do { } while (0)
+#endif
 
 // byte offset of element (row, kk) inside a K-major tile with 64-byte rows and 64-byte swizzle
 __host__ __device__ __forceinline__ uint32_t sw64_off(uint32_t row, uint32_t kk) {
@@ -157,16 +178,31 @@ __global__ void __launch_bounds__(256) w_image16_kernel(const float* __restrict_
 }
 
 // grid: (example tiles of 128, column tiles x nsplit, blocks)
+//
+// Roles: 8 producer warps (they also compute the per-example maximum of FWD and run the epilogue),
+// one MMA thread, one weight-copy thread.  Shared memory (96 KB, two CTAs per SM): two 16 KB A
+// stages and a 64 KB ring of weight chunks that the copy thread fills as far ahead as it reaches
+// (2 chunks of a 256-column tile, 8 of a 64-column tile: the small layers of the chain do not wait
+// for weights).  Whatever comes from global memory in bulk outside the K loop comes by cp.async.bulk
+// into the same 96 KB while they are idle: the child rows of the maximum pass (FWD, before the
+// weights start to arrive) and the children's value rows of the child-flow epilogue (BWD) — plain
+// loads of row-strided 512-byte pieces reach a third of what the copy engine delivers.
 template <int MODE>
-__global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(MnArgs a) {
+__global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_constant__ CUtensorMap tm_rows, MnArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* ctl = smem + STAGES * STAGE_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(ctl);          // [STAGES]
-  uint64_t* empty = full + STAGES;                            // [STAGES]
-  uint64_t* accfull = empty + STAGES;                         // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accfull + 1);
-  float* mxs = reinterpret_cast<float*>(ctl + 128);           // [128] per-example max of the tile
+  uint8_t* aring = smem;
+  uint8_t* wring = smem + A_STAGES * A_STAGE;
+  uint8_t* ctl = smem + BUF_BYTES;
+  uint64_t* wfull = reinterpret_cast<uint64_t*>(ctl);         // [W_MAX_STAGES]
+  uint64_t* wempty = wfull + W_MAX_STAGES;                    // [W_MAX_STAGES]
+  uint64_t* afull = wempty + W_MAX_STAGES;                    // [A_STAGES]
+  uint64_t* aempty = afull + A_STAGES;                        // [A_STAGES]
+  uint64_t* accfull = aempty + A_STAGES;                      // [1]
+  uint64_t* wgo = accfull + 1;                                // [1] FWD: the staging area is free for weights
+  uint64_t* xbar = wgo + 1;                                   // [3] row-copy rounds
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 3);
+  float* mxs = reinterpret_cast<float*>(ctl + 512);           // [128] per-example max of the tile
   float* part = reinterpret_cast<float*>(ctl + 1024);         // [PW/2][128] partial maxima (FWD)
 
   pcb_grid_dep_launch();
@@ -180,232 +216,352 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(MnArgs a) {
   const uint32_t m0 = blockIdx.x * TM, jn = blockIdx.y / a.nsplit, part0 = (blockIdx.y % a.nsplit) * sw;
   const uint32_t n0 = jn * TN + part0;
   if (n0 >= ncols) return;
-  const uint32_t n_count = min(sw, ncols - n0);
   const uint32_t nchunks = (kdim + KC - 1) / KC;
   const PcbDenseImg im = a.imgs[blockIdx.z];
   const uint32_t img_rows = MODE == MN_FWD ? im.rows_f : im.rows_t;
   const uint32_t nch = MODE == MN_FWD ? im.nch_f : im.nch_t;
-  // first K chunk of this CTA's rows in the weight image; rows beyond n_count are zero in the image
+  // first K chunk of this CTA's rows in the weight image; rows beyond the block are zero in the image
   const float* img_tile = a.w_img + (MODE == MN_FWD ? im.off_f : im.off_t) + (size_t)jn * nch * 2 * img_rows * KC + part0 * KC;
   const uint32_t n_tile = min(sw, img_rows - part0);
+  const uint32_t w_part = n_tile * KC * 4u;                    // bytes of one part (hi or lo) of a weight chunk
+  const uint32_t w_stages = min(W_MAX_STAGES, W_RING / (2u * w_part));
+  const bool w_reuse = w_stages < nchunks;                     // else every chunk has a slot of its own
   const bool has_sub = k.d0 != PCB_NONE;
+  const uint32_t ex = min(TM, ld - m0), rowb = ex * 4u;        // examples of this tile (the pitch is a multiple of 32)
 
   // ---- set-up: barriers, tensor memory ---------------------------------------------------------
   if (tid == 0) {
-    for (uint32_t s = 0; s < STAGES; ++s) { mbar_init(&full[s], PW); mbar_init(&empty[s], 1); }
+    for (uint32_t s = 0; s < W_MAX_STAGES; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wempty[s], 1); }
+    for (uint32_t s = 0; s < A_STAGES; ++s) { mbar_init(&afull[s], PW); mbar_init(&aempty[s], 1); }
     mbar_init(accfull, 1);
+    mbar_init(wgo, 1);
+    for (uint32_t s = 0; s < 3; ++s) mbar_init(&xbar[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == PW) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"(TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // Up to here only static circuit data was read: a launch with programmatic stream serialization
-  // may have come this far while the previous kernel of the stream was still running.
-  pcb_grid_dep_wait();
-
-  // A thread's four examples m0 + 4*lane .. +3 are the same in every pass: lane -> (32-example group,
-  // 16-byte slot), warp -> K row of the chunk
-  const uint32_t bq = m0 + 4u * lane;
-  const bool bok = bq < ld;                  // the row pitch is a multiple of 32: a group of four is in or out as a whole
-  const uint32_t bb = bok ? bq : 0u;
-  const float* rowsA = MODE == MN_FWD ? a.mars + (size_t)k.c0 * ld + bb : a.mars + (size_t)k.p0 * ld + bb;
-  const float* rowsB = MODE == MN_FWD ? a.mars + (size_t)(has_sub ? k.d0 : k.c0) * ld + bb : a.flows + (size_t)k.p0 * ld + bb;
-
-  if (MODE == MN_FWD && warp < PW) {
-    // ---- per-example maximum of the child values over all K children ------------------------------
-    // Warp w scans K rows w, w + 8, ...: one coalesced 512-byte request per row (and per sub row);
-    // eight rows are requested before the first is used.  The K loop reads the rows again from L2.
-    float4 mx = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-    for (uint32_t t0 = 0; t0 < kdim; t0 += 8 * PW) {
-      float4 p[8], q[8];
-#pragma unroll
-      for (uint32_t u = 0; u < 8; ++u) {
-        const uint32_t t = t0 + u * PW + warp;
-        const size_t o = (size_t)(t < kdim ? t : 0u) * ld;
-        p[u] = ldg4(rowsA + o);
-        if (has_sub) q[u] = ldg4(rowsB + o);
-      }
-#pragma unroll
-      for (uint32_t u = 0; u < 8; ++u) {
-        const uint32_t t = t0 + u * PW + warp;
-        if (t < kdim) {
-          float4 v = p[u];
-          if (has_sub) { v.x += q[u].x; v.y += q[u].y; v.z += q[u].z; v.w += q[u].w; }
-          mx = f4max(mx, v);
-        }
-      }
-    }
-    // combine the eight warps: two rounds through shared memory
-    if (warp >= PW / 2) *reinterpret_cast<float4*>(part + (warp - PW / 2) * 128u + 4u * lane) = mx;
-    asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");
-    if (warp < PW / 2) {
-      mx = f4max(mx, *reinterpret_cast<const float4*>(part + warp * 128u + 4u * lane));
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");
-    if (warp < PW / 2) *reinterpret_cast<float4*>(part + warp * 128u + 4u * lane) = mx;
-    asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");
-    if (warp == 0) {
-#pragma unroll
-      for (uint32_t u = 1; u < PW / 2; ++u) mx = f4max(mx, *reinterpret_cast<const float4*>(part + u * 128u + 4u * lane));
-      if (!bok) mx = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-      *reinterpret_cast<float4*>(mxs + 4u * lane) = mx;
-      // kept for the backward kernels (one CTA per example tile writes)
-      if (bok && blockIdx.y == 0) *reinterpret_cast<float4*>(a.blk_mx + (size_t)k.mx_row * ld + bq) = mx;
-    }
-  }
-  if (MODE == MN_BWD_CHILD && tid < 128) {
-    const float* mxrow = a.blk_mx + (size_t)k.mx_row * ld;
-    mxs[tid] = (m0 + tid < ld) ? mxrow[m0 + tid] : -INFINITY;
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Up to here only static circuit data was read: a launch with programmatic stream serialization
+  // may have come this far while the previous kernel of the stream was still running.
+  if (tid == 0) MN_TRACE(0);
+  pcb_grid_dep_wait();
+  if (tid == 0) MN_TRACE(1);
   bool ok = true;
 
   if (warp < PW) {
     // =========================== producers ===================================================
-    // Chunk i = K rows 16 i .. 16 i + 15; warp w takes rows w and w + 8 of the chunk.  The loads of
-    // chunk i + 1 are in flight while chunk i is transformed and stored.
-    float4 mx4 = *reinterpret_cast<const float4*>(mxs + 4u * lane);
-    // a masked example (outside the batch, or no child possible): FWD exp(x - inf) = 0; BWD exp(-inf - m) = 0
-    const float dead = MODE == MN_FWD ? INFINITY : -INFINITY;
-    if (!bok || mx4.x == -INFINITY) mx4.x = dead;
-    if (!bok || mx4.y == -INFINITY) mx4.y = dead;
-    if (!bok || mx4.z == -INFINITY) mx4.z = dead;
-    if (!bok || mx4.w == -INFINITY) mx4.w = dead;
-    // byte offset of this thread's 16 bytes inside an A part: K row kr = 8 * pass + warp lies in row
-    // kr % 4 of the atom (kr / 4, lane / 8); the lane's 32-byte unit (lane % 8) / 2 is XORed with the row
-    const uint32_t r4 = warp & 3u;
-    const uint32_t aoff = ((warp >> 2) * 4u + (lane >> 3)) * 512u + r4 * 128u + (((((lane & 7u) >> 1) ^ r4)) << 5) +
-                          ((lane & 1u) << 4);
-    struct Regs { float4 x[2], y[2]; };
-    auto load = [&](uint32_t i, Regs& r) {
-#pragma unroll
-      for (uint32_t ps = 0; ps < 2; ++ps) {
-        const uint32_t t = i * KC + ps * 8u + warp;
-        const size_t o = (size_t)(t < kdim ? t : 0u) * ld;
-        r.x[ps] = ldg4(rowsA + o);
-        if (MODE == MN_BWD_CHILD || has_sub) r.y[ps] = ldg4(rowsB + o);
-      }
+    // A thread's four examples m0 + 4*lane .. +3 are the same in every chunk: lane -> (32-example
+    // group, 16-byte slot); warp -> K rows warp and warp + 8 of the chunk.
+    const uint32_t bq = m0 + 4u * lane;
+    const bool bok = bq < ld;                  // the row pitch is a multiple of 32: a group of four is in or out as a whole
+    const uint32_t bb = bok ? bq : 0u;
+    const float* rowsA = MODE == MN_FWD ? a.mars + (size_t)k.c0 * ld + bb : a.mars + (size_t)k.p0 * ld + bb;
+    const float* rowsB = MODE == MN_FWD ? a.mars + (size_t)(has_sub ? k.d0 : k.c0) * ld + bb : a.flows + (size_t)k.p0 * ld + bb;
+    const float4 ninf4 = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    auto lds4 = [](const uint8_t* p) { return *reinterpret_cast<const float4*>(p); };
+    auto wait_warp = [&](uint64_t* bar, uint32_t parity) {   // one lane polls, the warp follows
+      bool got = lane != 0 || mbar_wait(bar, parity, a.status);
+      return __all_sync(0xffffffffu, got);
     };
-    auto process = [&](uint32_t i, const Regs& r) -> bool {
-      const uint32_t s = i & (STAGES - 1), ph = (i / STAGES) & 1u;
-      // one lane per warp polls; __all_sync orders the other lanes' stores behind the observed phase
-      bool got = lane != 0 || mbar_wait(&empty[s], ph ^ 1u, a.status);
-      got = __all_sync(0xffffffffu, got);
-      if (!got) return false;
-      uint8_t* a_hi = smem + s * STAGE_BYTES;
-      uint8_t* a_lo = a_hi + A_BYTES;
-      if (tid == 0) {   // weight tile of the chunk: hi and lo parts straight from the image
-        const uint32_t bytes = n_tile * KC * 4u;
-        const float* src = img_tile + (size_t)i * 2 * img_rows * KC;
-        mbar_expect_tx(&full[s], 2 * bytes);
-        bulk_g2s(a_hi + 2 * A_BYTES, src, bytes, &full[s]);
-        bulk_g2s(a_hi + 2 * A_BYTES + B_BYTES, src + (size_t)img_rows * KC, bytes, &full[s]);
-      }
+
+    if (MODE == MN_FWD) {
+      // ---- per-example maximum of the child values over all K children ------------------------------
+      // The child rows come by bulk copies, three chunks per round (slot of 16 KB per chunk: [16 prime
+      // rows | 16 sub rows]), two rounds in flight through the still idle 96 KB; warp w reads rows w
+      // and w + 8 of every chunk.  The K loop reads the rows again, from L2.
+      const uint32_t nrounds = (nchunks + MAXP_CHUNKS - 1) / MAXP_CHUNKS;
+      auto issue_round = [&](uint32_t R) {   // called by every producer thread (one barrier inside)
+        asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");   // the slots' readers are done
+        if (tid == 0) {
+          // one tensor-map copy per chunk and operand: a [16 rows][128 examples] slab as it lies in memory
+          // (rows past the block belong to other nodes or are zero-filled; their values are never used)
+          const uint32_t c_first = R * MAXP_CHUNKS, nc = min(MAXP_CHUNKS, nchunks - c_first);
+          mbar_arrive_expect_tx(&xbar[R & 1u], nc * (has_sub ? 2u : 1u) * A_BYTES);
+          for (uint32_t c = 0; c < nc; ++c) {
+            uint8_t* slot = smem + ((R & 1u) * MAXP_CHUNKS + c) * A_STAGE;
+            tma_load_2d(slot, &tm_rows, (int32_t)m0, (int32_t)(k.c0 + (c_first + c) * KC), &xbar[R & 1u]);
+            if (has_sub) tma_load_2d(slot + A_BYTES, &tm_rows, (int32_t)m0, (int32_t)(k.d0 + (c_first + c) * KC), &xbar[R & 1u]);
+          }
+        }
+      };
+      float4 mx = ninf4;
+      issue_round(0);
+      if (nrounds > 1) issue_round(1);
+      for (uint32_t R = 0; R < nrounds; ++R) {
+        const bool got = wait_warp(&xbar[R & 1u], (R >> 1) & 1u);
+        ok = ok && got;
 #pragma unroll
-      for (uint32_t ps = 0; ps < 2; ++ps) {
-        const bool tok = i * KC + ps * 8u + warp < kdim;
-        float4 v;
-        if (MODE == MN_FWD) {
-          v = r.x[ps];
-          if (has_sub) { v.x += r.y[ps].x; v.y += r.y[ps].y; v.z += r.y[ps].z; v.w += r.y[ps].w; }
-          v.x = __expf(v.x - mx4.x); v.y = __expf(v.y - mx4.y); v.z = __expf(v.z - mx4.z); v.w = __expf(v.w - mx4.w);
-        } else {   // x: mars of the parent, y: flows of the parent
+        for (uint32_t c = 0; c < MAXP_CHUNKS; ++c) {
+          const uint8_t* slot = smem + ((R & 1u) * MAXP_CHUNKS + c) * A_STAGE + lane * 16u;
+#pragma unroll
+          for (uint32_t ps = 0; ps < 2; ++ps) {
+            const uint32_t row = ps * 8u + warp;
+            if (got && (R * MAXP_CHUNKS + c) * KC + row < kdim) {
+              float4 v = lds4(slot + row * ROW_BYTES);
+              if (has_sub) { const float4 q = lds4(slot + A_BYTES + row * ROW_BYTES); v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w; }
+              mx = f4max(mx, v);
+            }
+          }
+        }
+        if (R + 2 < nrounds) {   // CTA-uniform
+          fence_proxy_async();   // these generic reads precede the next copies into the same slots
+          issue_round(R + 2);
+        }
+      }
+      // combine the eight warps: two rounds through shared memory
+      if (warp >= PW / 2) *reinterpret_cast<float4*>(part + (warp - PW / 2) * 128u + 4u * lane) = mx;
+      fence_proxy_async();
+      asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");   // also: every read of the staging area is done
+      if (tid == 0) mbar_arrive(wgo);                              // the weight copies may start
+      if (warp < PW / 2) mx = f4max(mx, *reinterpret_cast<const float4*>(part + warp * 128u + 4u * lane));
+      asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");
+      if (warp < PW / 2) *reinterpret_cast<float4*>(part + warp * 128u + 4u * lane) = mx;
+      asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");
+#pragma unroll
+      for (uint32_t u = 0; u < PW / 2; ++u) mx = f4max(mx, *reinterpret_cast<const float4*>(part + u * 128u + 4u * lane));
+      if (!bok) mx = ninf4;
+      if (warp == 0) {
+        *reinterpret_cast<float4*>(mxs + 4u * lane) = mx;   // for the epilogue (read after the barrier behind the K loop)
+        // kept for the backward kernels (one CTA per example tile writes)
+        if (bok && blockIdx.y == 0) *reinterpret_cast<float4*>(a.blk_mx + (size_t)k.mx_row * ld + bq) = mx;
+      }
+      if (tid == 0) MN_TRACE(2);   // per-example maximum known
+      // a masked example (outside the batch, or no child possible): exp(x - inf) = 0
+      if (mx.x == -INFINITY) mx.x = INFINITY;
+      if (mx.y == -INFINITY) mx.y = INFINITY;
+      if (mx.z == -INFINITY) mx.z = INFINITY;
+      if (mx.w == -INFINITY) mx.w = INFINITY;
+      {
+        const float4 mx4 = mx;
+        // byte offset of this thread's 16 bytes inside an A part: K row kr = 8 * pass + warp lies in row
+        // kr % 4 of the atom (kr / 4, lane / 8); the lane's 32-byte unit (lane % 8) / 2 is XORed with the row
+        const uint32_t r4 = warp & 3u;
+        const uint32_t aoff = ((warp >> 2) * 4u + (lane >> 3)) * 512u + r4 * 128u + (((((lane & 7u) >> 1) ^ r4)) << 5) +
+                              ((lane & 1u) << 4);
+        struct Regs { float4 x[2], y[2]; };
+        auto load = [&](uint32_t i, Regs& r) {
+#pragma unroll
+          for (uint32_t ps = 0; ps < 2; ++ps) {
+            const uint32_t t = i * KC + ps * 8u + warp;
+            const size_t o = (size_t)(t < kdim ? t : 0u) * ld;
+            r.x[ps] = ldg4(rowsA + o);
+            if (has_sub) r.y[ps] = ldg4(rowsB + o);
+          }
+        };
+        auto process = [&](uint32_t i, const Regs& r) -> bool {
+          const uint32_t s = i & (A_STAGES - 1), ph = (i / A_STAGES) & 1u;
+          if (!wait_warp(&aempty[s], ph ^ 1u)) return false;
+          uint8_t* a_hi = aring + s * A_STAGE;
+#pragma unroll
+          for (uint32_t ps = 0; ps < 2; ++ps) {
+            float4 v = r.x[ps];
+            if (has_sub) { v.x += r.y[ps].x; v.y += r.y[ps].y; v.z += r.y[ps].z; v.w += r.y[ps].w; }
+            v.x = __expf(v.x - mx4.x); v.y = __expf(v.y - mx4.y); v.z = __expf(v.z - mx4.z); v.w = __expf(v.w - mx4.w);
+            if (i * KC + ps * 8u + warp >= kdim) v = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+            const uint32_t o = aoff + ps * 4096u;
+            *reinterpret_cast<float4*>(a_hi + o) = h;
+            *reinterpret_cast<float4*>(a_hi + A_BYTES + o) = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+          }
+          fence_proxy_async();   // make the generic-proxy writes visible to the tensor core
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&afull[s]);
+          if (tid == 0 && i < 32) MN_TRACE(16 + i);   // chunk i stored
+          return true;
+        };
+        Regs r0, r1;
+        load(0, r0);
+        for (uint32_t i = 0; i < nchunks && ok; i += 2) {
+          if (i + 1 < nchunks) load(i + 1, r1);
+          ok = process(i, r0);
+          if (!ok || i + 1 >= nchunks) break;
+          if (i + 2 < nchunks) load(i + 2, r0);
+          ok = process(i + 1, r1);
+        }
+      }
+    } else {
+      // ---- G = flows * exp(mx - mars) of the parents; the loads of chunk i + 1 are in flight while chunk i is stored
+      const float* mxrow = a.blk_mx + (size_t)k.mx_row * ld;
+      float4 mx4 = bok ? *reinterpret_cast<const float4*>(mxrow + bq) : ninf4;   // -inf: exp(-inf - m) = 0
+      if (tid < 128) mxs[tid] = (m0 + tid < ld) ? mxrow[m0 + tid] : -INFINITY;
+      const uint32_t r4 = warp & 3u;
+      const uint32_t aoff = ((warp >> 2) * 4u + (lane >> 3)) * 512u + r4 * 128u + (((((lane & 7u) >> 1) ^ r4)) << 5) +
+                            ((lane & 1u) << 4);
+      struct Regs { float4 x[2], y[2]; };
+      auto load = [&](uint32_t i, Regs& r) {
+#pragma unroll
+        for (uint32_t ps = 0; ps < 2; ++ps) {
+          const uint32_t t = i * KC + ps * 8u + warp;
+          const size_t o = (size_t)(t < kdim ? t : 0u) * ld;
+          r.x[ps] = ldg4(rowsA + o);
+          r.y[ps] = ldg4(rowsB + o);
+        }
+      };
+      auto process = [&](uint32_t i, const Regs& r) -> bool {
+        const uint32_t s = i & (A_STAGES - 1), ph = (i / A_STAGES) & 1u;
+        if (!wait_warp(&aempty[s], ph ^ 1u)) return false;
+        uint8_t* a_hi = aring + s * A_STAGE;
+#pragma unroll
+        for (uint32_t ps = 0; ps < 2; ++ps) {
+          float4 v;   // x: mars of the parent, y: flows of the parent
           v.x = r.y[ps].x * __expf(mx4.x - r.x[ps].x); v.y = r.y[ps].y * __expf(mx4.y - r.x[ps].y);
           v.z = r.y[ps].z * __expf(mx4.z - r.x[ps].z); v.w = r.y[ps].w * __expf(mx4.w - r.x[ps].w);
+          if (i * KC + ps * 8u + warp >= kdim) v = make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+          const uint32_t o = aoff + ps * 4096u;
+          *reinterpret_cast<float4*>(a_hi + o) = h;
+          *reinterpret_cast<float4*>(a_hi + A_BYTES + o) = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
         }
-        if (!tok) v = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
-        const uint32_t o = aoff + ps * 4096u;
-        *reinterpret_cast<float4*>(a_hi + o) = h;
-        *reinterpret_cast<float4*>(a_lo + o) = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&afull[s]);
+        if (tid == 0 && i < 32) MN_TRACE(16 + i);
+        return true;
+      };
+      Regs r0, r1;
+      load(0, r0);
+      for (uint32_t i = 0; i < nchunks && ok; i += 2) {
+        if (i + 1 < nchunks) load(i + 1, r1);
+        ok = process(i, r0);
+        if (!ok || i + 1 >= nchunks) break;
+        if (i + 2 < nchunks) load(i + 2, r0);
+        ok = process(i + 1, r1);
       }
-      fence_proxy_async();   // make the generic-proxy writes visible to the tensor core
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&full[s]);
-      return true;
-    };
-    Regs r0, r1;
-    load(0, r0);
-    for (uint32_t i = 0; i < nchunks && ok; i += 2) {
-      if (i + 1 < nchunks) load(i + 1, r1);
-      ok = process(i, r0);
-      if (!ok || i + 1 >= nchunks) break;
-      if (i + 2 < nchunks) load(i + 2, r0);
-      ok = process(i + 1, r1);
     }
+    if (tid == 0) MN_TRACE(3);   // last chunk stored
+    asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");   // mxs is complete for every epilogue warp
 
     // =========================== epilogue ====================================================
     if (ok && lane == 0) ok = mbar_wait(accfull, 0, a.status);
     ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
-      tc_fence_after();
-      // warp -> (TMEM lane quarter, column half); a thread owns one example and walks 16 columns at a time
-      const uint32_t q4 = warp & 3, half = warp >> 2;
-      const uint32_t CG = max(16u, ((n_tile + 31u) / 32u) * 16u);   // columns per half, a multiple of 16
-      const uint32_t row = q4 * 32 + lane, b = m0 + row;
-      const uint32_t c_begin = half * CG, c_end = min(n_tile, c_begin + CG);
-      const float mx = mxs[row];
-      float acc[16];
-      for (uint32_t c0 = c_begin; c0 < c_end; c0 += 16) {
-        tmem_ld16(tmem_base + ((q4 * 32u) << 16) + c0, acc);
-        if (b >= ld) continue;
-        if (MODE == MN_FWD) {
+    if (tid == 0) MN_TRACE(4);   // accumulator complete
+    const uint32_t q4 = warp & 3, half = warp >> 2;   // warp -> (TMEM lane quarter, column half)
+    const uint32_t row = q4 * 32 + lane, b = m0 + row;
+    const float mx = mxs[row];
+    float acc[16];
+    if (MODE == MN_FWD) {
+      if (ok) {
+        tc_fence_after();
+        // a thread owns one example and walks 16 columns at a time
+        const uint32_t CG = max(16u, ((n_tile + 31u) / 32u) * 16u);   // columns per half, a multiple of 16
+        const uint32_t c_begin = half * CG, c_end = min(n_tile, c_begin + CG);
+        for (uint32_t c0 = c_begin; c0 < c_end; c0 += 16) {
+          tmem_ld16(tmem_base + ((q4 * 32u) << 16) + c0, acc);
+          if (b >= ld) continue;
 #pragma unroll
           for (uint32_t j = 0; j < 16; ++j) {
             const uint32_t r = n0 + c0 + j;
             if (r < k.R) a.mars[(size_t)(k.p0 + r) * ld + b] = mx == -INFINITY ? -INFINITY : __logf(acc[j]) + mx;
           }
-        } else {
-          // all child values first (independent loads), then the products and the stores
-          float cv[16], dv[16];
-#pragma unroll
-          for (uint32_t j = 0; j < 16; ++j) {
-            const uint32_t t = n0 + c0 + j;
-            const uint32_t tt = t < k.K ? t : 0u;
-            cv[j] = __ldcg(a.mars + (size_t)(k.c0 + tt) * ld + b);
-            dv[j] = has_sub ? __ldcg(a.mars + (size_t)(k.d0 + tt) * ld + b) : 0.0f;
+        }
+      }
+    } else {
+      // Child flows f[t][b] = acc[b][t] * exp(M[t][b] - mx[b]) need the children's value rows: copied 32
+      // columns per round into the idle 96 KB (32 KB per round: [32 prime rows | 32 sub rows]), three
+      // rounds in flight; warp (q4, half) takes columns 16 half .. 16 half + 15 of every round.
+      const uint32_t nrounds = (n_tile + EPI_COLS - 1) / EPI_COLS;
+      const uint32_t per = has_sub ? 2u : 1u;
+      auto issue_round = [&](uint32_t R) {   // called by every producer thread (one barrier inside)
+        asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");   // the buffer's readers are done
+        if (tid == 0) {
+          // buffer: [32 prime rows | 32 sub rows] of 512 bytes, fetched as slabs of 16 rows
+          const uint32_t c_first = R * EPI_COLS;
+          const uint32_t groups = c_first + 16u < ncols - n0 ? 2u : 1u;
+          uint8_t* buf = smem + (R % 3u) * (EPI_COLS * 1024u);
+          mbar_arrive_expect_tx(&xbar[R % 3u], groups * per * A_BYTES);
+          for (uint32_t g = 0; g < groups; ++g) {
+            tma_load_2d(buf + g * A_BYTES, &tm_rows, (int32_t)m0, (int32_t)(k.c0 + n0 + c_first + g * 16u), &xbar[R % 3u]);
+            if (has_sub)
+              tma_load_2d(buf + EPI_COLS * ROW_BYTES + g * A_BYTES, &tm_rows, (int32_t)m0, (int32_t)(k.d0 + n0 + c_first + g * 16u), &xbar[R % 3u]);
           }
+        }
+      };
+      fence_proxy_async();
+      for (uint32_t R = 0; R < min(3u, nrounds); ++R) issue_round(R);
+      for (uint32_t R = 0; R < nrounds; ++R) {
+        const bool got = wait_warp(&xbar[R % 3u], (R / 3u) & 1u);
+        const uint32_t c0 = R * EPI_COLS + half * 16u;   // first column of this warp in the round (within the CTA's tile)
+        if (c0 < n_tile) {
+          if (ok) { tc_fence_after(); tmem_ld16(tmem_base + ((q4 * 32u) << 16) + c0, acc); }
+          if (ok && got && b < ld) {
+            const uint8_t* sp = smem + (R % 3u) * (EPI_COLS * 1024u) + (half * 16u) * ROW_BYTES + row * 4u;
 #pragma unroll
-          for (uint32_t j = 0; j < 16; ++j) {
-            const uint32_t t = n0 + c0 + j;
-            if (t < k.K) {
-              const float f = mx == -INFINITY ? 0.0f : acc[j] * __expf((cv[j] + dv[j]) - mx);
-              a.flows[(size_t)(k.c0 + t) * ld + b] = f;
-              if (has_sub) a.flows[(size_t)(k.d0 + t) * ld + b] = f;
+            for (uint32_t j = 0; j < 16; ++j) {
+              const uint32_t t = n0 + c0 + j;
+              if (t < k.K) {
+                float cv = *reinterpret_cast<const float*>(sp + j * ROW_BYTES);
+                if (has_sub) cv += *reinterpret_cast<const float*>(sp + EPI_COLS * ROW_BYTES + j * ROW_BYTES);
+                const float f = mx == -INFINITY ? 0.0f : acc[j] * __expf(cv - mx);
+                a.flows[(size_t)(k.c0 + t) * ld + b] = f;
+                if (has_sub) a.flows[(size_t)(k.d0 + t) * ld + b] = f;
+              }
             }
           }
         }
+        if (R + 3 < nrounds) {   // CTA-uniform
+          fence_proxy_async();   // these generic reads precede the next copies into the same buffer
+          issue_round(R + 3);
+        }
       }
     }
-  } else {
+    if (tid == 0) MN_TRACE(5);   // epilogue of warp 0 done
+  } else if (warp == MMA_WARP) {
     // =========================== MMA issuer ==================================================
     if (lane == 0) {
       const uint32_t idesc = idesc_mn(TM, n_tile);
       for (uint32_t i = 0; i < nchunks && ok; ++i) {
-        const uint32_t s = i & (STAGES - 1), ph = (i / STAGES) & 1u;
-        ok = mbar_wait(&full[s], ph, a.status);
+        const uint32_t sa = i & (A_STAGES - 1), pa = (i / A_STAGES) & 1u;
+        const uint32_t sb = i % w_stages, pb = (i / w_stages) & 1u;
+        ok = mbar_wait(&wfull[sb], pb, a.status) && mbar_wait(&afull[sa], pa, a.status);
+        if (i < 32) MN_TRACE(96 + i);    // operands of chunk i ready
         if (!ok) break;
         tc_fence_after();
-        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+        const uint32_t aa = smem_u32(aring + sa * A_STAGE), wa = smem_u32(wring + sb * 2u * w_part);
 #pragma unroll
         for (uint32_t ks = 0; ks < KC / 8; ++ks) {
           // A: the next 8 K rows are the next eight atoms (4 KB); W: 8 tf32 = 32 bytes along the row
-          const uint64_t d_ahi = desc_mn128(sa + ks * 4096u), d_alo = desc_mn128(sa + A_BYTES + ks * 4096u);
-          const uint64_t d_bhi = desc_k64(sa + 2 * A_BYTES) + (uint64_t)((ks * 32u) >> 4);
-          const uint64_t d_blo = desc_k64(sa + 2 * A_BYTES + B_BYTES) + (uint64_t)((ks * 32u) >> 4);
+          const uint64_t d_ahi = desc_mn128(aa + ks * 4096u), d_alo = desc_mn128(aa + A_BYTES + ks * 4096u);
+          const uint64_t d_bhi = desc_k64(wa) + (uint64_t)((ks * 32u) >> 4);
+          const uint64_t d_blo = desc_k64(wa + w_part) + (uint64_t)((ks * 32u) >> 4);
           umma_tf32(tmem_base, d_ahi, d_bhi, idesc, (i | ks) ? 1u : 0u);
           umma_tf32(tmem_base, d_alo, d_bhi, idesc, 1u);
           umma_tf32(tmem_base, d_ahi, d_blo, idesc, 1u);
         }
-        umma_commit(&empty[s]);   // the stage may be refilled once these MMAs have read it
+        umma_commit(&aempty[sa]);              // the A stage may be refilled once these MMAs have read it
+        if (w_reuse) umma_commit(&wempty[sb]);
       }
       if (ok) umma_commit(accfull);
+    }
+    __syncwarp();
+  } else {
+    // =========================== weight copies ===============================================
+    if (lane == 0) {
+      // FWD: the ring doubles as the staging area of the maximum pass; wait until it has been read
+      bool go = MODE != MN_FWD || mbar_wait(wgo, 0, a.status);
+      uint32_t issued = 0;
+      for (uint32_t i = 0; i < nchunks && go; ++i) {
+        const uint32_t sb = i % w_stages, pb = (i / w_stages) & 1u;
+        if (w_reuse && !mbar_wait(&wempty[sb], pb ^ 1u, a.status)) break;
+        uint8_t* dst = wring + sb * 2u * w_part;
+        const float* src = img_tile + (size_t)i * 2 * img_rows * KC;   // hi part, then lo part img_rows x 16 floats later
+        if (i < 32) MN_TRACE(128 + i);   // copies of chunk i issued
+        mbar_arrive_expect_tx(&wfull[sb], 2u * w_part);
+        bulk_g2s(dst, src, w_part, &wfull[sb]);
+        bulk_g2s(dst + w_part, src + (size_t)img_rows * KC, w_part, &wfull[sb]);
+        issued = i + 1;
+      }
+      if (issued < nchunks) {
+        // a wait was lost: let the copies already issued land before the CTA gives its memory back
+        for (uint32_t j = issued > w_stages ? issued - w_stages : 0; j < issued; ++j)
+          mbar_wait(&wfull[j % w_stages], (j / w_stages) & 1u, a.status);
+      }
     }
     __syncwarp();
   }
@@ -413,21 +569,47 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(MnArgs a) {
   // ---- common exit: release tensor memory ---------------------------------------------------------
   tc_fence_before();
   __syncthreads();
-  if (warp == PW) {
+  if (tid == 0) MN_TRACE(6);
+  if (warp == MMA_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
 template <int MODE>
-int32_t launch(dim3 grid, const MnArgs& args, cudaStream_t st, bool pdl) {
+int32_t launch(dim3 grid, const pcb_workspace* ws, const MnArgs& args, cudaStream_t st, bool pdl) {
+  if (!ws->have_tm_rows)
+    return pcb_fail(PCB_ERR_CUDA, "cuTensorMapEncodeTiled is not available: the dense-block kernels cannot fetch their row slabs");
   static PcbPerDeviceOnce once;
   PCB_CUDA(once.run([] {
     return cudaFuncSetAttribute(dense_mn_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
   }));
-  PCB_CUDA(pcb_launch_pdl(dense_mn_kernel<MODE>, grid, dim3(NTHREADS), SMEM_BYTES, st, pdl, args));
+  alignas(64) CUtensorMap tm;
+  memcpy(&tm, ws->tm_rows, sizeof(tm));
+  PCB_CUDA(pcb_launch_pdl(dense_mn_kernel<MODE>, grid, dim3(NTHREADS), SMEM_BYTES, st, pdl, tm, args));
   return PCB_OK;
 }
+
+#ifdef PCB_DIAG
+unsigned long long* g_mn_trace = nullptr;
+uint32_t g_mn_minz = 0, g_mn_maxz = 0xffffffffu;   // only launches with that many blocks are traced
+unsigned long long* mn_trace() {
+  if (!g_mn_trace && getenv("PCB_TC_TRACE")) {
+    if (const char* e = getenv("PCB_TC_TRACE_MINZ")) g_mn_minz = (uint32_t)atoi(e);
+    if (const char* e = getenv("PCB_TC_TRACE_MAXZ")) g_mn_maxz = (uint32_t)atoi(e);
+    cudaMalloc((void**)&g_mn_trace, 512 * sizeof(unsigned long long));
+    cudaMemset(g_mn_trace, 0, 512 * sizeof(unsigned long long));
+  }
+  return g_mn_trace;
+}
+unsigned long long* mn_trace_for(uint32_t blocks) {
+  unsigned long long* t = mn_trace();
+  return (t && blocks >= g_mn_minz && blocks <= g_mn_maxz) ? t : nullptr;
+}
+#else
+unsigned long long* mn_trace() { return nullptr; }
+unsigned long long* mn_trace_for(uint32_t) { return nullptr; }
+#endif
 
 // A layer that would not fill the GPU (two CTAs per SM) with 256-column tiles is cut into narrower
 // tiles: the CTAs of one tile repeat the production of the data-dependent operand, but each has
@@ -483,15 +665,19 @@ int32_t pcb_dense_mn_refresh(pcb_circuit* c, cudaStream_t st) {
   return PCB_OK;
 }
 
+// Diagnostic (-DPCB_DIAG builds with PCB_TC_TRACE set): the stamps of the last traced launches,
+// forward in words [0, 256), child flows in [256, 512); null otherwise.
+unsigned long long* pcb_dense_mn_trace() { return mn_trace(); }
+
 int32_t pcb_dense_mn_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st) {
   uint32_t o0 = c->h_dense_off[layer], o1 = c->h_dense_off[layer + 1];
   if (o1 == o0) return PCB_OK;
   const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM, ct = (c->max_dense_R + TN - 1) / TN;
   MnArgs args{ws->mars, ws->flows, ws->blk_mx, c->w_img16, c->dense + o0, c->dense_img16 + o0, c->status, ws->ld,
-              pick_nsplit(bt * ct * (o1 - o0), c->max_dense_R, c->tc_nsplit)};
+              pick_nsplit(bt * ct * (o1 - o0), c->max_dense_R, c->tc_nsplit), mn_trace_for(o1 - o0)};
   dim3 grid(bt, ct * args.nsplit, o1 - o0);
   PcbProfScope ps(c, st, PCB_K_DENSE_FWD);
-  return launch<MN_FWD>(grid, args, st, c->pdl);
+  return launch<MN_FWD>(grid, ws, args, st, c->pdl);
 }
 
 int32_t pcb_dense_mn_backward_child(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st) {
@@ -499,8 +685,8 @@ int32_t pcb_dense_mn_backward_child(pcb_circuit* c, pcb_workspace* ws, uint32_t 
   if (o1 == o0) return PCB_OK;
   const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM, ct = (c->max_dense_K + TN - 1) / TN;
   MnArgs args{ws->mars, ws->flows, ws->blk_mx, c->w_img16, c->dense + o0, c->dense_img16 + o0, c->status, ws->ld,
-              pick_nsplit(bt * ct * (o1 - o0), c->max_dense_K, c->tc_nsplit)};
+              pick_nsplit(bt * ct * (o1 - o0), c->max_dense_K, c->tc_nsplit), mn_trace_for(o1 - o0)};
   dim3 grid(bt, ct * args.nsplit, o1 - o0);
   PcbProfScope ps(c, st, PCB_K_DENSE_BWD_CHILD);
-  return launch<MN_BWD_CHILD>(grid, args, st, c->pdl);
+  return launch<MN_BWD_CHILD>(grid, ws, args, st, c->pdl);
 }

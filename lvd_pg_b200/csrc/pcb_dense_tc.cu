@@ -990,7 +990,12 @@ int32_t pcb_side_join(pcb_circuit* c, cudaStream_t st) {
 }
 
 // Diagnostic: copies the timing trace of the last traced kernel (PCB_TC_TRACE set) to the host.
+unsigned long long* pcb_dense_mn_trace();
 extern "C" int32_t pcb_debug_read_trace(unsigned long long* out) {
+  if (unsigned long long* t = pcb_dense_mn_trace()) {   // the example-major kernels are the ones in use
+    cudaDeviceSynchronize();
+    return cudaMemcpy(out, t, 512 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? PCB_OK : PCB_ERR_CUDA;
+  }
   if (!g_trace) return PCB_ERR_STATE;
   cudaDeviceSynchronize();
   return cudaMemcpy(out, g_trace, 512 * sizeof(unsigned long long), cudaMemcpyDeviceToHost) == cudaSuccess ? PCB_OK : PCB_ERR_CUDA;

@@ -205,6 +205,9 @@ struct pcb_workspace {
   // tensor maps over mars / flows for the copy-fed edge-statistics kernel (128-byte opaque objects)
   alignas(64) unsigned char tm[3][128];
   bool have_tm = false;
+  // tensor map over mars with boxes of [16 rows][128 examples] (row slabs of the values / child-flow kernels)
+  alignas(64) unsigned char tm_rows[128];
+  bool have_tm_rows = false;
   // state of the last forward
   uint32_t B = 0;
   const uint8_t* data = nullptr;
