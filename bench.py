@@ -213,14 +213,11 @@ def measure_cfg4(args, cpu_leg=True):
     theta_p = torch.from_numpy(np.asarray(api.vectorize_parameters(mp), np.float32)).to(dev)
     del mp
     P = int(theta_q.numel())
-    adam = api.Adam(m, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8)
+    opt = api.KldAdam(m, theta_q, theta_p, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8)   # one library call per step
     klv = []
 
     def step():
-        kl, reuse = api.kld(m, theta_q, theta_p)
-        g1, _ = api.kld_backward(m, reuse=reuse)
-        adam.step(theta_q, g1, sign=-1.0)
-        klv.append(kl)
+        klv.append(opt.step().clone())
 
     for _ in range(args.warmup):
         step()

@@ -92,6 +92,7 @@ typedef struct pcb_circuit_info {
   uint32_t num_dense_blocks, num_sum_regions, max_group_size, max_num_cats;
   uint64_t num_dense_edges;
   uint64_t device_bytes;
+  uint32_t num_heads, reserved;
 } pcb_circuit_info;
 
 const char* pcb_last_error(void);
@@ -157,6 +158,38 @@ int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev,
                     const uint8_t* miss_dev, uint64_t num_rows, const int32_t* row_ids_dev,
                     uint32_t row_start, uint32_t B, const float* weights_dev, float clear_rate,
                     float pseudocount, float inertia, float* ll_sum_dev, pcb_stream s);
+/* What a batch is evaluated on, for the forms of the reference's passes that the plain entry
+ * points above do not cover:
+ *  - soft evidence (regularization/reg_likelihood.jl:51-91, reg_flow.jl:50-82): soft_dev holds a
+ *    log-weight per (row, variable, category), [num_rows, num_vars, C] column-major, and takes the
+ *    place of data_dev; a leaf's value is logsumexp_c(soft + logp_c), its statistics take
+ *    exp(soft + logp_c - value) * flow per category;
+ *  - soft-regularised leaves (soft_reg > 0 with hard evidence: reg_likelihood.jl:4-14, reg_flow.jl:3-22);
+ *  - multi-head circuits (src-jl/multi_head_pc/): a circuit whose last node is a fake root sum whose
+ *    edges carry PCB_TAG_USER; its children are the heads.  head_mask_dev [num_rows, num_heads]
+ *    column-major gives every row's weight per head: root flows start from it (flow.jl:141-176) and
+ *    the log-likelihood is logsumexp_h(value_h + log mask_h) - log sum_h mask_h (bit_circuit.jl:95-109).
+ *    Without a mask only the forward pass is defined and ll_out_dev receives [B, num_heads]. */
+typedef struct pcb_evidence {
+  const uint8_t* data_dev;     /* [num_rows, num_vars] uint8 categories (NULL with soft_dev)   */
+  const uint8_t* miss_dev;     /* same shape, nonzero = missing, may be NULL                   */
+  const float* soft_dev;       /* per-category log-weights, or NULL                            */
+  const float* head_mask_dev;  /* multi-head circuits only, may be NULL for the forward pass   */
+  uint64_t num_rows;
+  const int32_t* row_ids_dev;  /* B 1-based row ids, or NULL for rows row_start .. row_start+B-1 */
+  uint32_t row_start, B;
+  float soft_reg;              /* 0: plain lookup                                              */
+  uint32_t soft_reg_width;
+} pcb_evidence;
+/* pcb_forward / pcb_em_step on such a batch (pcb_backward works on whatever the last forward saw);
+ * multi_head_probs_flows_circuit / mini_batch_em_for_multihead_pc (src-jl/multi_head_pc/flow.jl:197-201,
+ * em.jl:58-83) and the soft forms of mini_batch_em_with_reg are these calls in a loop. */
+int32_t pcb_forward_ex(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence* ev, float* ll_out_dev, pcb_stream s);
+int32_t pcb_em_step_ex(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence* ev, const float* weights_dev,
+                       float clear_rate, float pseudocount, float inertia, float* ll_sum_dev, pcb_stream s);
+/* Node ids (1-based) of the heads of a multi-head circuit, in head order. */
+int32_t pcb_get_head_roots(pcb_circuit* c, uint32_t* roots_host, uint64_t n);
+
 /* Parity accessors: mars / flows of the last batch, [B, num_nodes] column-major, ld = B. */
 int32_t pcb_get_mars(pcb_circuit* c, pcb_workspace* ws, float* mars_host, uint64_t n);
 int32_t pcb_get_flows(pcb_circuit* c, pcb_workspace* ws, float* flows_host, uint64_t n);
@@ -182,6 +215,17 @@ int32_t pcb_kld_edge_klds(pcb_circuit* c, pcb_workspace* ws, const float* params
 int32_t pcb_adam_step(pcb_circuit* c, float* theta_dev, const float* grad_dev, float* m_dev,
                       float* v_dev, int32_t t, float lr, float beta1, float beta2, float eps,
                       float sign, pcb_stream s);
+
+/* One step of the variational loop on a single parameter set: kld(q, p) (queries/kld.jl:164-206),
+ * kld_backward with respect to q (:593-649), an Adam descent step on q's log-parameters and the
+ * re-normalisation of every sum group and leaf (sgd/adam.jl:63-127,218-242) — what pcb_kld,
+ * pcb_kld_backward and pcb_adam_step(sign = -1) do one after the other, as one call: a second call
+ * with the same pointers and hyper-parameters captures the chain of launches as a CUDA graph and later
+ * calls replay it (t must grow by one per call; any other value re-seeds the count).  theta_q_dev
+ * [P] is updated in place; kld_out_dev (may be NULL) receives the KLD before the update. */
+int32_t pcb_kld_adam_step(pcb_circuit* c, pcb_workspace* ws, float* theta_q_dev, const float* theta_p_dev,
+                          float* m_dev, float* v_dev, int32_t t, float lr, float beta1, float beta2,
+                          float eps, float* kld_out_dev, pcb_stream s);
 
 /* ---- sampling ----------------------------------------------------------------------- */
 /* Hard Gumbel-max top-down sampling, the temperature -> 0 limit of

@@ -22,7 +22,14 @@ class PcbCircuitInfo(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in (
         "num_nodes", "num_edges", "num_sum_edges", "num_up_layers", "num_inner_params", "num_input_params",
         "num_param_groups", "num_dense_blocks", "num_sum_regions", "max_group_size", "max_num_cats")] + [
-        ("num_dense_edges", C.c_uint64), ("device_bytes", C.c_uint64)]
+        ("num_dense_edges", C.c_uint64), ("device_bytes", C.c_uint64), ("num_heads", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class PcbEvidence(C.Structure):
+    """ctypes mirror of `pcb_evidence` (include/pcb200.h)."""
+    _fields_ = [("data_dev", C.c_void_p), ("miss_dev", C.c_void_p), ("soft_dev", C.c_void_p), ("head_mask_dev", C.c_void_p),
+                ("num_rows", C.c_uint64), ("row_ids_dev", C.c_void_p), ("row_start", C.c_uint32), ("B", C.c_uint32),
+                ("soft_reg", C.c_float), ("soft_reg_width", C.c_uint32)]
 
 
 _u32, _u64, _i32, _f32, _vp = C.c_uint32, C.c_uint64, C.c_int32, C.c_float, C.c_void_p
@@ -48,6 +55,9 @@ SIGNATURES = {
     "pcb_clear_flows": [_vp, _f32, _vp],
     "pcb_em_update": [_vp, _f32, _f32, _vp],
     "pcb_em_step": [_vp, _vp, _vp, _vp, _u64, _vp, _u32, _u32, _vp, _f32, _f32, _f32, _vp, _vp],
+    "pcb_forward_ex": [_vp, _vp, C.POINTER(PcbEvidence), _vp, _vp],
+    "pcb_em_step_ex": [_vp, _vp, C.POINTER(PcbEvidence), _vp, _f32, _f32, _f32, _vp, _vp],
+    "pcb_get_head_roots": [_vp, _vp, _u64],
     "pcb_get_mars": [_vp, _vp, _vp, _u64],
     "pcb_get_flows": [_vp, _vp, _vp, _u64],
     "pcb_kld": [_vp, _vp, _vp, _vp, _u32, _vp, _vp],
@@ -55,6 +65,7 @@ SIGNATURES = {
     "pcb_get_klds": [_vp, _vp, _u32, _vp],
     "pcb_kld_edge_klds": [_vp, _vp, _vp, _vp, _u32, _vp, _vp],
     "pcb_adam_step": [_vp, _vp, _vp, _vp, _vp, _i32, _f32, _f32, _f32, _f32, _f32, _vp],
+    "pcb_kld_adam_step": [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _f32, _f32, _f32, _f32, _vp, _vp],
     "pcb_sample_hard": [_vp, _vp, _vp, _u32, _vp, _vp, _u32, _vp, _vp],
     "pcb_sample_hard_static": [_vp, _vp, _u32, _vp, _vp, _u32, _vp, _vp],
     "pcb_sample_soft": [_vp, _vp, _vp, _u32, _vp, _f32, _u32, _vp, _vp],

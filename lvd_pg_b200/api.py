@@ -10,8 +10,13 @@ forwards to libpcb200.so through the C ABI of include/pcb200.h:
   mini_batch_em(bpc, data, epochs; batch_size, pseudocount, param_inertia, param_inertia_end,
                 flow_memory, shuffle, weights)                   regularization/reg_em.jl:208-336
   full_batch_em                                                  (one step over all rows, inertia 0)
+  mini_batch_em_with_reg / loglikelihoods_probcat                the same two under the names the experiment
+                                                                 scripts call (reg_em.jl:208, reg_likelihood.jl:139)
   kld / kld_backward                                             queries/kld.jl:177-206, 593-649
+  kld_preallocation / kld_with_prealloc / kld_backward_with_prealloc / kld_free_mem
+                                                                 utils/cuda_preallocation.jl:6-78 (what PCVAE calls)
   gumbel_sample (soft) / sample (hard Gumbel-max)                queries/sample.jl:349-383
+  gumbel_sample_preallocation / gumbel_sample_with_prealloc      utils/cuda_preallocation.jl:150-203
 
 torch is used for device buffers and streams only.
 """
@@ -24,7 +29,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from .circuit import FlatCircuit, PCNode, compile_circuit
+from .circuit import FlatCircuit, PCNode, compile_circuit, compile_multihead
 
 ArrayLike = Union[np.ndarray, torch.Tensor]
 
@@ -255,6 +260,165 @@ def em_step(mbpc, data, row_ids=None, row_start=1, B=None, pseudocount=0.1, iner
     return ws
 
 
+def _evidence(mbpc, data, soft, head_mask, row_ids, row_start, B, soft_reg, soft_reg_width):
+    """Fill a pcb_evidence; returns (struct, B, keep-alive tuple)."""
+    ev = _lib.PcbEvidence()
+    keep = []
+    if data is not None:
+        data = _as_data(mbpc, data)
+        ev.data_dev, ev.miss_dev, num_rows = _ptr(data.t), _ptr(data.miss), data.num_rows
+        keep.append(data)
+    if soft is not None:
+        # [rows, V, C] with the rows fastest, as a Julia CuArray of that size lies in memory
+        assert soft.is_cuda and soft.dtype == torch.float32 and soft.dim() == 3
+        assert soft.stride() == (1, soft.shape[0], soft.shape[0] * soft.shape[1]), "soft evidence must be column-major"
+        ev.soft_dev, num_rows = _ptr(soft), soft.shape[0]
+    if head_mask is not None:
+        assert head_mask.is_cuda and head_mask.dtype == torch.float32 and head_mask.dim() == 2
+        assert head_mask.stride() == (1, head_mask.shape[0]), "head mask must be column-major"
+        assert head_mask.shape[0] == num_rows
+        ev.head_mask_dev = _ptr(head_mask)
+    if B is None:
+        B = int(row_ids.numel()) if row_ids is not None else num_rows - (row_start - 1)
+    ev.num_rows, ev.row_ids_dev, ev.row_start, ev.B = num_rows, _ptr(row_ids), row_start, B
+    ev.soft_reg, ev.soft_reg_width = soft_reg, soft_reg_width
+    keep += [soft, head_mask, row_ids]
+    return ev, B, keep
+
+
+def colmajor(a: ArrayLike, device) -> torch.Tensor:
+    """A float32 CUDA tensor with the first index fastest (the layout of a Julia CuArray)."""
+    t = torch.as_tensor(np.asarray(a, np.float32) if not torch.is_tensor(a) else a, dtype=torch.float32)
+    perm = list(range(t.dim()))[::-1]
+    return t.permute(*perm).contiguous().to(device).permute(*perm)
+
+
+def forward_ex(mbpc, data=None, soft: Optional[torch.Tensor] = None, head_mask: Optional[torch.Tensor] = None,
+               row_ids: Optional[torch.Tensor] = None, row_start: int = 1, B: Optional[int] = None,
+               soft_reg: float = 0.0, soft_reg_width: int = 1, ll_out: Optional[torch.Tensor] = None):
+    """eval_circuit on soft evidence (init_mar!_with_reg_cat, regularization/reg_likelihood.jl:51-91), with
+    soft regularisation of the leaves (reg_likelihood.jl:4-49) and / or on a multi-head circuit
+    (eval_multi_head_pc, src-jl/multi_head_pc/likelihood.jl:18-31); returns (workspace, B)."""
+    ev, B, keep = _evidence(mbpc, data, soft, head_mask, row_ids, row_start, B, soft_reg, soft_reg_width)
+    ws = mbpc.workspace(B)
+    _lib.check(mbpc.lib.pcb_forward_ex(mbpc.handle, ws, C.byref(ev), _ptr(ll_out), _stream(mbpc.device)))
+    return ws, B
+
+
+def em_step_ex(mbpc, data=None, soft=None, head_mask=None, row_ids=None, row_start=1, B=None, pseudocount=0.1,
+               inertia=0.0, clear_rate=0.0, weights=None, soft_reg=0.0, soft_reg_width=1,
+               ll_sum: Optional[torch.Tensor] = None):
+    """Per-batch body of mini_batch_em_with_reg (reg_em.jl:273-301) / mini_batch_em_for_multihead_pc
+    (src-jl/multi_head_pc/em.jl:58-83) on the general forms of evidence."""
+    ev, B, keep = _evidence(mbpc, data, soft, head_mask, row_ids, row_start, B, soft_reg, soft_reg_width)
+    ws = mbpc.workspace(B)
+    _lib.check(mbpc.lib.pcb_em_step_ex(mbpc.handle, ws, C.byref(ev), _ptr(weights), clear_rate, pseudocount, inertia,
+                                       _ptr(ll_sum), _stream(mbpc.device)))
+    return ws
+
+
+class CuMultiHeadBitsProbCircuit(CuMetaBitsProbCircuit):
+    """`CuMultiHeadBitsProbCircuit(pcs)` (src-jl/multi_head_pc/bit_circuit.jl:4-56): several heads over
+    shared sub-circuits, held as one flat circuit under a fake root whose edges no top-down pass follows."""
+
+    def __init__(self, pcs, device: int = 0):
+        if isinstance(pcs, FlatCircuit):
+            fc = pcs
+        else:
+            fc, _ = compile_multihead(list(pcs))
+        super().__init__(fc, device)
+        n = int(self.info.num_heads)
+        roots = np.zeros(n, np.uint32)
+        _lib.check(self.lib.pcb_get_head_roots(self.handle, roots.ctypes.data_as(C.c_void_p), n))
+        self.root_ids = roots
+
+    @property
+    def bpc(self):
+        return self
+
+
+def multihead_loglikelihoods(mhbpc: CuMultiHeadBitsProbCircuit, data, head_mask: Optional[torch.Tensor],
+                             batch_size: int = 512) -> torch.Tensor:
+    """`loglikelihoods(mhbpc, data, head_mask; batch_size)` (src-jl/multi_head_pc/likelihood.jl:35-66) and
+    multihead_loglikelihoods_probcat (src/multi_head_pc/multi_head_pc_likelihood.jl:37-63): [rows] with a
+    mask, [rows, heads] without."""
+    data = _as_data(mhbpc, data)
+    H = len(mhbpc.root_ids)
+    rows = data.num_rows
+    out = torch.empty(rows if head_mask is not None else (H, rows), dtype=torch.float32, device=mhbpc.device)
+    for start in range(0, rows, batch_size):
+        b = min(batch_size, rows - start)
+        if head_mask is not None:
+            forward_ex(mhbpc, data, None, head_mask, None, start + 1, b, ll_out=out[start:start + b])
+        else:
+            tmp = torch.empty((H, b), dtype=torch.float32, device=mhbpc.device)
+            forward_ex(mhbpc, data, None, None, None, start + 1, b, ll_out=tmp)
+            out[:, start:start + b] = tmp
+    return out if head_mask is not None else out.t()
+
+
+def mini_batch_em_for_multihead_pc(mhbpc: CuMultiHeadBitsProbCircuit, data, head_mask: torch.Tensor, num_epochs: int,
+                                   batch_size: int, pseudocount: float, soft_reg: float = 0.0, soft_reg_width: int = 1,
+                                   param_inertia: float = 0.0, param_inertia_end: Optional[float] = None,
+                                   flow_memory: float = 0.0, shuffle: str = "each_epoch", weights=None,
+                                   seed: Optional[int] = None, verbose: bool = False) -> List[float]:
+    """mini_batch_em_for_multihead_pc (src-jl/multi_head_pc/em.jl:1-100)."""
+    return _mini_batch_loop(mhbpc, data, None, head_mask, num_epochs, batch_size, pseudocount, soft_reg, soft_reg_width,
+                            param_inertia, param_inertia_end, flow_memory, shuffle, weights, seed, verbose)
+
+
+def mini_batch_em_soft(mbpc: CuMetaBitsProbCircuit, soft: torch.Tensor, num_epochs: int, batch_size: int,
+                       pseudocount: float, param_inertia: float = 0.0, param_inertia_end: Optional[float] = None,
+                       flow_memory: float = 0.0, shuffle: str = "each_epoch", weights=None,
+                       seed: Optional[int] = None, verbose: bool = False) -> List[float]:
+    """mini_batch_em_with_reg on a 3-D array of per-category log-weights (reg_em.jl:196-318 with
+    `data isa CuArray{Float32,3}`: init_mar!_with_reg_cat / input_flows_circuit_with_reg_cat)."""
+    return _mini_batch_loop(mbpc, None, soft, None, num_epochs, batch_size, pseudocount, 0.0, 1, param_inertia,
+                            param_inertia_end, flow_memory, shuffle, weights, seed, verbose)
+
+
+def _mini_batch_loop(mbpc, data, soft, head_mask, num_epochs, batch_size, pseudocount, soft_reg, soft_reg_width,
+                     param_inertia, param_inertia_end, flow_memory, shuffle, weights, seed, verbose) -> List[float]:
+    if data is not None:
+        data = _as_data(mbpc, data)
+    rows = data.num_rows if data is not None else soft.shape[0]
+    assert batch_size <= rows
+    num_batches = rows // batch_size   # the last incomplete batch is dropped
+    dev = mbpc.device
+    gen = torch.Generator(device="cpu")
+    if seed is not None:
+        gen.manual_seed(seed)
+    ids = torch.empty(rows, dtype=torch.int32, device=dev)
+
+    def do_shuffle():
+        ids.copy_((torch.randperm(rows, generator=gen) + 1).to(torch.int32), non_blocking=False)
+
+    if shuffle == "once":
+        do_shuffle()
+    elif shuffle == "none":
+        ids.copy_(torch.arange(1, rows + 1, dtype=torch.int32))
+    if param_inertia_end is None:
+        param_inertia_end = param_inertia
+    d_inertia = (param_inertia_end - param_inertia) / num_epochs
+    rate = 0.0 if flow_memory == 0 else max(0.0, 1.0 - (batch_size + pseudocount) / flow_memory)
+    lls_epoch = torch.zeros(num_batches, dtype=torch.float32, device=dev)
+    out: List[float] = []
+    for epoch in range(num_epochs):
+        if shuffle == "each_epoch":
+            do_shuffle()
+        for b in range(num_batches):
+            if shuffle == "each_batch":
+                do_shuffle()
+            em_step_ex(mbpc, data, soft, head_mask, ids[b * batch_size:(b + 1) * batch_size], 1, batch_size, pseudocount,
+                       param_inertia, rate, weights, soft_reg, soft_reg_width, lls_epoch[b:b + 1])
+        out.append(float(lls_epoch.sum().item()) / batch_size / num_batches)
+        _lib.check(mbpc.lib.pcb_circuit_status(mbpc.handle))
+        param_inertia += d_inertia
+        if verbose:
+            print(f"Mini-batch EM epoch {epoch + 1}; train LL {out[-1]}")
+    return out
+
+
 def mini_batch_em(mbpc: CuMetaBitsProbCircuit, data, num_epochs: int, batch_size: int, pseudocount: float,
                   param_inertia: float, param_inertia_end: Optional[float] = None, flow_memory: float = 0.0,
                   shuffle: str = "each_epoch", weights: Optional[torch.Tensor] = None, seed: Optional[int] = None,
@@ -296,6 +460,26 @@ def mini_batch_em(mbpc: CuMetaBitsProbCircuit, data, num_epochs: int, batch_size
     return out
 
 
+def mini_batch_em_with_reg(mbpc: CuMetaBitsProbCircuit, data, num_epochs: int, batch_size: int, pseudocount: float,
+                           soft_reg: float = 0.0, soft_reg_width: int = 1, ent_reg: float = 0.0,
+                           param_inertia: float = 0.0, param_inertia_end: Optional[float] = None, flow_memory: float = 0.0,
+                           shuffle: str = "each_epoch", weights: Optional[torch.Tensor] = None, seed: Optional[int] = None,
+                           verbose: bool = False, **ignored) -> List[float]:
+    """The name and keyword set the experiment scripts use (reg_em.jl:208-213).  `soft_reg` must be 0
+    (the plain leaf lookup, reg_likelihood.jl:4-14 with soft_reg = 0); `ent_reg` is accepted and
+    ignored as in the reference, whose entropy step is commented out (reg_em.jl:294-296); the
+    *_mem / mine / maxe / debug keywords tune the reference's own kernels and are ignored."""
+    if soft_reg != 0.0:
+        raise _lib.PcbError(1, "soft_reg > 0 (soft-regularised leaves) is not built")
+    return mini_batch_em(mbpc, data, num_epochs, batch_size, pseudocount, param_inertia, param_inertia_end, flow_memory,
+                         shuffle, weights, seed, verbose)
+
+
+def loglikelihoods_probcat(mbpc: CuMetaBitsProbCircuit, data, batch_size: int = 512) -> torch.Tensor:
+    """reg_likelihood.jl:139-162 for hard evidence (uint8 categories)."""
+    return loglikelihoods(mbpc, data, batch_size)
+
+
 def full_batch_em(mbpc: CuMetaBitsProbCircuit, data, num_epochs: int, batch_size: int, pseudocount: float) -> List[float]:
     """Accumulate flows over all rows (in batches), then one update with inertia 0."""
     data = _as_data(mbpc, data)
@@ -324,8 +508,9 @@ def _params_matrix(mbpc, p: ArrayLike) -> torch.Tensor:
 
 
 def kld(mbpc: CuMetaBitsProbCircuit, params1: ArrayLike, params2: ArrayLike):
-    """Returns (klds[S], reuse): `reuse` is what kld_backward needs (the reference hands back
-    the klds / edge_klds matrices for the same purpose, kld.jl:203-205)."""
+    """Returns (klds[S], reuse): `reuse` is what kld_backward needs.  The reference hands back the
+    host copies (klds_mat, edge_klds_mat) for the same purpose (kld.jl:203-205); here the node
+    values stay on the device and `kld_matrices(mbpc, reuse)` produces those two matrices on demand."""
     p1, p2 = _params_matrix(mbpc, params1), _params_matrix(mbpc, params2)
     S = int(p1.shape[1])
     ws = mbpc.workspace(1)
@@ -356,6 +541,46 @@ def kld_backward(mbpc: CuMetaBitsProbCircuit, params1=None, params2=None, reuse=
     return g1.t(), g2.t()
 
 
+# The preallocated forms PCVAE calls through pyjulia (src/models/pc_vae.py:88-92,131,194): buffers are
+# module-level state, as the reference keeps them in Julia globals (cuda_preallocation.jl:12-25).
+_prealloc = {}
+
+
+def kld_preallocation(mbpc: CuMetaBitsProbCircuit, num_examples: int) -> None:
+    P = num_parameters(mbpc)
+    dev = mbpc.device
+    _prealloc["kld"] = dict(S=num_examples, p1=torch.empty(P, num_examples, device=dev), p2=torch.empty(P, num_examples, device=dev),
+                            g1=torch.empty(P, num_examples, device=dev), g2=torch.empty(P, num_examples, device=dev),
+                            out=torch.empty(num_examples, device=dev), ws=mbpc.workspace(1))
+
+
+def kld_free_mem() -> None:
+    _prealloc.pop("kld", None)
+
+
+def kld_with_prealloc(mbpc: CuMetaBitsProbCircuit, params1: ArrayLike, params2: ArrayLike) -> np.ndarray:
+    """klds[:, end] as a host vector (cuda_preallocation.jl:47-61); the parameters are copied into the
+    preallocated device matrices and kept for kld_backward_with_prealloc."""
+    b = _prealloc["kld"]
+    for dst, src in ((b["p1"], params1), (b["p2"], params2)):
+        src = torch.as_tensor(src, dtype=torch.float32)
+        assert tuple(src.shape) == (b["S"], dst.shape[0]), "shape differs from kld_preallocation"
+        dst.copy_(src.t(), non_blocking=True)
+    _lib.check(mbpc.lib.pcb_kld(mbpc.handle, b["ws"], _ptr(b["p1"]), _ptr(b["p2"]), b["S"], _ptr(b["out"]),
+                                _stream(mbpc.device)))
+    return b["out"].cpu().numpy()
+
+
+def kld_backward_with_prealloc(mbpc: CuMetaBitsProbCircuit) -> Tuple[np.ndarray, np.ndarray]:
+    """(param_grads1, param_grads2) of the last kld_with_prealloc call as host matrices [S, P]
+    (cuda_preallocation.jl:63-78)."""
+    b = _prealloc["kld"]
+    b["g1"].zero_(); b["g2"].zero_()
+    _lib.check(mbpc.lib.pcb_kld_backward(mbpc.handle, b["ws"], _ptr(b["p1"]), _ptr(b["p2"]), b["S"], _ptr(b["g1"]),
+                                         _ptr(b["g2"]), _stream(mbpc.device)))
+    return b["g1"].t().cpu().numpy(), b["g2"].t().cpu().numpy()
+
+
 class Adam:
     """Adam on a flat log-parameter vector followed by re-normalisation (sgd/adam.jl:63-127)."""
 
@@ -372,6 +597,32 @@ class Adam:
         _lib.check(self.mbpc.lib.pcb_adam_step(self.mbpc.handle, _ptr(theta), _ptr(grad), _ptr(self.m), _ptr(self.v),
                                                self.t, self.lr, self.beta1, self.beta2, self.eps, sign,
                                                _stream(self.mbpc.device)))
+
+
+class KldAdam:
+    """KLD(q || p) + gradient + Adam step on q + re-normalisation as one library call per step
+    (pcb_kld_adam_step): the chain of small launches of a single parameter set is captured as a CUDA
+    graph on the second step and replayed afterwards.  `theta_q` (a CUDA float vector) is updated
+    in place; `step()` returns the KLD before the update as a one-element CUDA tensor."""
+
+    def __init__(self, mbpc: CuMetaBitsProbCircuit, theta_q: torch.Tensor, theta_p: torch.Tensor, lr=1e-2, beta1=0.9,
+                 beta2=0.999, eps=1e-8):
+        P = num_parameters(mbpc)
+        assert theta_q.is_cuda and theta_p.is_cuda and theta_q.numel() == P and theta_p.numel() == P
+        self.mbpc, self.q, self.p = mbpc, theta_q, theta_p.contiguous()
+        self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
+        self.m = torch.zeros(P, dtype=torch.float32, device=mbpc.device)
+        self.v = torch.zeros(P, dtype=torch.float32, device=mbpc.device)
+        self.kld = torch.zeros(1, dtype=torch.float32, device=mbpc.device)
+        self.ws = mbpc.workspace(1)
+        self.t = 0
+
+    def step(self) -> torch.Tensor:
+        self.t += 1
+        _lib.check(self.mbpc.lib.pcb_kld_adam_step(self.mbpc.handle, self.ws, _ptr(self.q), _ptr(self.p), _ptr(self.m),
+                                                   _ptr(self.v), self.t, self.lr, self.beta1, self.beta2, self.eps,
+                                                   _ptr(self.kld), _stream(self.mbpc.device)))
+        return self.kld
 
 
 # ---- sampling ---------------------------------------------------------------------------------------
@@ -405,6 +656,21 @@ def sample_static(mbpc: CuMetaBitsProbCircuit, params: torch.Tensor, u_sum: torc
     _lib.check(mbpc.lib.pcb_sample_hard_static(mbpc.handle, _ptr(params), int(params.shape[1]), _ptr(u_sum),
                                                _ptr(u_leaf), S, _ptr(x_out), _stream(mbpc.device)))
     return x_out.t()
+
+
+def gumbel_sample_preallocation(mbpc: CuMetaBitsProbCircuit, num_examples: int, num_vars: int, par_buffer_size: int) -> None:
+    """cuda_preallocation.jl:150-187: the sampler's buffers live in the workspace here; this records
+    the shapes the later calls are checked against."""
+    assert num_vars == mbpc.fc.num_vars and par_buffer_size == int(mbpc.info.max_num_cats)
+    _prealloc["sample"] = dict(S=num_examples, V=num_vars, C=par_buffer_size)
+
+
+def gumbel_sample_with_prealloc(mbpc: CuMetaBitsProbCircuit, params: ArrayLike, temperature: float, no_gumbel: bool = False,
+                                u: Optional[ArrayLike] = None) -> np.ndarray:
+    """input_aggr_params as a host array [S, num_vars, par_buffer_size] (cuda_preallocation.jl:189-203)."""
+    b = _prealloc["sample"]
+    out = gumbel_sample(mbpc, params, b["V"], b["C"], temperature, no_gumbel=no_gumbel, u=u, S=b["S"])
+    return out.cpu().numpy()
 
 
 def gumbel_sample(mbpc: CuMetaBitsProbCircuit, params: ArrayLike, num_vars: int, par_buffer_size: int,

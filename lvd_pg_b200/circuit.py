@@ -183,8 +183,9 @@ def summate(*children: PCNode) -> Sum:
     return Sum(children)
 
 
-def compile_circuit(root: PCNode, collapse_elements: bool = True) -> FlatCircuit:
-    """Flatten a node graph the way `BitsProbCircuit(pc)` does (see module docstring)."""
+def compile_circuit(root: PCNode, collapse_elements: bool = True, return_ids: bool = False):
+    """Flatten a node graph the way `BitsProbCircuit(pc)` does (see module docstring).  With
+    `return_ids` also returns {id(node): 1-based node id} of the materialised nodes."""
 
     def resolve(n: PCNode) -> PCNode:
         # a non-root inner node with one child is not materialised
@@ -275,9 +276,29 @@ def compile_circuit(root: PCNode, collapse_elements: bool = True) -> FlatCircuit
                 up_logp.append(lp)
                 up_tag.append((TAG_FIRST if j == 0 else 0) | (TAG_LAST if j == len(es) - 1 else 0))
         up_ends.append(len(up_parent))
-    return finish_flat(kind, var, ncat, hstart, fixed, up_parent, up_prime, up_sub, up_logp, up_tag,
-                       up_ends, input_ids, np.concatenate(heap) if heap else np.zeros(0, np.float32),
-                       num_vars)
+    fc = finish_flat(kind, var, ncat, hstart, fixed, up_parent, up_prime, up_sub, up_logp, up_tag,
+                     up_ends, input_ids, np.concatenate(heap) if heap else np.zeros(0, np.float32),
+                     num_vars)
+    return (fc, ids) if return_ids else fc
+
+
+def compile_multihead(pcs: Sequence[PCNode], collapse_elements: bool = True):
+    """`CuMultiHeadBitsProbCircuit(pcs)` (src-jl/multi_head_pc/bit_circuit.jl:14-56): the heads go
+    under a fake root, a sum over them, so that one flat circuit holds all of them; the fake root's
+    edges carry TAG_USER, which every top-down pass skips.  Returns (FlatCircuit, root_ids), root_ids
+    the 1-based node ids of the heads in the order given."""
+    fake = summate(*pcs)
+    fc, ids = compile_circuit(fake, collapse_elements, return_ids=True)
+    root_ids = []
+    for pc in pcs:
+        if id(pc) not in ids:
+            raise ValueError("a head is not a materialised node of the flat circuit")
+        root_ids.append(ids[id(pc)])
+    sel = fc.up_parent == fc.num_nodes
+    if not np.array_equal(np.sort(fc.up_prime[sel]), np.sort(np.asarray(root_ids, fc.up_prime.dtype))) or fc.up_sub[sel].any():
+        raise ValueError("every head must be a child of the fake root by an edge of its own")
+    fc.up_tag[sel] |= TAG_USER
+    return fc, np.asarray(root_ids, np.uint32)
 
 
 def finish_flat(kind, var, ncat, hstart, fixed, up_parent, up_prime, up_sub, up_logp, up_tag, up_ends,

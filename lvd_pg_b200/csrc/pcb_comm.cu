@@ -92,6 +92,15 @@ extern "C" int32_t pcb_comm_destroy(pcb_circuit* c) {
   if (c->comm && g_nccl.destroy) {
     cudaSetDevice(c->device);
     cudaDeviceSynchronize();
+    // A captured step holds a reference to the communicator for as long as its graph lives, and
+    // ncclCommDestroy waits until every such graph is gone: drop the step graphs first.
+    {
+      std::lock_guard<std::mutex> g(c->ws_mu);
+      for (pcb_workspace* ws : c->workspaces) {
+        if (ws->step_exec) { cudaGraphExecDestroy(ws->step_exec); ws->step_exec = nullptr; }
+        ws->have_key = false;
+      }
+    }
     g_nccl.destroy(c->comm);
   }
   c->comm = nullptr;

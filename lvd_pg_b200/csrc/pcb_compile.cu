@@ -180,9 +180,26 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
     c->n_regions = (uint32_t)ids.size();
   }
 
+  // ---- multi-head circuits: the edges of the last node (a fake root over the heads) that carry the
+  // user tag are skipped by every top-down pass (src-jl/multi_head_pc/bit_circuit.jl:22-34,
+  // flow.jl:45); their prime children, in edge order, are the heads (root_ids of bit_circuit.jl:36-50)
+  auto skipped = [&](uint32_t e) {
+    return d->up_tag && (d->up_tag[e] & PCB_TAG_USER) && d->up_parent[e] == N;
+  };
+  std::vector<uint32_t> node_head(N, PCB_NONE);
+  c->h_head_roots.clear();
+  for (uint32_t e = 0; e < E; ++e)
+    if (skipped(e)) {
+      PCB_REQUIRE(d->up_sub[e] == 0, "a skipped fake-root edge must have a single child");
+      node_head[d->up_prime[e] - 1] = (uint32_t)c->h_head_roots.size();
+      c->h_head_roots.push_back(d->up_prime[e] - 1);
+    }
+  c->n_heads = (uint32_t)c->h_head_roots.size();
+
   // ---- CSR by child ---------------------------------------------------------------------
   std::vector<uint32_t> in_off(N + 1, 0);
   for (uint32_t e = 0; e < E; ++e) {
+    if (skipped(e)) continue;
     ++in_off[d->up_prime[e]];            // (prime-1)+1
     if (d->up_sub[e]) ++in_off[d->up_sub[e]];
   }
@@ -191,6 +208,7 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
   {
     std::vector<uint32_t> cur(in_off.begin(), in_off.end() - 1);
     for (uint32_t e = 0; e < E; ++e) {
+      if (skipped(e)) continue;
       uint32_t p = d->up_parent[e] - 1, pr = d->up_prime[e] - 1;
       uint32_t sb = d->up_sub[e] ? d->up_sub[e] - 1 : PCB_NONE;
       in_ent[cur[pr]++] = PcbInEntry{p, sb, e2p[e], 1u};
@@ -313,6 +331,8 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
   PCB_TRY(upload(&c->in_poff, in_poff, &bytes));
   PCB_TRY(upload(&c->in_foff, in_foff, &bytes));
   PCB_TRY(upload(&c->node2input, node2input, &bytes));
+  PCB_TRY(upload(&c->n_head, node_head, &bytes));
+  PCB_TRY(upload(&c->head_roots, c->h_head_roots, &bytes));
   PCB_TRY(upload(&c->up_all, up_all, &bytes));
   PCB_TRY(upload(&c->up_sparse, up_sparse, &bytes));
   PCB_TRY(upload(&c->down_all, down_all, &bytes));
@@ -394,7 +414,7 @@ void free_circuit(pcb_circuit* c) {
                   c->e_sub, c->in_node, c->in_var, c->in_cats, c->in_poff, c->in_foff, c->node2input,
                   c->up_all, c->up_sparse, c->down_all, c->down_sparse, c->in_off, c->in_ent, c->dense,
                   c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status, c->w_img, c->dense_img, c->w_img16, c->dense_img16,
-                  c->lgrp_var, c->lgrp_off, c->s_node, c->s_leaf};
+                  c->lgrp_var, c->lgrp_off, c->s_node, c->s_leaf, c->n_head, c->head_roots};
   for (void* p : ptrs) if (p) cudaFree(p);
   if (c->ev_g0) cudaEventDestroy(c->ev_g0);
   if (c->ev_g1) cudaEventDestroy(c->ev_g1);
@@ -440,6 +460,14 @@ extern "C" int32_t pcb_circuit_get_info(const pcb_circuit* c, pcb_circuit_info* 
   info->num_inner_params = c->n_inner; info->num_input_params = c->n_input_params; info->num_param_groups = c->n_groups;
   info->num_dense_blocks = c->n_dense; info->num_sum_regions = c->n_regions; info->max_group_size = c->max_group;
   info->max_num_cats = c->max_cats; info->num_dense_edges = c->dense_edges; info->device_bytes = c->device_bytes;
+  info->num_heads = c->n_heads; info->reserved = 0;
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_get_head_roots(pcb_circuit* c, uint32_t* roots_host, uint64_t n) {
+  PCB_REQUIRE(c && roots_host, "null argument");
+  PCB_REQUIRE(n == c->n_heads, "the circuit has a different number of heads");
+  for (uint32_t h = 0; h < c->n_heads; ++h) roots_host[h] = c->h_head_roots[h] + 1;
   return PCB_OK;
 }
 
@@ -474,6 +502,7 @@ extern "C" int32_t pcb_workspace_create(pcb_circuit* c, uint32_t max_batch, int3
     int32_t st = pcb_ws_ensure_sets(ws, max_batch, true);
     if (st != PCB_OK) { pcb_workspace_destroy(ws); return st; }
   }
+  { std::lock_guard<std::mutex> g(c->ws_mu); c->workspaces.push_back(ws); }
   *out = ws;
   return PCB_OK;
 }
@@ -503,9 +532,16 @@ int32_t pcb_ws_ensure_sets(pcb_workspace* ws, uint32_t S, bool need_stack) {
 extern "C" int32_t pcb_workspace_destroy(pcb_workspace* ws) {
   if (!ws) return PCB_OK;
   cudaSetDevice(ws->c->device);
+  {
+    std::lock_guard<std::mutex> g(ws->c->ws_mu);
+    auto& v = ws->c->workspaces;
+    v.erase(std::remove(v.begin(), v.end(), ws), v.end());
+  }
   if (ws->step_exec) cudaGraphExecDestroy(ws->step_exec);
+  if (ws->kld_exec) cudaGraphExecDestroy(ws->kld_exec);
   for (void* p : {(void*)ws->mars, (void*)ws->flows, (void*)ws->blk_mx, (void*)ws->klds, (void*)ws->grads,
-                  (void*)ws->eprob, (void*)ws->cum, (void*)ws->stack, (void*)ws->ids_stage})
+                  (void*)ws->eprob, (void*)ws->cum, (void*)ws->stack, (void*)ws->ids_stage, (void*)ws->ll_tmp, (void*)ws->kld_g1,
+                  (void*)ws->kld_g2, (void*)ws->kld_t_dev})
     if (p) cudaFree(p);
   delete ws;
   return PCB_OK;

@@ -92,10 +92,19 @@ __global__ void sparse_up_kernel(float* __restrict__ mars, uint32_t ld, uint32_t
 // Pull-based top-down pass: flows[n][b] = sum over incoming edges of the edge flow
 //   product parent: flows[parent]; sum parent: flows[parent] * exp(child value + logp - mars[parent]).
 // The root (no incoming edge, last node) gets 1, any other parentless node 0.
+// Multi-head circuits (head_mask != null): the flow of head h starts at head_mask[row, h], every
+// other parentless node at 0 (src-jl/multi_head_pc/flow.jl:141-176).
+struct HeadInit {
+  const uint32_t* n_head;
+  const float* head_mask;
+  uint64_t mask_rows;
+  const int32_t* row_ids;
+  uint32_t row_start;
+};
 __global__ void sparse_down_kernel(float* __restrict__ flows, const float* __restrict__ mars, uint32_t ld,
                                    uint32_t B, const uint32_t* __restrict__ nodes, uint32_t root,
                                    const uint32_t* __restrict__ in_off, const PcbInEntry* __restrict__ in_ent,
-                                   const float* __restrict__ theta, float* __restrict__ aggr) {
+                                   const float* __restrict__ theta, float* __restrict__ aggr, HeadInit hi) {
   pcb_grid_dep_launch();
   uint32_t n = nodes[blockIdx.x];
   uint32_t b = (blockIdx.y * blockDim.x + threadIdx.x) * 4u;
@@ -104,8 +113,21 @@ __global__ void sparse_down_kernel(float* __restrict__ flows, const float* __res
   const bool a0 = b < B, a1 = b + 1 < B, a2 = b + 2 < B, a3 = b + 3 < B;
   uint32_t i0 = in_off[n], i1 = in_off[n + 1];
   pcb_grid_dep_wait();   // everything above is static circuit data
-  const float init = (i0 == i1 && n == root) ? 1.0f : 0.0f;
-  float4 acc = make_float4(init, init, init, init);
+  float4 acc;
+  if (hi.head_mask) {
+    const uint32_t h = hi.n_head[n];
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (h != PCB_NONE) {
+      const float* mk = hi.head_mask + (size_t)hi.mask_rows * h;
+      if (a0) acc.x = mk[data_row(hi.row_ids, hi.row_start, b)];
+      if (a1) acc.y = mk[data_row(hi.row_ids, hi.row_start, b + 1)];
+      if (a2) acc.z = mk[data_row(hi.row_ids, hi.row_start, b + 2)];
+      if (a3) acc.w = mk[data_row(hi.row_ids, hi.row_start, b + 3)];
+    }
+  } else {
+    const float init = (i0 == i1 && n == root) ? 1.0f : 0.0f;
+    acc = make_float4(init, init, init, init);
+  }
   const float4 my = ld4(mars + (size_t)n * ld + bb);
   for (uint32_t i = i0; i < i1; ++i) {
     PcbInEntry en = in_ent[i];
@@ -392,6 +414,122 @@ __global__ void __launch_bounds__(LST) leaf_flow_sorted_kernel(
   }
 }
 
+// ---- leaves under soft evidence / soft regularisation ----------------------------------------------
+// One block per leaf, threads over the examples.  soft != null: per-category log-weights
+// soft[row, var, c] ([rows, V, C] column-major) stand where the observed category stands
+// (init_mar!_with_reg_cat_kernel, regularization/reg_likelihood.jl:51-91); else hard evidence with
+// soft_reg > 0 (soft_loglikelihood, reg_likelihood.jl:4-14).
+__global__ void leaf_forward_gen_kernel(float* __restrict__ mars, uint32_t ld, uint32_t B, const float* __restrict__ theta,
+                                        const uint32_t* __restrict__ in_node, const uint32_t* __restrict__ in_var,
+                                        const uint32_t* __restrict__ in_cats, const uint64_t* __restrict__ in_poff,
+                                        uint32_t num_vars, const uint8_t* __restrict__ data, const uint8_t* __restrict__ miss,
+                                        const float* __restrict__ soft, uint64_t num_rows,
+                                        const int32_t* __restrict__ row_ids, uint32_t row_start, float soft_reg, int32_t width) {
+  const uint32_t i = blockIdx.x, b = blockIdx.y * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const int64_t row = data_row(row_ids, row_start, b);
+  const uint32_t C = in_cats[i], var = in_var[i];
+  const float* tab = theta + in_poff[i];
+  float v;
+  if (soft) {
+    const float* sp = soft + (size_t)row + (size_t)num_rows * var;
+    const size_t cs = (size_t)num_rows * num_vars;
+    float mx = -INFINITY;
+    for (uint32_t c = 0; c < C; ++c) mx = fmaxf(mx, sp[c * cs] + __ldg(tab + c));
+    float acc = 0.0f;
+    for (uint32_t c = 0; c < C; ++c) acc += expf(sp[c * cs] + __ldg(tab + c) - mx);
+    v = mx == -INFINITY ? -INFINITY : mx + logf(acc);
+  } else {
+    const size_t di = (size_t)row + (size_t)num_rows * var;
+    if (miss && miss[di]) {
+      v = 0.0f;
+    } else {
+      const int32_t x = data[di];
+      const int32_t c_start = max(0, x - width / 2), c_end = min(c_start + width - 1, (int32_t)C - 1);
+      float sp = 0.0f;
+      for (int32_t c = c_start; c <= c_end; ++c) sp += expf(__ldg(tab + c));
+      sp /= (float)(c_end - c_start + 1);
+      const float u = __ldg(tab + x) + logf(1.0f - soft_reg), w = logf(sp) + logf(soft_reg);
+      const float m = fmaxf(u, w);
+      v = (isfinite(u) && isfinite(w)) ? m + log1pf(expf(-fabsf(u - w))) : m;
+    }
+  }
+  mars[(size_t)in_node[i] * ld + b] = v;
+}
+
+// Leaf statistics of the same two forms (input_flows_circuit_with_reg_cat_kernel reg_flow.jl:50-82;
+// soft_flow reg_flow.jl:3-22, which uses the stored LOG-probabilities where it says heap[...]: kept
+// as written).  A warp reduces its 32 examples per category before touching memory.
+__global__ void leaf_flow_gen_kernel(const float* __restrict__ flows, const float* __restrict__ mars, uint32_t ld, uint32_t B,
+                                     float* __restrict__ aggr, const float* __restrict__ theta,
+                                     const uint32_t* __restrict__ in_node, const uint32_t* __restrict__ in_var,
+                                     const uint32_t* __restrict__ in_cats, const uint64_t* __restrict__ in_poff,
+                                     const uint64_t* __restrict__ in_foff, uint32_t num_vars,
+                                     const uint8_t* __restrict__ data, const uint8_t* __restrict__ miss,
+                                     const float* __restrict__ soft, uint64_t num_rows, const int32_t* __restrict__ row_ids,
+                                     uint32_t row_start, const float* __restrict__ weights, float soft_reg, int32_t width) {
+  const uint32_t i = blockIdx.x, b = blockIdx.y * blockDim.x + threadIdx.x, lane = threadIdx.x & 31;
+  const uint64_t fo = in_foff[i];
+  if (fo == ~0ull) return;   // fixed leaf
+  const bool active = b < B;
+  const int64_t row = active ? data_row(row_ids, row_start, b) : 0;
+  const uint32_t C = in_cats[i], var = in_var[i];
+  const float* tab = theta + in_poff[i];
+  float f = active ? flows[(size_t)in_node[i] * ld + b] : 0.0f;
+  if (active && weights) f *= weights[row];
+  if (soft) {
+    const float logp = active ? mars[(size_t)in_node[i] * ld + b] : 0.0f;
+    const float* sp = soft + (size_t)row + (size_t)num_rows * var;
+    const size_t cs = (size_t)num_rows * num_vars;
+    for (uint32_t c = 0; c < C; ++c) {
+      float v = active ? expf(sp[c * cs] + __ldg(tab + c) - logp) * f : 0.0f;
+      v = warp_sum(v);
+      if (lane == 0 && v != 0.0f) atomicAdd(aggr + fo + c, v);
+    }
+    return;
+  }
+  if (!active) return;
+  const size_t di = (size_t)row + (size_t)num_rows * var;
+  if (miss && miss[di]) { atomicAdd(aggr + fo + C, f); return; }
+  const int32_t x = data[di];
+  const int32_t c_start = max(0, x - width / 2), c_end = min(c_start + width - 1, (int32_t)C - 1);
+  float sp = 0.0f;
+  for (int32_t c = c_start; c <= c_end; ++c) sp += expf(__ldg(tab + c));
+  sp /= (float)(c_end - c_start + 1);
+  const float base = (1.0f - soft_reg) * __ldg(tab + x) + soft_reg * sp;
+  atomicAdd(aggr + fo + x, (1.0f - soft_reg) * __ldg(tab + x) * f / base);
+  for (int32_t c = c_start; c <= c_end; ++c)
+    atomicAdd(aggr + fo + c, soft_reg / (float)(c_end - c_start + 1) * __ldg(tab + c) * f / base);
+}
+
+// Log-likelihoods of a multi-head circuit (extract_lls_from_root_nodes,
+// src-jl/multi_head_pc/bit_circuit.jl:95-109): with a mask out[b] = logsumexp_h(mars[root_h][b] +
+// log mask[row, h]) - log sum_h mask[row, h]; without one out is [B, H] with the roots' values.
+__global__ void head_ll_kernel(const float* __restrict__ mars, uint32_t ld, uint32_t B, const uint32_t* __restrict__ roots,
+                               uint32_t H, const float* __restrict__ head_mask, uint64_t mask_rows,
+                               const int32_t* __restrict__ row_ids, uint32_t row_start, float* __restrict__ out) {
+  const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  if (!head_mask) {
+    for (uint32_t h = 0; h < H; ++h) out[(size_t)h * B + b] = mars[(size_t)roots[h] * ld + b];
+    return;
+  }
+  const int64_t row = data_row(row_ids, row_start, b);
+  float mx = -INFINITY, tot = 0.0f;
+  for (uint32_t h = 0; h < H; ++h) {
+    const float m = head_mask[(size_t)row + mask_rows * h];
+    mx = fmaxf(mx, mars[(size_t)roots[h] * ld + b] + logf(m));
+    tot += m;
+  }
+  float acc = 0.0f;
+  for (uint32_t h = 0; h < H; ++h) {
+    const float m = head_mask[(size_t)row + mask_rows * h];
+    const float v = mars[(size_t)roots[h] * ld + b] + logf(m);
+    if (v != -INFINITY) acc += expf(v - mx);
+  }
+  out[b] = (mx == -INFINITY ? -INFINITY : mx + logf(acc)) - logf(tot);
+}
+
 __global__ void scale_kernel(float* __restrict__ x, uint64_t n, float rate) {
   uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
@@ -543,24 +681,35 @@ dim3 grid2v(uint32_t items, uint32_t B) { return dim3(items, (B + 4 * TPB - 1) /
     if (_s != PCB_OK) return _s;   \
   } while (0)
 
-extern "C" int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev,
-                               const uint8_t* miss_dev, uint64_t num_rows, const int32_t* row_ids_dev,
-                               uint32_t row_start, uint32_t B, float* ll_out_dev, pcb_stream s) {
-  PCB_REQUIRE(c && ws && data_dev, "null argument");
+static int32_t forward_impl(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence& ev, float* ll_out_dev,
+                            cudaStream_t st) {
+  const uint32_t B = ev.B;
+  PCB_REQUIRE(ev.data_dev || ev.soft_dev, "null argument");
   PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
   PCB_REQUIRE(B >= 1 && B <= ws->max_batch, "batch size exceeds the workspace");
-  PCB_REQUIRE(row_ids_dev || (row_start >= 1 && (uint64_t)row_start - 1 + B <= num_rows), "row range out of bounds");
+  PCB_REQUIRE(ev.row_ids_dev || (ev.row_start >= 1 && (uint64_t)ev.row_start - 1 + B <= ev.num_rows),
+              "row range out of bounds");
+  PCB_REQUIRE(ev.soft_reg >= 0.0f && ev.soft_reg < 1.0f, "soft_reg must lie in [0, 1)");
+  PCB_REQUIRE(ev.soft_reg == 0.0f || ev.soft_dev || ev.soft_reg_width >= 1, "soft_reg_width must be at least 1");
+  PCB_REQUIRE(!ev.head_mask_dev || c->n_heads, "a head mask needs a multi-head circuit");
   PCB_CUDA(cudaSetDevice(c->device));
-  cudaStream_t st = (cudaStream_t)s;
-  ws->B = B; ws->data = data_dev; ws->miss = miss_dev; ws->num_rows = num_rows;
-  ws->row_ids = row_ids_dev; ws->row_start = row_start; ws->have_forward = false;
+  ws->B = B; ws->data = ev.data_dev; ws->miss = ev.miss_dev; ws->num_rows = ev.num_rows;
+  ws->row_ids = ev.row_ids_dev; ws->row_start = ev.row_start; ws->have_forward = false;
+  ws->soft = ev.soft_dev; ws->head_mask = ev.head_mask_dev;
+  ws->soft_reg = ev.soft_dev ? 0.0f : ev.soft_reg; ws->soft_width = ev.soft_reg_width;
   if (c->use_tc) PCB_TRY(pcb_dense_tc_refresh(c, st));
   if (c->n_inputs) {
     PcbProfScope ps(c, st, PCB_K_LEAF_FWD);
-    dim3 grid(c->n_lgrps, (B + LBT - 1) / LBT);   // groups of up to 64 leaves of one variable share the staged values
-    leaf_forward_chunk_kernel<<<grid, LTH, 0, st>>>(ws->mars, ws->ld, B, c->theta, c->in_node, c->in_poff,
-                                                    c->lgrp_var, c->lgrp_off, c->lchunk_inputs, data_dev,
-                                                    miss_dev, num_rows, row_ids_dev, row_start);
+    if (ws->soft || ws->soft_reg > 0.0f) {
+      leaf_forward_gen_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(
+          ws->mars, ws->ld, B, c->theta, c->in_node, c->in_var, c->in_cats, c->in_poff, c->V, ev.data_dev, ev.miss_dev,
+          ws->soft, ev.num_rows, ev.row_ids_dev, ev.row_start, ws->soft_reg, (int32_t)ws->soft_width);
+    } else {
+      dim3 grid(c->n_lgrps, (B + LBT - 1) / LBT);   // groups of up to 64 leaves of one variable share the staged values
+      leaf_forward_chunk_kernel<<<grid, LTH, 0, st>>>(ws->mars, ws->ld, B, c->theta, c->in_node, c->in_poff,
+                                                      c->lgrp_var, c->lgrp_off, c->lchunk_inputs, ev.data_dev,
+                                                      ev.miss_dev, ev.num_rows, ev.row_ids_dev, ev.row_start);
+    }
   }
   const bool fwd_split = c->fwd_split;
   for (uint32_t lay = 1; lay <= c->L; ++lay) {
@@ -585,12 +734,42 @@ extern "C" int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
       PCB_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));
     }
   }
-  if (ll_out_dev)
-    PCB_CUDA(cudaMemcpyAsync(ll_out_dev, ws->mars + (size_t)(c->N - 1) * ws->ld, B * sizeof(float),
-                             cudaMemcpyDeviceToDevice, st));
+  if (ll_out_dev) {
+    if (c->n_heads) {
+      PcbProfScope ps(c, st, PCB_K_MISC);
+      head_ll_kernel<<<(B + 255) / 256, 256, 0, st>>>(ws->mars, ws->ld, B, c->head_roots, c->n_heads, ws->head_mask,
+                                                      ev.num_rows, ev.row_ids_dev, ev.row_start, ll_out_dev);
+    } else {
+      PCB_CUDA(cudaMemcpyAsync(ll_out_dev, ws->mars + (size_t)(c->N - 1) * ws->ld, B * sizeof(float),
+                               cudaMemcpyDeviceToDevice, st));
+    }
+  }
   PCB_CUDA(cudaGetLastError());
   ws->have_forward = true;
   return PCB_OK;
+}
+
+static pcb_evidence hard_evidence(const uint8_t* data_dev, const uint8_t* miss_dev, uint64_t num_rows,
+                                  const int32_t* row_ids_dev, uint32_t row_start, uint32_t B) {
+  pcb_evidence ev;
+  memset(&ev, 0, sizeof(ev));
+  ev.data_dev = data_dev; ev.miss_dev = miss_dev; ev.num_rows = num_rows; ev.row_ids_dev = row_ids_dev;
+  ev.row_start = row_start; ev.B = B; ev.soft_reg_width = 1;
+  return ev;
+}
+
+extern "C" int32_t pcb_forward(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev,
+                               const uint8_t* miss_dev, uint64_t num_rows, const int32_t* row_ids_dev,
+                               uint32_t row_start, uint32_t B, float* ll_out_dev, pcb_stream s) {
+  PCB_REQUIRE(c && ws && data_dev, "null argument");
+  return forward_impl(c, ws, hard_evidence(data_dev, miss_dev, num_rows, row_ids_dev, row_start, B), ll_out_dev,
+                      (cudaStream_t)s);
+}
+
+extern "C" int32_t pcb_forward_ex(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence* ev, float* ll_out_dev,
+                                  pcb_stream s) {
+  PCB_REQUIRE(c && ws && ev, "null argument");
+  return forward_impl(c, ws, *ev, ll_out_dev, (cudaStream_t)s);
 }
 
 extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* weights_dev, pcb_stream s) {
@@ -600,13 +779,15 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
   PCB_CUDA(cudaSetDevice(c->device));
   cudaStream_t st = (cudaStream_t)s;
   const uint32_t B = ws->B;
+  PCB_REQUIRE(!c->n_heads || ws->head_mask, "the flows of a multi-head circuit need a head mask");
+  const HeadInit hi{c->n_head, ws->head_mask, ws->num_rows, ws->row_ids, ws->row_start};
   c->edge_lo = c->edge_hi = 0;
   auto sparse_down = [&](int64_t lay, cudaStream_t ss, bool pdl) -> int32_t {
     uint32_t o0 = c->h_down_sparse_off[lay], o1 = c->h_down_sparse_off[lay + 1];
     if (o1 > o0) {
       PcbProfScope ps(c, ss, PCB_K_SPARSE_DOWN);
       PCB_CUDA(pcb_launch_pdl(sparse_down_kernel, grid2v(o1 - o0, B), dim3(TPB), 0, ss, pdl, ws->flows, ws->mars, ws->ld,
-                              B, c->down_sparse + o0, c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr));
+                              B, c->down_sparse + o0, c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr, hi));
     }
     return PCB_OK;
   };
@@ -636,7 +817,12 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
     // sorted segments pay off once a variable has enough values to keep a block's threads busy;
     // PCB_LEAF_FLOW_IMPL=atomic / sorted (read when the circuit is created) forces one of the two kernels
     const bool want_sorted = c->leaf_flow_impl ? c->leaf_flow_impl == 2 : c->max_cats >= 16;
-    if (c->max_cats <= LSC && want_sorted) {
+    if (ws->soft || ws->soft_reg > 0.0f) {
+      leaf_flow_gen_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(
+          ws->flows, ws->mars, ws->ld, B, c->aggr, c->theta, c->in_node, c->in_var, c->in_cats, c->in_poff, c->in_foff,
+          c->V, ws->data, ws->miss, ws->soft, ws->num_rows, ws->row_ids, ws->row_start, weights_dev, ws->soft_reg,
+          (int32_t)ws->soft_width);
+    } else if (c->max_cats <= LSC && want_sorted) {
       dim3 grid(c->n_lgrps, (B + LSB - 1) / LSB);
       leaf_flow_sorted_kernel<<<grid, LST, weights_dev ? LSB * sizeof(float) : 0, st>>>(
           ws->flows, ws->ld, B, c->aggr, c->in_node, c->in_cats, c->in_foff, c->lgrp_var, c->lgrp_off,
@@ -692,35 +878,42 @@ extern "C" int32_t pcb_em_update(pcb_circuit* c, float pseudocount, float inerti
 
 // clear, forward, backward, (all-reduce,) update: the launches of one EM step on stream st.  The
 // batch log-likelihood stays in the last slot of the statistics vector; pcb_em_step copies it out.
-static int32_t em_step_body(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev, const uint8_t* miss_dev,
-                            uint64_t num_rows, const int32_t* row_ids_dev, uint32_t row_start, uint32_t B,
-                            const float* weights_dev, float clear_rate, float pseudocount, float inertia,
-                            cudaStream_t st) {
+static int32_t em_step_body(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence& ev, const float* weights_dev,
+                            float clear_rate, float pseudocount, float inertia, cudaStream_t st) {
   pcb_stream s = (pcb_stream)st;
+  const uint32_t B = ev.B;
   // With a communicator every rank enters the step holding the same summed statistics of the last
   // step (pseudocount included, as the reference keeps it in edge_aggr); the all-reduce below adds
   // the ranks' vectors, so each rank carries rate / nranks of them and the sum is rate * previous
   // + this step's flows, as reg_em.jl:276-284 computes it on one device.
   const float carried = (c->comm && c->nranks > 1) ? clear_rate / (float)c->nranks : clear_rate;
   PCB_TRY(pcb_clear_flows(c, carried, s));
-  PCB_TRY(pcb_forward(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, nullptr, s));
+  // multi-head circuits: the per-example log-likelihoods mix the heads (em.jl:71 of multi_head_pc)
+  PCB_TRY(forward_impl(c, ws, ev, c->n_heads ? ws->ll_tmp : nullptr, st));
   PCB_TRY(pcb_backward(c, ws, weights_dev, s));
   // batch log-likelihood into the last slot of the statistics vector, so it is reduced with them
-  { PcbProfScope ps(c, st, PCB_K_MISC); ll_sum_kernel<<<1, 256, 0, st>>>(ws->mars + (size_t)(c->N - 1) * ws->ld, B, c->aggr + c->aggr_len - 1); }
+  { PcbProfScope ps(c, st, PCB_K_MISC);
+    ll_sum_kernel<<<1, 256, 0, st>>>(c->n_heads ? ws->ll_tmp : ws->mars + (size_t)(c->N - 1) * ws->ld, B,
+                                     c->aggr + c->aggr_len - 1); }
   if (c->comm) { PcbProfScope ps(c, st, PCB_K_ALLREDUCE); PCB_TRY(pcb_allreduce_aggr(c, st)); }
   PCB_TRY(pcb_em_update(c, pseudocount, inertia, s));
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
 }
 
-extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev,
-                               const uint8_t* miss_dev, uint64_t num_rows, const int32_t* row_ids_dev,
-                               uint32_t row_start, uint32_t B, const float* weights_dev, float clear_rate,
-                               float pseudocount, float inertia, float* ll_sum_dev, pcb_stream s) {
-  PCB_REQUIRE(c && ws, "null argument");
+static int32_t em_step_impl(pcb_circuit* c, pcb_workspace* ws, pcb_evidence ev, const float* weights_dev,
+                            float clear_rate, float pseudocount, float inertia, float* ll_sum_dev, pcb_stream s) {
   PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
+  const uint32_t B = ev.B;
   PCB_REQUIRE(B >= 1 && B <= ws->max_batch, "batch size exceeds the workspace");
+  PCB_REQUIRE(!c->n_heads || ev.head_mask_dev, "the flows of a multi-head circuit need a head mask");
   PCB_CUDA(cudaSetDevice(c->device));
+  if (c->n_heads && !ws->ll_tmp) PCB_CUDA(cudaMalloc(&ws->ll_tmp, (size_t)ws->max_batch * sizeof(float)));
+  const uint8_t* data_dev = ev.data_dev;
+  const uint8_t* miss_dev = ev.miss_dev;
+  const uint64_t num_rows = ev.num_rows;
+  const int32_t* row_ids_dev = ev.row_ids_dev;
+  uint32_t row_start = ev.row_start;
   cudaStream_t st = (cudaStream_t)s;
   // the step reads the row ids from the workspace's own buffer, so a replayed graph sees the ids
   // of the current call
@@ -733,6 +926,7 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
     row_start = 1;
   }
   row_ids_dev = ws->ids_stage;
+  ev.row_ids_dev = row_ids_dev; ev.row_start = row_start;
   // The log-likelihood leaves through a copy issued after the step (the update does not touch its
   // slot), outside any captured graph: a training loop hands in a different slot for every batch.
   auto ll_out = [&](cudaStream_t on) -> int32_t {
@@ -741,8 +935,7 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
     return PCB_OK;
   };
   auto plain = [&]() -> int32_t {
-    PCB_TRY(em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
-                         pseudocount, inertia, st));
+    PCB_TRY(em_step_body(c, ws, ev, weights_dev, clear_rate, pseudocount, inertia, st));
     return ll_out(st);
   };
   if (!c->graph_enabled || c->prof.on) return plain();
@@ -753,6 +946,7 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   key.stream = (void*)st; key.num_rows = num_rows; key.row_start = row_start; key.B = B;
   key.clear_rate = clear_rate; key.pseudocount = pseudocount; key.inertia = inertia;
   key.has_ids = row_ids_dev != nullptr; key.w_valid = c->w_img_valid;
+  key.soft = ev.soft_dev; key.head_mask = ev.head_mask_dev; key.soft_reg = ev.soft_reg; key.soft_width = ev.soft_reg_width;
 
   // the legacy default stream cannot be captured: graphs run on a stream of the circuit's own,
   // ordered after and before the caller's stream with two events
@@ -784,6 +978,8 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
     for (int k = 0; k < PCB_K_COUNT; ++k) c->prof.launches[k] += ws->step_launches[k];
     ws->B = B; ws->data = data_dev; ws->miss = miss_dev; ws->num_rows = num_rows;
     ws->row_ids = row_ids_dev; ws->row_start = row_start; ws->have_forward = true;
+    ws->soft = ev.soft_dev; ws->head_mask = ev.head_mask_dev;
+    ws->soft_reg = ev.soft_dev ? 0.0f : ev.soft_reg; ws->soft_width = ev.soft_reg_width;
     c->w_img_valid = false;
     return PCB_OK;
   }
@@ -797,8 +993,7 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   for (int k = 0; k < PCB_K_COUNT; ++k) before[k] = c->prof.launches[k];
   PCB_TRY(enter());
   PCB_CUDA(cudaStreamBeginCapture(gs, cudaStreamCaptureModeRelaxed));
-  int32_t body = em_step_body(c, ws, data_dev, miss_dev, num_rows, row_ids_dev, row_start, B, weights_dev, clear_rate,
-                              pseudocount, inertia, gs);
+  int32_t body = em_step_body(c, ws, ev, weights_dev, clear_rate, pseudocount, inertia, gs);
   cudaGraph_t graph = nullptr;
   cudaError_t ce = cudaStreamEndCapture(gs, &graph);
   if (body != PCB_OK || ce != cudaSuccess || !graph) {
@@ -826,6 +1021,23 @@ extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t*
   PCB_TRY(ll_out(gs));
   PCB_TRY(leave());
   return PCB_OK;
+}
+
+extern "C" int32_t pcb_em_step(pcb_circuit* c, pcb_workspace* ws, const uint8_t* data_dev,
+                               const uint8_t* miss_dev, uint64_t num_rows, const int32_t* row_ids_dev,
+                               uint32_t row_start, uint32_t B, const float* weights_dev, float clear_rate,
+                               float pseudocount, float inertia, float* ll_sum_dev, pcb_stream s) {
+  PCB_REQUIRE(c && ws && data_dev, "null argument");
+  return em_step_impl(c, ws, hard_evidence(data_dev, miss_dev, num_rows, row_ids_dev, row_start, B), weights_dev,
+                      clear_rate, pseudocount, inertia, ll_sum_dev, s);
+}
+
+extern "C" int32_t pcb_em_step_ex(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence* ev, const float* weights_dev,
+                                  float clear_rate, float pseudocount, float inertia, float* ll_sum_dev,
+                                  pcb_stream s) {
+  PCB_REQUIRE(c && ws && ev, "null argument");
+  PCB_REQUIRE(ev->data_dev || ev->soft_dev, "null argument");
+  return em_step_impl(c, ws, *ev, weights_dev, clear_rate, pseudocount, inertia, ll_sum_dev, s);
 }
 
 static int32_t get_matrix(pcb_circuit* c, pcb_workspace* ws, const float* src, float* host, uint64_t n) {

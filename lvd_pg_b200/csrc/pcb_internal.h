@@ -22,6 +22,7 @@
 
 #include <atomic>
 #include <string>
+#include <mutex>
 #include <vector>
 
 #include "../../include/pcb200.h"
@@ -100,6 +101,14 @@ struct pcb_circuit {
   uint64_t* in_poff = nullptr;    // [n_inputs] offset of the log-probs in theta
   uint64_t* in_foff = nullptr;    // [n_inputs] offset of the flow slots in aggr, ~0 for fixed
   uint32_t* node2input = nullptr; // [N] input index or PCB_NONE
+  // multi-head circuits: heads = children of the fake root's skipped edges, in edge order
+  uint32_t* n_head = nullptr;     // [N] head index or PCB_NONE
+  uint32_t* head_roots = nullptr; // [n_heads] node ids
+  std::vector<uint32_t> h_head_roots;
+  uint32_t n_heads = 0;
+  // live workspaces of this circuit: their captured step graphs hold references to the communicator
+  std::vector<pcb_workspace*> workspaces;
+  std::mutex ws_mu;
   // packed per-node and per-leaf records for the sampling walk (one 16-byte load per visited node):
   // node: {first edge, edge count, first parameter id (sum) or input index (leaf), kind | region << 2}
   // leaf: {parameter offset lo, hi, categories, variable}
@@ -192,6 +201,7 @@ struct pcb_workspace {
   // their address does not change from step to step).
   struct StepKey {
     const void* data; const void* miss; const void* weights; void* comm; void* stream;
+    const void* soft; const void* head_mask; float soft_reg; uint32_t soft_width;
     uint64_t num_rows;
     uint32_t row_start, B;
     float clear_rate, pseudocount, inertia;
@@ -202,6 +212,7 @@ struct pcb_workspace {
   cudaGraphExec_t step_exec = nullptr;
   uint64_t step_launches[PCB_K_COUNT] = {0};   // launches of one replay, per kernel class
   int32_t* ids_stage = nullptr;                 // [max_batch]
+  float* ll_tmp = nullptr;                      // [max_batch] per-example log-likelihoods of a multi-head step
   // tensor maps over mars / flows for the copy-fed edge-statistics kernel (128-byte opaque objects)
   alignas(64) unsigned char tm[3][128];
   bool have_tm = false;
@@ -216,6 +227,10 @@ struct pcb_workspace {
   const int32_t* row_ids = nullptr;
   uint32_t row_start = 1;
   bool have_forward = false;
+  const float* soft = nullptr;        // soft evidence [num_rows, V, C] or null
+  const float* head_mask = nullptr;   // [num_rows, n_heads] or null
+  float soft_reg = 0.0f;
+  uint32_t soft_width = 1;
   // per-parameter-set buffers, allocated on first use
   uint32_t S_cap = 0, ldS = 0;
   float* klds = nullptr;     // [N][ldS]
@@ -226,6 +241,20 @@ struct pcb_workspace {
   uint32_t stack_cap = 0;
   uint32_t kld_S = 0;
   bool have_kld = false;
+  // the fused KLD + gradient + Adam step (pcb_kld_adam_step): gradient buffers, the device word that
+  // holds the step count, and the captured chain
+  float* kld_g1 = nullptr;
+  float* kld_g2 = nullptr;
+  int* kld_t_dev = nullptr;
+  int32_t kld_t_host = -1;
+  struct KldKey {
+    const void* q; const void* p; const void* m; const void* v; const void* out; void* stream;
+    float lr, b1, b2, eps;
+  };
+  KldKey kld_last_key{}, kld_exec_key{};
+  bool have_kld_key = false;
+  cudaGraphExec_t kld_exec = nullptr;
+  uint64_t kld_launches[PCB_K_COUNT] = {0};
 };
 
 // ---- helpers ----

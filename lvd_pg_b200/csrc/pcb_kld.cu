@@ -12,6 +12,7 @@
 // [N][ldS].  Threads are laid out (set, node): blockDim.x covers sets, blockDim.y nodes, so a
 // single parameter set still fills the block.
 #include <algorithm>
+#include <cstring>
 
 #include "pcb_internal.h"
 
@@ -90,6 +91,7 @@ __global__ void kld_up_warp_kernel(float* __restrict__ klds, uint32_t ld, uint32
                                    const uint8_t* __restrict__ kind, const uint32_t* __restrict__ n_estart,
                                    const uint32_t* __restrict__ n_ecount, const uint32_t* __restrict__ n_pid0,
                                    const uint32_t* __restrict__ e_prime, const uint32_t* __restrict__ e_sub) {
+  pcb_grid_dep_launch();
   const uint32_t w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= count * S) return;
   const uint32_t i = w / S, s = w % S;
@@ -97,6 +99,7 @@ __global__ void kld_up_warp_kernel(float* __restrict__ klds, uint32_t ld, uint32
   const uint32_t e0 = n_estart[n], cnt = n_ecount[n];
   const bool issum = kind[n] == PCB_SUM;
   const uint32_t pid0 = n_pid0[n];
+  pcb_grid_dep_wait();   // everything above is static circuit data
   float acc = 0.0f;
   for (uint32_t j = lane; j < cnt; j += 32) {
     float k = klds[(size_t)e_prime[e0 + j] * ld + s];
@@ -179,11 +182,13 @@ __global__ void kld_down_warp_kernel(float* __restrict__ grads, const float* __r
                                      const uint32_t* __restrict__ nodes, uint32_t count, uint32_t root,
                                      const uint32_t* __restrict__ in_off, const PcbInEntry* __restrict__ in_ent,
                                      float* __restrict__ g1, float* __restrict__ g2) {
+  pcb_grid_dep_launch();
   const uint32_t w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= count * S) return;
   const uint32_t i = w / S, s = w % S;
   const uint32_t n = nodes[i];
   const uint32_t i0 = in_off[n], i1 = in_off[n + 1];
+  pcb_grid_dep_wait();   // everything above is static circuit data
   const float myk = klds[(size_t)n * ld + s];
   float acc = 0.0f;
   for (uint32_t x = i0 + lane; x < i1; x += 32) {
@@ -232,9 +237,18 @@ __global__ void copy_root_kernel(const float* __restrict__ klds_root, uint32_t S
   if (s < S) out[s] = klds_root[s];
 }
 
+__global__ void bump_step_kernel(int* __restrict__ t) { *t += 1; }
+
+// t_dev != null: the step count comes from a device word (a replayed CUDA graph cannot take it as an
+// argument) and the bias corrections 1 - beta^t are computed here
 __global__ void adam_kernel(float* __restrict__ theta, const float* __restrict__ g, float* __restrict__ m,
                             float* __restrict__ v, uint64_t n, float lr, float b1, float b2, float eps, float c1,
-                            float c2, float sign) {
+                            float c2, float sign, const int* __restrict__ t_dev) {
+  if (t_dev) {
+    const float t = (float)*t_dev;
+    c1 = 1.0f - powf(b1, t);
+    c2 = 1.0f - powf(b2, t);
+  }
   uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
   for (; i < n; i += stride) {
@@ -301,9 +315,9 @@ extern "C" int32_t pcb_kld(pcb_circuit* c, pcb_workspace* ws, const float* param
     Shape2 sh = shape_for(S, o1 - o0);
     ++c->prof.launches[PCB_K_KLD];
     if (S <= 8) {
-      kld_up_warp_kernel<<<(uint32_t)(((uint64_t)(o1 - o0) * S + 7) / 8), 256, 0, st>>>(
-          ws->klds, ld, S, params1_dev, params2_dev, c->up_all + o0, o1 - o0, c->kind, c->n_estart, c->n_ecount,
-          c->n_pid0, c->e_prime, c->e_sub);
+      PCB_CUDA(pcb_launch_pdl(kld_up_warp_kernel, dim3((uint32_t)(((uint64_t)(o1 - o0) * S + 7) / 8)), dim3(256), 0, st, c->pdl,
+                              ws->klds, ld, S, params1_dev, params2_dev, c->up_all + o0, o1 - o0, c->kind, c->n_estart,
+                              c->n_ecount, c->n_pid0, c->e_prime, c->e_sub));
       continue;
     }
     kld_up_kernel<<<sh.grid, sh.block, 0, st>>>(ws->klds, ld, S, params1_dev, params2_dev, c->up_all + o0, o1 - o0,
@@ -333,9 +347,9 @@ extern "C" int32_t pcb_kld_backward(pcb_circuit* c, pcb_workspace* ws, const flo
     Shape2 sh = shape_for(S, o1 - o0);
     ++c->prof.launches[PCB_K_KLD];
     if (S <= 8) {
-      kld_down_warp_kernel<<<(uint32_t)(((uint64_t)(o1 - o0) * S + 7) / 8), 256, 0, st>>>(
-          ws->grads, ws->klds, ld, S, params1_dev, params2_dev, c->down_all + o0, o1 - o0, c->N - 1, c->in_off,
-          c->in_ent, grads1_dev, grads2_dev);
+      PCB_CUDA(pcb_launch_pdl(kld_down_warp_kernel, dim3((uint32_t)(((uint64_t)(o1 - o0) * S + 7) / 8)), dim3(256), 0, st, c->pdl,
+                              ws->grads, (const float*)ws->klds, ld, S, params1_dev, params2_dev, c->down_all + o0, o1 - o0,
+                              c->N - 1, c->in_off, c->in_ent, grads1_dev, grads2_dev));
       continue;
     }
     kld_down_kernel<<<sh.grid, sh.block, 0, st>>>(ws->grads, ws->klds, ld, S, params1_dev, params2_dev,
@@ -391,7 +405,7 @@ extern "C" int32_t pcb_adam_step(pcb_circuit* c, float* theta_dev, const float* 
   if (c->P) {
     uint32_t blocks = (uint32_t)std::min<uint64_t>((c->P + 255) / 256, 148 * 16);
     ++c->prof.launches[PCB_K_KLD];
-    adam_kernel<<<blocks, 256, 0, st>>>(theta_dev, grad_dev, m_dev, v_dev, c->P, lr, beta1, beta2, eps, c1, c2, sign);
+    adam_kernel<<<blocks, 256, 0, st>>>(theta_dev, grad_dev, m_dev, v_dev, c->P, lr, beta1, beta2, eps, c1, c2, sign, nullptr);
     uint32_t warps = c->n_groups + c->n_inputs;
     ++c->prof.launches[PCB_K_KLD];
     renorm_kernel<<<(warps + 7) / 8, 256, 0, st>>>(theta_dev, c->n_groups, c->grp_node, c->n_pid0, c->n_ecount,
@@ -399,4 +413,118 @@ extern "C" int32_t pcb_adam_step(pcb_circuit* c, float* theta_dev, const float* 
   }
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
+}
+
+// ---- KLD + gradient + Adam as one unit --------------------------------------------------------------
+// One step of the variational loop on a single parameter set q against p: kld (queries/kld.jl:164-206),
+// kld_backward with respect to q (:593-649), Adam descent on q's log-parameters and the
+// re-normalisation of every sum group and leaf (sgd/adam.jl:63-127,218-242).  A single parameter set
+// has no batch dimension, so the step is a chain of ~2 L small launches: the second call with the same
+// arguments captures the chain as a CUDA graph (the step count lives in a device word that the graph
+// increments itself) and later calls replay it.
+namespace {
+__global__ void set_step_kernel(int* __restrict__ t, int value) { *t = value; }
+}
+
+static int32_t kld_adam_body(pcb_circuit* c, pcb_workspace* ws, float* theta_q, const float* theta_p, float* m_dev,
+                             float* v_dev, float lr, float beta1, float beta2, float eps, float* kld_out, cudaStream_t st) {
+  pcb_stream s = (pcb_stream)st;
+  ++c->prof.launches[PCB_K_KLD];
+  bump_step_kernel<<<1, 1, 0, st>>>(ws->kld_t_dev);
+  int32_t r = pcb_kld(c, ws, theta_q, theta_p, 1, kld_out, s);
+  if (r != PCB_OK) return r;
+  r = pcb_kld_backward(c, ws, theta_q, theta_p, 1, ws->kld_g1, ws->kld_g2, s);
+  if (r != PCB_OK) return r;
+  if (c->P) {
+    uint32_t blocks = (uint32_t)std::min<uint64_t>((c->P + 255) / 256, 148 * 16);
+    ++c->prof.launches[PCB_K_KLD];
+    adam_kernel<<<blocks, 256, 0, st>>>(theta_q, ws->kld_g1, m_dev, v_dev, c->P, lr, beta1, beta2, eps, 1.0f, 1.0f, -1.0f,
+                                        ws->kld_t_dev);
+    uint32_t warps = c->n_groups + c->n_inputs;
+    ++c->prof.launches[PCB_K_KLD];
+    renorm_kernel<<<(warps + 7) / 8, 256, 0, st>>>(theta_q, c->n_groups, c->grp_node, c->n_pid0, c->n_ecount, c->n_inputs,
+                                                   c->P, c->in_cats, c->in_poff);
+  }
+  PCB_CUDA(cudaGetLastError());
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_kld_adam_step(pcb_circuit* c, pcb_workspace* ws, float* theta_q_dev, const float* theta_p_dev,
+                                     float* m_dev, float* v_dev, int32_t t, float lr, float beta1, float beta2,
+                                     float eps, float* kld_out_dev, pcb_stream s) {
+  PCB_REQUIRE(c && ws && theta_q_dev && theta_p_dev && m_dev && v_dev, "null argument");
+  PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
+  PCB_REQUIRE(t >= 1, "Adam step count starts at 1");
+  PCB_CUDA(cudaSetDevice(c->device));
+  int32_t st0 = pcb_ws_ensure_sets(ws, 1, false);
+  if (st0 != PCB_OK) return st0;
+  cudaStream_t st = (cudaStream_t)s;
+  if (!ws->kld_g1) {
+    PCB_CUDA(cudaMalloc((void**)&ws->kld_g1, std::max<uint64_t>(c->P, 1) * sizeof(float)));
+    PCB_CUDA(cudaMalloc((void**)&ws->kld_g2, std::max<uint64_t>(c->P, 1) * sizeof(float)));
+    PCB_CUDA(cudaMalloc((void**)&ws->kld_t_dev, sizeof(int)));
+    ws->kld_t_host = -1;
+  }
+  // the graph increments the device word itself; it is set from the host only when the caller's
+  // count does not continue the last call's
+  cudaStream_t gs = st;
+  const bool legacy = st == nullptr || st == cudaStreamLegacy;
+  if (legacy) {
+    if (!c->gstream) {
+      PCB_CUDA(cudaStreamCreateWithFlags(&c->gstream, cudaStreamNonBlocking));
+      PCB_CUDA(cudaEventCreateWithFlags(&c->ev_g0, cudaEventDisableTiming));
+      PCB_CUDA(cudaEventCreateWithFlags(&c->ev_g1, cudaEventDisableTiming));
+    }
+    gs = c->gstream;
+    PCB_CUDA(cudaEventRecord(c->ev_g0, st));
+    PCB_CUDA(cudaStreamWaitEvent(gs, c->ev_g0, 0));
+  }
+  auto leave = [&]() -> int32_t {
+    if (legacy) { PCB_CUDA(cudaEventRecord(c->ev_g1, gs)); PCB_CUDA(cudaStreamWaitEvent(st, c->ev_g1, 0)); }
+    return PCB_OK;
+  };
+  if (ws->kld_t_host != t - 1) set_step_kernel<<<1, 1, 0, gs>>>(ws->kld_t_dev, t - 1);
+  ws->kld_t_host = t;
+
+  pcb_workspace::KldKey key;
+  memset(&key, 0, sizeof(key));
+  key.q = theta_q_dev; key.p = theta_p_dev; key.m = m_dev; key.v = v_dev; key.out = kld_out_dev; key.stream = (void*)st;
+  key.lr = lr; key.b1 = beta1; key.b2 = beta2; key.eps = eps;
+  auto plain = [&]() -> int32_t {
+    int32_t r = kld_adam_body(c, ws, theta_q_dev, theta_p_dev, m_dev, v_dev, lr, beta1, beta2, eps, kld_out_dev, gs);
+    if (r != PCB_OK) return r;
+    return leave();
+  };
+  if (!c->graph_enabled || c->prof.on) return plain();
+  if (ws->kld_exec && !memcmp(&key, &ws->kld_exec_key, sizeof(key))) {
+    PCB_CUDA(cudaGraphLaunch(ws->kld_exec, gs));
+    for (int k = 0; k < PCB_K_COUNT; ++k) c->prof.launches[k] += ws->kld_launches[k];
+    ws->have_kld = true; ws->kld_S = 1;
+    return leave();
+  }
+  const bool capture = ws->have_kld_key && !memcmp(&key, &ws->kld_last_key, sizeof(key));
+  ws->kld_last_key = key;
+  ws->have_kld_key = true;
+  if (!capture) return plain();
+  if (ws->kld_exec) { cudaGraphExecDestroy(ws->kld_exec); ws->kld_exec = nullptr; }
+  uint64_t before[PCB_K_COUNT];
+  for (int k = 0; k < PCB_K_COUNT; ++k) before[k] = c->prof.launches[k];
+  PCB_CUDA(cudaStreamBeginCapture(gs, cudaStreamCaptureModeRelaxed));
+  int32_t body = kld_adam_body(c, ws, theta_q_dev, theta_p_dev, m_dev, v_dev, lr, beta1, beta2, eps, kld_out_dev, gs);
+  cudaGraph_t graph = nullptr;
+  cudaError_t ce = cudaStreamEndCapture(gs, &graph);
+  if (body == PCB_OK && ce == cudaSuccess && graph) ce = cudaGraphInstantiate(&ws->kld_exec, graph, 0);
+  if (graph) cudaGraphDestroy(graph);
+  if (body != PCB_OK || ce != cudaSuccess || !ws->kld_exec) {
+    ws->kld_exec = nullptr;
+    cudaGetLastError();
+    c->graph_enabled = false;   // this chain does not capture: stay with plain launches
+    for (int k = 0; k < PCB_K_COUNT; ++k) c->prof.launches[k] = before[k];
+    if (body != PCB_OK) return body;
+    return plain();
+  }
+  for (int k = 0; k < PCB_K_COUNT; ++k) ws->kld_launches[k] = c->prof.launches[k] - before[k];
+  ws->kld_exec_key = key;
+  PCB_CUDA(cudaGraphLaunch(ws->kld_exec, gs));
+  return leave();
 }

@@ -182,13 +182,18 @@ function mini_batch_em(c::PcbCircuit, data::CuMatrix{UInt8}, num_epochs; batch_s
                         wptr, rate, pseudocount, param_inertia, pointer(ll_batches, b), stream()))
         end
         push!(lls, sum(ll_batches) / batch_size / num_batches)
+        circuit_status(c)   # the loop synchronises here anyway (reg_em.jl:303)
         param_inertia += Δ
         verbose && println("Mini-batch EM epoch $epoch/$num_epochs; train LL $(lls[end])")
     end
     lls
 end
 
-"kld(mbpc, params1, params2) — queries/kld.jl:177-206; params are [S, P] CuMatrix"
+"""
+kld(mbpc, params1, params2) — queries/kld.jl:177-206; params are [S, P] CuMatrix.  Returns what the
+reference returns: `(klds[:, end], (klds_mat, edge_klds_mat))` with host copies of the node values
+[S, N] and the edge values [S, E]; the node values also stay in the workspace for `kld_backward`.
+"""
 function kld(c::PcbCircuit, params1::CuMatrix{Float32}, params2::CuMatrix{Float32})
     S = size(params1, 1)
     out = CUDA.zeros(Float32, S)
@@ -196,18 +201,127 @@ function kld(c::PcbCircuit, params1::CuMatrix{Float32}, params2::CuMatrix{Float3
     check(ccall((:pcb_kld, libpcb200), Int32,
                 (Ptr{Cvoid}, Ptr{Cvoid}, CuPtr{Cfloat}, CuPtr{Cfloat}, UInt32, CuPtr{Cfloat}, Ptr{Cvoid}),
                 c.handle, ws, params1, params2, S, out, stream()))
-    Array(out), ws
+    N = length(c.bpc.nodes); E = length(c.bpc.edge_layers_up.vectors)
+    klds_mat = Matrix{Float32}(undef, S, N)
+    check(ccall((:pcb_get_klds, libpcb200), Int32, (Ptr{Cvoid}, Ptr{Cvoid}, UInt32, Ptr{Cfloat}), c.handle, ws, S, klds_mat))
+    edge_klds = CUDA.zeros(Float32, S, E)
+    check(ccall((:pcb_kld_edge_klds, libpcb200), Int32,
+                (Ptr{Cvoid}, Ptr{Cvoid}, CuPtr{Cfloat}, CuPtr{Cfloat}, UInt32, CuPtr{Cfloat}, Ptr{Cvoid}),
+                c.handle, ws, params1, params2, S, edge_klds, stream()))
+    Array(out), (klds_mat, Array(edge_klds))
 end
 
-"kld_backward(mbpc, params1, params2; reuse) — queries/kld.jl:593-649"
-function kld_backward(c::PcbCircuit, params1::CuMatrix{Float32}, params2::CuMatrix{Float32}; reuse)
+"kld_backward(mbpc, params1, params2; reuse) — queries/kld.jl:593-649 (of the last `kld` call on this circuit)"
+function kld_backward(c::PcbCircuit, params1::CuMatrix{Float32}, params2::CuMatrix{Float32}; reuse = nothing)
     S, P = size(params1)
     g1 = CUDA.zeros(Float32, S, P); g2 = CUDA.zeros(Float32, S, P)
     check(ccall((:pcb_kld_backward, libpcb200), Int32,
                 (Ptr{Cvoid}, Ptr{Cvoid}, CuPtr{Cfloat}, CuPtr{Cfloat}, UInt32, CuPtr{Cfloat}, CuPtr{Cfloat}, Ptr{Cvoid}),
-                c.handle, reuse, params1, params2, S, g1, g2, stream()))
+                c.handle, workspace(c, 1), params1, params2, S, g1, g2, stream()))
     Array(g1), Array(g2)
 end
+
+# ---- the preallocated forms PCVAE calls (utils/cuda_preallocation.jl:6-78,150-203) ------------------
+const prealloc = Dict{Symbol,Any}()
+
+function kld_preallocation(c::PcbCircuit; num_examples)
+    P = num_parameters(c)
+    prealloc[:kld] = (p1 = CUDA.zeros(Float32, num_examples, P), p2 = CUDA.zeros(Float32, num_examples, P),
+                      g1 = CUDA.zeros(Float32, num_examples, P), g2 = CUDA.zeros(Float32, num_examples, P),
+                      out = CUDA.zeros(Float32, num_examples))
+    nothing
+end
+kld_free_mem() = (delete!(prealloc, :kld); nothing)
+
+function kld_with_prealloc(c::PcbCircuit, params1, params2; norm_params = false)
+    b = prealloc[:kld]
+    copyto!(b.p1, params1); copyto!(b.p2, params2)
+    S = size(b.p1, 1)
+    check(ccall((:pcb_kld, libpcb200), Int32,
+                (Ptr{Cvoid}, Ptr{Cvoid}, CuPtr{Cfloat}, CuPtr{Cfloat}, UInt32, CuPtr{Cfloat}, Ptr{Cvoid}),
+                c.handle, workspace(c, 1), b.p1, b.p2, S, b.out, stream()))
+    Array(b.out)
+end
+
+function kld_backward_with_prealloc(c::PcbCircuit; norm_params = false, grad_wrt_logparams = true)
+    b = prealloc[:kld]
+    S = size(b.p1, 1)
+    fill!(b.g1, 0f0); fill!(b.g2, 0f0)
+    check(ccall((:pcb_kld_backward, libpcb200), Int32,
+                (Ptr{Cvoid}, Ptr{Cvoid}, CuPtr{Cfloat}, CuPtr{Cfloat}, UInt32, CuPtr{Cfloat}, CuPtr{Cfloat}, Ptr{Cvoid}),
+                c.handle, workspace(c, 1), b.p1, b.p2, S, b.g1, b.g2, stream()))
+    Array(b.g1), Array(b.g2)
+end
+
+"""
+adam_step!(mbpc, theta, grad, m, v, t; lr, beta1, beta2, eps, sign) — apply_gradients + hard_update_params of
+sgd/adam.jl:63-127 on a flat log-parameter vector (sign = -1 descends, as the KLD loop does).
+"""
+function adam_step!(c::PcbCircuit, theta::CuVector{Float32}, grad::CuVector{Float32}, m::CuVector{Float32},
+                    v::CuVector{Float32}, t::Integer; lr = 1f-2, beta1 = 0.9f0, beta2 = 0.999f0, eps = 1f-8, sign = -1f0)
+    check(ccall((:pcb_adam_step, libpcb200), Int32,
+                (Ptr{Cvoid}, CuPtr{Cfloat}, CuPtr{Cfloat}, CuPtr{Cfloat}, CuPtr{Cfloat}, Int32, Cfloat, Cfloat, Cfloat, Cfloat, Cfloat, Ptr{Cvoid}),
+                c.handle, theta, grad, m, v, t, lr, beta1, beta2, eps, sign, stream()))
+    theta
+end
+
+"One step KLD(q || p) + gradient + Adam on q + re-normalisation as a single (graph-replayed) library call."
+function kld_adam_step!(c::PcbCircuit, theta_q::CuVector{Float32}, theta_p::CuVector{Float32}, m::CuVector{Float32},
+                        v::CuVector{Float32}, t::Integer, kld_out::CuVector{Float32}; lr = 1f-2, beta1 = 0.9f0,
+                        beta2 = 0.999f0, eps = 1f-8)
+    check(ccall((:pcb_kld_adam_step, libpcb200), Int32,
+                (Ptr{Cvoid}, Ptr{Cvoid}, CuPtr{Cfloat}, CuPtr{Cfloat}, CuPtr{Cfloat}, CuPtr{Cfloat}, Int32, Cfloat, Cfloat, Cfloat, Cfloat, CuPtr{Cfloat}, Ptr{Cvoid}),
+                c.handle, workspace(c, 1), theta_q, theta_p, m, v, t, lr, beta1, beta2, eps, kld_out, stream()))
+    kld_out
+end
+
+"""
+gumbel_sample(mbpc, params, num_vars, par_buffer_size; temperature, no_gumbel, u) — queries/sample.jl:349-383.
+The reference draws its noise in the kernel; here `u` ([S, num_inner_params] uniforms) is passed in, or
+`no_gumbel = true` selects the noise-free variant PCVAE uses.  Returns input_aggr_params [S, V, C] on the host.
+"""
+function gumbel_sample(c::PcbCircuit, params::CuMatrix{Float32}, num_vars, par_buffer_size; temperature,
+                       no_gumbel = false, u = nothing)
+    S = size(params, 1)
+    out = CUDA.zeros(Float32, S, num_vars, par_buffer_size)
+    uptr = no_gumbel ? CU_NULL : pointer(u)
+    check(ccall((:pcb_sample_soft, libpcb200), Int32,
+                (Ptr{Cvoid}, Ptr{Cvoid}, CuPtr{Cfloat}, UInt32, CuPtr{Cfloat}, Cfloat, UInt32, CuPtr{Cfloat}, Ptr{Cvoid}),
+                c.handle, workspace(c, 1), params, S, uptr, temperature, S, out, stream()))
+    Array(out)
+end
+gumbel_sample_with_prealloc(c::PcbCircuit, params; temperature, no_gumbel = false, norm_params = false, u = nothing) =
+    gumbel_sample(c, cu(params), Int(maximum(n.variable for n in c.bpc.nodes if n isa BitsInput)),
+                  Int(maximum(dist(n).num_cats for n in c.bpc.nodes if n isa BitsInput)); temperature, no_gumbel, u)
+
+"""
+mini_batch_em_with_reg(bpc, data, num_epochs; ...) — the name and keywords the experiment scripts use
+(regularization/reg_em.jl:208-213).  soft_reg must be 0; ent_reg is ignored as in the reference
+(its entropy step is commented out, reg_em.jl:294-296); the *_mem / mine / maxe / debug keywords are ignored.
+"""
+function mini_batch_em_with_reg(c::PcbCircuit, data::CuMatrix{UInt8}, num_epochs; batch_size, pseudocount,
+                                soft_reg = 0f0, soft_reg_width = 1, ent_reg = 0f0, param_inertia,
+                                param_inertia_end = param_inertia, flow_memory = 0f0, shuffle = :each_epoch,
+                                weights = nothing, verbose = true, kwargs...)
+    iszero(soft_reg) || throw(PcbError(1, "soft_reg > 0 (soft-regularised leaves) is not built"))
+    mini_batch_em(c, data, num_epochs; batch_size, pseudocount, param_inertia, param_inertia_end, flow_memory,
+                  shuffle, weights, verbose)
+end
+"loglikelihoods_probcat(bpc, data; batch_size) — regularization/reg_likelihood.jl:139-162, hard evidence"
+loglikelihoods_probcat(c::PcbCircuit, data::CuMatrix{UInt8}; batch_size = 512, kwargs...) = loglikelihoods(c, data; batch_size)
+
+"Waits for the device and throws if a kernel of this circuit gave up a bounded wait (call where the loop synchronises)."
+circuit_status(c::PcbCircuit) = check(ccall((:pcb_circuit_status, libpcb200), Int32, (Ptr{Cvoid},), c.handle))
+
+# ---- multi-GPU: one NCCL communicator per process (no counterpart in the reference) ------------------
+function comm_unique_id()
+    id = zeros(UInt8, 128)
+    check(ccall((:pcb_comm_unique_id, libpcb200), Int32, (Ptr{UInt8},), id))
+    id
+end
+comm_init(c::PcbCircuit, id::Vector{UInt8}, rank::Integer, nranks::Integer) =
+    check(ccall((:pcb_comm_init, libpcb200), Int32, (Ptr{Cvoid}, Ptr{UInt8}, Int32, Int32), c.handle, id, rank, nranks))
+comm_destroy(c::PcbCircuit) = check(ccall((:pcb_comm_destroy, libpcb200), Int32, (Ptr{Cvoid},), c.handle))
 
 """
 sample(mbpc, params, U_sum, U_leaf) — hard Gumbel-max sampling with caller-supplied uniforms.

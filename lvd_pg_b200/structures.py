@@ -45,6 +45,15 @@ def simple_3vars_circuit(num_cats: int = 5, fixed: bool = True, rng=None, pertur
     return pc
 
 
+def simple_multihead_circuit(num_cats: int = 5, heads: int = 2, rng=None, perturbation: float = 0.4):
+    """simple_circuits.jl:54-66: `heads` mixtures over the same two fully factorised products."""
+    def leaf(v):
+        return Input(v, _perturbed(rng, num_cats, perturbation), False)
+    n1 = multiply(leaf(1), leaf(2), leaf(3))
+    n2 = multiply(leaf(1), leaf(2), leaf(3))
+    return [Sum([n1, n2], _perturbed(rng, 2, perturbation)) for _ in range(heads)]
+
+
 def fully_factorized_categorical_fixed(num_vars: int = 3, num_cats: int = 8, eps: float = 1e-6):
     """simple_circuits.jl:40-52: per variable a sum over near-one-hot fixed leaves."""
     sums = []

@@ -163,6 +163,101 @@ def input_flows(fc, flows, data, row_ids=None, row_start=1, miss=None, weights=N
                           C.c_uint64(data.shape[0]), _p(rid), C.c_uint32(row_start), C.c_uint32(B), _p(w))
 
 
+def _soft(soft):
+    """[rows, V, C] per-category log-weights in the reference's column-major layout."""
+    return None if soft is None else np.asfortranarray(soft, dtype=np.float32)
+
+
+def forward_ex(fc, data=None, soft=None, row_ids=None, row_start=1, B=None, miss=None, soft_reg=0.0, soft_reg_width=1):
+    """eval_circuit with soft evidence (init_mar!_with_reg_cat_kernel, reg_likelihood.jl:51-91) or with
+    soft-regularised leaves (soft_loglikelihood, reg_likelihood.jl:4-14)."""
+    d = fc.desc()
+    soft = _soft(soft)
+    if data is None:
+        rows = soft.shape[0]
+        rid = None if row_ids is None else np.ascontiguousarray(row_ids, np.int32)
+        B = int(B if B is not None else (len(rid) if rid is not None else rows - (row_start - 1)))
+    else:
+        data, miss, rid, B = _data_args(data, miss, row_ids, row_start, B)
+        rows = data.shape[0]
+    mars = _f((B, fc.num_nodes))
+    lib().orc_forward_ex(C.byref(d), _p(fc.up_logp), _p(fc.heap), _p(data), _p(miss), _p(soft), C.c_uint64(rows),
+                         _p(rid), C.c_uint32(row_start), C.c_uint32(B), C.c_float(soft_reg), C.c_int32(soft_reg_width),
+                         _p(mars), None)
+    return mars
+
+
+def backward_ex(fc, mars, head_roots, head_mask, row_ids=None, row_start=1, edge_aggr=None):
+    """multi_head_flows_circuit (src-jl/multi_head_pc/flow.jl:178-195): head_roots 1-based node ids,
+    head_mask [rows, H]."""
+    d = fc.desc()
+    B = mars.shape[0]
+    flows = _f((B, fc.num_nodes))
+    if edge_aggr is None:
+        edge_aggr = np.zeros(fc.num_edges, np.float32)
+    roots = np.ascontiguousarray(head_roots, np.uint32)
+    mask = np.asfortranarray(head_mask, dtype=np.float32)
+    rid = None if row_ids is None else np.ascontiguousarray(row_ids, np.int32)
+    lib().orc_backward_ex(C.byref(d), _p(fc.up_logp), _p(np.asfortranarray(mars)), C.c_uint32(B), _p(flows), None,
+                          _p(edge_aggr), _p(roots), C.c_uint32(len(roots)), _p(mask), C.c_uint64(mask.shape[0]),
+                          _p(rid), C.c_uint32(row_start))
+    return flows, edge_aggr
+
+
+def multihead_lls(fc, mars, head_roots, head_mask=None, row_ids=None, row_start=1):
+    """extract_lls_from_root_nodes (src-jl/multi_head_pc/bit_circuit.jl:95-109)."""
+    d = fc.desc()
+    B = mars.shape[0]
+    roots = np.ascontiguousarray(head_roots, np.uint32)
+    mask = None if head_mask is None else np.asfortranarray(head_mask, dtype=np.float32)
+    rid = None if row_ids is None else np.ascontiguousarray(row_ids, np.int32)
+    lls = _f((B,)) if mask is not None else _f((B, len(roots)))
+    lib().orc_multihead_lls(C.byref(d), _p(np.asfortranarray(mars)), C.c_uint32(B), _p(roots), C.c_uint32(len(roots)),
+                            _p(mask), C.c_uint64(0 if mask is None else mask.shape[0]), _p(rid), C.c_uint32(row_start),
+                            _p(lls))
+    return lls
+
+
+def input_flows_ex(fc, flows, data=None, soft=None, row_ids=None, row_start=1, miss=None, weights=None, soft_reg=0.0,
+                   soft_reg_width=1):
+    """input_flows_circuit_with_reg(_cat) (reg_flow.jl:24-82) into fc.heap."""
+    d = fc.desc()
+    soft = _soft(soft)
+    B = flows.shape[0]
+    if data is None:
+        rows = soft.shape[0]
+        rid = None if row_ids is None else np.ascontiguousarray(row_ids, np.int32)
+    else:
+        data, miss, rid, B = _data_args(data, miss, row_ids, row_start, B)
+        rows = data.shape[0]
+    w = None if weights is None else np.ascontiguousarray(weights, np.float32)
+    lib().orc_input_flows_ex(C.byref(d), _p(fc.heap), _p(np.asfortranarray(flows)), _p(data), _p(miss), _p(soft),
+                             C.c_uint64(rows), _p(rid), C.c_uint32(row_start), C.c_uint32(B), _p(w),
+                             C.c_float(soft_reg), C.c_int32(soft_reg_width))
+
+
+def em_step_ex(fc, data=None, soft=None, head_roots=None, head_mask=None, row_ids=None, row_start=1, B=None,
+               pseudocount=0.1, inertia=0.0, miss=None, weights=None, edge_aggr=None, clear_rate=0.0, soft_reg=0.0,
+               soft_reg_width=1):
+    """Per-batch body of mini_batch_em_with_reg (reg_em.jl:273-301) on soft evidence / soft-regularised
+    leaves, or of mini_batch_em_for_multihead_pc (src-jl/multi_head_pc/em.jl:58-83) when head_roots is
+    given.  Mutates fc.up_logp and fc.heap; returns (sum of batch LLs, edge_aggr before the update)."""
+    if edge_aggr is None:
+        edge_aggr = np.zeros(fc.num_edges, np.float32)
+    clear_flows(fc, edge_aggr, clear_rate)
+    mars = forward_ex(fc, data, soft, row_ids, row_start, B, miss, soft_reg, soft_reg_width)
+    if head_roots is not None:
+        flows, edge_aggr = backward_ex(fc, mars, head_roots, head_mask, row_ids, row_start, edge_aggr)
+        ll = float(multihead_lls(fc, mars, head_roots, head_mask, row_ids, row_start).astype(np.float64).sum())
+    else:
+        flows, edge_aggr = backward(fc, mars, edge_aggr)
+        ll = float(mars[:, -1].astype(np.float64).sum())
+    input_flows_ex(fc, flows, data, soft, row_ids, row_start, miss, weights, soft_reg, soft_reg_width)
+    aggr_before = edge_aggr.copy()
+    em_update(fc, edge_aggr, pseudocount, inertia)
+    return ll, aggr_before
+
+
 def clear_flows(fc, edge_aggr, rate=0.0):
     d = fc.desc()
     lib().orc_clear_flows(C.byref(d), _p(edge_aggr), _p(fc.heap), C.c_float(rate))

@@ -171,10 +171,50 @@ static uint32_t g_row_block = ORC_RB;
 /* rows per block, 1 .. ORC_RB: a short batch timed on many threads takes smaller blocks */
 void orc_set_row_block(int n) { g_row_block = n < 1 ? 1u : (n > ORC_RB ? (uint32_t)ORC_RB : (uint32_t)n); }
 
+/* Leaf value of one example.
+ *  - hard evidence, soft_reg = 0: the plain lookup (reg_likelihood.jl:4-14 reduces to it);
+ *  - hard evidence, soft_reg > 0: soft_loglikelihood, reg_likelihood.jl:4-14 (window of `width`
+ *    categories starting at max(0, x - width / 2), clipped at the last category);
+ *  - soft evidence: per-category log-weights soft[row, var, c] ([rows, V, C] column-major), binary
+ *    logsumexp fold in category order, init_mar!_with_reg_cat_kernel reg_likelihood.jl:51-91. */
+static real leaf_value(const pcb_circuit_desc* d, const real* heap, uint32_t n, int64_t row, const uint8_t* data,
+                       const uint8_t* miss, const float* soft, uint64_t num_rows, real soft_reg, int32_t width) {
+  const uint32_t var0 = d->node_var[n] - 1, C = d->node_num_cats[n];
+  const real* tab = heap + d->node_heap_start[n] - 1;
+  if (soft) {
+    real logp = -(real)INFINITY;
+    for (uint32_t c = 0; c < C; ++c)
+      logp = lse2(logp, (real)soft[(size_t)row + (size_t)num_rows * (var0 + (size_t)d->num_vars * c)] + tab[c]);
+    return logp;
+  }
+  size_t di = (size_t)row + (size_t)num_rows * var0;
+  if (miss && miss[di]) return (real)0;
+  int32_t x = data[di];
+  if (soft_reg == (real)0) return tab[x];
+  int32_t c_start = x - width / 2 > 0 ? x - width / 2 : 0;
+  int32_t c_end = c_start + width - 1 < (int32_t)C - 1 ? c_start + width - 1 : (int32_t)C - 1;
+  real sp = (real)0;
+  for (int32_t c = c_start; c <= c_end; ++c) sp += REXP(tab[c]);
+  sp /= (real)(c_end - c_start + 1);
+  return lse2(tab[x] + RLOG((real)1 - soft_reg), RLOG(sp) + RLOG(soft_reg));
+}
+
+void orc_forward_ex(const pcb_circuit_desc* d, const real* up_logp, const real* heap,
+                    const uint8_t* data, const uint8_t* miss, const float* soft, uint64_t num_rows,
+                    const int32_t* row_ids, uint32_t row_start, uint32_t B, real soft_reg, int32_t soft_reg_width,
+                    real* mars, real* edge_mars);
+
 void orc_forward(const pcb_circuit_desc* d, const real* up_logp, const real* heap,
                  const uint8_t* data, const uint8_t* miss, uint64_t num_rows,
                  const int32_t* row_ids, uint32_t row_start, uint32_t B, real* mars,
                  real* edge_mars) {
+  orc_forward_ex(d, up_logp, heap, data, miss, NULL, num_rows, row_ids, row_start, B, (real)0, 1, mars, edge_mars);
+}
+
+void orc_forward_ex(const pcb_circuit_desc* d, const real* up_logp, const real* heap,
+                    const uint8_t* data, const uint8_t* miss, const float* soft, uint64_t num_rows,
+                    const int32_t* row_ids, uint32_t row_start, uint32_t B, real soft_reg, int32_t soft_reg_width,
+                    real* mars, real* edge_mars) {
   const uint32_t N = d->num_nodes, E = d->num_edges, RB = g_row_block;
   const int64_t nblk = ((int64_t)B + RB - 1) / RB;
 #pragma omp parallel for schedule(dynamic, 1)
@@ -189,12 +229,8 @@ void orc_forward(const pcb_circuit_desc* d, const real* up_logp, const real* hea
       if (d->node_kind[n] == PCB_SUM) { for (uint32_t j = 0; j < nb; ++j) out[j] = -(real)INFINITY; }
       else if (d->node_kind[n] == PCB_PRODUCT) { for (uint32_t j = 0; j < nb; ++j) out[j] = (real)0; }
       else {
-        const size_t col = (size_t)num_rows * (d->node_var[n] - 1);
-        const real* tab = heap + d->node_heap_start[n] - 1;
-        for (uint32_t j = 0; j < nb; ++j) {
-          size_t di = (size_t)rows[j] + col;
-          out[j] = (miss && miss[di]) ? (real)0 : tab[data[di]];
-        }
+        for (uint32_t j = 0; j < nb; ++j)
+          out[j] = leaf_value(d, heap, n, rows[j], data, miss, soft, num_rows, soft_reg, soft_reg_width);
       }
     }
     /* likelihood.jl:18-64, one thread owning every edge of the node */
@@ -229,8 +265,22 @@ void orc_forward(const pcb_circuit_desc* d, const real* up_logp, const real* hea
  * edge_aggr [E] in down-edge order, accumulated into (flow.jl:75-81), may be NULL.  The sum over
  * the examples of an edge is collected in one double per edge shared by all threads (one atomic
  * add per edge and block of rows) and rounded once at the end. */
+void orc_backward_ex(const pcb_circuit_desc* d, const real* up_logp, const real* mars, uint32_t B,
+                     real* flows, real* edge_flows, real* edge_aggr, const uint32_t* head_roots, uint32_t H,
+                     const float* head_mask, uint64_t mask_rows, const int32_t* row_ids, uint32_t row_start);
+
 void orc_backward(const pcb_circuit_desc* d, const real* up_logp, const real* mars, uint32_t B,
                   real* flows, real* edge_flows, real* edge_aggr) {
+  orc_backward_ex(d, up_logp, mars, B, flows, edge_flows, edge_aggr, NULL, 0, NULL, 0, NULL, 1);
+}
+
+/* With head_roots / head_mask the circuit has several roots under a fake root sum (the last node):
+ * the flow of root h starts at head_mask[row, h] ([rows, H] column-major), every other node at 0
+ * (src-jl/multi_head_pc/flow.jl:141-176), and the fake root's edges — tagged with the user bit by
+ * the builder, bit_circuit.jl:22-34 — are skipped (flow.jl:45). */
+void orc_backward_ex(const pcb_circuit_desc* d, const real* up_logp, const real* mars, uint32_t B,
+                     real* flows, real* edge_flows, real* edge_aggr, const uint32_t* head_roots, uint32_t H,
+                     const float* head_mask, uint64_t mask_rows, const int32_t* row_ids, uint32_t row_start) {
   const uint32_t N = d->num_nodes, E = d->num_edges;
   double* part = edge_aggr ? (double*)calloc((size_t)E, sizeof(double)) : NULL;
   const uint32_t RB = g_row_block;
@@ -241,13 +291,23 @@ void orc_backward(const pcb_circuit_desc* d, const real* up_logp, const real* ma
     const uint32_t nb = B - b0 < RB ? B - b0 : RB;
     for (uint32_t n = 0; n < N; ++n) { /* flow.jl:140-143 */
       real* f = flows + IDX(b0, n, B);
-      const real init = n == N - 1 ? (real)1 : (real)0;
+      const real init = (n == N - 1 && !head_mask) ? (real)1 : (real)0;
       for (uint32_t j = 0; j < nb; ++j) f[j] = init;
     }
+    if (head_mask)
+      for (uint32_t h = 0; h < H; ++h) {
+        real* f = flows + IDX(b0, head_roots[h] - 1, B);
+        for (uint32_t j = 0; j < nb; ++j)
+          f[j] = (real)head_mask[(size_t)data_row(row_ids, row_start, b0 + j) + (size_t)mask_rows * h];
+      }
     for (uint32_t de = 0; de < E; ++de) {
       const uint32_t e = d->down2up[de] - 1;
       const uint32_t parent = d->up_parent[e] - 1, prime = d->up_prime[e] - 1, sub = d->up_sub[e];
       const int issum = edge_is_sum(d, e);
+      if (H > 0 && d->up_tag && (d->up_tag[e] & PCB_TAG_USER)) {   /* skipped edge: contributes nothing */
+        if (edge_flows) for (uint32_t j = 0; j < nb; ++j) edge_flows[IDX(b0 + j, e, B)] = (real)0;
+        continue;
+      }
       const real* fp = flows + IDX(b0, parent, B);
       const real* mp = mars + IDX(b0, parent, B);
       const real* mc = mars + IDX(b0, prime, B);
@@ -298,6 +358,75 @@ void orc_input_flows(const pcb_circuit_desc* d, real* heap, const real* flows,
       size_t di = (size_t)row + (size_t)num_rows * (d->node_var[n] - 1);
       if (miss && miss[di]) acc[C] += (double)f;
       else acc[data[di]] += (double)f;
+    }
+    for (uint32_t c = 0; c <= C; ++c) heap[hs + C + c] = (real)((double)heap[hs + C + c] + acc[c]);
+    free(acc);
+  }
+}
+
+/* extract_lls_from_root_nodes (src-jl/multi_head_pc/bit_circuit.jl:95-109): with a head mask
+ * lls[b] = logsumexp_h(mars[b, root_h] + log mask[row, h]) - log sum_h mask[row, h]; without one
+ * lls is [B, H] with the roots' values. */
+void orc_multihead_lls(const pcb_circuit_desc* d, const real* mars, uint32_t B, const uint32_t* head_roots,
+                       uint32_t H, const float* head_mask, uint64_t mask_rows, const int32_t* row_ids,
+                       uint32_t row_start, real* lls) {
+  (void)d;
+  for (uint32_t b = 0; b < B; ++b) {
+    if (!head_mask) {
+      for (uint32_t h = 0; h < H; ++h) lls[IDX(b, h, B)] = mars[IDX(b, head_roots[h] - 1, B)];
+      continue;
+    }
+    int64_t row = data_row(row_ids, row_start, b);
+    real acc = -(real)INFINITY, tot = (real)0;
+    for (uint32_t h = 0; h < H; ++h) {
+      real m = (real)head_mask[(size_t)row + (size_t)mask_rows * h];
+      acc = lse2(acc, mars[IDX(b, head_roots[h] - 1, B)] + RLOG(m));
+      tot += m;
+    }
+    lls[b] = acc - RLOG(tot);
+  }
+}
+
+/* Leaf statistics for soft evidence (input_flows_circuit_with_reg_cat_kernel, reg_flow.jl:50-82:
+ * slot c += exp(soft[row, var, c] + logp_c - logp) * flow) and for hard evidence with soft_reg > 0
+ * (soft_flow, reg_flow.jl:3-22 — which mixes the heap's LOG-probabilities where probabilities would
+ * be expected; restated as written). */
+void orc_input_flows_ex(const pcb_circuit_desc* d, real* heap, const real* flows,
+                        const uint8_t* data, const uint8_t* miss, const float* soft, uint64_t num_rows,
+                        const int32_t* row_ids, uint32_t row_start, uint32_t B, const real* weights,
+                        real soft_reg, int32_t width) {
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int64_t i = 0; i < (int64_t)d->num_input_nodes; ++i) {
+    uint32_t n = d->input_node_ids[i] - 1;
+    if (d->node_fixed[n]) continue;
+    const uint32_t C = d->node_num_cats[n], var0 = d->node_var[n] - 1;
+    size_t hs = d->node_heap_start[n] - 1;
+    double* acc = (double*)calloc(C + 1, sizeof(double));
+    for (uint32_t b = 0; b < B; ++b) {
+      int64_t row = data_row(row_ids, row_start, b);
+      real f = flows[IDX(b, n, B)];
+      if (weights) f *= weights[row];
+      if (soft) {
+        real logp = -(real)INFINITY;
+        for (uint32_t c = 0; c < C; ++c)
+          logp = lse2(logp, (real)soft[(size_t)row + (size_t)num_rows * (var0 + (size_t)d->num_vars * c)] + heap[hs + c]);
+        for (uint32_t c = 0; c < C; ++c)
+          acc[c] += (double)(REXP((real)soft[(size_t)row + (size_t)num_rows * (var0 + (size_t)d->num_vars * c)] + heap[hs + c] - logp) * f);
+        continue;
+      }
+      size_t di = (size_t)row + (size_t)num_rows * var0;
+      if (miss && miss[di]) { acc[C] += (double)f; continue; }
+      int32_t x = data[di];
+      if (soft_reg == (real)0) { acc[x] += (double)f; continue; }
+      int32_t c_start = x - width / 2 > 0 ? x - width / 2 : 0;
+      int32_t c_end = c_start + width - 1 < (int32_t)C - 1 ? c_start + width - 1 : (int32_t)C - 1;
+      real sp = (real)0;
+      for (int32_t c = c_start; c <= c_end; ++c) sp += REXP(heap[hs + c]);
+      sp /= (real)(c_end - c_start + 1);
+      real base = ((real)1 - soft_reg) * heap[hs + x] + soft_reg * sp;
+      acc[x] += (double)(((real)1 - soft_reg) * heap[hs + x] * f / base);
+      for (int32_t c = c_start; c <= c_end; ++c)
+        acc[c] += (double)(soft_reg / (real)(c_end - c_start + 1) * heap[hs + c] * f / base);
     }
     for (uint32_t c = 0; c <= C; ++c) heap[hs + C + c] = (real)((double)heap[hs + C + c] + acc[c]);
     free(acc);
