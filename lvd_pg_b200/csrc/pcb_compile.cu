@@ -288,6 +288,28 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
   }
   c->h_up_all_off[c->L] = (uint32_t)up_all.size();
   c->h_up_sparse_off[c->L] = (uint32_t)up_sparse.size();
+  // Chunks of eight consecutive nodes of a layer list whose edges lead to the same children in the
+  // same order (the k sums of one HCLT variable do): a top-down pass that pushes to the children
+  // adds the eight contributions in shared memory first.
+  std::vector<uint8_t> up_same;
+  c->h_up_chunk_off.assign(c->L + 1, 0);
+  for (uint32_t lay = 1; lay <= c->L; ++lay) {
+    c->h_up_chunk_off[lay - 1] = (uint32_t)up_same.size();
+    const uint32_t o0 = c->h_up_all_off[lay - 1], o1 = c->h_up_all_off[lay];
+    for (uint32_t b = o0; b < o1; b += 8) {
+      const uint32_t first = up_all[b];
+      bool same = kind[first] == PCB_SUM && ecount[first] <= 256;
+      for (uint32_t i = b + 1; same && i < std::min(o1, b + 8); ++i) {
+        const uint32_t n = up_all[i];
+        same = kind[n] == PCB_SUM && ecount[n] == ecount[first] &&
+               !memcmp(&d->up_prime[estart[n]], &d->up_prime[estart[first]], ecount[n] * sizeof(uint32_t)) &&
+               !memcmp(&d->up_sub[estart[n]], &d->up_sub[estart[first]], ecount[n] * sizeof(uint32_t));
+      }
+      up_same.push_back(same ? 1 : 0);
+    }
+  }
+  c->h_up_chunk_off[c->L] = (uint32_t)up_same.size();
+  if (up_same.empty()) up_same.push_back(0);
   std::vector<std::vector<uint32_t>> by_layer(c->L + 1);
   for (uint32_t n = 0; n < N; ++n) by_layer[layer[n]].push_back(n);
   c->h_down_all_off.assign(c->L + 2, 0); c->h_down_sparse_off.assign(c->L + 2, 0);
@@ -334,6 +356,7 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
   PCB_TRY(upload(&c->n_head, node_head, &bytes));
   PCB_TRY(upload(&c->head_roots, c->h_head_roots, &bytes));
   PCB_TRY(upload(&c->up_all, up_all, &bytes));
+  PCB_TRY(upload(&c->up_same, up_same, &bytes));
   PCB_TRY(upload(&c->up_sparse, up_sparse, &bytes));
   PCB_TRY(upload(&c->down_all, down_all, &bytes));
   PCB_TRY(upload(&c->down_sparse, down_sparse, &bytes));
@@ -414,7 +437,7 @@ void free_circuit(pcb_circuit* c) {
                   c->e_sub, c->in_node, c->in_var, c->in_cats, c->in_poff, c->in_foff, c->node2input,
                   c->up_all, c->up_sparse, c->down_all, c->down_sparse, c->in_off, c->in_ent, c->dense,
                   c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status, c->w_img, c->dense_img, c->w_img16, c->dense_img16,
-                  c->lgrp_var, c->lgrp_off, c->s_node, c->s_leaf, c->n_head, c->head_roots};
+                  c->lgrp_var, c->lgrp_off, c->s_node, c->s_leaf, c->n_head, c->head_roots, c->up_same};
   for (void* p : ptrs) if (p) cudaFree(p);
   if (c->ev_g0) cudaEventDestroy(c->ev_g0);
   if (c->ev_g1) cudaEventDestroy(c->ev_g1);
@@ -513,7 +536,9 @@ int32_t pcb_ws_ensure_sets(pcb_workspace* ws, uint32_t S, bool need_stack) {
     for (void* p : {(void*)ws->klds, (void*)ws->grads, (void*)ws->eprob, (void*)ws->cum, (void*)ws->stack}) if (p) cudaFree(p);
     ws->klds = ws->grads = ws->eprob = ws->cum = nullptr; ws->stack = nullptr;
     ws->S_cap = S;
-    ws->ldS = pcb_round_up(S, 32);
+    // a handful of sets stays unpadded: the per-node values of neighbouring nodes then share 32-byte
+    // sectors, which is what the gathers of a single-set KLD chain pay for
+    ws->ldS = S <= 8 ? S : pcb_round_up(S, 32);
     PCB_CUDA(cudaMalloc((void**)&ws->klds, (size_t)c->N * ws->ldS * sizeof(float)));
     PCB_CUDA(cudaMalloc((void**)&ws->grads, (size_t)c->N * ws->ldS * sizeof(float)));
     ws->have_kld = false;

@@ -126,6 +126,8 @@ struct pcb_circuit {
   uint32_t n_lgrps = 0;
   // layer lists: all inner nodes by layer / only those outside dense blocks
   uint32_t* up_all = nullptr;     // [n_inner_nodes]
+  uint8_t* up_same = nullptr;     // per chunk of 8 entries of a layer of up_all: same children in the same order
+  std::vector<uint32_t> h_up_chunk_off;   // [L+1] first chunk of a layer (index = layer-1)
   uint32_t* up_sparse = nullptr;
   uint32_t* down_all = nullptr;   // [N] every node, by layer
   uint32_t* down_sparse = nullptr;
@@ -246,6 +248,7 @@ struct pcb_workspace {
   float* kld_g1 = nullptr;
   float* kld_g2 = nullptr;
   int* kld_t_dev = nullptr;
+  int* kld_bump = nullptr;   // set while the fused step runs: the leaf kernel counts the step here
   int32_t kld_t_host = -1;
   struct KldKey {
     const void* q; const void* p; const void* m; const void* v; const void* out; void* stream;

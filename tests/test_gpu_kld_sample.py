@@ -98,11 +98,20 @@ def test_adam_step_matches_oracle(oracle):
         assert np.abs(theta.cpu().numpy() - th_ref).max() <= TOL
 
 
-def test_fused_kld_adam_steps_match_oracle(oracle):
+FUSED_CASES = [("hclt_k16_c3", lambda: random_hclt(12, 16, 3, 9)),          # leaves by thread, chunks of equal sums
+               ("hclt_k64_binary", lambda: random_hclt(24, 64, 2, 2)),     # the shape of the variational configuration
+               ("hclt_k5_c7", lambda: random_hclt(9, 5, 7, 4)),            # leaves by warp, chunks that mix nodes
+               ("hclt_k160_c2", lambda: random_hclt(3, 160, 2, 5)),        # groups wider than the registers hold
+               ("simple3", lambda: simple3(False, 5, 0)),
+               ("fixed_leaves", lambda: compile_circuit(st.fully_factorized_categorical_fixed(3, 8)))]
+
+
+@pytest.mark.parametrize("name,make", FUSED_CASES, ids=[c[0] for c in FUSED_CASES])
+def test_fused_kld_adam_steps_match_oracle(oracle, name, make):
     """pcb_kld_adam_step: five steps (the second captures the chain as a CUDA graph, the later ones
     replay it) against kld + kld_backward + Adam of the oracle, then a re-seeded step count."""
     torch, api = _cuda()
-    fc = random_hclt(12, 16, 3, 9)
+    fc = make()
     m = api.CuMetaBitsProbCircuit(fc)
     q, p = _param_sets(oracle, fc, 1, 5)[0], _param_sets(oracle, fc, 1, 6)[0]
     theta = torch.from_numpy(q.copy()).to(m.device)
