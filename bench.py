@@ -390,6 +390,7 @@ def main():
     ap.add_argument("--reference-seconds", type=float, default=200.0,
                     help="--impl reference: CPU time for all warm-up and timed steps together")
     ap.add_argument("--no-also", action="store_true", help="skip the config 2 / config 4 side measurements of the N=1 run")
+    ap.add_argument("--no-weak", action="store_true", help="N > 1: skip the fixed-batch-per-GPU measurement")
     ap.add_argument("--no-parity", action="store_true", help="N>1: skip the comparison with a 1-GPU run of the same steps")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="strong: the config's global batch is split over the GPUs (config 5 as stated); "
@@ -582,6 +583,44 @@ def main():
         e2e = {"value": Bg * args.steps / float(tt.item()), "unit": "samples/s",
                "h2d_bytes_per_step": int(B * fc.num_vars * world), "d2h_bytes_per_step": 4 * world}
 
+    # ---- N > 1: what the collectives leave exposed, and the same ranks at a fixed batch per GPU -------
+    comm = None
+    weak = None
+    if world > 1:
+        def timed(fn, k):
+            for i in range(2):
+                fn(i)
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for i in range(k):
+                fn(args.warmup + i % max(1, args.steps))
+            b.record()
+            barrier()
+            tt = torch.tensor([a.elapsed_time(b) / k], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            return float(tt.item())
+
+        k_c = min(args.steps, 5)
+        with_comm = timed(step, k_c)
+        m.lib.pcb_comm_set_enabled(m.handle, 0)      # the same steps, every rank on its own statistics
+        without = timed(step, k_c)
+        m.lib.pcb_comm_set_enabled(m.handle, 1)
+        comm = {"exposed_comm_ms": with_comm - without, "ms_per_step_with": with_comm, "ms_per_step_without": without,
+                "allreduce_bytes": 4 * (int(m.info.num_inner_params) + fc.num_input_params + 1),
+                "steps": k_c, "how": "device time of the same steps with the collectives skipped, max over ranks"}
+        if not args.no_weak:
+            # weak scaling beside the strong headline: every rank keeps the configuration's full batch
+            ids_w = [p.to(dev) if rank == 0 else torch.roll(p, 97 * rank).to(dev) for p in perms[:args.warmup + max(1, args.steps)]]
+
+            def step_w(i):
+                api.em_step(m, data, ids_w[i], 1, Bg, PSEUDOCOUNT, INERTIA, 0.0, None, ll)
+
+            ms_w = timed(step_w, k_c)
+            weak = {"scaling": "weak", "global_batch": Bg * world, "ms_per_step": ms_w,
+                    "value": Bg * world / (ms_w * 1e-3), "unit": "samples/s", "steps": k_c}
+            del ids_w
+
     # ---- N > 1: the same steps on one GPU with the whole batch, from the same parameters ------------
     parity = None
     if p_init is not None:
@@ -643,6 +682,11 @@ def main():
             line["cpu_baseline"] = cpu_baseline
         if parity:
             line["parity_vs_1gpu"] = parity
+        if comm:
+            line["exposed_comm_ms"] = comm["exposed_comm_ms"]
+            line["comm"] = comm
+        if weak:
+            line["weak"] = weak
         if world == 1 and not args.no_also and args.config == "cfg5":
             # the other configurations' headline figures, measured in the same run (a second of GPU time each)
             del m, data, images

@@ -263,6 +263,10 @@ int32_t pcb_sample_soft(pcb_circuit* c, pcb_workspace* ws, const float* params_d
 int32_t pcb_comm_unique_id(uint8_t* id_out_128);
 int32_t pcb_comm_init(pcb_circuit* c, const uint8_t* id_128, int32_t rank, int32_t nranks);
 int32_t pcb_comm_destroy(pcb_circuit* c);
+/* enabled = 0: pcb_em_step skips its collectives although a communicator is attached (every rank then
+ * updates from its own statistics).  For measuring how much of a step the communication leaves
+ * exposed; not for training. */
+int32_t pcb_comm_set_enabled(pcb_circuit* c, int32_t enabled);
 
 /* ---- launch accounting ---------------------------------------------------------------- */
 /* The library counts its kernel launches per kernel class; with profiling enabled every launch

@@ -72,6 +72,7 @@ SIGNATURES = {
     "pcb_comm_unique_id": [_vp],
     "pcb_comm_init": [_vp, _vp, _i32, _i32],
     "pcb_comm_destroy": [_vp],
+    "pcb_comm_set_enabled": [_vp, _i32],
     "pcb_profile_num_classes": [],
     "pcb_profile_enable": [_vp, _i32],
     "pcb_profile_read": [_vp, _vp, _vp, _i32],

@@ -9,6 +9,7 @@
 // that a host process which already carries NCCL (PyTorch, CUDA.jl) shares the one copy.
 #include <dlfcn.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "pcb_internal.h"
@@ -84,6 +85,19 @@ extern "C" int32_t pcb_comm_init(pcb_circuit* c, const uint8_t* id_128, int32_t 
   c->comm = comm;
   c->rank = rank;
   c->nranks = nranks;
+  c->comm_enabled = true;
+  if (const char* e = getenv("PCB_COMM_SPLIT")) c->comm_split = atoi(e) != 0;
+  if (!c->comm_stream) {
+    PCB_CUDA(cudaStreamCreateWithFlags(&c->comm_stream, cudaStreamNonBlocking));
+    for (cudaEvent_t* ev : {&c->ev_c0, &c->ev_c1, &c->ev_c2, &c->ev_c3})
+      PCB_CUDA(cudaEventCreateWithFlags(ev, cudaEventDisableTiming));
+  }
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_comm_set_enabled(pcb_circuit* c, int32_t enabled) {
+  PCB_REQUIRE(c, "null argument");
+  c->comm_enabled = enabled != 0;
   return PCB_OK;
 }
 
@@ -109,10 +123,12 @@ extern "C" int32_t pcb_comm_destroy(pcb_circuit* c) {
   return PCB_OK;
 }
 
-int32_t pcb_allreduce_aggr(pcb_circuit* c, cudaStream_t st) {
-  if (!c->comm || c->nranks == 1) return PCB_OK;
+int32_t pcb_allreduce_range(pcb_circuit* c, uint64_t first, uint64_t count, cudaStream_t st) {
+  if (!c->comm || c->nranks == 1 || !c->comm_enabled || count == 0) return PCB_OK;
   // ncclFloat32 = 7, ncclSum = 0 (nccl.h: ncclDataType_t / ncclRedOp_t)
-  int rc = g_nccl.allreduce(c->aggr, c->aggr, (size_t)c->aggr_len, 7, 0, c->comm, st);
+  int rc = g_nccl.allreduce(c->aggr + first, c->aggr + first, (size_t)count, 7, 0, c->comm, st);
   if (rc != 0) return nccl_fail("ncclAllReduce", rc);
   return PCB_OK;
 }
+
+int32_t pcb_allreduce_aggr(pcb_circuit* c, cudaStream_t st) { return pcb_allreduce_range(c, 0, c->aggr_len, st); }

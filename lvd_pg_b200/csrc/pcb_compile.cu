@@ -444,6 +444,8 @@ void free_circuit(pcb_circuit* c) {
   if (c->gstream) cudaStreamDestroy(c->gstream);
   if (c->ev_fork2) cudaEventDestroy(c->ev_fork2);
   if (c->ev_join2) cudaEventDestroy(c->ev_join2);
+  for (cudaEvent_t ev : {c->ev_c0, c->ev_c1, c->ev_c2, c->ev_c3}) if (ev) cudaEventDestroy(ev);
+  if (c->comm_stream) cudaStreamDestroy(c->comm_stream);
   if (c->side2) cudaStreamDestroy(c->side2);
   if (c->ev_fork) cudaEventDestroy(c->ev_fork);
   if (c->ev_join) cudaEventDestroy(c->ev_join);

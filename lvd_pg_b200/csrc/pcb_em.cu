@@ -772,12 +772,41 @@ extern "C" int32_t pcb_forward_ex(pcb_circuit* c, pcb_workspace* ws, const pcb_e
   return forward_impl(c, ws, *ev, ll_out_dev, (cudaStream_t)s);
 }
 
+// Multi-GPU step: once every edge statistic of the batch is final (the sparse nodes' in stream order,
+// the dense blocks' on the side stream) their slice of the statistics vector is summed over the ranks
+// on the communication stream, while this stream goes on to the leaf statistics.
+static int32_t comm_edges_begin(pcb_circuit* c, cudaStream_t st) {
+  PCB_CUDA(cudaEventRecord(c->ev_c0, st));
+  PCB_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_c0, 0));
+  if (c->side && c->side_busy) {
+    PCB_CUDA(cudaEventRecord(c->ev_c1, c->side));
+    PCB_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_c1, 0));
+  }
+  PcbProfScope ps(c, c->comm_stream, PCB_K_ALLREDUCE);
+  return pcb_allreduce_range(c, 0, c->n_inner, c->comm_stream);
+}
+// ... and the rest (leaf slots, batch log-likelihood) after them; the caller's stream waits for both.
+static int32_t comm_rest_and_join(pcb_circuit* c, cudaStream_t st) {
+  PCB_CUDA(cudaEventRecord(c->ev_c2, st));
+  PCB_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_c2, 0));
+  { PcbProfScope ps(c, c->comm_stream, PCB_K_ALLREDUCE);
+    PCB_TRY(pcb_allreduce_range(c, c->n_inner, c->aggr_len - c->n_inner, c->comm_stream)); }
+  PCB_CUDA(cudaEventRecord(c->ev_c3, c->comm_stream));
+  PCB_CUDA(cudaStreamWaitEvent(st, c->ev_c3, 0));
+  return PCB_OK;
+}
+
+static int32_t backward_impl(pcb_circuit* c, pcb_workspace* ws, const float* weights_dev, cudaStream_t st, bool split_comm);
+
 extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* weights_dev, pcb_stream s) {
   PCB_REQUIRE(c && ws, "null argument");
+  return backward_impl(c, ws, weights_dev, (cudaStream_t)s, false);
+}
+
+static int32_t backward_impl(pcb_circuit* c, pcb_workspace* ws, const float* weights_dev, cudaStream_t st, bool split_comm) {
   PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
   if (!ws->have_forward) return pcb_fail(PCB_ERR_STATE, "pcb_backward needs a preceding pcb_forward on this workspace");
   PCB_CUDA(cudaSetDevice(c->device));
-  cudaStream_t st = (cudaStream_t)s;
   const uint32_t B = ws->B;
   PCB_REQUIRE(!c->n_heads || ws->head_mask, "the flows of a multi-head circuit need a head mask");
   const HeadInit hi{c->n_head, ws->head_mask, ws->num_rows, ws->row_ids, ws->row_start};
@@ -812,6 +841,7 @@ extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* 
     }
   }
   if (c->use_tc) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
+  if (split_comm) PCB_TRY(comm_edges_begin(c, st));
   if (c->n_inputs) {
     PcbProfScope ps(c, st, PCB_K_LEAF_FLOW);
     // sorted segments pay off once a variable has enough values to keep a block's threads busy;
@@ -890,12 +920,15 @@ static int32_t em_step_body(pcb_circuit* c, pcb_workspace* ws, const pcb_evidenc
   PCB_TRY(pcb_clear_flows(c, carried, s));
   // multi-head circuits: the per-example log-likelihoods mix the heads (em.jl:71 of multi_head_pc)
   PCB_TRY(forward_impl(c, ws, ev, c->n_heads ? ws->ll_tmp : nullptr, st));
-  PCB_TRY(pcb_backward(c, ws, weights_dev, s));
+  const bool multi = c->comm && c->nranks > 1 && c->comm_enabled;
+  const bool split = multi && c->comm_split && !c->prof.on;   // per-class timing wants every class alone on the GPU
+  PCB_TRY(backward_impl(c, ws, weights_dev, st, split));
   // batch log-likelihood into the last slot of the statistics vector, so it is reduced with them
   { PcbProfScope ps(c, st, PCB_K_MISC);
     ll_sum_kernel<<<1, 256, 0, st>>>(c->n_heads ? ws->ll_tmp : ws->mars + (size_t)(c->N - 1) * ws->ld, B,
                                      c->aggr + c->aggr_len - 1); }
-  if (c->comm) { PcbProfScope ps(c, st, PCB_K_ALLREDUCE); PCB_TRY(pcb_allreduce_aggr(c, st)); }
+  if (split) PCB_TRY(comm_rest_and_join(c, st));
+  else if (multi) { PcbProfScope ps(c, st, PCB_K_ALLREDUCE); PCB_TRY(pcb_allreduce_aggr(c, st)); }
   PCB_TRY(pcb_em_update(c, pseudocount, inertia, s));
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
@@ -945,7 +978,7 @@ static int32_t em_step_impl(pcb_circuit* c, pcb_workspace* ws, pcb_evidence ev, 
   key.data = data_dev; key.miss = miss_dev; key.weights = weights_dev; key.comm = c->comm;
   key.stream = (void*)st; key.num_rows = num_rows; key.row_start = row_start; key.B = B;
   key.clear_rate = clear_rate; key.pseudocount = pseudocount; key.inertia = inertia;
-  key.has_ids = row_ids_dev != nullptr; key.w_valid = c->w_img_valid;
+  key.has_ids = row_ids_dev != nullptr; key.w_valid = c->w_img_valid; key.comm_on = c->comm_enabled;
   key.soft = ev.soft_dev; key.head_mask = ev.head_mask_dev; key.soft_reg = ev.soft_reg; key.soft_width = ev.soft_reg_width;
 
   // the legacy default stream cannot be captured: graphs run on a stream of the circuit's own,

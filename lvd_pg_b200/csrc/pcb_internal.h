@@ -190,6 +190,10 @@ struct pcb_circuit {
   // ---- multi-GPU ----
   void* comm = nullptr;  // ncclComm_t
   int nranks = 1, rank = 0;
+  bool comm_enabled = true;             // false: the step skips its collectives (timing of the exposed share only)
+  bool comm_split = false;              // edge statistics summed on comm_stream while the leaf statistics are still formed
+  cudaStream_t comm_stream = nullptr;   // created with the communicator
+  cudaEvent_t ev_c0 = nullptr, ev_c1 = nullptr, ev_c2 = nullptr, ev_c3 = nullptr;
 };
 
 struct pcb_workspace {
@@ -203,7 +207,7 @@ struct pcb_workspace {
   // their address does not change from step to step).
   struct StepKey {
     const void* data; const void* miss; const void* weights; void* comm; void* stream;
-    const void* soft; const void* head_mask; float soft_reg; uint32_t soft_width;
+    const void* soft; const void* head_mask; float soft_reg; uint32_t soft_width; uint32_t comm_on;
     uint64_t num_rows;
     uint32_t row_start, B;
     float clear_rate, pseudocount, inertia;
@@ -333,6 +337,7 @@ __device__ __forceinline__ void pcb_grid_dep_launch() { asm volatile("griddepcon
 
 // entry points implemented across translation units and used by pcb_em_step
 int32_t pcb_allreduce_aggr(pcb_circuit* c, cudaStream_t st);
+int32_t pcb_allreduce_range(pcb_circuit* c, uint64_t first, uint64_t count, cudaStream_t st);
 int32_t pcb_dense_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
 int32_t pcb_dense_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
 int32_t pcb_ws_ensure_sets(pcb_workspace* ws, uint32_t S, bool need_stack);

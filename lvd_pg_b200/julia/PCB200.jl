@@ -294,21 +294,156 @@ gumbel_sample_with_prealloc(c::PcbCircuit, params; temperature, no_gumbel = fals
     gumbel_sample(c, cu(params), Int(maximum(n.variable for n in c.bpc.nodes if n isa BitsInput)),
                   Int(maximum(dist(n).num_cats for n in c.bpc.nodes if n isa BitsInput)); temperature, no_gumbel, u)
 
+# mirror of pcb_evidence (include/pcb200.h)
+struct Evidence
+    data::CuPtr{UInt8}
+    miss::CuPtr{UInt8}
+    soft::CuPtr{Cfloat}
+    head_mask::CuPtr{Cfloat}
+    num_rows::UInt64
+    row_ids::CuPtr{Int32}
+    row_start::UInt32
+    B::UInt32
+    soft_reg::Cfloat
+    soft_reg_width::UInt32
+end
+
+evidence(data::CuMatrix{UInt8}; head_mask = nothing, row_ids = CU_NULL, row_start = 1, B, soft_reg = 0f0, soft_reg_width = 1) =
+    Evidence(pointer(data), CU_NULL, CU_NULL, head_mask === nothing ? CU_NULL : pointer(head_mask), size(data, 1),
+             row_ids, row_start, B, soft_reg, soft_reg_width)
+# a 3-D Float32 array of per-category log-weights [rows, vars, cats] (reg_likelihood.jl:51-91)
+evidence(data::CuArray{Float32,3}; head_mask = nothing, row_ids = CU_NULL, row_start = 1, B, kwargs...) =
+    Evidence(CU_NULL, CU_NULL, pointer(data), head_mask === nothing ? CU_NULL : pointer(head_mask), size(data, 1),
+             row_ids, row_start, B, 0f0, 1)
+
+function forward_ex(c::PcbCircuit, ws, ev::Evidence, ll_out)
+    check(ccall((:pcb_forward_ex, libpcb200), Int32, (Ptr{Cvoid}, Ptr{Cvoid}, Ref{Evidence}, CuPtr{Cfloat}, Ptr{Cvoid}),
+                c.handle, ws, Ref(ev), ll_out, stream()))
+end
+function em_step_ex(c::PcbCircuit, ws, ev::Evidence, weights, rate, pseudocount, inertia, ll_sum)
+    check(ccall((:pcb_em_step_ex, libpcb200), Int32,
+                (Ptr{Cvoid}, Ptr{Cvoid}, Ref{Evidence}, CuPtr{Cfloat}, Cfloat, Cfloat, Cfloat, CuPtr{Cfloat}, Ptr{Cvoid}),
+                c.handle, ws, Ref(ev), weights, rate, pseudocount, inertia, ll_sum, stream()))
+end
+
+# the loop of mini_batch_em_with_reg / mini_batch_em_for_multihead_pc over any form of evidence
+function em_loop(c::PcbCircuit, data, head_mask, num_epochs; batch_size, pseudocount, soft_reg, soft_reg_width,
+                 param_inertia, param_inertia_end, flow_memory, shuffle, weights, verbose)
+    n = size(data, 1)
+    num_batches = n ÷ batch_size
+    ws = workspace(c, batch_size)
+    ids_cpu = Vector{Int32}(1:n); ids = CuVector{Int32}(ids_cpu)
+    do_shuffle() = (ids_cpu .= Int32.(randperm(n)); copyto!(ids, ids_cpu))
+    shuffle == :once && do_shuffle()
+    Δ = (param_inertia_end - param_inertia) / num_epochs
+    rate = iszero(flow_memory) ? 0f0 : max(0f0, 1f0 - (batch_size + pseudocount) / flow_memory)
+    lls = Float32[]
+    ll_batches = CUDA.zeros(Float32, num_batches)
+    wptr = weights === nothing ? CU_NULL : pointer(weights)
+    for epoch in 1:num_epochs
+        shuffle == :each_epoch && do_shuffle()
+        for b in 1:num_batches
+            shuffle == :each_batch && do_shuffle()
+            ev = evidence(data; head_mask, row_ids = pointer(ids, 1 + (b - 1) * batch_size), B = batch_size,
+                          soft_reg = Float32(soft_reg), soft_reg_width)
+            em_step_ex(c, ws, ev, wptr, rate, pseudocount, param_inertia, pointer(ll_batches, b))
+        end
+        push!(lls, sum(ll_batches) / batch_size / num_batches)
+        circuit_status(c)
+        param_inertia += Δ
+        verbose && println("Mini-batch EM epoch $epoch/$num_epochs; train LL $(lls[end])")
+    end
+    lls
+end
+
 """
 mini_batch_em_with_reg(bpc, data, num_epochs; ...) — the name and keywords the experiment scripts use
-(regularization/reg_em.jl:208-213).  soft_reg must be 0; ent_reg is ignored as in the reference
-(its entropy step is commented out, reg_em.jl:294-296); the *_mem / mine / maxe / debug keywords are ignored.
+(regularization/reg_em.jl:208-213).  `data` is a UInt8 matrix of categories or a 3-D Float32 array of
+per-category log-weights; soft_reg / soft_reg_width regularise the leaves of hard evidence
+(reg_likelihood.jl:4-14, reg_flow.jl:3-22).  ent_reg is ignored as in the reference (its entropy step is
+commented out, reg_em.jl:294-296); the *_mem / mine / maxe / debug keywords are ignored.
 """
-function mini_batch_em_with_reg(c::PcbCircuit, data::CuMatrix{UInt8}, num_epochs; batch_size, pseudocount,
-                                soft_reg = 0f0, soft_reg_width = 1, ent_reg = 0f0, param_inertia,
-                                param_inertia_end = param_inertia, flow_memory = 0f0, shuffle = :each_epoch,
-                                weights = nothing, verbose = true, kwargs...)
-    iszero(soft_reg) || throw(PcbError(1, "soft_reg > 0 (soft-regularised leaves) is not built"))
-    mini_batch_em(c, data, num_epochs; batch_size, pseudocount, param_inertia, param_inertia_end, flow_memory,
-                  shuffle, weights, verbose)
+function mini_batch_em_with_reg(c::PcbCircuit, data::Union{CuMatrix{UInt8},CuArray{Float32,3}}, num_epochs;
+                                batch_size, pseudocount, soft_reg = 0f0, soft_reg_width = 1, ent_reg = 0f0,
+                                param_inertia, param_inertia_end = param_inertia, flow_memory = 0f0,
+                                shuffle = :each_epoch, weights = nothing, verbose = true, kwargs...)
+    if data isa CuMatrix{UInt8} && iszero(soft_reg)
+        return mini_batch_em(c, data, num_epochs; batch_size, pseudocount, param_inertia, param_inertia_end,
+                             flow_memory, shuffle, weights, verbose)
+    end
+    em_loop(c, data, nothing, num_epochs; batch_size, pseudocount, soft_reg, soft_reg_width, param_inertia,
+            param_inertia_end, flow_memory, shuffle, weights, verbose)
 end
-"loglikelihoods_probcat(bpc, data; batch_size) — regularization/reg_likelihood.jl:139-162, hard evidence"
+
+"loglikelihoods_probcat(bpc, data; batch_size) — regularization/reg_likelihood.jl:139-162, hard or soft evidence"
 loglikelihoods_probcat(c::PcbCircuit, data::CuMatrix{UInt8}; batch_size = 512, kwargs...) = loglikelihoods(c, data; batch_size)
+function loglikelihoods_probcat(c::PcbCircuit, data::CuArray{Float32,3}; batch_size = 512, kwargs...)
+    n = size(data, 1)
+    out = CUDA.zeros(Float32, n)
+    ws = workspace(c, batch_size)
+    for start in 1:batch_size:n
+        b = min(batch_size, n - start + 1)
+        forward_ex(c, ws, evidence(data; row_start = start, B = b), pointer(out, start))
+    end
+    out
+end
+
+# ---- multi-head circuits (src-jl/multi_head_pc) ---------------------------------------------------------
+"""
+CuMultiHeadBitsProbCircuit(pcs) — bit_circuit.jl:4-56: the heads under a fake root whose edges carry
+tag bit 4 (value 16 of the tag byte), which the library's top-down passes skip.
+"""
+struct PcbMultiHeadCircuit
+    bpc::PcbCircuit
+    root_ids::Vector{UInt32}
+end
+function PcbMultiHeadCircuit(pcs::Vector{<:ProbCircuit}; kw...)
+    bpc = BitsProbCircuit(summate(pcs...))
+    fake = length(bpc.nodes)
+    up = bpc.edge_layers_up.vectors
+    for (i, e) in enumerate(up)   # the library reads the tags of the up edges
+        if e isa SumEdge && e.parent_id == fake
+            up[i] = SumEdge(e.parent_id, e.prime_id, e.sub_id, e.logp, e.tag | 0x10)
+        end
+    end
+    c = PcbCircuit(bpc; kw...)
+    roots = zeros(UInt32, length(pcs))
+    check(ccall((:pcb_get_head_roots, libpcb200), Int32, (Ptr{Cvoid}, Ptr{UInt32}, UInt64), c.handle, roots, length(roots)))
+    PcbMultiHeadCircuit(c, roots)
+end
+
+"loglikelihoods(mhbpc, data, head_mask; batch_size) — likelihood.jl:35-66: [rows] with a mask, [rows, heads] without"
+function loglikelihoods(m::PcbMultiHeadCircuit, data::CuMatrix{UInt8}, head_mask; batch_size = 512)
+    n = size(data, 1); H = length(m.root_ids)
+    ws = workspace(m.bpc, batch_size)
+    if head_mask === nothing
+        out = CUDA.zeros(Float32, n, H)
+        tmp = CUDA.zeros(Float32, batch_size, H)
+        for start in 1:batch_size:n
+            b = min(batch_size, n - start + 1)
+            forward_ex(m.bpc, ws, evidence(data; row_start = start, B = b), pointer(tmp))
+            out[start:start+b-1, :] .= reshape(view(tmp, 1:b*H), b, H)
+        end
+        return out
+    end
+    out = CUDA.zeros(Float32, n)
+    for start in 1:batch_size:n
+        b = min(batch_size, n - start + 1)
+        forward_ex(m.bpc, ws, evidence(data; head_mask, row_start = start, B = b), pointer(out, start))
+    end
+    out
+end
+multihead_loglikelihoods_probcat(m::PcbMultiHeadCircuit, data, head_mask; batch_size, kwargs...) =
+    loglikelihoods(m, data, head_mask; batch_size)
+
+"mini_batch_em_for_multihead_pc(mhbpc, data, head_mask, num_epochs; ...) — em.jl:1-100"
+function mini_batch_em_for_multihead_pc(m::PcbMultiHeadCircuit, data::CuMatrix{UInt8}, head_mask::CuMatrix{Float32},
+                                        num_epochs; batch_size, pseudocount, soft_reg = 0f0, soft_reg_width = 1,
+                                        param_inertia, param_inertia_end = param_inertia, flow_memory = 0f0,
+                                        shuffle = :each_epoch, weights = nothing, verbose = true, kwargs...)
+    em_loop(m.bpc, data, head_mask, num_epochs; batch_size, pseudocount, soft_reg, soft_reg_width, param_inertia,
+            param_inertia_end, flow_memory, shuffle, weights, verbose)
+end
 
 "Waits for the device and throws if a kernel of this circuit gave up a bounded wait (call where the loop synchronises)."
 circuit_status(c::PcbCircuit) = check(ccall((:pcb_circuit_status, libpcb200), Int32, (Ptr{Cvoid},), c.handle))
@@ -322,6 +457,9 @@ end
 comm_init(c::PcbCircuit, id::Vector{UInt8}, rank::Integer, nranks::Integer) =
     check(ccall((:pcb_comm_init, libpcb200), Int32, (Ptr{Cvoid}, Ptr{UInt8}, Int32, Int32), c.handle, id, rank, nranks))
 comm_destroy(c::PcbCircuit) = check(ccall((:pcb_comm_destroy, libpcb200), Int32, (Ptr{Cvoid},), c.handle))
+"enabled = false skips the step's collectives (to time what they leave exposed; not for training)"
+comm_set_enabled(c::PcbCircuit, enabled::Bool) =
+    check(ccall((:pcb_comm_set_enabled, libpcb200), Int32, (Ptr{Cvoid}, Int32), c.handle, enabled ? 1 : 0))
 
 """
 sample(mbpc, params, U_sum, U_leaf) — hard Gumbel-max sampling with caller-supplied uniforms.
