@@ -122,8 +122,9 @@ def algorithmic_work(fc, info, B):
 
 # DRAM bytes per dense block (256 parents x 256 children) at 2048 examples, dram__bytes_read.sum +
 # dram__bytes_write.sum of one ncu capture of the largest launches of the 384-variable cut of the
-# workload (profiles/dense_tc_kernels_cfg5s.md); traffic grows in proportion to blocks x examples.
-NCU_DRAM_BYTES_PER_BLOCK = {"dense_bwd_edge": 2444.6e6 / 287, "dense_bwd_child": 690.4e6 / 55, "dense_fwd": 345.6e6 / 55}
+# workload (profiles/dense_mn_kernels_cfg5s.md, profiles/dense_edge_tma_kernel_cfg5s.md); traffic grows in
+# proportion to blocks x examples.
+NCU_DRAM_BYTES_PER_BLOCK = {"dense_bwd_edge": 2445.3e6 / 287, "dense_bwd_child": 673.7e6 / 55, "dense_fwd": 407.1e6 / 55}
 
 
 def measured_traffic(kernel_class, info, B, launches_per_step):

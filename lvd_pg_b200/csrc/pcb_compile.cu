@@ -406,6 +406,7 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
     c->bwd_split = !flag("PCB_NO_BWD_SPLIT");
     if (const char* e = getenv("PCB_LEAF_FLOW_IMPL")) c->leaf_flow_impl = !strcmp(e, "sorted") ? 2 : !strcmp(e, "atomic") ? 1 : 0;
     if (const char* e = getenv("PCB_TC_NSPLIT")) { int v = atoi(e); c->tc_nsplit = (v == 1 || v == 2 || v == 4) ? v : 0; }
+    if (const char* e = getenv("PCB_TC_A_STAGES")) { int v = atoi(e); c->tc_a_stages = (v == 2 || v == 4 || v == 8) ? v : 0; }
     if (const char* e = getenv("PCB_EDGE_IMPL")) c->edge_ld = !strcmp(e, "ld");
     if (c->use_tc) PCB_TRY(pcb_dense_tc_prepare(c, &bytes));
   }

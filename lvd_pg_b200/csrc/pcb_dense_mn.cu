@@ -51,12 +51,14 @@ constexpr uint32_t NTHREADS = NPROD + 64;
 constexpr uint32_t ROW_BYTES = TM * 4;          // one row of a tile: 128 examples
 constexpr uint32_t A_BYTES = KC * ROW_BYTES;    // one A part (hi or lo): 16 swizzle atoms of 512 bytes
 constexpr uint32_t A_STAGE = 2 * A_BYTES;       // hi | lo
-constexpr uint32_t A_STAGES = 2;
+constexpr uint32_t A_STAGES = 2;                // A stages of a launch that fills the GPU (two CTAs per SM)
+constexpr uint32_t A_MAX_STAGES = 8;            // ... of a launch of at most one CTA per SM (the small layers of the chain)
 constexpr uint32_t W_RING = 64 * 1024;          // weight chunks [hi | lo] of n_tile rows x 64 bytes: 2 chunks of a 256-column
 constexpr uint32_t W_MAX_STAGES = 16;           // tile, 8 of a 64-column tile
 constexpr uint32_t BUF_BYTES = A_STAGES * A_STAGE + W_RING;   // 96 KB: also the staging area of the row copies
 constexpr uint32_t CTL_BYTES = 4096;            // barriers, per-example maxima, partial maxima
 constexpr uint32_t SMEM_BYTES = BUF_BYTES + 1024 /*alignment*/ + CTL_BYTES;
+constexpr uint32_t SMEM_BYTES_MAX = A_MAX_STAGES * A_STAGE + W_RING + 1024 + CTL_BYTES;
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t MAXP_CHUNKS = 3;             // FWD maximum pass: chunks of rows per copy round, two rounds in flight
 constexpr uint32_t EPI_COLS = 32;               // BWD epilogue: child rows of 32 columns per round, three rounds in flight
@@ -71,6 +73,7 @@ struct MnArgs {
   int* status;
   uint32_t ld;
   uint32_t nsplit;   // CTAs sharing one 256-column tile (1, 2 or 4), each taking 256 / nsplit columns
+  uint32_t a_stages; // stages of the A ring (a power of two up to A_MAX_STAGES); the launch sizes shared memory to it
   unsigned long long* trace;   // -DPCB_DIAG builds: %globaltimer stamps of CTA (0,0,0), else null
 };
 
@@ -192,13 +195,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* aring = smem;
-  uint8_t* wring = smem + A_STAGES * A_STAGE;
-  uint8_t* ctl = smem + BUF_BYTES;
+  const uint32_t a_stages = a.a_stages, a_mask = a_stages - 1u, a_shift = 31u - __clz(a_stages);
+  uint8_t* wring = smem + a_stages * A_STAGE;
+  uint8_t* ctl = wring + W_RING;
   uint64_t* wfull = reinterpret_cast<uint64_t*>(ctl);         // [W_MAX_STAGES]
   uint64_t* wempty = wfull + W_MAX_STAGES;                    // [W_MAX_STAGES]
-  uint64_t* afull = wempty + W_MAX_STAGES;                    // [A_STAGES]
-  uint64_t* aempty = afull + A_STAGES;                        // [A_STAGES]
-  uint64_t* accfull = aempty + A_STAGES;                      // [1]
+  uint64_t* afull = wempty + W_MAX_STAGES;                    // [A_MAX_STAGES]
+  uint64_t* aempty = afull + A_MAX_STAGES;                    // [A_MAX_STAGES]
+  uint64_t* accfull = aempty + A_MAX_STAGES;                  // [1]
   uint64_t* wgo = accfull + 1;                                // [1] FWD: the staging area is free for weights
   uint64_t* xbar = wgo + 1;                                   // [3] row-copy rounds
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 3);
@@ -232,7 +236,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
   // ---- set-up: barriers, tensor memory ---------------------------------------------------------
   if (tid == 0) {
     for (uint32_t s = 0; s < W_MAX_STAGES; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wempty[s], 1); }
-    for (uint32_t s = 0; s < A_STAGES; ++s) { mbar_init(&afull[s], PW); mbar_init(&aempty[s], 1); }
+    for (uint32_t s = 0; s < a_stages; ++s) { mbar_init(&afull[s], PW); mbar_init(&aempty[s], 1); }
     mbar_init(accfull, 1);
     mbar_init(wgo, 1);
     for (uint32_t s = 0; s < 3; ++s) mbar_init(&xbar[s], 1);
@@ -356,7 +360,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
           }
         };
         auto process = [&](uint32_t i, const Regs& r) -> bool {
-          const uint32_t s = i & (A_STAGES - 1), ph = (i / A_STAGES) & 1u;
+          const uint32_t s = i & a_mask, ph = (i >> a_shift) & 1u;
           if (!wait_warp(&aempty[s], ph ^ 1u)) return false;
           uint8_t* a_hi = aring + s * A_STAGE;
 #pragma unroll
@@ -405,7 +409,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
         }
       };
       auto process = [&](uint32_t i, const Regs& r) -> bool {
-        const uint32_t s = i & (A_STAGES - 1), ph = (i / A_STAGES) & 1u;
+        const uint32_t s = i & a_mask, ph = (i >> a_shift) & 1u;
         if (!wait_warp(&aempty[s], ph ^ 1u)) return false;
         uint8_t* a_hi = aring + s * A_STAGE;
 #pragma unroll
@@ -517,7 +521,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
     if (lane == 0) {
       const uint32_t idesc = idesc_mn(TM, n_tile);
       for (uint32_t i = 0; i < nchunks && ok; ++i) {
-        const uint32_t sa = i & (A_STAGES - 1), pa = (i / A_STAGES) & 1u;
+        const uint32_t sa = i & a_mask, pa = (i >> a_shift) & 1u;
         const uint32_t sb = i % w_stages, pb = (i / w_stages) & 1u;
         ok = mbar_wait(&wfull[sb], pb, a.status) && mbar_wait(&afull[sa], pa, a.status);
         if (i < 32) MN_TRACE(96 + i);    // operands of chunk i ready
@@ -582,11 +586,12 @@ int32_t launch(dim3 grid, const pcb_workspace* ws, const MnArgs& args, cudaStrea
     return pcb_fail(PCB_ERR_CUDA, "cuTensorMapEncodeTiled is not available: the dense-block kernels cannot fetch their row slabs");
   static PcbPerDeviceOnce once;
   PCB_CUDA(once.run([] {
-    return cudaFuncSetAttribute(dense_mn_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    return cudaFuncSetAttribute(dense_mn_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES_MAX);
   }));
   alignas(64) CUtensorMap tm;
   memcpy(&tm, ws->tm_rows, sizeof(tm));
-  PCB_CUDA(pcb_launch_pdl(dense_mn_kernel<MODE>, grid, dim3(NTHREADS), SMEM_BYTES, st, pdl, tm, args));
+  const uint32_t smem = args.a_stages * A_STAGE + W_RING + 1024 + CTL_BYTES;
+  PCB_CUDA(pcb_launch_pdl(dense_mn_kernel<MODE>, grid, dim3(NTHREADS), smem, st, pdl, tm, args));
   return PCB_OK;
 }
 
@@ -614,6 +619,14 @@ unsigned long long* mn_trace_for(uint32_t) { return nullptr; }
 // A layer that would not fill the GPU (two CTAs per SM) with 256-column tiles is cut into narrower
 // tiles: the CTAs of one tile repeat the production of the data-dependent operand, but each has
 // half (a quarter) of the weight tile to fetch, of the MMAs to wait for and of the epilogue.
+// A launch of at most one CTA per SM has the shared memory of a whole SM to itself: the A ring then
+// holds eight chunks, so the producers of a small layer never wait for the tensor core to hand a
+// stage back (with two stages that round trip, not the loads, paces the K loop of such a launch).
+uint32_t pick_a_stages(dim3 grid, const pcb_circuit* c) {
+  if (c->tc_a_stages) return (uint32_t)c->tc_a_stages;
+  return (uint64_t)grid.x * grid.y * grid.z <= 148 ? A_MAX_STAGES : A_STAGES;
+}
+
 uint32_t pick_nsplit(uint32_t ctas, uint32_t max_cols, int forced) {
   if (forced == 1 || forced == 2 || forced == 4) return (uint32_t)forced;
   uint32_t n = 1;
@@ -674,8 +687,9 @@ int32_t pcb_dense_mn_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, 
   if (o1 == o0) return PCB_OK;
   const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM, ct = (c->max_dense_R + TN - 1) / TN;
   MnArgs args{ws->mars, ws->flows, ws->blk_mx, c->w_img16, c->dense + o0, c->dense_img16 + o0, c->status, ws->ld,
-              pick_nsplit(bt * ct * (o1 - o0), c->max_dense_R, c->tc_nsplit), mn_trace_for(o1 - o0)};
+              pick_nsplit(bt * ct * (o1 - o0), c->max_dense_R, c->tc_nsplit), A_STAGES, mn_trace_for(o1 - o0)};
   dim3 grid(bt, ct * args.nsplit, o1 - o0);
+  args.a_stages = pick_a_stages(grid, c);
   PcbProfScope ps(c, st, PCB_K_DENSE_FWD);
   return launch<MN_FWD>(grid, ws, args, st, c->pdl);
 }
@@ -685,8 +699,9 @@ int32_t pcb_dense_mn_backward_child(pcb_circuit* c, pcb_workspace* ws, uint32_t 
   if (o1 == o0) return PCB_OK;
   const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM, ct = (c->max_dense_K + TN - 1) / TN;
   MnArgs args{ws->mars, ws->flows, ws->blk_mx, c->w_img16, c->dense + o0, c->dense_img16 + o0, c->status, ws->ld,
-              pick_nsplit(bt * ct * (o1 - o0), c->max_dense_K, c->tc_nsplit), mn_trace_for(o1 - o0)};
+              pick_nsplit(bt * ct * (o1 - o0), c->max_dense_K, c->tc_nsplit), A_STAGES, mn_trace_for(o1 - o0)};
   dim3 grid(bt, ct * args.nsplit, o1 - o0);
+  args.a_stages = pick_a_stages(grid, c);
   PcbProfScope ps(c, st, PCB_K_DENSE_BWD_CHILD);
   return launch<MN_BWD_CHILD>(grid, ws, args, st, c->pdl);
 }

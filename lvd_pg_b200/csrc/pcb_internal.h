@@ -181,6 +181,7 @@ struct pcb_circuit {
   bool fwd_split = true, bwd_split = true;   // side-stream splits of the forward / backward layer loops
   int leaf_flow_impl = 0;                    // 0 by category count, 1 shared-memory histograms, 2 sorted segments
   int tc_nsplit = 0;                         // 0 automatic, else 1 / 2 / 4 column splits of a dense tile
+  int tc_a_stages = 0;                       // 0 automatic, else 2 / 4 / 8 stages of the dense kernels' A ring
   bool edge_ld = false;                      // edge statistics by the load-fed kernel instead of tensor-map copies
   // dense blocks [edge_lo, edge_hi) whose edge statistics are still to be launched, and the number
   // of tiles at which the range is launched
