@@ -404,6 +404,7 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
     c->pdl = !flag("PCB_NO_PDL");
     c->fwd_split = !flag("PCB_NO_FWD_SPLIT");
     c->bwd_split = !flag("PCB_NO_BWD_SPLIT");
+    c->early_update = flag("PCB_EARLY_UPDATE");
     if (const char* e = getenv("PCB_LEAF_FLOW_IMPL")) c->leaf_flow_impl = !strcmp(e, "sorted") ? 2 : !strcmp(e, "atomic") ? 1 : 0;
     if (const char* e = getenv("PCB_TC_NSPLIT")) { int v = atoi(e); c->tc_nsplit = (v == 1 || v == 2 || v == 4) ? v : 0; }
     if (const char* e = getenv("PCB_TC_A_STAGES")) { int v = atoi(e); c->tc_a_stages = (v == 2 || v == 4 || v == 8) ? v : 0; }

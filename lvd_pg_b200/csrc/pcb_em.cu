@@ -796,14 +796,20 @@ static int32_t comm_rest_and_join(pcb_circuit* c, cudaStream_t st) {
   return PCB_OK;
 }
 
-static int32_t backward_impl(pcb_circuit* c, pcb_workspace* ws, const float* weights_dev, cudaStream_t st, bool split_comm);
+// early: a single-GPU step updates the sum parameters (and refreshes the weight images) on the side
+// stream as soon as the last edge statistics are in, beside the leaf statistics of this stream.
+struct EarlyUpdate { float pseudocount, inertia; bool done; };
+static int32_t em_update_sums(pcb_circuit* c, float pseudocount, float inertia, cudaStream_t st);
+static int32_t backward_impl(pcb_circuit* c, pcb_workspace* ws, const float* weights_dev, cudaStream_t st, bool split_comm,
+                             EarlyUpdate* early = nullptr);
 
 extern "C" int32_t pcb_backward(pcb_circuit* c, pcb_workspace* ws, const float* weights_dev, pcb_stream s) {
   PCB_REQUIRE(c && ws, "null argument");
   return backward_impl(c, ws, weights_dev, (cudaStream_t)s, false);
 }
 
-static int32_t backward_impl(pcb_circuit* c, pcb_workspace* ws, const float* weights_dev, cudaStream_t st, bool split_comm) {
+static int32_t backward_impl(pcb_circuit* c, pcb_workspace* ws, const float* weights_dev, cudaStream_t st, bool split_comm,
+                             EarlyUpdate* early) {
   PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
   if (!ws->have_forward) return pcb_fail(PCB_ERR_STATE, "pcb_backward needs a preceding pcb_forward on this workspace");
   PCB_CUDA(cudaSetDevice(c->device));
@@ -842,6 +848,15 @@ static int32_t backward_impl(pcb_circuit* c, pcb_workspace* ws, const float* wei
   }
   if (c->use_tc) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
   if (split_comm) PCB_TRY(comm_edges_begin(c, st));
+  if (early && c->side && c->use_tc && !c->prof.on) {
+    // every edge statistic is final once this stream's kernels so far and the side stream's are done
+    PCB_CUDA(cudaEventRecord(c->ev_fork, st));
+    PCB_CUDA(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
+    PCB_TRY(em_update_sums(c, early->pseudocount, early->inertia, c->side));
+    PCB_TRY(pcb_dense_tc_refresh(c, c->side));
+    c->side_busy = true;
+    early->done = true;
+  }
   if (c->n_inputs) {
     PcbProfScope ps(c, st, PCB_K_LEAF_FLOW);
     // sorted segments pay off once a variable has enough values to keep a block's threads busy;
@@ -891,17 +906,26 @@ extern "C" int32_t pcb_clear_flows(pcb_circuit* c, float rate, pcb_stream s) {
   return PCB_OK;
 }
 
+static int32_t em_update_sums(pcb_circuit* c, float pseudocount, float inertia, cudaStream_t st) {
+  if (c->n_groups)
+    { PcbProfScope ps(c, st, PCB_K_UPDATE); em_update_sum_kernel<<<(c->n_groups + 7) / 8, 256, 0, st>>>(c->theta, c->aggr, c->grp_node, c->n_groups,
+                                                                c->n_pid0, c->n_ecount, pseudocount, inertia); }
+  c->w_img_valid = false;  // the weights changed
+  return PCB_OK;
+}
+static int32_t em_update_leaves(pcb_circuit* c, float pseudocount, float inertia, cudaStream_t st) {
+  if (c->n_inputs)
+    { PcbProfScope ps(c, st, PCB_K_UPDATE); em_update_leaf_kernel<<<(c->n_inputs + 7) / 8, 256, 0, st>>>(c->theta, c->aggr, c->n_inputs, c->in_cats,
+                                                                 c->in_poff, c->in_foff, pseudocount, inertia); }
+  return PCB_OK;
+}
+
 extern "C" int32_t pcb_em_update(pcb_circuit* c, float pseudocount, float inertia, pcb_stream s) {
   PCB_REQUIRE(c, "null argument");
   PCB_CUDA(cudaSetDevice(c->device));
   cudaStream_t st = (cudaStream_t)s;
-  if (c->n_groups)
-    { PcbProfScope ps(c, st, PCB_K_UPDATE); em_update_sum_kernel<<<(c->n_groups + 7) / 8, 256, 0, st>>>(c->theta, c->aggr, c->grp_node, c->n_groups,
-                                                                c->n_pid0, c->n_ecount, pseudocount, inertia); }
-  if (c->n_inputs)
-    { PcbProfScope ps(c, st, PCB_K_UPDATE); em_update_leaf_kernel<<<(c->n_inputs + 7) / 8, 256, 0, st>>>(c->theta, c->aggr, c->n_inputs, c->in_cats,
-                                                                 c->in_poff, c->in_foff, pseudocount, inertia); }
-  c->w_img_valid = false;  // the weights changed
+  PCB_TRY(em_update_sums(c, pseudocount, inertia, st));
+  PCB_TRY(em_update_leaves(c, pseudocount, inertia, st));
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
 }
@@ -922,14 +946,16 @@ static int32_t em_step_body(pcb_circuit* c, pcb_workspace* ws, const pcb_evidenc
   PCB_TRY(forward_impl(c, ws, ev, c->n_heads ? ws->ll_tmp : nullptr, st));
   const bool multi = c->comm && c->nranks > 1 && c->comm_enabled;
   const bool split = multi && c->comm_split && !c->prof.on;   // per-class timing wants every class alone on the GPU
-  PCB_TRY(backward_impl(c, ws, weights_dev, st, split));
+  EarlyUpdate early{pseudocount, inertia, false};
+  PCB_TRY(backward_impl(c, ws, weights_dev, st, split, (!multi && c->early_update) ? &early : nullptr));
   // batch log-likelihood into the last slot of the statistics vector, so it is reduced with them
   { PcbProfScope ps(c, st, PCB_K_MISC);
     ll_sum_kernel<<<1, 256, 0, st>>>(c->n_heads ? ws->ll_tmp : ws->mars + (size_t)(c->N - 1) * ws->ld, B,
                                      c->aggr + c->aggr_len - 1); }
   if (split) PCB_TRY(comm_rest_and_join(c, st));
   else if (multi) { PcbProfScope ps(c, st, PCB_K_ALLREDUCE); PCB_TRY(pcb_allreduce_aggr(c, st)); }
-  PCB_TRY(pcb_em_update(c, pseudocount, inertia, s));
+  if (early.done) PCB_TRY(em_update_leaves(c, pseudocount, inertia, st));
+  else PCB_TRY(pcb_em_update(c, pseudocount, inertia, s));
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
 }
@@ -1013,7 +1039,7 @@ static int32_t em_step_impl(pcb_circuit* c, pcb_workspace* ws, pcb_evidence ev, 
     ws->row_ids = row_ids_dev; ws->row_start = row_start; ws->have_forward = true;
     ws->soft = ev.soft_dev; ws->head_mask = ev.head_mask_dev;
     ws->soft_reg = ev.soft_dev ? 0.0f : ev.soft_reg; ws->soft_width = ev.soft_reg_width;
-    c->w_img_valid = false;
+    c->w_img_valid = ws->exec_end_w_valid;
     return PCB_OK;
   }
   const bool capture = ws->have_key && !memcmp(&key, &ws->last_key, sizeof(key));
@@ -1050,6 +1076,7 @@ static int32_t em_step_impl(pcb_circuit* c, pcb_workspace* ws, pcb_evidence ev, 
   }
   for (int k = 0; k < PCB_K_COUNT; ++k) ws->step_launches[k] = c->prof.launches[k] - before[k];
   ws->exec_key = key;
+  ws->exec_end_w_valid = c->w_img_valid;   // host-side state the captured step ends in
   PCB_CUDA(cudaGraphLaunch(ws->step_exec, gs));
   PCB_TRY(ll_out(gs));
   PCB_TRY(leave());

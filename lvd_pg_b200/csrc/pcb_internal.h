@@ -179,6 +179,7 @@ struct pcb_circuit {
   bool pdl = true;   // chain kernels are launched with programmatic stream serialization
   // tuning switches, read from the environment once when the circuit is created
   bool fwd_split = true, bwd_split = true;   // side-stream splits of the forward / backward layer loops
+  bool early_update = false;                 // single-GPU step: sum update + weight images beside the leaf statistics (measured neutral)
   int leaf_flow_impl = 0;                    // 0 by category count, 1 shared-memory histograms, 2 sorted segments
   int tc_nsplit = 0;                         // 0 automatic, else 1 / 2 / 4 column splits of a dense tile
   int tc_a_stages = 0;                       // 0 automatic, else 2 / 4 / 8 stages of the dense kernels' A ring
@@ -219,6 +220,7 @@ struct pcb_workspace {
   cudaGraphExec_t step_exec = nullptr;
   uint64_t step_launches[PCB_K_COUNT] = {0};   // launches of one replay, per kernel class
   int32_t* ids_stage = nullptr;                 // [max_batch]
+  bool exec_end_w_valid = false;                // w_img_valid after a replay of step_exec
   float* ll_tmp = nullptr;                      // [max_batch] per-example log-likelihoods of a multi-head step
   // tensor maps over mars / flows for the copy-fed edge-statistics kernel (128-byte opaque objects)
   alignas(64) unsigned char tm[3][128];
