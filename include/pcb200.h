@@ -187,6 +187,16 @@ typedef struct pcb_evidence {
 int32_t pcb_forward_ex(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence* ev, float* ll_out_dev, pcb_stream s);
 int32_t pcb_em_step_ex(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence* ev, const float* weights_dev,
                        float clear_rate, float pseudocount, float inertia, float* ll_sum_dev, pcb_stream s);
+/* per_sample_normalized_flows (queries/flow.jl:417-494): for every row of the batch, the flow of
+ * every sum edge divided by the flow of its node, and of every leaf parameter by its leaf's, as
+ * log(flow / (sum + 1e-8) + 1e-8) (map_flows_kernel :496-528) and log(flow / sum)
+ * (map_input_flows_kernel :549-593), written to out_dev [num_rows, P] column-major at the row's data
+ * index.  params_dev = NULL: the circuit's own parameters (the call runs pcb_forward_ex and
+ * pcb_backward on the workspace, statistics included); else [num_rows, P] log-parameters, one vector
+ * per data row (eval_circuit / flows_circuit with params, queries/likelihood.jl:119-302,
+ * flow.jl:240-403).  Hard evidence without missing values, single-head circuits. */
+int32_t pcb_normalized_flows(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence* ev, const float* params_dev,
+                             float* out_dev, pcb_stream s);
 /* Node ids (1-based) of the heads of a multi-head circuit, in head order. */
 int32_t pcb_get_head_roots(pcb_circuit* c, uint32_t* roots_host, uint64_t n);
 

@@ -58,6 +58,7 @@ SIGNATURES = {
     "pcb_forward_ex": [_vp, _vp, C.POINTER(PcbEvidence), _vp, _vp],
     "pcb_em_step_ex": [_vp, _vp, C.POINTER(PcbEvidence), _vp, _f32, _f32, _f32, _vp, _vp],
     "pcb_get_head_roots": [_vp, _vp, _u64],
+    "pcb_normalized_flows": [_vp, _vp, C.POINTER(PcbEvidence), _vp, _vp, _vp],
     "pcb_get_mars": [_vp, _vp, _vp, _u64],
     "pcb_get_flows": [_vp, _vp, _vp, _u64],
     "pcb_kld": [_vp, _vp, _vp, _vp, _u32, _vp, _vp],

@@ -317,6 +317,27 @@ def em_step_ex(mbpc, data=None, soft=None, head_mask=None, row_ids=None, row_sta
     return ws
 
 
+def per_sample_normalized_flows(mbpc: CuMetaBitsProbCircuit, data, params: Optional[torch.Tensor] = None,
+                                batch_size: int = 512) -> torch.Tensor:
+    """`per_sample_normalized_flows(mbpc, data[, params]; batch_size)` (queries/flow.jl:417-494): a
+    [rows, P] tensor (row index fastest, as the reference's CuMatrix) with, per data row, the log of every
+    parameter's share of the flow of its sum node / leaf.  `params`: None for the circuit's own
+    parameters, else [rows, P] log-parameters with the row index fastest, one vector per data row."""
+    data = _as_data(mbpc, data)
+    rows, P = data.num_rows, num_parameters(mbpc)
+    if params is not None:
+        assert params.is_cuda and params.dtype == torch.float32 and tuple(params.shape) == (rows, P)
+        assert params.stride() == (1, rows), "per-row parameters must be column-major"
+    out = torch.zeros((P, rows), dtype=torch.float32, device=mbpc.device).t()   # [rows, P], rows fastest
+    ws = mbpc.workspace(min(batch_size, rows))
+    for start in range(0, rows, batch_size):
+        b = min(batch_size, rows - start)
+        ev, _, keep = _evidence(mbpc, data, None, None, None, start + 1, b, 0.0, 1)
+        _lib.check(mbpc.lib.pcb_normalized_flows(mbpc.handle, ws, C.byref(ev), _ptr(params), _ptr(out),
+                                                 _stream(mbpc.device)))
+    return out
+
+
 class CuMultiHeadBitsProbCircuit(CuMetaBitsProbCircuit):
     """`CuMultiHeadBitsProbCircuit(pcs)` (src-jl/multi_head_pc/bit_circuit.jl:4-56): several heads over
     shared sub-circuits, held as one flat circuit under a fake root whose edges no top-down pass follows."""

@@ -1,0 +1,217 @@
+// pcb_persample.cu — per-sample normalised flows, with the circuit's own parameters or with one
+// parameter vector per data row.
+//
+// Reference kernels replaced (paths relative to VariationalJuice.jl/src):
+//   ps_leaf_kernel    init_mar!_kernel with params          queries/likelihood.jl:214-283
+//   ps_up_kernel      layer_up_kernel with params           queries/likelihood.jl:119-210
+//   ps_down_kernel    layer_down_kernel with params         queries/flow.jl:240-403
+//   norm_sum_kernel   map_flows_kernel                      queries/flow.jl:496-547
+//   norm_leaf_kernel  input_flows_circuit_kernel +          queries/flow.jl:165-226,
+//                     map_input_flows_kernel                queries/flow.jl:549-612
+//   pcb_normalized_flows   per_sample_normalized_flows      queries/flow.jl:417-494
+//
+// The reference materialises edge_mars and edge_flows ([B, E] each) and normalises them in a third
+// pass.  Here an edge flow is formed where it is consumed: the normalising kernel recomputes
+// flow(parent) * exp(child + log theta - parent) from the node matrices, sums a parameter group in
+// registers and writes log(flow / (sum + 1e-8) + 1e-8) straight to the [rows, P] output, whose row
+// index is the fastest one, so a warp writes 128 contiguous bytes per parameter.  With the
+// circuit's own parameters the node matrices come from the ordinary forward / backward passes
+// (tensor-core blocks included); with per-row parameters every sum edge has one weight per example
+// and the passes are the gather kernels of this file.
+#include <algorithm>
+
+#include "pcb_internal.h"
+
+namespace {
+
+constexpr uint32_t TPB = 128;
+
+__device__ __forceinline__ int64_t data_row(const int32_t* row_ids, uint32_t row_start, uint32_t b) {
+  return row_ids ? (int64_t)row_ids[b] - 1 : (int64_t)row_start - 1 + b;
+}
+
+// log-parameter of parameter `pid` for example b: the row's own vector, or the circuit's
+struct Params {
+  const float* per_row;   // [rows, P] column-major, or null
+  const float* theta;     // [P]
+  uint64_t rows;
+  __device__ __forceinline__ float at(int64_t row, uint64_t pid) const {
+    return per_row ? per_row[(size_t)row + (size_t)rows * pid] : __ldg(theta + pid);
+  }
+};
+
+__global__ void ps_leaf_kernel(float* __restrict__ mars, uint32_t ld, uint32_t B, Params p, uint64_t P,
+                               const uint32_t* __restrict__ in_node, const uint32_t* __restrict__ in_var,
+                               const uint64_t* __restrict__ in_poff, const uint8_t* __restrict__ data,
+                               const uint8_t* __restrict__ miss, uint64_t num_rows, const int32_t* __restrict__ row_ids,
+                               uint32_t row_start) {
+  const uint32_t i = blockIdx.x, b = blockIdx.y * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const int64_t row = data_row(row_ids, row_start, b);
+  const size_t di = (size_t)row + (size_t)num_rows * in_var[i];
+  float v = 0.0f;   // a missing value marginalises the leaf
+  if (!(miss && miss[di])) {
+    const uint64_t po = in_poff[i] + data[di];
+    v = in_poff[i] < P ? p.at(row, po) : __ldg(p.theta + po);   // fixed leaves live behind P in the circuit's vector
+  }
+  mars[(size_t)in_node[i] * ld + b] = v;
+}
+
+__global__ void ps_up_kernel(float* __restrict__ mars, uint32_t ld, uint32_t B, Params p,
+                             const uint32_t* __restrict__ nodes, const uint4* __restrict__ s_node,
+                             const uint32_t* __restrict__ e_prime, const uint32_t* __restrict__ e_sub,
+                             const int32_t* __restrict__ row_ids, uint32_t row_start) {
+  const uint32_t n = nodes[blockIdx.x], b = blockIdx.y * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const uint4 sn = s_node[n];   // edge start, edge count, first parameter, kind | region << 2
+  const int64_t row = data_row(row_ids, row_start, b);
+  const bool issum = (sn.w & 3u) == PCB_SUM;
+  float m = -INFINITY, acc = 0.0f;   // running maximum and sum of exp(v - m)
+  for (uint32_t j = 0; j < sn.y; ++j) {
+    float v = mars[(size_t)e_prime[sn.x + j] * ld + b];
+    const uint32_t sb = e_sub[sn.x + j];
+    if (sb != PCB_NONE) v += mars[(size_t)sb * ld + b];
+    if (!issum) { acc += v; continue; }
+    v += p.at(row, sn.z + j);
+    if (v > m) { acc = acc * __expf(m - v) + 1.0f; m = v; }
+    else if (v != -INFINITY) acc += __expf(v - m);
+  }
+  mars[(size_t)n * ld + b] = issum ? (m == -INFINITY ? -INFINITY : m + __logf(acc)) : acc;
+}
+
+__global__ void ps_down_kernel(float* __restrict__ flows, const float* __restrict__ mars, uint32_t ld, uint32_t B,
+                               Params p, const uint32_t* __restrict__ nodes, uint32_t root,
+                               const uint32_t* __restrict__ in_off, const PcbInEntry* __restrict__ in_ent,
+                               const int32_t* __restrict__ row_ids, uint32_t row_start) {
+  const uint32_t n = nodes[blockIdx.x], b = blockIdx.y * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const uint32_t i0 = in_off[n], i1 = in_off[n + 1];
+  const int64_t row = data_row(row_ids, row_start, b);
+  const float mine = mars[(size_t)n * ld + b];
+  float acc = (i0 == i1 && n == root) ? 1.0f : 0.0f;
+  for (uint32_t x = i0; x < i1; ++x) {
+    const PcbInEntry en = in_ent[x];
+    float ef = flows[(size_t)en.parent * ld + b];
+    if (en.pid != PCB_NONE && ef != 0.0f) {
+      float child = mine + p.at(row, en.pid);
+      if (en.sib != PCB_NONE) child += mars[(size_t)en.sib * ld + b];
+      ef *= __expf(child - mars[(size_t)en.parent * ld + b]);
+    }
+    acc += ef;
+  }
+  flows[(size_t)n * ld + b] = acc;
+}
+
+// One thread per (sum node, example): the node's edge flows are summed, then written normalised.
+__global__ void norm_sum_kernel(const float* __restrict__ flows, const float* __restrict__ mars, uint32_t ld, uint32_t B,
+                                Params p, const uint32_t* __restrict__ grp_node, const uint4* __restrict__ s_node,
+                                const uint32_t* __restrict__ e_prime, const uint32_t* __restrict__ e_sub,
+                                const int32_t* __restrict__ row_ids, uint32_t row_start, float* __restrict__ out,
+                                uint64_t out_rows) {
+  const uint32_t n = grp_node[blockIdx.x], b = blockIdx.y * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const uint4 sn = s_node[n];
+  const int64_t row = data_row(row_ids, row_start, b);
+  const float pf = flows[(size_t)n * ld + b], pm = mars[(size_t)n * ld + b];
+  auto edge_flow = [&](uint32_t j) {
+    if (pf == 0.0f) return 0.0f;
+    float child = mars[(size_t)e_prime[sn.x + j] * ld + b] + p.at(row, sn.z + j);
+    const uint32_t sb = e_sub[sn.x + j];
+    if (sb != PCB_NONE) child += mars[(size_t)sb * ld + b];
+    return pf * __expf(child - pm);
+  };
+  float total = 1e-8f;   // par_groups .= 1e-8 (flow.jl:535)
+  for (uint32_t j = 0; j < sn.y; ++j) total += edge_flow(j);
+  for (uint32_t j = 0; j < sn.y; ++j)
+    out[(size_t)row + (size_t)out_rows * (sn.z + j)] = logf(edge_flow(j) / total + 1e-8f);
+}
+
+// A learnable leaf hands its whole flow to the observed category (get_edge_flow,
+// nodes/fixable_categorical_dist.jl:162-176): log(flow / flow) = 0 there and log(0) = -inf elsewhere;
+// a leaf without flow gives 0 / 0 as in the reference.
+__global__ void norm_leaf_kernel(const float* __restrict__ flows, uint32_t ld, uint32_t B, uint64_t P,
+                                 const uint32_t* __restrict__ in_node, const uint32_t* __restrict__ in_var,
+                                 const uint32_t* __restrict__ in_cats, const uint64_t* __restrict__ in_poff,
+                                 const uint8_t* __restrict__ data, uint64_t num_rows,
+                                 const int32_t* __restrict__ row_ids, uint32_t row_start, float* __restrict__ out,
+                                 uint64_t out_rows) {
+  const uint32_t i = blockIdx.x, b = blockIdx.y * blockDim.x + threadIdx.x;
+  if (b >= B || in_poff[i] >= P) return;
+  const int64_t row = data_row(row_ids, row_start, b);
+  const size_t di = (size_t)row + (size_t)num_rows * in_var[i];
+  const float f = flows[(size_t)in_node[i] * ld + b];
+  const uint32_t x = data[di], C = in_cats[i];
+  for (uint32_t c = 0; c < C; ++c)
+    out[(size_t)row + (size_t)out_rows * (in_poff[i] + c)] = logf((c == x ? f : 0.0f) / f);
+}
+
+dim3 grid2(uint32_t items, uint32_t B) { return dim3(items, (B + TPB - 1) / TPB, 1); }
+
+}  // namespace
+
+#define PCB_TRY(expr)              \
+  do {                             \
+    int32_t _s = (expr);           \
+    if (_s != PCB_OK) return _s;   \
+  } while (0)
+
+extern "C" int32_t pcb_normalized_flows(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence* ev, const float* params_dev,
+                                        float* out_dev, pcb_stream s) {
+  PCB_REQUIRE(c && ws && ev && out_dev, "null argument");
+  PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
+  PCB_REQUIRE(ev->data_dev && !ev->miss_dev && !ev->soft_dev && ev->soft_reg == 0.0f && !ev->head_mask_dev,
+              "normalised flows take hard evidence without missing values");
+  PCB_REQUIRE(!c->n_heads, "normalised flows take a single-head circuit");
+  const uint32_t B = ev->B;
+  PCB_REQUIRE(B >= 1 && B <= ws->max_batch, "batch size exceeds the workspace");
+  PCB_REQUIRE(ev->row_ids_dev || (ev->row_start >= 1 && (uint64_t)ev->row_start - 1 + B <= ev->num_rows),
+              "row range out of bounds");
+  PCB_CUDA(cudaSetDevice(c->device));
+  cudaStream_t st = (cudaStream_t)s;
+  const Params p{params_dev, c->theta, ev->num_rows};
+  if (!params_dev) {
+    // the circuit's own parameters: the ordinary passes (their statistics side effect included)
+    PCB_TRY(pcb_forward_ex(c, ws, ev, nullptr, s));
+    PCB_TRY(pcb_backward(c, ws, nullptr, s));
+  } else {
+    ws->have_forward = false;
+    ws->B = B; ws->data = ev->data_dev; ws->miss = ev->miss_dev; ws->num_rows = ev->num_rows;
+    ws->row_ids = ev->row_ids_dev; ws->row_start = ev->row_start;
+    ws->soft = nullptr; ws->head_mask = nullptr; ws->soft_reg = 0.0f;
+    if (c->n_inputs) {
+      ++c->prof.launches[PCB_K_MISC];
+      ps_leaf_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(ws->mars, ws->ld, B, p, c->P, c->in_node, c->in_var, c->in_poff,
+                                                           ev->data_dev, ev->miss_dev, ev->num_rows, ev->row_ids_dev,
+                                                           ev->row_start);
+    }
+    for (uint32_t lay = 1; lay <= c->L; ++lay) {
+      const uint32_t o0 = c->h_up_all_off[lay - 1], o1 = c->h_up_all_off[lay];
+      if (o1 == o0) continue;
+      ++c->prof.launches[PCB_K_MISC];
+      ps_up_kernel<<<grid2(o1 - o0, B), TPB, 0, st>>>(ws->mars, ws->ld, B, p, c->up_all + o0, c->s_node, c->e_prime,
+                                                     c->e_sub, ev->row_ids_dev, ev->row_start);
+    }
+    for (int64_t lay = c->L; lay >= 0; --lay) {
+      const uint32_t o0 = c->h_down_all_off[lay], o1 = c->h_down_all_off[lay + 1];
+      if (o1 == o0) continue;
+      ++c->prof.launches[PCB_K_MISC];
+      ps_down_kernel<<<grid2(o1 - o0, B), TPB, 0, st>>>(ws->flows, ws->mars, ws->ld, B, p, c->down_all + o0, c->N - 1,
+                                                       c->in_off, c->in_ent, ev->row_ids_dev, ev->row_start);
+    }
+    ws->have_forward = true;
+  }
+  if (c->n_groups) {
+    ++c->prof.launches[PCB_K_MISC];
+    norm_sum_kernel<<<grid2(c->n_groups, B), TPB, 0, st>>>(ws->flows, ws->mars, ws->ld, B, p, c->grp_node, c->s_node,
+                                                          c->e_prime, c->e_sub, ev->row_ids_dev, ev->row_start, out_dev,
+                                                          ev->num_rows);
+  }
+  if (c->n_inputs) {
+    ++c->prof.launches[PCB_K_MISC];
+    norm_leaf_kernel<<<grid2(c->n_inputs, B), TPB, 0, st>>>(ws->flows, ws->ld, B, c->P, c->in_node, c->in_var, c->in_cats,
+                                                           c->in_poff, ev->data_dev, ev->num_rows, ev->row_ids_dev,
+                                                           ev->row_start, out_dev, ev->num_rows);
+  }
+  PCB_CUDA(cudaGetLastError());
+  return PCB_OK;
+}

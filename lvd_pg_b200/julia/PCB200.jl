@@ -388,6 +388,25 @@ function loglikelihoods_probcat(c::PcbCircuit, data::CuArray{Float32,3}; batch_s
     out
 end
 
+"""
+per_sample_normalized_flows(mbpc, data[, params]; batch_size) — queries/flow.jl:417-494: an (n, P) CuMatrix
+with, per data row, the log of every parameter's share of the flow of its sum node / leaf; `params` is an
+(n, P) CuMatrix of log-parameters, one vector per row, or `nothing` for the circuit's own.
+"""
+function per_sample_normalized_flows(c::PcbCircuit, data::CuMatrix{UInt8}, params = nothing; batch_size = 512, kwargs...)
+    n = size(data, 1)
+    out = CUDA.zeros(Float32, n, num_parameters(c))
+    ws = workspace(c, min(batch_size, n))
+    for start in 1:batch_size:n
+        b = min(batch_size, n - start + 1)
+        check(ccall((:pcb_normalized_flows, libpcb200), Int32,
+                    (Ptr{Cvoid}, Ptr{Cvoid}, Ref{Evidence}, CuPtr{Cfloat}, CuPtr{Cfloat}, Ptr{Cvoid}),
+                    c.handle, ws, Ref(evidence(data; row_start = start, B = b)),
+                    params === nothing ? CU_NULL : pointer(params), out, stream()))
+    end
+    out
+end
+
 # ---- multi-head circuits (src-jl/multi_head_pc) ---------------------------------------------------------
 """
 CuMultiHeadBitsProbCircuit(pcs) — bit_circuit.jl:4-56: the heads under a fake root whose edges carry

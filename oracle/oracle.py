@@ -258,6 +258,43 @@ def em_step_ex(fc, data=None, soft=None, head_roots=None, head_mask=None, row_id
     return ll, aggr_before
 
 
+def per_sample_normalized_flows(fc, data, params=None):
+    """per_sample_normalized_flows (queries/flow.jl:417-494) for small cases: every row is evaluated with
+    its own parameter vector (params [rows, P]) by the forward / backward passes above, the edge flows
+    are normalised per sum node as map_flows_kernel does (flow.jl:496-528: log(flow / (1e-8 + sum) + 1e-8))
+    and the leaf parameters as map_input_flows_kernel does (flow.jl:549-593: log(flow / sum), the whole
+    flow of a leaf going to the observed category, fixable_categorical_dist.jl:162-176)."""
+    data = np.asfortranarray(data, dtype=np.uint8)
+    rows = data.shape[0]
+    ni, nl, _ = counts(fc)
+    e2p = meta(fc)["edge2param"].astype(np.int64)            # 1-based parameter id per up edge, 0 for product edges
+    out = np.zeros((rows, ni + nl), np.float32)
+    sum_edges = np.nonzero(e2p > 0)[0]
+    for r in range(rows):
+        g = fc if params is None else fc.copy()
+        if params is not None:
+            update_parameters(g, np.ascontiguousarray(params[r], np.float32))
+        mars = forward(g, data, row_start=r + 1, B=1)
+        flows, ef, _ = backward(g, mars, want_edge_flows=True)
+        ef = ef[0].astype(np.float32)
+        group = np.full(fc.num_nodes + 1, np.float32(1e-8), np.float32)
+        np.add.at(group, fc.up_parent[sum_edges].astype(np.int64), ef[sum_edges])
+        with np.errstate(divide="ignore", invalid="ignore"):
+            out[r, e2p[sum_edges] - 1] = np.log(ef[sum_edges] / group[fc.up_parent[sum_edges].astype(np.int64)]
+                                                + np.float32(1e-8))
+            pos = ni
+            for nid in fc.input_node_ids.astype(np.int64):
+                if fc.node_fixed[nid - 1]:
+                    continue
+                C_ = int(fc.node_num_cats[nid - 1])
+                f = np.float32(flows[0, nid - 1])
+                e = np.zeros(C_, np.float32)
+                e[int(data[r, int(fc.node_var[nid - 1]) - 1])] = f
+                out[r, pos:pos + C_] = np.log(e / e.sum(dtype=np.float32))
+                pos += C_
+    return out
+
+
 def clear_flows(fc, edge_aggr, rate=0.0):
     d = fc.desc()
     lib().orc_clear_flows(C.byref(d), _p(edge_aggr), _p(fc.heap), C.c_float(rate))

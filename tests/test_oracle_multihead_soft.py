@@ -115,3 +115,30 @@ def test_soft_evidence_flows_sum_to_the_node_flow():
         n0 = int(n) - 1
         C = int(fc.node_num_cats[n0]); hs = int(fc.node_heap_start[n0]) - 1
         np.testing.assert_allclose(fc.heap[hs + C:hs + 2 * C].sum(), flows[:, n0].sum(), rtol=1e-5)
+
+
+def test_per_sample_normalized_flows_definitions():
+    # map_flows_kernel / map_input_flows_kernel (queries/flow.jl:496-612): the shares of a sum node's
+    # edges add up to one, a leaf gives everything to the observed category, and per-row parameter
+    # vectors that all equal the circuit's give the circuit's answer
+    rng = np.random.default_rng(2)
+    fc = compile_circuit(st.simple_3vars_circuit(num_cats=5, fixed=False, rng=rng))
+    data = rng.integers(0, 5, size=(6, 3)).astype(np.uint8)
+    out = orc.per_sample_normalized_flows(fc, data)
+    ni = orc.counts(fc)[0]
+    np.testing.assert_allclose(np.exp(out[:, :ni]).sum(1), 1.0, rtol=1e-5)     # one sum node: the root
+    leaf = out[:, ni:].reshape(6, -1, 5)
+    for r in range(6):
+        for i, nid in enumerate(fc.input_node_ids.astype(np.int64)):
+            x = data[r, int(fc.node_var[nid - 1]) - 1]
+            assert leaf[r, i, x] == 0.0 and np.isneginf(np.delete(leaf[r, i], x)).all()
+    same = np.tile(orc.vectorize(fc), (6, 1))
+    got = orc.per_sample_normalized_flows(fc, data, same)
+    np.testing.assert_array_equal(np.isneginf(got), np.isneginf(out))
+    np.testing.assert_allclose(np.exp(got), np.exp(out), atol=1e-6)
+    # the root's edge flows are the posterior of the mixture component (flow_tests.jl:112-113)
+    mars, em = orc.forward(fc, data, want_edge_mars=True)
+    root_edges = np.nonzero(fc.up_parent == fc.num_nodes)[0]
+    post = np.exp(em[:, root_edges] - mars[:, [-1]])
+    e2p = orc.meta(fc)["edge2param"].astype(np.int64)
+    np.testing.assert_allclose(np.exp(out[:, e2p[root_edges] - 1]), post, atol=1e-6)
