@@ -250,6 +250,23 @@ def measure_cfg4(args, cpu_leg=True):
     e1.record()
     torch.cuda.synchronize()
     samp_ms = e0.elapsed_time(e1) / reps
+    # per-sample normalised flows of 512 rows with the circuit's own parameters (the encoder side of the
+    # variational loop, utils/cuda_preallocation.jl:287-304): output [512, P]
+    rows_nf = 512
+    rng_nf = np.random.default_rng(9)
+    data_nf = api.DeviceData(rng_nf.integers(0, 2, size=(rows_nf, q.num_vars)).astype(np.uint8), dev)
+    api.update_parameters(m, theta_q)
+    for _ in range(2):
+        nf = api.per_sample_normalized_flows(m, data_nf, batch_size=rows_nf)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(5):
+        nf = api.per_sample_normalized_flows(m, data_nf, batch_size=rows_nf)
+    e1.record()
+    torch.cuda.synchronize()
+    nf_ms = e0.elapsed_time(e1) / 5
+    nf_bytes = 4.0 * rows_nf * P
+    del nf
     peaks = measured_peaks()
     kld_bytes = 48.0 * P
     samp_bytes = 8.0 * S * (shp_s[1] * shp_s[2] + shp_l[1] * shp_l[2])
@@ -277,6 +294,9 @@ def measure_cfg4(args, cpu_leg=True):
                          "note": "latency-bound: one launch per layer on a single parameter set"},
             "sampling": {"samples_per_s": S / (samp_ms * 1e-3), "ms_per_call": samp_ms, "S": S,
                          "hbm_gbs": samp_bytes / (samp_ms * 1e-3) / 1e9, "hbm_frac": samp_bytes / (samp_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+            "normalized_flows": {"rows": rows_nf, "ms_per_call": nf_ms, "rows_per_s": rows_nf / (nf_ms * 1e-3),
+                                 "output_gbs": nf_bytes / (nf_ms * 1e-3) / 1e9,
+                                 "note": "forward + backward + normalising kernels; the output is [rows, P] floats"},
             "clocks": clocks.summary(), "gpu_launches": int(sum(v[1] for v in m.profile_read(reset=True).values()))}
     if cpu:
         line["cpu_baseline"] = cpu

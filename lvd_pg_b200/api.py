@@ -328,7 +328,7 @@ def per_sample_normalized_flows(mbpc: CuMetaBitsProbCircuit, data, params: Optio
     if params is not None:
         assert params.is_cuda and params.dtype == torch.float32 and tuple(params.shape) == (rows, P)
         assert params.stride() == (1, rows), "per-row parameters must be column-major"
-    out = torch.zeros((P, rows), dtype=torch.float32, device=mbpc.device).t()   # [rows, P], rows fastest
+    out = torch.empty((P, rows), dtype=torch.float32, device=mbpc.device).t()   # [rows, P], rows fastest; every column is written
     ws = mbpc.workspace(min(batch_size, rows))
     for start in range(0, rows, batch_size):
         b = min(batch_size, rows - start)

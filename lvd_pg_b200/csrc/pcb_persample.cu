@@ -102,28 +102,125 @@ __global__ void ps_down_kernel(float* __restrict__ flows, const float* __restric
   flows[(size_t)n * ld + b] = acc;
 }
 
-// One thread per (sum node, example): the node's edge flows are summed, then written normalised.
-__global__ void norm_sum_kernel(const float* __restrict__ flows, const float* __restrict__ mars, uint32_t ld, uint32_t B,
-                                Params p, const uint32_t* __restrict__ grp_node, const uint4* __restrict__ s_node,
-                                const uint32_t* __restrict__ e_prime, const uint32_t* __restrict__ e_sub,
-                                const int32_t* __restrict__ row_ids, uint32_t row_start, float* __restrict__ out,
-                                uint64_t out_rows) {
+// One block per (sum node, 128 examples), one thread per example: the node's edge list (and, with the
+// circuit's own parameters, its weights) is staged in shared memory once, a thread keeps up to 32
+// edge flows in registers between the sum and the normalised write; wider nodes recompute them.
+constexpr uint32_t NS_REG = 32, NS_STAGE = 256;
+__global__ void __launch_bounds__(TPB) norm_sum_kernel(const float* __restrict__ flows, const float* __restrict__ mars,
+                                                       uint32_t ld, uint32_t B, Params p,
+                                                       const uint32_t* __restrict__ grp_node, const uint4* __restrict__ s_node,
+                                                       const uint32_t* __restrict__ e_prime, const uint32_t* __restrict__ e_sub,
+                                                       const int32_t* __restrict__ row_ids, uint32_t row_start,
+                                                       float* __restrict__ out, uint64_t out_rows) {
+  __shared__ uint32_t s_pr[NS_STAGE], s_sb[NS_STAGE];
+  __shared__ float s_w[NS_STAGE];
   const uint32_t n = grp_node[blockIdx.x], b = blockIdx.y * blockDim.x + threadIdx.x;
-  if (b >= B) return;
   const uint4 sn = s_node[n];
+  const uint32_t cnt = sn.y, staged = min(cnt, NS_STAGE);
+  for (uint32_t j = threadIdx.x; j < staged; j += blockDim.x) {
+    s_pr[j] = e_prime[sn.x + j];
+    s_sb[j] = e_sub[sn.x + j];
+    s_w[j] = p.per_row ? 0.0f : __ldg(p.theta + sn.z + j);
+  }
+  __syncthreads();
+  if (b >= B) return;
   const int64_t row = data_row(row_ids, row_start, b);
   const float pf = flows[(size_t)n * ld + b], pm = mars[(size_t)n * ld + b];
   auto edge_flow = [&](uint32_t j) {
     if (pf == 0.0f) return 0.0f;
-    float child = mars[(size_t)e_prime[sn.x + j] * ld + b] + p.at(row, sn.z + j);
-    const uint32_t sb = e_sub[sn.x + j];
+    const uint32_t pr = j < NS_STAGE ? s_pr[j] : e_prime[sn.x + j], sb = j < NS_STAGE ? s_sb[j] : e_sub[sn.x + j];
+    float child = mars[(size_t)pr * ld + b];
+    child += p.per_row ? p.per_row[(size_t)row + (size_t)p.rows * (sn.z + j)] : (j < NS_STAGE ? s_w[j] : __ldg(p.theta + sn.z + j));
     if (sb != PCB_NONE) child += mars[(size_t)sb * ld + b];
     return pf * __expf(child - pm);
   };
+  float ef[NS_REG];
   float total = 1e-8f;   // par_groups .= 1e-8 (flow.jl:535)
-  for (uint32_t j = 0; j < sn.y; ++j) total += edge_flow(j);
-  for (uint32_t j = 0; j < sn.y; ++j)
-    out[(size_t)row + (size_t)out_rows * (sn.z + j)] = logf(edge_flow(j) / total + 1e-8f);
+#pragma unroll
+  for (uint32_t j = 0; j < NS_REG; ++j) {
+    ef[j] = j < cnt ? edge_flow(j) : 0.0f;
+    total += ef[j];
+  }
+  for (uint32_t j = NS_REG; j < cnt; ++j) total += edge_flow(j);
+  float* o = out + (size_t)row + (size_t)out_rows * sn.z;
+  const float inv = 1.0f / total;
+#pragma unroll
+  for (uint32_t j = 0; j < NS_REG; ++j)
+    if (j < cnt) o[(size_t)out_rows * j] = __logf(ef[j] * inv + 1e-8f);
+  for (uint32_t j = NS_REG; j < cnt; ++j) o[(size_t)out_rows * j] = __logf(edge_flow(j) * inv + 1e-8f);
+}
+
+// The same with four consecutive examples per thread (16-byte loads of the node rows, 16-byte stores):
+// a block of 128 threads then writes 2 KB of every output column in one piece.  Columns are a whole
+// matrix row apart, and with 512-byte pieces per column the writes of the resident blocks land on as
+// many DRAM pages as there are pieces (measured 0.6 TB/s); used when the batch is a row range whose
+// start and the output's row count are multiples of four.
+constexpr uint32_t NS_REG4 = 16;
+__global__ void __launch_bounds__(TPB) norm_sum4_kernel(const float* __restrict__ flows, const float* __restrict__ mars,
+                                                        uint32_t ld, uint32_t B, Params p,
+                                                        const uint32_t* __restrict__ grp_node, const uint4* __restrict__ s_node,
+                                                        const uint32_t* __restrict__ e_prime, const uint32_t* __restrict__ e_sub,
+                                                        uint32_t row_start, float* __restrict__ out, uint64_t out_rows) {
+  __shared__ uint32_t s_pr[NS_STAGE], s_sb[NS_STAGE];
+  __shared__ float s_w[NS_STAGE];
+  const uint32_t n = grp_node[blockIdx.x], b = (blockIdx.y * blockDim.x + threadIdx.x) * 4u;
+  const uint4 sn = s_node[n];
+  const uint32_t cnt = sn.y, staged = min(cnt, NS_STAGE);
+  for (uint32_t j = threadIdx.x; j < staged; j += blockDim.x) {
+    s_pr[j] = e_prime[sn.x + j];
+    s_sb[j] = e_sub[sn.x + j];
+    s_w[j] = p.per_row ? 0.0f : __ldg(p.theta + sn.z + j);
+  }
+  __syncthreads();
+  if (b >= B) return;
+  const size_t row = (size_t)row_start - 1 + b;
+  auto ld4 = [](const float* q) { return *reinterpret_cast<const float4*>(q); };
+  const float4 pf = ld4(flows + (size_t)n * ld + b), pm = ld4(mars + (size_t)n * ld + b);
+  auto edge_flow = [&](uint32_t j) {
+    const uint32_t pr = j < NS_STAGE ? s_pr[j] : e_prime[sn.x + j], sb = j < NS_STAGE ? s_sb[j] : e_sub[sn.x + j];
+    float4 c = ld4(mars + (size_t)pr * ld + b);
+    if (sb != PCB_NONE) { const float4 d = ld4(mars + (size_t)sb * ld + b); c.x += d.x; c.y += d.y; c.z += d.z; c.w += d.w; }
+    if (p.per_row) {
+      const float4 w = ld4(p.per_row + row + (size_t)p.rows * (sn.z + j));
+      c.x += w.x; c.y += w.y; c.z += w.z; c.w += w.w;
+    } else {
+      const float w = j < NS_STAGE ? s_w[j] : __ldg(p.theta + sn.z + j);
+      c.x += w; c.y += w; c.z += w; c.w += w;
+    }
+    float4 e;
+    e.x = pf.x == 0.0f ? 0.0f : pf.x * __expf(c.x - pm.x);
+    e.y = pf.y == 0.0f ? 0.0f : pf.y * __expf(c.y - pm.y);
+    e.z = pf.z == 0.0f ? 0.0f : pf.z * __expf(c.z - pm.z);
+    e.w = pf.w == 0.0f ? 0.0f : pf.w * __expf(c.w - pm.w);
+    return e;
+  };
+  float4 ef[NS_REG4];
+  float4 total = make_float4(1e-8f, 1e-8f, 1e-8f, 1e-8f);
+#pragma unroll
+  for (uint32_t j = 0; j < NS_REG4; ++j) {
+    ef[j] = j < cnt ? edge_flow(j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    total.x += ef[j].x; total.y += ef[j].y; total.z += ef[j].z; total.w += ef[j].w;
+  }
+  for (uint32_t j = NS_REG4; j < cnt; ++j) {
+    const float4 e = edge_flow(j);
+    total.x += e.x; total.y += e.y; total.z += e.z; total.w += e.w;
+  }
+  const float4 inv = make_float4(1.0f / total.x, 1.0f / total.y, 1.0f / total.z, 1.0f / total.w);
+  float* o = out + row + (size_t)out_rows * sn.z;
+  const bool whole = b + 4 <= B;
+  auto put = [&](uint32_t j, const float4& e) {
+    const float4 v = make_float4(__logf(e.x * inv.x + 1e-8f), __logf(e.y * inv.y + 1e-8f), __logf(e.z * inv.z + 1e-8f),
+                                 __logf(e.w * inv.w + 1e-8f));
+    float* q = o + (size_t)out_rows * j;
+    if (whole) { *reinterpret_cast<float4*>(q) = v; return; }
+    q[0] = v.x;
+    if (b + 1 < B) q[1] = v.y;
+    if (b + 2 < B) q[2] = v.z;
+  };
+#pragma unroll
+  for (uint32_t j = 0; j < NS_REG4; ++j)
+    if (j < cnt) put(j, ef[j]);
+  for (uint32_t j = NS_REG4; j < cnt; ++j) put(j, edge_flow(j));
 }
 
 // A learnable leaf hands its whole flow to the observed category (get_edge_flow,
@@ -200,7 +297,13 @@ extern "C" int32_t pcb_normalized_flows(pcb_circuit* c, pcb_workspace* ws, const
     }
     ws->have_forward = true;
   }
-  if (c->n_groups) {
+  const bool quads = !ev->row_ids_dev && (ev->row_start - 1) % 4 == 0 && ev->num_rows % 4 == 0 &&
+                     (reinterpret_cast<uintptr_t>(out_dev) & 15) == 0 && (!params_dev || (reinterpret_cast<uintptr_t>(params_dev) & 15) == 0);
+  if (c->n_groups && quads) {
+    ++c->prof.launches[PCB_K_MISC];
+    norm_sum4_kernel<<<dim3(c->n_groups, (B + 4 * TPB - 1) / (4 * TPB)), TPB, 0, st>>>(
+        ws->flows, ws->mars, ws->ld, B, p, c->grp_node, c->s_node, c->e_prime, c->e_sub, ev->row_start, out_dev, ev->num_rows);
+  } else if (c->n_groups) {
     ++c->prof.launches[PCB_K_MISC];
     norm_sum_kernel<<<grid2(c->n_groups, B), TPB, 0, st>>>(ws->flows, ws->mars, ws->ld, B, p, c->grp_node, c->s_node,
                                                           c->e_prime, c->e_sub, ev->row_ids_dev, ev->row_start, out_dev,
