@@ -197,6 +197,15 @@ int32_t pcb_em_step_ex(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence* ev
  * flow.jl:240-403).  Hard evidence without missing values, single-head circuits. */
 int32_t pcb_normalized_flows(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence* ev, const float* params_dev,
                              float* out_dev, pcb_stream s);
+/* normalize_params(mbpc, params; undo) (misc.jl:363-392, 405-480) on [S, P] parameter sets, in place:
+ * leaves become probabilities (exp, divided by the leaf's sum; undo: log(p + 1e-6) of the positive
+ * entries), sum groups log-normalised (in both directions, as in the reference). */
+int32_t pcb_normalize_params(pcb_circuit* c, float* params_dev, uint32_t S, int32_t undo, pcb_stream s);
+/* map_pc_parameters_kernel (utils/map_params.jl:128-146): dst[s, ids_dst[i]] = src[s, ids_src[i]] for
+ * i < n; both matrices have S rows (row index fastest), ids are 1-based parameter ids on the device.
+ * The matching of two circuits' parameters (compute_mbpc_mapping) stays host code of the caller. */
+int32_t pcb_map_param_columns(float* dst_dev, const float* src_dev, uint32_t S, const uint32_t* ids_dst_dev,
+                              const uint32_t* ids_src_dev, uint32_t n, pcb_stream s);
 /* Node ids (1-based) of the heads of a multi-head circuit, in head order. */
 int32_t pcb_get_head_roots(pcb_circuit* c, uint32_t* roots_host, uint64_t n);
 

@@ -58,6 +58,8 @@ SIGNATURES = {
     "pcb_forward_ex": [_vp, _vp, C.POINTER(PcbEvidence), _vp, _vp],
     "pcb_em_step_ex": [_vp, _vp, C.POINTER(PcbEvidence), _vp, _f32, _f32, _f32, _vp, _vp],
     "pcb_get_head_roots": [_vp, _vp, _u64],
+    "pcb_normalize_params": [_vp, _vp, _u32, _i32, _vp],
+    "pcb_map_param_columns": [_vp, _vp, _u32, _vp, _vp, _u32, _vp],
     "pcb_normalized_flows": [_vp, _vp, C.POINTER(PcbEvidence), _vp, _vp, _vp],
     "pcb_get_mars": [_vp, _vp, _vp, _u64],
     "pcb_get_flows": [_vp, _vp, _vp, _u64],

@@ -260,6 +260,16 @@ def em_step(mbpc, data, row_ids=None, row_start=1, B=None, pseudocount=0.1, iner
     return ws
 
 
+def _is_colmajor(t: torch.Tensor) -> bool:
+    """First index fastest; the stride of an index of extent one is free."""
+    want = 1
+    for n, st in zip(t.shape, t.stride()):
+        if n != 1 and st != want:
+            return False
+        want *= n
+    return True
+
+
 def _evidence(mbpc, data, soft, head_mask, row_ids, row_start, B, soft_reg, soft_reg_width):
     """Fill a pcb_evidence; returns (struct, B, keep-alive tuple)."""
     ev = _lib.PcbEvidence()
@@ -271,11 +281,11 @@ def _evidence(mbpc, data, soft, head_mask, row_ids, row_start, B, soft_reg, soft
     if soft is not None:
         # [rows, V, C] with the rows fastest, as a Julia CuArray of that size lies in memory
         assert soft.is_cuda and soft.dtype == torch.float32 and soft.dim() == 3
-        assert soft.stride() == (1, soft.shape[0], soft.shape[0] * soft.shape[1]), "soft evidence must be column-major"
+        assert _is_colmajor(soft), "soft evidence must be column-major"
         ev.soft_dev, num_rows = _ptr(soft), soft.shape[0]
     if head_mask is not None:
         assert head_mask.is_cuda and head_mask.dtype == torch.float32 and head_mask.dim() == 2
-        assert head_mask.stride() == (1, head_mask.shape[0]), "head mask must be column-major"
+        assert _is_colmajor(head_mask), "head mask must be column-major"
         assert head_mask.shape[0] == num_rows
         ev.head_mask_dev = _ptr(head_mask)
     if B is None:
@@ -327,7 +337,7 @@ def per_sample_normalized_flows(mbpc: CuMetaBitsProbCircuit, data, params: Optio
     rows, P = data.num_rows, num_parameters(mbpc)
     if params is not None:
         assert params.is_cuda and params.dtype == torch.float32 and tuple(params.shape) == (rows, P)
-        assert params.stride() == (1, rows), "per-row parameters must be column-major"
+        assert _is_colmajor(params), "per-row parameters must be column-major"
     out = torch.empty((P, rows), dtype=torch.float32, device=mbpc.device).t()   # [rows, P], rows fastest; every column is written
     ws = mbpc.workspace(min(batch_size, rows))
     for start in range(0, rows, batch_size):
@@ -336,6 +346,39 @@ def per_sample_normalized_flows(mbpc: CuMetaBitsProbCircuit, data, params: Optio
         _lib.check(mbpc.lib.pcb_normalized_flows(mbpc.handle, ws, C.byref(ev), _ptr(params), _ptr(out),
                                                  _stream(mbpc.device)))
     return out
+
+
+def normalize_params(mbpc: CuMetaBitsProbCircuit, params: torch.Tensor, undo: bool = False) -> torch.Tensor:
+    """`normalize_params(mbpc, params; undo)` (misc.jl:448-480) on a [S, P] CUDA tensor with the set index
+    fastest, in place: leaves become probabilities, sum groups log-normalised."""
+    assert params.is_cuda and params.dtype == torch.float32 and params.dim() == 2
+    assert _is_colmajor(params) and params.shape[1] == num_parameters(mbpc)
+    _lib.check(mbpc.lib.pcb_normalize_params(mbpc.handle, _ptr(params), params.shape[0], int(undo), _stream(mbpc.device)))
+    return params
+
+
+def map_pc_parameters(params1: torch.Tensor, params2: torch.Tensor, ids1: torch.Tensor, ids2: torch.Tensor) -> torch.Tensor:
+    """The device half of `map_pc_parameters` (utils/map_params.jl:12-50): params1[:, ids1] = params2[:, ids2]
+    with 1-based int32 / uint32 id vectors on the device (the caller computed the matching once)."""
+    assert params1.is_cuda and params2.is_cuda and params1.shape[0] == params2.shape[0]
+    assert _is_colmajor(params1) and _is_colmajor(params2)
+    assert ids1.numel() == ids2.numel() and ids1.is_cuda and ids2.is_cuda and ids1.element_size() == 4 and ids2.element_size() == 4
+    _lib.check(_lib.lib().pcb_map_param_columns(_ptr(params1), _ptr(params2), params1.shape[0], _ptr(ids1), _ptr(ids2),
+                                                ids1.numel(), _stream(params1.device)))
+    return params1
+
+
+def normalized_flows(mbpc_xz: CuMetaBitsProbCircuit, mbpc_z: CuMetaBitsProbCircuit, data, mapping,
+                     batch_size: int = 512) -> torch.Tensor:
+    """`normalized_flows_with_prealloc(mbpc_xz, mbpc_z, data)` (utils/cuda_preallocation.jl:287-304): the
+    normalised flows of the joint circuit, copied onto the latent circuit's parameters through
+    `mapping` = (ids_z, ids_xz), clamped to [-20, 0] and normalised; returns [rows, P_z]."""
+    nf = per_sample_normalized_flows(mbpc_xz, data, None, batch_size)
+    rows = nf.shape[0]
+    pz = torch.zeros((num_parameters(mbpc_z), rows), dtype=torch.float32, device=mbpc_z.device).t()
+    map_pc_parameters(pz, nf, mapping[0], mapping[1])
+    pz.clamp_(-20.0, 0.0)
+    return normalize_params(mbpc_z, pz, undo=False)
 
 
 class CuMultiHeadBitsProbCircuit(CuMetaBitsProbCircuit):

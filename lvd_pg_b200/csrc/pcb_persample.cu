@@ -242,6 +242,52 @@ __global__ void norm_leaf_kernel(const float* __restrict__ flows, uint32_t ld, u
     out[(size_t)row + (size_t)out_rows * (in_poff[i] + c)] = logf((c == x ? f : 0.0f) / f);
 }
 
+// normalize_params (misc.jl:363-392, 405-447): on a [S, P] matrix of parameter sets, in place.
+// Leaves: exp and division by the leaf's sum, i.e. PROBABILITIES (undo: log(p + 1e-6) of positive
+// entries, the others kept); sum groups: log-parameters minus the log of the group's summed exp
+// (in both directions: the reference's inner kernel has no undo form).
+__global__ void normalize_leaf_kernel(float* __restrict__ params, uint32_t S, uint32_t n_inputs, uint64_t P,
+                                      const uint32_t* __restrict__ in_cats, const uint64_t* __restrict__ in_poff, int undo) {
+  const uint32_t i = blockIdx.x, s = blockIdx.y * blockDim.x + threadIdx.x;
+  if (s >= S || in_poff[i] >= P) return;
+  float* q = params + s + (size_t)S * in_poff[i];
+  const uint32_t C = in_cats[i];
+  if (undo) {
+    for (uint32_t k = 0; k < C; ++k) {
+      const float v = q[(size_t)S * k];
+      if (v > 0.0f) q[(size_t)S * k] = logf(v + 1e-6f);
+    }
+    return;
+  }
+  float total = 0.0f;
+  for (uint32_t k = 0; k < C; ++k) {
+    const float v = expf(q[(size_t)S * k]);
+    q[(size_t)S * k] = v;
+    total += v;
+  }
+  for (uint32_t k = 0; k < C; ++k) q[(size_t)S * k] /= total;
+}
+
+__global__ void normalize_sum_kernel(float* __restrict__ params, uint32_t S, const uint32_t* __restrict__ grp_node,
+                                     const uint4* __restrict__ s_node) {
+  const uint32_t s = blockIdx.y * blockDim.x + threadIdx.x;
+  if (s >= S) return;
+  const uint4 sn = s_node[grp_node[blockIdx.x]];
+  float* q = params + s + (size_t)S * sn.z;
+  float total = 0.0f;
+  for (uint32_t j = 0; j < sn.y; ++j) total += expf(q[(size_t)S * j]);
+  const float lt = logf(total);
+  for (uint32_t j = 0; j < sn.y; ++j) q[(size_t)S * j] -= lt;
+}
+
+// map_pc_parameters_kernel (utils/map_params.jl:128-146): dst[s, ids_dst[i]] = src[s, ids_src[i]], ids 1-based
+__global__ void map_columns_kernel(float* __restrict__ dst, const float* __restrict__ src, uint32_t S,
+                                   const uint32_t* __restrict__ ids_dst, const uint32_t* __restrict__ ids_src) {
+  const uint32_t s = blockIdx.y * blockDim.x + threadIdx.x;
+  if (s >= S) return;
+  dst[s + (size_t)S * (ids_dst[blockIdx.x] - 1)] = src[s + (size_t)S * (ids_src[blockIdx.x] - 1)];
+}
+
 dim3 grid2(uint32_t items, uint32_t B) { return dim3(items, (B + TPB - 1) / TPB, 1); }
 
 }  // namespace
@@ -315,6 +361,36 @@ extern "C" int32_t pcb_normalized_flows(pcb_circuit* c, pcb_workspace* ws, const
                                                            c->in_poff, ev->data_dev, ev->num_rows, ev->row_ids_dev,
                                                            ev->row_start, out_dev, ev->num_rows);
   }
+  PCB_CUDA(cudaGetLastError());
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_normalize_params(pcb_circuit* c, float* params_dev, uint32_t S, int32_t undo, pcb_stream s) {
+  PCB_REQUIRE(c && params_dev, "null argument");
+  PCB_REQUIRE(S >= 1, "no parameter sets");
+  PCB_CUDA(cudaSetDevice(c->device));
+  cudaStream_t st = (cudaStream_t)s;
+  const uint32_t tpb = S >= TPB ? TPB : 32;
+  const uint32_t gy = (S + tpb - 1) / tpb;
+  if (c->n_inputs) {
+    ++c->prof.launches[PCB_K_MISC];
+    normalize_leaf_kernel<<<dim3(c->n_inputs, gy), tpb, 0, st>>>(params_dev, S, c->n_inputs, c->P, c->in_cats, c->in_poff, undo);
+  }
+  if (c->n_groups) {
+    ++c->prof.launches[PCB_K_MISC];
+    normalize_sum_kernel<<<dim3(c->n_groups, gy), tpb, 0, st>>>(params_dev, S, c->grp_node, c->s_node);
+  }
+  PCB_CUDA(cudaGetLastError());
+  return PCB_OK;
+}
+
+extern "C" int32_t pcb_map_param_columns(float* dst_dev, const float* src_dev, uint32_t S, const uint32_t* ids_dst_dev,
+                                         const uint32_t* ids_src_dev, uint32_t n, pcb_stream s) {
+  PCB_REQUIRE(dst_dev && src_dev && (n == 0 || (ids_dst_dev && ids_src_dev)), "null argument");
+  PCB_REQUIRE(S >= 1, "no parameter sets");
+  if (n == 0) return PCB_OK;
+  const uint32_t tpb = S >= TPB ? TPB : 32;
+  map_columns_kernel<<<dim3(n, (S + tpb - 1) / tpb), tpb, 0, (cudaStream_t)s>>>(dst_dev, src_dev, S, ids_dst_dev, ids_src_dev);
   PCB_CUDA(cudaGetLastError());
   return PCB_OK;
 }

@@ -407,6 +407,30 @@ function per_sample_normalized_flows(c::PcbCircuit, data::CuMatrix{UInt8}, param
     out
 end
 
+"normalize_params(mbpc, params; undo) — misc.jl:448-480, in place on an (S, P) CuMatrix"
+function normalize_params(c::PcbCircuit, params::CuMatrix{Float32}; undo = false, kwargs...)
+    check(ccall((:pcb_normalize_params, libpcb200), Int32, (Ptr{Cvoid}, CuPtr{Cfloat}, UInt32, Int32, Ptr{Cvoid}),
+                c.handle, params, size(params, 1), undo ? 1 : 0, stream()))
+    params
+end
+
+"The device half of map_pc_parameters (utils/map_params.jl:12-50): params1[:, ids1] = params2[:, ids2]"
+function map_pc_parameters!(params1::CuMatrix{Float32}, params2::CuMatrix{Float32}, ids1::CuVector{UInt32}, ids2::CuVector{UInt32})
+    check(ccall((:pcb_map_param_columns, libpcb200), Int32,
+                (CuPtr{Cfloat}, CuPtr{Cfloat}, UInt32, CuPtr{UInt32}, CuPtr{UInt32}, UInt32, Ptr{Cvoid}),
+                params1, params2, size(params1, 1), ids1, ids2, length(ids1), stream()))
+    params1
+end
+
+"normalized_flows_with_prealloc(mbpc_xz, mbpc_z, data) — utils/cuda_preallocation.jl:287-304, mapping = (ids_z, ids_xz)"
+function normalized_flows(c_xz::PcbCircuit, c_z::PcbCircuit, data::CuMatrix{UInt8}, mapping; batch_size = size(data, 1))
+    nf = per_sample_normalized_flows(c_xz, data; batch_size)
+    pz = CUDA.zeros(Float32, size(data, 1), num_parameters(c_z))
+    map_pc_parameters!(pz, nf, mapping[1], mapping[2])
+    clamp!(pz, -20f0, 0f0)
+    normalize_params(c_z, pz)
+end
+
 # ---- multi-head circuits (src-jl/multi_head_pc) ---------------------------------------------------------
 """
 CuMultiHeadBitsProbCircuit(pcs) — bit_circuit.jl:4-56: the heads under a fake root whose edges carry

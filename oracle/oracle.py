@@ -295,6 +295,31 @@ def per_sample_normalized_flows(fc, data, params=None):
     return out
 
 
+def normalize_params(fc, params, undo=False):
+    """normalize_params (misc.jl:363-392, 405-480) on [S, P] parameter sets; returns a new array."""
+    out = np.array(params, np.float32, copy=True)
+    ni, nl, _ = counts(fc)
+    pos = ni
+    for nid in fc.input_node_ids.astype(np.int64):
+        if fc.node_fixed[nid - 1]:
+            continue
+        C_ = int(fc.node_num_cats[nid - 1])
+        blk = out[:, pos:pos + C_]
+        if undo:
+            with np.errstate(invalid="ignore"):
+                blk[...] = np.where(blk > 0, np.log(blk + np.float32(1e-6), where=blk > 0, out=np.zeros_like(blk)), blk)
+        else:
+            e = np.exp(blk)
+            blk[...] = e / e.sum(1, keepdims=True, dtype=np.float32)
+        pos += C_
+    m = meta(fc)
+    p2g = m["param2group"].astype(np.int64)
+    tot = np.zeros((out.shape[0], p2g.max() + 1 if ni else 1), np.float32)
+    np.add.at(tot.T, p2g, np.exp(out[:, :ni]).T)
+    out[:, :ni] -= np.log(tot[:, p2g])
+    return out
+
+
 def clear_flows(fc, edge_aggr, rate=0.0):
     d = fc.desc()
     lib().orc_clear_flows(C.byref(d), _p(edge_aggr), _p(fc.heap), C.c_float(rate))

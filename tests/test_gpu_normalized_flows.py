@@ -64,3 +64,51 @@ def test_normalized_flows_with_per_row_parameters(oracle, name, make, c, rows):
     a = api.per_sample_normalized_flows(m, data, api.colmajor(same, m.device), batch_size=16).cpu().numpy()
     b = api.per_sample_normalized_flows(m, data, batch_size=16).cpu().numpy()
     _compare(a, b)
+
+
+def test_normalize_params_and_column_mapping(oracle):
+    """pcb_normalize_params (misc.jl:448-480, both directions) and pcb_map_param_columns
+    (utils/map_params.jl:128-146) against the numpy restatement."""
+    import torch
+    from lvd_pg_b200 import api
+    fc = random_hclt(7, 8, 3, 5)
+    m = api.CuMetaBitsProbCircuit(fc)
+    P = api.num_parameters(m)
+    rng = np.random.default_rng(3)
+    for S in (1, 5, 200):
+        params = rng.normal(-1.0, 1.0, (S, P)).astype(np.float32)
+        d = api.colmajor(params, m.device)
+        want = oracle.normalize_params(fc, params)
+        got = api.normalize_params(m, d).cpu().numpy()
+        np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
+        back = api.normalize_params(m, d, undo=True).cpu().numpy()
+        np.testing.assert_allclose(back, oracle.normalize_params(fc, want, undo=True), rtol=1e-5, atol=1e-5)
+    # column mapping: a random partial injection of columns
+    S = 33
+    src = rng.normal(size=(S, 50)).astype(np.float32)
+    ids_src = (rng.permutation(50)[:20] + 1).astype(np.int32)
+    ids_dst = (rng.permutation(P)[:20] + 1).astype(np.int32)
+    dst = api.colmajor(np.zeros((S, P), np.float32), m.device)
+    api.map_pc_parameters(dst, api.colmajor(src, m.device), torch.from_numpy(ids_dst).to(m.device),
+                          torch.from_numpy(ids_src).to(m.device))
+    want = np.zeros((S, P), np.float32)
+    want[:, ids_dst - 1] = src[:, ids_src - 1]
+    np.testing.assert_array_equal(dst.cpu().numpy(), want)
+
+
+def test_normalized_flows_onto_a_latent_circuit(oracle):
+    """normalized_flows_with_prealloc (utils/cuda_preallocation.jl:287-304) with the identity mapping of
+    the sum parameters of a circuit onto a copy of itself: map, clamp to [-20, 0], normalise."""
+    import torch
+    from lvd_pg_b200 import api
+    fc = random_hclt(6, 8, 3, 9)
+    m = api.CuMetaBitsProbCircuit(fc)
+    data, _ = random_data(20, fc.num_vars, 3, 2)
+    ni = m.num_inner_params
+    ids = torch.arange(1, ni + 1, dtype=torch.int32, device=m.device)
+    got = api.normalized_flows(m, m, data, (ids, ids), batch_size=8).cpu().numpy()
+    nf = oracle.per_sample_normalized_flows(fc, data)
+    pz = np.zeros_like(nf)
+    pz[:, :ni] = nf[:, :ni]
+    want = oracle.normalize_params(fc, np.clip(pz, -20.0, 0.0))
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-4)

@@ -142,3 +142,20 @@ def test_per_sample_normalized_flows_definitions():
     post = np.exp(em[:, root_edges] - mars[:, [-1]])
     e2p = orc.meta(fc)["edge2param"].astype(np.int64)
     np.testing.assert_allclose(np.exp(out[:, e2p[root_edges] - 1]), post, atol=1e-6)
+
+
+def test_normalize_params_definitions():
+    # normalize_params (misc.jl:363-392, 405-480): leaves become probabilities, sum groups are
+    # log-normalised; undo takes log(p + 1e-6) of the leaves and normalises the sum groups again
+    rng = np.random.default_rng(4)
+    fc = compile_circuit(st.simple_3vars_circuit(num_cats=4, fixed=False, rng=rng))
+    ni, nl, _ = orc.counts(fc)
+    params = rng.normal(-1.0, 1.0, (3, ni + nl)).astype(np.float32)
+    n = orc.normalize_params(fc, params)
+    np.testing.assert_allclose(np.exp(n[:, :ni]).sum(1), 1.0, rtol=1e-5)         # the root's two edges
+    np.testing.assert_allclose(n[:, ni:].reshape(3, -1, 4).sum(2), 1.0, rtol=1e-5)
+    np.testing.assert_allclose(n[:, ni:ni + 4], np.exp(params[:, ni:ni + 4]) / np.exp(params[:, ni:ni + 4]).sum(1, keepdims=True),
+                               rtol=1e-5)
+    u = orc.normalize_params(fc, n, undo=True)
+    np.testing.assert_allclose(u[:, ni:], np.log(n[:, ni:] + 1e-6), rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(u[:, :ni], n[:, :ni], atol=1e-6)
