@@ -275,6 +275,16 @@ int32_t pcb_sample_soft(pcb_circuit* c, pcb_workspace* ws, const float* params_d
                         const float* u_dev, float temperature, uint32_t S, float* out_dev,
                         pcb_stream s);
 
+/* conditioned_td_prob(mbpc, marked_pc_idx1, marked_pc_idx2, node_probs, input_aggr_params)
+ * (queries/td_prob.jl:161-291): top-down probabilities with the circuit's own weights in which
+ * inner node n with marked_var[n] > 0 takes node_probs[s, marked_var[n], marked_cat[n]] (1-based,
+ * node_probs [S, Z1, Z2] column-major) instead of what its parents send; the leaves spread theirs
+ * over their categories into out_dev [S, num_vars, max_num_cats] (zeroed by the call).
+ * marked_*_dev: [num_nodes] int32 on the device. */
+int32_t pcb_cond_td_prob(pcb_circuit* c, pcb_workspace* ws, const int32_t* marked_var_dev,
+                         const int32_t* marked_cat_dev, const float* node_probs_dev, uint32_t S, uint32_t Z1,
+                         float* out_dev, pcb_stream s);
+
 /* ---- multi-GPU ---------------------------------------------------------------------- */
 /* One NCCL communicator per process; pcb_em_step then sums [edge_aggr | leaf flows | LL]
  * over ranks before the replicated update.  The reference has no counterpart (it runs one

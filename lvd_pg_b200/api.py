@@ -381,6 +381,24 @@ def normalized_flows(mbpc_xz: CuMetaBitsProbCircuit, mbpc_z: CuMetaBitsProbCircu
     return normalize_params(mbpc_z, pz, undo=False)
 
 
+def conditioned_td_prob(mbpc: CuMetaBitsProbCircuit, marked_var: torch.Tensor, marked_cat: torch.Tensor,
+                        node_probs: torch.Tensor) -> torch.Tensor:
+    """`conditioned_td_prob` / `cond_td_prob_with_prealloc` (queries/td_prob.jl:277-291,
+    utils/cuda_preallocation.jl): marked_var / marked_cat are int32 CUDA vectors over the nodes (0 = not
+    marked, else the 1-based latent variable and category of `mark_nodes`), node_probs [S, Z1, Z2] with
+    the set index fastest; returns [S, num_vars, max_num_cats] with the set index fastest."""
+    assert node_probs.is_cuda and node_probs.dtype == torch.float32 and node_probs.dim() == 3 and _is_colmajor(node_probs)
+    assert marked_var.dtype == torch.int32 and marked_cat.dtype == torch.int32
+    assert marked_var.numel() == mbpc.fc.num_nodes and marked_cat.numel() == mbpc.fc.num_nodes
+    S, Z1 = int(node_probs.shape[0]), int(node_probs.shape[1])
+    V, Cm = mbpc.fc.num_vars, int(mbpc.info.max_num_cats)
+    out = torch.empty((Cm, V, S), dtype=torch.float32, device=mbpc.device).permute(2, 1, 0)
+    ws = mbpc.workspace(1)
+    _lib.check(mbpc.lib.pcb_cond_td_prob(mbpc.handle, ws, _ptr(marked_var), _ptr(marked_cat), _ptr(node_probs), S, Z1,
+                                         _ptr(out), _stream(mbpc.device)))
+    return out
+
+
 class CuMultiHeadBitsProbCircuit(CuMetaBitsProbCircuit):
     """`CuMultiHeadBitsProbCircuit(pcs)` (src-jl/multi_head_pc/bit_circuit.jl:4-56): several heads over
     shared sub-circuits, held as one flat circuit under a fake root whose edges no top-down pass follows."""

@@ -275,6 +275,69 @@ extern "C" int32_t pcb_sample_soft(pcb_circuit* c, pcb_workspace* ws, const floa
   return PCB_OK;
 }
 
+// ---- conditioned top-down probabilities ------------------------------------------------------------------
+// conditioned_td_prob (queries/td_prob.jl:161-291): the top-down pass with the circuit's own weights in
+// which a marked inner node does not take what its parents send but node_probs[s, z_var, z_cat]; the
+// leaves then spread their probability over their categories (gumbel_input_sample_down with the
+// circuit's leaf parameters, queries/sample.jl:233-336).  As in the reference nothing starts at the
+// root: an unmarked node without parents has probability 0.
+namespace {
+__global__ void cond_td_down_kernel(float* __restrict__ td, uint32_t ld, uint32_t S, const float* __restrict__ theta,
+                                    const uint32_t* __restrict__ nodes, uint32_t count, const uint8_t* __restrict__ kind,
+                                    const uint32_t* __restrict__ in_off, const PcbInEntry* __restrict__ in_ent,
+                                    const int32_t* __restrict__ marked_var, const int32_t* __restrict__ marked_cat,
+                                    const float* __restrict__ node_probs, uint32_t Z1) {
+  uint32_t i = blockIdx.x * blockDim.y + threadIdx.y;
+  uint32_t s = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= count || s >= S) return;
+  const uint32_t n = nodes[i];
+  float acc = 0.0f;
+  if (kind[n] != PCB_INPUT && marked_var[n] > 0) {
+    acc = node_probs[s + (size_t)S * ((uint32_t)(marked_var[n] - 1) + (size_t)Z1 * (uint32_t)(marked_cat[n] - 1))];
+  } else {
+    for (uint32_t x = in_off[n]; x < in_off[n + 1]; ++x) {
+      const PcbInEntry en = in_ent[x];
+      float tp = td[(size_t)en.parent * ld + s];
+      if (en.pid != PCB_NONE) tp *= expf(__ldg(theta + en.pid));
+      acc += tp;
+    }
+  }
+  td[(size_t)n * ld + s] = acc;
+}
+}  // namespace
+
+extern "C" int32_t pcb_cond_td_prob(pcb_circuit* c, pcb_workspace* ws, const int32_t* marked_var_dev,
+                                    const int32_t* marked_cat_dev, const float* node_probs_dev, uint32_t S, uint32_t Z1,
+                                    float* out_dev, pcb_stream s) {
+  PCB_REQUIRE(c && ws && marked_var_dev && marked_cat_dev && node_probs_dev && out_dev, "null argument");
+  PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
+  PCB_REQUIRE(S >= 1 && Z1 >= 1, "empty input");
+  PCB_CUDA(cudaSetDevice(c->device));
+  int32_t st0 = pcb_ws_ensure_sets(ws, S, false);
+  if (st0 != PCB_OK) return st0;
+  cudaStream_t st = (cudaStream_t)s;
+  const uint32_t ld = ws->ldS;
+  ws->have_kld = false;   // the gradient rows are reused for the top-down probabilities
+  float* td = ws->grads;
+  PCB_CUDA(cudaMemsetAsync(out_dev, 0, (size_t)S * c->V * c->max_cats * sizeof(float), st));
+  for (int64_t lay = c->L; lay >= 0; --lay) {
+    uint32_t o0 = c->h_down_all_off[lay], o1 = c->h_down_all_off[lay + 1];
+    if (o1 == o0) continue;
+    Shape2 sh = shape_for(S, o1 - o0);
+    ++c->prof.launches[PCB_K_SAMPLE];
+    cond_td_down_kernel<<<sh.grid, sh.block, 0, st>>>(td, ld, S, c->theta, c->down_all + o0, o1 - o0, c->kind, c->in_off,
+                                                      c->in_ent, marked_var_dev, marked_cat_dev, node_probs_dev, Z1);
+  }
+  if (c->n_inputs) {
+    Shape2 sh = shape_for(S, c->n_inputs);
+    ++c->prof.launches[PCB_K_SAMPLE];
+    soft_leaf_kernel<<<sh.grid, sh.block, 0, st>>>(td, ld, S, c->theta, 1, c->n_inputs, c->V, c->in_node, c->in_var,
+                                                   c->in_cats, c->in_poff, c->P, c->theta, out_dev);
+  }
+  PCB_CUDA(cudaGetLastError());
+  return PCB_OK;
+}
+
 // ---- hard sampling without any allocation --------------------------------------------------------------
 // Some hosts of this library must not see it allocate device memory.  Julia's CUDA.jl, which is
 // where the reference lives, keeps nearly all free device memory in its own pool, so a

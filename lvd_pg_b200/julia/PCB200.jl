@@ -431,6 +431,21 @@ function normalized_flows(c_xz::PcbCircuit, c_z::PcbCircuit, data::CuMatrix{UInt
     normalize_params(c_z, pz)
 end
 
+"""
+conditioned_td_prob(mbpc, marked_pc_idx1, marked_pc_idx2, node_probs) — queries/td_prob.jl:277-291; the marks are
+Int32 CuVectors over the nodes (`mark_nodes`), node_probs an (S, Z1, Z2) CuArray; returns (S, num_vars, max_cats).
+"""
+function conditioned_td_prob(c::PcbCircuit, marked1::CuVector{Int32}, marked2::CuVector{Int32},
+                             node_probs::CuArray{Float32,3}; num_vars, num_cats)
+    S = size(node_probs, 1)
+    out = CUDA.zeros(Float32, S, num_vars, num_cats)
+    ws = workspace(c, 1)
+    check(ccall((:pcb_cond_td_prob, libpcb200), Int32,
+                (Ptr{Cvoid}, Ptr{Cvoid}, CuPtr{Int32}, CuPtr{Int32}, CuPtr{Cfloat}, UInt32, UInt32, CuPtr{Cfloat}, Ptr{Cvoid}),
+                c.handle, ws, marked1, marked2, node_probs, S, size(node_probs, 2), out, stream()))
+    out
+end
+
 # ---- multi-head circuits (src-jl/multi_head_pc) ---------------------------------------------------------
 """
 CuMultiHeadBitsProbCircuit(pcs) — bit_circuit.jl:4-56: the heads under a fake root whose edges carry

@@ -320,6 +320,33 @@ def normalize_params(fc, params, undo=False):
     return out
 
 
+def conditioned_td_prob(fc, marked_var, marked_cat, node_probs):
+    """conditioned_td_prob (queries/td_prob.jl:161-291) edge by edge in down order, then
+    gumbel_input_sample_down with the circuit's own leaf parameters (queries/sample.jl:233-296);
+    small cases only.  marked_* are [N] (0 = unmarked, else 1-based), node_probs [S, Z1, Z2]."""
+    S = node_probs.shape[0]
+    N = fc.num_nodes
+    td = np.zeros((S, N), np.float32)
+    for de in range(fc.num_edges):
+        e = int(fc.down2up[de]) - 1
+        parent, prime, sub = int(fc.up_parent[e]) - 1, int(fc.up_prime[e]) - 1, int(fc.up_sub[e])
+        if marked_var[parent] > 0:
+            td[:, parent] = node_probs[:, marked_var[parent] - 1, marked_cat[parent] - 1]
+        etd = td[:, parent].copy()
+        if fc.edge_is_sum[e]:
+            etd = etd * np.exp(np.float32(fc.up_logp[e]))
+        if sub != 0:
+            td[:, sub - 1] += etd
+        td[:, prime] += etd
+    cmax = int(fc.node_num_cats.max())
+    out = np.zeros((S, fc.num_vars, cmax), np.float32)
+    for nid in fc.input_node_ids.astype(np.int64):
+        C_ = int(fc.node_num_cats[nid - 1])
+        hs = int(fc.node_heap_start[nid - 1]) - 1
+        out[:, int(fc.node_var[nid - 1]) - 1, :C_] += td[:, [nid - 1]] * np.exp(fc.heap[hs:hs + C_])[None, :]
+    return out, td
+
+
 def clear_flows(fc, edge_aggr, rate=0.0):
     d = fc.desc()
     lib().orc_clear_flows(C.byref(d), _p(edge_aggr), _p(fc.heap), C.c_float(rate))

@@ -112,3 +112,27 @@ def test_normalized_flows_onto_a_latent_circuit(oracle):
     pz[:, :ni] = nf[:, :ni]
     want = oracle.normalize_params(fc, np.clip(pz, -20.0, 0.0))
     np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("S", [1, 7, 130])
+def test_conditioned_td_prob(oracle, S):
+    """pcb_cond_td_prob (queries/td_prob.jl:161-291): random marks on inner nodes, random node_probs."""
+    import torch
+    from lvd_pg_b200 import api
+    fc = random_hclt(8, 6, 5, 12)
+    m = api.CuMetaBitsProbCircuit(fc)
+    N = fc.num_nodes
+    rng = np.random.default_rng(S)
+    inner = np.nonzero(fc.node_kind != 0)[0]
+    marked = rng.choice(inner, size=len(inner) // 3, replace=False)
+    Z1, Z2 = 4, 6
+    mv, mc = np.zeros(N, np.int32), np.zeros(N, np.int32)
+    mv[marked] = rng.integers(1, Z1 + 1, len(marked))
+    mc[marked] = rng.integers(1, Z2 + 1, len(marked))
+    mv[N - 1], mc[N - 1] = 1, 1                      # the root, so that something flows from the top
+    node_probs = rng.random((S, Z1, Z2)).astype(np.float32)
+    want, _ = oracle.conditioned_td_prob(fc, mv, mc, node_probs)
+    got = api.conditioned_td_prob(m, torch.from_numpy(mv).to(m.device), torch.from_numpy(mc).to(m.device),
+                                  api.colmajor(node_probs, m.device)).cpu().numpy()
+    assert got.shape == want.shape
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-6)

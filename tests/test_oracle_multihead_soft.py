@@ -159,3 +159,24 @@ def test_normalize_params_definitions():
     u = orc.normalize_params(fc, n, undo=True)
     np.testing.assert_allclose(u[:, ni:], np.log(n[:, ni:] + 1e-6), rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(u[:, :ni], n[:, :ni], atol=1e-6)
+
+
+def test_conditioned_td_prob_definitions():
+    # conditioned_td_prob (queries/td_prob.jl:161-291): with the root marked and given probability one
+    # the leaves' spread is the marginal of every variable; nothing flows without a marked node
+    from tests.helpers import random_hclt
+    fc = random_hclt(5, 3, 4, 1)
+    N = fc.num_nodes
+    mv, mc = np.zeros(N, np.int32), np.zeros(N, np.int32)
+    out, td = orc.conditioned_td_prob(fc, mv, mc, np.ones((2, 1, 1), np.float32))
+    assert not out.any() and not td.any()
+    mv[N - 1] = mc[N - 1] = 1
+    out, td = orc.conditioned_td_prob(fc, mv, mc, np.ones((2, 1, 1), np.float32))
+    np.testing.assert_allclose(out.sum(2), 1.0, rtol=1e-5)
+    # the marginal of variable v by brute force over all assignments
+    import itertools
+    grid = np.array(list(itertools.product(range(4), repeat=5)), np.uint8)
+    p = np.exp(orc.forward(fc, grid)[:, -1].astype(np.float64))
+    for v in range(5):
+        want = np.array([p[grid[:, v] == c].sum() for c in range(4)])
+        np.testing.assert_allclose(out[0, v], want, rtol=1e-4)
