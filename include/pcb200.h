@@ -285,6 +285,16 @@ int32_t pcb_cond_td_prob(pcb_circuit* c, pcb_workspace* ws, const int32_t* marke
                          const int32_t* marked_cat_dev, const float* node_probs_dev, uint32_t S, uint32_t Z1,
                          float* out_dev, pcb_stream s);
 
+/* ---- structure learning input ------------------------------------------------------------ */
+/* pairwise_MI_chunked (utils/information.jl:3-157): mutual information of every pair of the
+ * num_vars categorical columns of data_dev ([num_rows, num_vars] uint8, column-major, values below
+ * num_cats, a power of two up to 256), with the pseudocount spread over the joint and the single
+ * tables as the reference does; mi_dev [num_vars, num_vars] (symmetric).  No circuit is involved:
+ * the call runs on the current device, allocates its scratch itself and returns when the result is
+ * there. */
+int32_t pcb_pairwise_mi(const uint8_t* data_dev, uint64_t num_rows, uint32_t num_vars, uint32_t num_cats,
+                        float pseudocount, float* mi_dev, pcb_stream s);
+
 /* ---- multi-GPU ---------------------------------------------------------------------- */
 /* One NCCL communicator per process; pcb_em_step then sums [edge_aggr | leaf flows | LL]
  * over ranks before the replicated update.  The reference has no counterpart (it runs one

@@ -73,6 +73,7 @@ SIGNATURES = {
     "pcb_sample_hard_static": [_vp, _vp, _u32, _vp, _vp, _u32, _vp, _vp],
     "pcb_sample_soft": [_vp, _vp, _vp, _u32, _vp, _f32, _u32, _vp, _vp],
     "pcb_cond_td_prob": [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _vp, _vp],
+    "pcb_pairwise_mi": [_vp, _u64, _u32, _u32, _f32, _vp, _vp],
     "pcb_comm_unique_id": [_vp],
     "pcb_comm_init": [_vp, _vp, _i32, _i32],
     "pcb_comm_destroy": [_vp],

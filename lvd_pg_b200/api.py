@@ -399,6 +399,30 @@ def conditioned_td_prob(mbpc: CuMetaBitsProbCircuit, marked_var: torch.Tensor, m
     return out
 
 
+def pairwise_mi(data, num_cats: int, pseudocount: float = 0.1, device: int = 0) -> torch.Tensor:
+    """`pairwise_MI_chunked(data; num_cats, pseudocount)` (utils/information.jl:98-157): the [V, V] matrix of
+    pairwise mutual information of the columns of `data` ([rows, V] uint8), computed on the tensor cores."""
+    if not torch.cuda.is_available():
+        raise _lib.PcbError(-1, "pcb200 needs a CUDA device; there is no CPU fallback")
+    dev = torch.device("cuda", device)
+    d = data if isinstance(data, DeviceData) else DeviceData(data, dev)
+    V = d.num_vars
+    out = torch.empty((V, V), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().pcb_pairwise_mi(_ptr(d.t), d.num_rows, V, num_cats, pseudocount, _ptr(out), _stream(dev)))
+    return out
+
+
+def learn_chow_liu_tree(data, num_cats: int, pseudocount: float = 0.1, device: int = 0) -> np.ndarray:
+    """The Chow-Liu tree of `data` as hclt() builds it (structures/hclts.jl:4-40, customizable_hclt.jl:106-126):
+    pairwise MI on the GPU, maximum spanning tree and rooting at the tree's centre on the host; returns
+    parent[v] (-1 at the root), the input of `structures.hclt_flat`."""
+    from . import structures as st
+    mi = pairwise_mi(data, num_cats, pseudocount, device).cpu().numpy().astype(np.float64)
+    v = mi.shape[0]
+    return st.root_tree_at_center(v, st.max_spanning_tree(mi))
+
+
 class CuMultiHeadBitsProbCircuit(CuMetaBitsProbCircuit):
     """`CuMultiHeadBitsProbCircuit(pcs)` (src-jl/multi_head_pc/bit_circuit.jl:4-56): several heads over
     shared sub-circuits, held as one flat circuit under a fake root whose edges no top-down pass follows."""

@@ -446,6 +446,15 @@ function conditioned_td_prob(c::PcbCircuit, marked1::CuVector{Int32}, marked2::C
     out
 end
 
+"pairwise_MI_chunked(data; num_cats, pseudocount) — utils/information.jl:98-157, as one call on the tensor cores"
+function pairwise_MI(data::CuMatrix{UInt8}; num_cats = Int(maximum(data)) + 1, pseudocount = 0.1f0, kwargs...)
+    v = size(data, 2)
+    mi = CUDA.zeros(Float32, v, v)
+    check(ccall((:pcb_pairwise_mi, libpcb200), Int32, (CuPtr{UInt8}, UInt64, UInt32, UInt32, Cfloat, CuPtr{Cfloat}, Ptr{Cvoid}),
+                data, size(data, 1), v, num_cats, pseudocount, mi, stream()))
+    mi
+end
+
 # ---- multi-head circuits (src-jl/multi_head_pc) ---------------------------------------------------------
 """
 CuMultiHeadBitsProbCircuit(pcs) — bit_circuit.jl:4-56: the heads under a fake root whose edges carry
