@@ -339,6 +339,14 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
       const uint32_t third = kind[n] == PCB_INPUT ? node2input[n] : n_pid0[n];
       const uint32_t reg = region[n] == PCB_NONE ? 0x3fffffffu : region[n];
       sn[n] = make_uint4(estart[n], ecount[n], third, (uint32_t)kind[n] | (reg << 2));
+      if (kind[n] == PCB_INPUT) {
+        // a leaf has no edges: the two words carry its parameter offset and categories | variable << 16, so that
+        // the sampler's walk needs no second record (0xffffffff: too large to pack, read s_leaf)
+        const uint32_t i = node2input[n];
+        const bool fits = in_poff[i] < 0xffffffffull && in_cats[i] < 65536u && in_var[i] < 65536u;
+        sn[n].x = fits ? (uint32_t)in_poff[i] : 0xffffffffu;
+        sn[n].y = fits ? (in_cats[i] | (in_var[i] << 16)) : 0u;
+      }
     }
     for (uint32_t i = 0; i < NI; ++i)
       sl[i] = make_uint4((uint32_t)(in_poff[i] & 0xffffffffu), (uint32_t)(in_poff[i] >> 32), in_cats[i], in_var[i]);

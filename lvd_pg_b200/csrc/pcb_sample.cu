@@ -79,9 +79,13 @@ __global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params,
     const uint4 nm = s_node[n];             // one load instead of kind / edge range / parameter id / region
     const uint8_t kd = (uint8_t)(nm.w & 3u);
     if (kd == PCB_INPUT) {
-      const uint4 lm = s_leaf[nm.z];
-      uint32_t C = lm.z, var = lm.w;
-      uint64_t off = (uint64_t)lm.x | ((uint64_t)lm.y << 32);
+      uint32_t C = nm.y & 0xffffu, var = nm.y >> 16;
+      uint64_t off = nm.x;
+      if (nm.x == 0xffffffffu) {   // a leaf whose record did not fit the node's own
+        const uint4 lm = s_leaf[nm.z];
+        C = lm.z; var = lm.w;
+        off = (uint64_t)lm.x | ((uint64_t)lm.y << 32);
+      }
       const float* us = u_leaf + ((size_t)s * V + var) * cmax;
       double best = 0.0;
       uint32_t bi = 0xffffffffu;
@@ -119,13 +123,25 @@ __global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params,
       const float* us = u_sum + ((size_t)s * R + (nm.w >> 2)) * kmax;
       double best = 0.0;
       uint32_t bi = 0xffffffffu;
+      // the children of this lane's first two edges are fetched with the parameters, not after the
+      // arg-max: one dependent load less on the walk's chain
+      uint32_t pr0 = PCB_NONE, sb0 = PCB_NONE, pr1 = PCB_NONE, sb1 = PCB_NONE;
+      if (lane < cnt) { pr0 = e_prime[e0 + lane]; sb0 = e_sub[e0 + lane]; }
+      if (lane + 32 < cnt) { pr1 = e_prime[e0 + lane + 32]; sb1 = e_sub[e0 + lane + 32]; }
       for (uint32_t j = lane; j < cnt; j += 32) {
         double key = pcb_gumbel_key(params[ps + pld * (size_t)(pid0 + j)], us[j]);
         if (bi == 0xffffffffu || key > best) { best = key; bi = j; }
       }
       warp_argmax(best, bi);
-      uint32_t e = e0 + bi;
-      uint32_t pr = e_prime[e], sb = e_sub[e];
+      uint32_t pr, sb;
+      if (bi < 64) {
+        const uint32_t src = bi & 31u;
+        const uint32_t a = __shfl_sync(0xffffffffu, bi < 32 ? pr0 : pr1, src);
+        const uint32_t b = __shfl_sync(0xffffffffu, bi < 32 ? sb0 : sb1, src);
+        pr = a; sb = b;
+      } else {
+        pr = e_prime[e0 + bi]; sb = e_sub[e0 + bi];
+      }
       uint32_t pushes = sb != PCB_NONE ? 2 : 1;
       if (sp + pushes > stack_cap) {
         if (lane == 0) atomicMax(status, 1);
