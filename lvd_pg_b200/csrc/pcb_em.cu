@@ -381,7 +381,6 @@ __global__ void __launch_bounds__(LST) leaf_flow_sorted_kernel(
     if (x <= miss_bin) perm[atomicAdd(&cursor[x], 1u)] = (uint16_t)b;
   }
   __syncthreads();
-  const bool whole = gridDim.y == 1;
   bool ok = true;
   for (uint32_t l = 0; l < nl; ++l) {
     const uint32_t i = linputs[l0 + l];
@@ -398,9 +397,10 @@ __global__ void __launch_bounds__(LST) leaf_flow_sorted_kernel(
         const uint32_t j1 = binoff[x + 1];
         if (weights) for (uint32_t j = binoff[x]; j < j1; ++j) acc += row[perm[j]] * wsm[perm[j]];
         else         for (uint32_t j = binoff[x]; j < j1; ++j) acc += row[perm[j]];
-        if (acc != 0.0f) {
-          if (whole) aggr[fo + slot] += acc; else atomicAdd(aggr + fo + slot, acc);
-        }
+        // one reduction per slot and block, never read back here: a fire-and-forget RED keeps the
+        // round trip of a read-modify-write off the loop (with one block per group it is the only
+        // addition to its address, so the sum does not depend on any order)
+        if (acc != 0.0f) atomicAdd(aggr + fo + slot, acc);
       }
     }
     __syncthreads();   // the buffer has been read by everyone
