@@ -79,6 +79,7 @@ struct MnArgs {
 
 // Timing stamps exist only in a build with -DPCB_DIAG; the default build compiles them out.
 #ifdef PCB_DIAG
+__device__ int g_mn_halfw;   // timing experiments (results are wrong): 1 half of every weight chunk, 2 no row loads in the K loop, 4 no maximum pass
 #define MN_TRACE(slot)                                                                                   \
   do {                                                                                                   \
     if (a.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[(MODE == MN_FWD ? 0 : 256) + (slot)] = gtime(); \
@@ -280,7 +281,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
       // The child rows come by bulk copies, three chunks per round (slot of 16 KB per chunk: [16 prime
       // rows | 16 sub rows]), two rounds in flight through the still idle 96 KB; warp w reads rows w
       // and w + 8 of every chunk.  The K loop reads the rows again, from L2.
-      const uint32_t nrounds = (nchunks + MAXP_CHUNKS - 1) / MAXP_CHUNKS;
+      uint32_t nrounds = (nchunks + MAXP_CHUNKS - 1) / MAXP_CHUNKS;
+#ifdef PCB_DIAG
+      if (g_mn_halfw & 4) nrounds = 1;
+#endif
       auto issue_round = [&](uint32_t R) {   // called by every producer thread (one barrier inside)
         asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");   // the slots' readers are done
         if (tid == 0) {
@@ -351,6 +355,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
                               ((lane & 1u) << 4);
         struct Regs { float4 x[2], y[2]; };
         auto load = [&](uint32_t i, Regs& r) {
+#ifdef PCB_DIAG
+          if ((g_mn_halfw & 2) && i > 0) return;
+#endif
 #pragma unroll
           for (uint32_t ps = 0; ps < 2; ++ps) {
             const uint32_t t = i * KC + ps * 8u + warp;
@@ -556,9 +563,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
         uint8_t* dst = wring + sb * 2u * w_part;
         const float* src = img_tile + (size_t)i * 2 * img_rows * KC;   // hi part, then lo part img_rows x 16 floats later
         if (i < 32) MN_TRACE(128 + i);   // copies of chunk i issued
-        mbar_arrive_expect_tx(&wfull[sb], 2u * w_part);
-        bulk_g2s(dst, src, w_part, &wfull[sb]);
-        bulk_g2s(dst + w_part, src + (size_t)img_rows * KC, w_part, &wfull[sb]);
+#ifdef PCB_DIAG
+        const uint32_t wb = (g_mn_halfw & 1) ? w_part / 2 : w_part;
+#else
+        const uint32_t wb = w_part;
+#endif
+        mbar_arrive_expect_tx(&wfull[sb], 2u * wb);
+        bulk_g2s(dst, src, wb, &wfull[sb]);
+        bulk_g2s(dst + w_part, src + (size_t)img_rows * KC, wb, &wfull[sb]);
         issued = i + 1;
       }
       if (issued < nchunks) {
@@ -598,7 +610,15 @@ int32_t launch(dim3 grid, const pcb_workspace* ws, const MnArgs& args, cudaStrea
 #ifdef PCB_DIAG
 unsigned long long* g_mn_trace = nullptr;
 uint32_t g_mn_minz = 0, g_mn_maxz = 0xffffffffu;   // only launches with that many blocks are traced
+void mn_diag_switches() {
+  static bool done = false;
+  if (done) return;
+  done = true;
+  int v = getenv("PCB_MN_HALFW") ? atoi(getenv("PCB_MN_HALFW")) : 0;
+  cudaMemcpyToSymbol(g_mn_halfw, &v, sizeof(v));
+}
 unsigned long long* mn_trace() {
+  mn_diag_switches();
   if (!g_mn_trace && getenv("PCB_TC_TRACE")) {
     if (const char* e = getenv("PCB_TC_TRACE_MINZ")) g_mn_minz = (uint32_t)atoi(e);
     if (const char* e = getenv("PCB_TC_TRACE_MAXZ")) g_mn_maxz = (uint32_t)atoi(e);
