@@ -413,6 +413,8 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
     c->fwd_split = !flag("PCB_NO_FWD_SPLIT");
     c->bwd_split = !flag("PCB_NO_BWD_SPLIT");
     c->early_update = flag("PCB_EARLY_UPDATE");
+    c->sample_walk_warp = flag("PCB_SAMPLE_WALK_WARP");
+    c->sample_exact_keys = flag("PCB_SAMPLE_EXACT_KEYS");
     if (const char* e = getenv("PCB_LEAF_FLOW_IMPL")) c->leaf_flow_impl = !strcmp(e, "sorted") ? 2 : !strcmp(e, "atomic") ? 1 : 0;
     if (const char* e = getenv("PCB_TC_NSPLIT")) { int v = atoi(e); c->tc_nsplit = (v == 1 || v == 2 || v == 4) ? v : 0; }
     if (const char* e = getenv("PCB_TC_A_STAGES")) { int v = atoi(e); c->tc_a_stages = (v == 2 || v == 4 || v == 8) ? v : 0; }
@@ -534,7 +536,7 @@ extern "C" int32_t pcb_workspace_create(pcb_circuit* c, uint32_t max_batch, int3
     if (st != PCB_OK) { pcb_workspace_destroy(ws); return st; }
   }
   if (sets) {
-    int32_t st = pcb_ws_ensure_sets(ws, max_batch, true);
+    int32_t st = pcb_ws_ensure_sets(ws, max_batch, PCB_WS_NODES | PCB_WS_STACK | PCB_WS_EDGES);
     if (st != PCB_OK) { pcb_workspace_destroy(ws); return st; }
   }
   { std::lock_guard<std::mutex> g(c->ws_mu); c->workspaces.push_back(ws); }
@@ -542,27 +544,37 @@ extern "C" int32_t pcb_workspace_create(pcb_circuit* c, uint32_t max_batch, int3
   return PCB_OK;
 }
 
-int32_t pcb_ws_ensure_sets(pcb_workspace* ws, uint32_t S, bool need_stack) {
+int32_t pcb_ws_ensure_sets(pcb_workspace* ws, uint32_t S, int need) {
   pcb_circuit* c = ws->c;
-  if (S > ws->S_cap) {
-    for (void* p : {(void*)ws->klds, (void*)ws->grads, (void*)ws->eprob, (void*)ws->cum, (void*)ws->stack}) if (p) cudaFree(p);
-    ws->klds = ws->grads = ws->eprob = ws->cum = nullptr; ws->stack = nullptr;
+  PCB_CUDA(cudaSetDevice(c->device));
+  if ((need & (PCB_WS_NODES | PCB_WS_EDGES)) && S > ws->S_cap) {
+    for (void* p : {(void*)ws->klds, (void*)ws->grads, (void*)ws->eprob, (void*)ws->cum}) if (p) cudaFree(p);
+    ws->klds = ws->grads = ws->eprob = ws->cum = nullptr;
     ws->S_cap = S;
     // a handful of sets stays unpadded: the per-node values of neighbouring nodes then share 32-byte
     // sectors, which is what the gathers of a single-set KLD chain pay for
     ws->ldS = S <= 8 ? S : pcb_round_up(S, 32);
+    ws->have_kld = false;
+  }
+  if ((need & PCB_WS_NODES) && !ws->klds) {
     PCB_CUDA(cudaMalloc((void**)&ws->klds, (size_t)c->N * ws->ldS * sizeof(float)));
     PCB_CUDA(cudaMalloc((void**)&ws->grads, (size_t)c->N * ws->ldS * sizeof(float)));
     ws->have_kld = false;
   }
-  if (need_stack && !ws->stack) {
-    // a pending entry of the walk stands for a sub-circuit over a scope disjoint from the other
-    // pending ones, so V + 2 slots always suffice for a decomposable circuit
-    ws->stack_cap = c->V + 2;
-    PCB_CUDA(cudaMalloc((void**)&ws->stack, (size_t)ws->S_cap * ws->stack_cap * sizeof(uint32_t)));
+  if ((need & PCB_WS_EDGES) && !ws->eprob) {   // the relaxed sampler's per-edge and per-group matrices
     PCB_CUDA(cudaMalloc((void**)&ws->eprob, (size_t)std::max(1u, c->n_inner) * ws->ldS * sizeof(float)));
     PCB_CUDA(cudaMalloc((void**)&ws->cum, (size_t)std::max(1u, c->n_groups) * ws->ldS * sizeof(float)));
   }
+  // a pending entry of the walk stands for a sub-circuit over a scope disjoint from the other
+  // pending ones, so V + 2 slots always suffice for a decomposable circuit
+  ws->stack_cap = c->V + 2;
+  if ((need & PCB_WS_STACK) && S > ws->stack_S) {
+    if (ws->stack) cudaFree(ws->stack);
+    ws->stack = nullptr;
+    PCB_CUDA(cudaMalloc((void**)&ws->stack, (size_t)S * ws->stack_cap * sizeof(uint32_t)));
+    ws->stack_S = S;
+  }
+  if (!ws->sample_status) PCB_CUDA(cudaMalloc((void**)&ws->sample_status, sizeof(int32_t)));
   return PCB_OK;
 }
 
@@ -577,7 +589,7 @@ extern "C" int32_t pcb_workspace_destroy(pcb_workspace* ws) {
   if (ws->step_exec) cudaGraphExecDestroy(ws->step_exec);
   if (ws->kld_exec) cudaGraphExecDestroy(ws->kld_exec);
   for (void* p : {(void*)ws->mars, (void*)ws->flows, (void*)ws->blk_mx, (void*)ws->klds, (void*)ws->grads,
-                  (void*)ws->eprob, (void*)ws->cum, (void*)ws->stack, (void*)ws->ids_stage, (void*)ws->ll_tmp, (void*)ws->kld_g1,
+                  (void*)ws->eprob, (void*)ws->cum, (void*)ws->stack, (void*)ws->sample_status, (void*)ws->ids_stage, (void*)ws->ll_tmp, (void*)ws->kld_g1,
                   (void*)ws->kld_g2, (void*)ws->kld_t_dev})
     if (p) cudaFree(p);
   delete ws;

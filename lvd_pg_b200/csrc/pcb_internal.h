@@ -184,6 +184,8 @@ struct pcb_circuit {
   int tc_nsplit = 0;                         // 0 automatic, else 1 / 2 / 4 column splits of a dense tile
   int tc_a_stages = 0;                       // 0 automatic, else 2 / 4 / 8 stages of the dense kernels' A ring
   bool edge_ld = false;                      // edge statistics by the load-fed kernel instead of tensor-map copies
+  bool sample_walk_warp = false;             // hard sampling: one warp per sample (the stack walk) instead of one CTA
+  bool sample_exact_keys = false;            // hard sampling: every key in fp64 (cross-check of the fp32 pre-selection)
   // dense blocks [edge_lo, edge_hi) whose edge statistics are still to be launched, and the number
   // of tiles at which the range is launched
   uint32_t edge_lo = 0, edge_hi = 0, edge_batch_tiles = 592;
@@ -241,7 +243,8 @@ struct pcb_workspace {
   float soft_reg = 0.0f;
   uint32_t soft_width = 1;
   // per-parameter-set buffers, allocated on first use
-  uint32_t S_cap = 0, ldS = 0;
+  uint32_t S_cap = 0, ldS = 0, stack_S = 0;
+  int32_t* sample_status = nullptr;   // status word of the hard sampler's walk
   float* klds = nullptr;     // [N][ldS]
   float* grads = nullptr;    // [N][ldS]  (also td_probs)
   float* eprob = nullptr;    // [n_inner][ldS]
@@ -343,7 +346,10 @@ int32_t pcb_allreduce_aggr(pcb_circuit* c, cudaStream_t st);
 int32_t pcb_allreduce_range(pcb_circuit* c, uint64_t first, uint64_t count, cudaStream_t st);
 int32_t pcb_dense_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
 int32_t pcb_dense_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
-int32_t pcb_ws_ensure_sets(pcb_workspace* ws, uint32_t S, bool need_stack);
+// which of a workspace's per-set buffers a call needs: node matrices (klds / grads), the walk stacks of the
+// one-warp-per-sample sampler, the relaxed sampler's per-edge matrices
+enum { PCB_WS_NODES = 1, PCB_WS_STACK = 2, PCB_WS_EDGES = 4 };
+int32_t pcb_ws_ensure_sets(pcb_workspace* ws, uint32_t S, int need);
 int32_t pcb_dense_tc_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
 int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
 int32_t pcb_check_status(pcb_circuit* c);

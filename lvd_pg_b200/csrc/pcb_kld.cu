@@ -426,7 +426,7 @@ extern "C" int32_t pcb_kld(pcb_circuit* c, pcb_workspace* ws, const float* param
   PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
   PCB_REQUIRE(S >= 1, "no parameter sets");
   PCB_CUDA(cudaSetDevice(c->device));
-  int32_t st0 = pcb_ws_ensure_sets(ws, S, false);
+  int32_t st0 = pcb_ws_ensure_sets(ws, S, PCB_WS_NODES);
   if (st0 != PCB_OK) return st0;
   cudaStream_t st = (cudaStream_t)s;
   const uint32_t ld = ws->ldS;
@@ -830,7 +830,7 @@ extern "C" int32_t pcb_kld_adam_step(pcb_circuit* c, pcb_workspace* ws, float* t
   PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
   PCB_REQUIRE(t >= 1, "Adam step count starts at 1");
   PCB_CUDA(cudaSetDevice(c->device));
-  int32_t st0 = pcb_ws_ensure_sets(ws, 1, false);
+  int32_t st0 = pcb_ws_ensure_sets(ws, 1, PCB_WS_NODES);
   if (st0 != PCB_OK) return st0;
   cudaStream_t st = (cudaStream_t)s;
   if (!ws->kld_t_dev) {

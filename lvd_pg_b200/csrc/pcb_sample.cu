@@ -42,6 +42,50 @@ __device__ __forceinline__ void warp_argmax(double& key, uint32_t& idx) {
   }
 }
 
+// Arg-max of up to 64 Gumbel keys by one warp (entries `lane` and `lane + 32`), with the same result
+// as the fp64 arg-max above, bit for bit, at a fraction of its cost: every key is first evaluated in
+// fp32 together with a bound eps on its distance from the fp64 key; an entry whose upper bound lies
+// below the best lower bound cannot win and drops out.  Almost always a single candidate is left and
+// is the answer; otherwise the fp64 keys of the candidates alone decide (lowest index on ties, as
+// before: an entry that dropped out is strictly below the winner, so it takes no part in a tie).
+// Bound: x = u (1 - 1e-6) + 1e-6 carries a relative error <= 2.4e-7 in fp32, so inner = -log x is off
+// by <= 2.4e-7 (1 + inner) + 1 ulp, g = -log inner by that over inner plus 1 ulp, the sum by 1 ulp more;
+// eps takes four times the total.  Entries whose inner is below 1e-4 (u within 1e-4 of one, where the
+// relative error of inner is no longer small) always stay candidates.
+__device__ __forceinline__ void key32(float lp, float u, float& key, float& eps) {
+  const float x = fmaf(u, 0.999999f, 1e-6f);
+  const float inner = -logf(x);
+  const float g = -logf(inner);
+  key = lp + g;
+  eps = inner < 1e-4f ? INFINITY : 1e-6f * (1.0f / inner + 2.0f + fabsf(g) + fabsf(lp));
+  if (lp == -INFINITY) { key = -INFINITY; eps = 0.0f; }
+}
+__device__ __forceinline__ uint32_t warp_select64(float lp0, float u0, bool v0, float lp1, float u1, bool v1, uint32_t lane,
+                                                  bool exact) {
+  float k0 = -INFINITY, e0 = 0.0f, k1 = -INFINITY, e1 = 0.0f;
+  if (v0) key32(lp0, u0, k0, e0);
+  if (v1) key32(lp1, u1, k1, e1);
+  if (exact) { e0 = INFINITY; e1 = INFINITY; }   // cross-check switch: every entry stays a candidate, fp64 decides
+  // best lower bound over the warp
+  float lo = fmaxf(v0 ? k0 - e0 : -INFINITY, v1 ? k1 - e1 : -INFINITY);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) lo = fmaxf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+  const bool all_impossible = lo == -INFINITY;            // every key is -inf (or unbounded): decide in fp64
+  const bool c0 = v0 && (all_impossible || k0 + e0 >= lo);
+  const bool c1 = v1 && (all_impossible || k1 + e1 >= lo);
+  const uint32_t b0 = __ballot_sync(0xffffffffu, c0), b1 = __ballot_sync(0xffffffffu, c1);
+  if (__popc(b0) + __popc(b1) == 1) return b0 ? (uint32_t)__ffs(b0) - 1u : 32u + (uint32_t)__ffs(b1) - 1u;
+  double best = 0.0;
+  uint32_t bi = 0xffffffffu;
+  if (c0) { best = pcb_gumbel_key(lp0, u0); bi = lane; }
+  if (c1) {
+    const double key = pcb_gumbel_key(lp1, u1);
+    if (bi == 0xffffffffu || key > best) { best = key; bi = lane + 32; }
+  }
+  warp_argmax(best, bi);
+  return bi;
+}
+
 // status word: 0 ok, 1 stack overflow, 2 iteration limit (malformed circuit)
 __global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params, uint32_t Sp,
                                    const float* __restrict__ u_sum, const float* __restrict__ u_leaf, uint32_t R,
@@ -55,7 +99,7 @@ __global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params,
                                    const float* __restrict__ theta, uint32_t* __restrict__ stack_all,
                                    uint32_t stack_cap, int32_t* __restrict__ x_out, int32_t* __restrict__ status,
                                    uint32_t smem_stack, const uint4* __restrict__ s_node,
-                                   const uint4* __restrict__ s_leaf) {
+                                   const uint4* __restrict__ s_leaf, bool exact) {
   extern __shared__ uint32_t sstack[];   // [warps per block][stack_cap] when smem_stack is set
   const uint32_t s = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t lane = threadIdx.x & 31;
@@ -89,13 +133,20 @@ __global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params,
       const float* us = u_leaf + ((size_t)s * V + var) * cmax;
       double best = 0.0;
       uint32_t bi = 0xffffffffu;
-      for (uint32_t c = lane; c < C; c += 32) {
-        // fixed leaves keep their log-probs in the circuit, not in the caller's parameter matrix
-        float lp = off < P ? params[ps + pld * (off + c)] : theta[off + c];
-        double key = pcb_gumbel_key(lp, us[c]);
-        if (bi == 0xffffffffu || key > best) { best = key; bi = c; }
+      // fixed leaves keep their log-probs in the circuit, not in the caller's parameter matrix
+      if (C <= 64) {
+        const bool v0 = lane < C, v1 = lane + 32 < C;
+        auto lpa = [&](uint32_t c) { return off < P ? params[ps + pld * (off + c)] : theta[off + c]; };
+        bi = warp_select64(v0 ? lpa(lane) : 0.0f, v0 ? us[lane] : 0.0f, v0, v1 ? lpa(lane + 32) : 0.0f,
+                           v1 ? us[lane + 32] : 0.0f, v1, lane, exact);
+      } else {
+        for (uint32_t c = lane; c < C; c += 32) {
+          float lp = off < P ? params[ps + pld * (off + c)] : theta[off + c];
+          double key = pcb_gumbel_key(lp, us[c]);
+          if (bi == 0xffffffffu || key > best) { best = key; bi = c; }
+        }
+        warp_argmax(best, bi);
       }
-      warp_argmax(best, bi);
       if (lane == 0) x_out[s + (size_t)S * var] = (int32_t)bi;
     } else if (kd == PCB_PRODUCT) {
       uint32_t e0 = nm.x, cnt = nm.y;
@@ -128,11 +179,17 @@ __global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params,
       uint32_t pr0 = PCB_NONE, sb0 = PCB_NONE, pr1 = PCB_NONE, sb1 = PCB_NONE;
       if (lane < cnt) { pr0 = e_prime[e0 + lane]; sb0 = e_sub[e0 + lane]; }
       if (lane + 32 < cnt) { pr1 = e_prime[e0 + lane + 32]; sb1 = e_sub[e0 + lane + 32]; }
-      for (uint32_t j = lane; j < cnt; j += 32) {
-        double key = pcb_gumbel_key(params[ps + pld * (size_t)(pid0 + j)], us[j]);
-        if (bi == 0xffffffffu || key > best) { best = key; bi = j; }
+      if (cnt <= 64) {
+        const bool v0 = lane < cnt, v1 = lane + 32 < cnt;
+        bi = warp_select64(v0 ? params[ps + pld * (size_t)(pid0 + lane)] : 0.0f, v0 ? us[lane] : 0.0f, v0,
+                           v1 ? params[ps + pld * (size_t)(pid0 + lane + 32)] : 0.0f, v1 ? us[lane + 32] : 0.0f, v1, lane, exact);
+      } else {
+        for (uint32_t j = lane; j < cnt; j += 32) {
+          double key = pcb_gumbel_key(params[ps + pld * (size_t)(pid0 + j)], us[j]);
+          if (bi == 0xffffffffu || key > best) { best = key; bi = j; }
+        }
+        warp_argmax(best, bi);
       }
-      warp_argmax(best, bi);
       uint32_t pr, sb;
       if (bi < 64) {
         const uint32_t src = bi & 31u;
@@ -154,6 +211,122 @@ __global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params,
       sp += pushes;
       __syncwarp();
     }
+  }
+}
+
+// The same walk with one CTA per sample: the pending nodes of a sample are roots of sub-circuits over
+// disjoint scopes, so they are independent, and a single warp that visits them one after another
+// spends its time in the dependent loads of each visit (node record -> parameters and noise ->
+// children: ~1.8 us per visit, 1600 visits per sample at 784 variables).  Here the warps of the CTA
+// take the pending nodes of a round in parallel and push what they select to the next round's list
+// (two lists in shared memory, at most one pending node per variable, so V + 2 entries each); the
+// arg-max at a node is the same computation, so the samples are the same bit for bit.
+constexpr uint32_t CW = 4;   // warps per sample
+__global__ void __launch_bounds__(CW * 32) sample_hard_cta_kernel(
+    uint32_t S, const float* __restrict__ params, uint32_t Sp, const float* __restrict__ u_sum,
+    const float* __restrict__ u_leaf, uint32_t R, uint32_t kmax, uint32_t cmax, uint32_t V, uint32_t N,
+    const uint32_t* __restrict__ e_prime, const uint32_t* __restrict__ e_sub, uint64_t P, const float* __restrict__ theta,
+    uint32_t cap, int32_t* __restrict__ x_out, int32_t* __restrict__ status, const uint4* __restrict__ s_node,
+    const uint4* __restrict__ s_leaf, bool exact) {
+  extern __shared__ uint32_t lists[];   // [2][cap]
+  __shared__ uint32_t count[2];
+  const uint32_t s = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t ps = Sp == 1 ? 0 : s, pld = Sp;
+  for (uint32_t v = threadIdx.x; v < V; v += blockDim.x) x_out[s + (size_t)S * v] = -1;
+  if (threadIdx.x == 0) { lists[0] = N - 1; count[0] = 1; count[1] = 0; }
+  __syncthreads();
+  uint32_t cur = 0;
+  for (uint32_t round = 0;; ++round) {
+    const uint32_t n_cur = count[cur];
+    if (n_cur == 0) break;
+    if (round > N + 8u) {   // a circuit is at most N levels deep
+      if (threadIdx.x == 0) atomicMax(status, 2);
+      break;
+    }
+    __syncthreads();                       // every thread has read the count
+    if (threadIdx.x == 0) count[cur] = 0;  // this list is the next round's target after the one being filled
+    uint32_t* out = lists + (cur ^ 1u) * cap;
+    uint32_t* out_n = &count[cur ^ 1u];
+    for (uint32_t idx = warp; idx < n_cur; idx += CW) {
+      const uint32_t n = lists[cur * cap + idx];
+      const uint4 nm = s_node[n];
+      const uint8_t kd = (uint8_t)(nm.w & 3u);
+      if (kd == PCB_INPUT) {
+        uint32_t C = nm.y & 0xffffu, var = nm.y >> 16;
+        uint64_t off = nm.x;
+        if (nm.x == 0xffffffffu) {
+          const uint4 lm = s_leaf[nm.z];
+          C = lm.z; var = lm.w;
+          off = (uint64_t)lm.x | ((uint64_t)lm.y << 32);
+        }
+        const float* us = u_leaf + ((size_t)s * V + var) * cmax;
+        double best = 0.0;
+        uint32_t bi = 0xffffffffu;
+        if (C <= 64) {
+          const bool v0 = lane < C, v1 = lane + 32 < C;
+          auto lpa = [&](uint32_t c) { return off < P ? params[ps + pld * (off + c)] : theta[off + c]; };
+          bi = warp_select64(v0 ? lpa(lane) : 0.0f, v0 ? us[lane] : 0.0f, v0, v1 ? lpa(lane + 32) : 0.0f,
+                             v1 ? us[lane + 32] : 0.0f, v1, lane, exact);
+        } else {
+          for (uint32_t c = lane; c < C; c += 32) {
+            float lp = off < P ? params[ps + pld * (off + c)] : theta[off + c];
+            double key = pcb_gumbel_key(lp, us[c]);
+            if (bi == 0xffffffffu || key > best) { best = key; bi = c; }
+          }
+          warp_argmax(best, bi);
+        }
+        if (lane == 0) x_out[s + (size_t)S * var] = (int32_t)bi;
+      } else if (kd == PCB_PRODUCT) {
+        const uint32_t e0 = nm.x, cnt = nm.y;
+        for (uint32_t j = lane; j < cnt; j += 32) {
+          const uint32_t pr = e_prime[e0 + j], sb = e_sub[e0 + j];
+          const uint32_t np = sb != PCB_NONE ? 2u : 1u;
+          const uint32_t pos = atomicAdd(out_n, np);
+          if (pos + np > cap) { atomicMax(status, 1); continue; }
+          out[pos] = pr;
+          if (sb != PCB_NONE) out[pos + 1] = sb;
+        }
+      } else {
+        const uint32_t e0 = nm.x, cnt = nm.y, pid0 = nm.z;
+        const float* us = u_sum + ((size_t)s * R + (nm.w >> 2)) * kmax;
+        double best = 0.0;
+        uint32_t bi = 0xffffffffu;
+        uint32_t pr0 = PCB_NONE, sb0 = PCB_NONE, pr1 = PCB_NONE, sb1 = PCB_NONE;
+        if (lane < cnt) { pr0 = e_prime[e0 + lane]; sb0 = e_sub[e0 + lane]; }
+        if (lane + 32 < cnt) { pr1 = e_prime[e0 + lane + 32]; sb1 = e_sub[e0 + lane + 32]; }
+        if (cnt <= 64) {
+          const bool v0 = lane < cnt, v1 = lane + 32 < cnt;
+          bi = warp_select64(v0 ? params[ps + pld * (size_t)(pid0 + lane)] : 0.0f, v0 ? us[lane] : 0.0f, v0,
+                             v1 ? params[ps + pld * (size_t)(pid0 + lane + 32)] : 0.0f, v1 ? us[lane + 32] : 0.0f, v1, lane, exact);
+        } else {
+          for (uint32_t j = lane; j < cnt; j += 32) {
+            double key = pcb_gumbel_key(params[ps + pld * (size_t)(pid0 + j)], us[j]);
+            if (bi == 0xffffffffu || key > best) { best = key; bi = j; }
+          }
+          warp_argmax(best, bi);
+        }
+        uint32_t pr, sb;
+        if (bi < 64) {
+          const uint32_t src = bi & 31u;
+          pr = __shfl_sync(0xffffffffu, bi < 32 ? pr0 : pr1, src);
+          sb = __shfl_sync(0xffffffffu, bi < 32 ? sb0 : sb1, src);
+        } else {
+          pr = e_prime[e0 + bi]; sb = e_sub[e0 + bi];
+        }
+        if (lane == 0) {
+          const uint32_t np = sb != PCB_NONE ? 2u : 1u;
+          const uint32_t pos = atomicAdd(out_n, np);
+          if (pos + np > cap) {
+            atomicMax(status, 1);
+          } else {
+            out[pos] = pr;
+            if (sb != PCB_NONE) out[pos + 1] = sb;
+          }
+        }
+      }
+    }
+    __syncthreads();   // the next list is complete
+    cur ^= 1u;
   }
 }
 
@@ -229,11 +402,28 @@ extern "C" int32_t pcb_sample_hard(pcb_circuit* c, pcb_workspace* ws, const floa
   PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
   PCB_REQUIRE(S >= 1 && (Sp == 1 || Sp == S), "params must hold 1 or S parameter sets");
   PCB_CUDA(cudaSetDevice(c->device));
-  int32_t st0 = pcb_ws_ensure_sets(ws, S, true);
+  // one CTA per sample keeps its lists in shared memory; only the one-warp walk of a very wide circuit
+  // (or on request) needs stacks in global memory
+  const bool cta_walk = (size_t)2 * (c->V + 2) * 4 <= 40 * 1024 && !c->sample_walk_warp;
+  int32_t st0 = pcb_ws_ensure_sets(ws, S, cta_walk ? 0 : PCB_WS_STACK);
   if (st0 != PCB_OK) return st0;
   cudaStream_t st = (cudaStream_t)s;
-  int32_t* status = reinterpret_cast<int32_t*>(ws->cum);  // scratch word
+  int32_t* status = ws->sample_status;
   PCB_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
+  if (cta_walk) {
+    // one CTA per sample, its warps sharing the rounds of pending nodes
+    ++c->prof.launches[PCB_K_SAMPLE];
+    sample_hard_cta_kernel<<<S, CW * 32, (size_t)2 * ws->stack_cap * 4, st>>>(
+        S, params_dev, Sp, u_sum_dev, u_leaf_dev, c->n_regions, c->max_group, c->max_cats, c->V, c->N, c->e_prime, c->e_sub,
+        c->P, c->theta, ws->stack_cap, x_out_dev, status, c->s_node, c->s_leaf, c->sample_exact_keys);
+    PCB_CUDA(cudaGetLastError());
+    int32_t h0 = 0;
+    PCB_CUDA(cudaMemcpyAsync(&h0, status, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+    PCB_CUDA(cudaStreamSynchronize(st));
+    if (h0 == 1) return pcb_fail(PCB_ERR_TOO_LARGE, "sampling walk overflowed its lists (circuit not decomposable?)");
+    if (h0 == 2) return pcb_fail(PCB_ERR_INVALID, "sampling walk exceeded its round limit (malformed circuit)");
+    return PCB_OK;
+  }
   uint32_t warps_per_block = 4;
   while (warps_per_block > 1 && (size_t)warps_per_block * ws->stack_cap * 4 > 48 * 1024) warps_per_block /= 2;
   const size_t sm = (size_t)warps_per_block * ws->stack_cap * 4;
@@ -242,7 +432,8 @@ extern "C" int32_t pcb_sample_hard(pcb_circuit* c, pcb_workspace* ws, const floa
   sample_hard_kernel<<<(S + warps_per_block - 1) / warps_per_block, warps_per_block * 32, smem_stack ? sm : 0, st>>>(
       S, params_dev, Sp, u_sum_dev, u_leaf_dev, c->n_regions, c->max_group, c->max_cats, c->V, c->N, c->kind,
       c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime, c->e_sub, c->node2input, c->in_var, c->in_cats,
-      c->in_poff, c->P, c->theta, ws->stack, ws->stack_cap, x_out_dev, status, smem_stack, c->s_node, c->s_leaf);
+      c->in_poff, c->P, c->theta, ws->stack, ws->stack_cap, x_out_dev, status, smem_stack, c->s_node, c->s_leaf,
+      c->sample_exact_keys);
   PCB_CUDA(cudaGetLastError());
   int32_t h = 0;
   PCB_CUDA(cudaMemcpyAsync(&h, status, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
@@ -259,7 +450,7 @@ extern "C" int32_t pcb_sample_soft(pcb_circuit* c, pcb_workspace* ws, const floa
   PCB_REQUIRE(S >= 1 && (Sp == 1 || Sp == S), "params must hold 1 or S parameter sets");
   PCB_REQUIRE(temperature > 0.0f, "temperature must be positive");
   PCB_CUDA(cudaSetDevice(c->device));
-  int32_t st0 = pcb_ws_ensure_sets(ws, S, true);
+  int32_t st0 = pcb_ws_ensure_sets(ws, S, PCB_WS_NODES | PCB_WS_EDGES);
   if (st0 != PCB_OK) return st0;
   cudaStream_t st = (cudaStream_t)s;
   const uint32_t ld = ws->ldS;
@@ -329,7 +520,7 @@ extern "C" int32_t pcb_cond_td_prob(pcb_circuit* c, pcb_workspace* ws, const int
   PCB_REQUIRE(ws->c == c, "workspace belongs to another circuit");
   PCB_REQUIRE(S >= 1 && Z1 >= 1, "empty input");
   PCB_CUDA(cudaSetDevice(c->device));
-  int32_t st0 = pcb_ws_ensure_sets(ws, S, false);
+  int32_t st0 = pcb_ws_ensure_sets(ws, S, PCB_WS_NODES);
   if (st0 != PCB_OK) return st0;
   cudaStream_t st = (cudaStream_t)s;
   const uint32_t ld = ws->ldS;
@@ -423,7 +614,8 @@ extern "C" int32_t pcb_sample_hard_static(pcb_circuit* c, const float* params_de
   sample_hard_kernel<<<(S + warps_per_block - 1) / warps_per_block, warps_per_block * 32, smem_stack ? sm : 0, st>>>(
       S, params_dev, Sp, u_sum_dev, u_leaf_dev, c->n_regions, c->max_group, c->max_cats, c->V, c->N, c->kind,
       c->n_estart, c->n_ecount, c->n_pid0, c->n_region, c->e_prime, c->e_sub, c->node2input, c->in_var, c->in_cats,
-      c->in_poff, c->P, c->theta, scratch, (uint32_t)stack_cap, x_out_dev, status, smem_stack, c->s_node, c->s_leaf);
+      c->in_poff, c->P, c->theta, scratch, (uint32_t)stack_cap, x_out_dev, status, smem_stack, c->s_node, c->s_leaf,
+      c->sample_exact_keys);
   PCB_CUDA(cudaGetLastError());
   int32_t h = 0;
   PCB_CUDA(cudaMemcpyAsync(&h, status, sizeof(int32_t), cudaMemcpyDeviceToHost, st));

@@ -173,3 +173,48 @@ def test_soft_sampling_matches_oracle(oracle, noise):
     ref, aux = oracle.sample_soft(fc, params, u, 0.7, S, 3)
     assert rel_err(out, ref) <= TOL
     assert np.allclose(out.sum(2), 1.0, atol=1e-4)  # every variable's relaxed marginal sums to one
+
+
+def test_fp32_preselection_never_changes_a_sample():
+    """The hard sampler picks every arg-max from fp32 keys with an error bound and falls back to the fp64
+    keys only among the entries that bound cannot separate; PCB_SAMPLE_EXACT_KEYS=1 turns the bound off
+    (all keys in fp64).  Both must give the same samples: 32768 samples of the 784-variable circuit
+    (1.7e9 keys), uniform noise; then noise quantised to eighths on uniform parameters, where most
+    arg-maxes are exact ties that the lowest index has to win; then noise next to one and next to zero."""
+    import os
+    torch, api = _cuda()
+    from lvd_pg_b200 import synth
+    q, _ = synth.config4()
+    fast = api.CuMetaBitsProbCircuit(q, 0)
+    os.environ["PCB_SAMPLE_EXACT_KEYS"] = "1"
+    try:
+        exact = api.CuMetaBitsProbCircuit(q, 0)
+    finally:
+        del os.environ["PCB_SAMPLE_EXACT_KEYS"]
+    theta = torch.from_numpy(np.asarray(api.vectorize_parameters(fast), np.float32)).to(fast.device)
+    g = torch.Generator(device=fast.device).manual_seed(11)
+
+    def same(S, u_sum, u_leaf, params):
+        a = api.sample(fast, params, u_sum, u_leaf)
+        b = api.sample(exact, params, u_sum, u_leaf)
+        assert torch.equal(a, b)
+        return a
+
+    S = 32768
+    shp_s, shp_l = api.noise_shapes(fast, S)
+    u_sum = torch.rand(shp_s, generator=g, device=fast.device)
+    u_leaf = torch.rand(shp_l, generator=g, device=fast.device)
+    same(S, u_sum, u_leaf, theta)
+    del u_sum, u_leaf
+    S = 2048
+    shp_s, shp_l = api.noise_shapes(fast, S)
+    u_sum = torch.rand(shp_s, generator=g, device=fast.device)
+    u_leaf = torch.rand(shp_l, generator=g, device=fast.device)
+    flat = torch.zeros_like(theta)   # unnormalised, all equal: the keys differ by the noise alone
+    x = same(S, torch.floor(u_sum * 8) / 8, torch.floor(u_leaf * 8) / 8, flat)
+    assert int((x == 0).sum()) > 0
+    same(S, 1.0 - u_sum * 1e-6, 1.0 - u_leaf * 1e-6, theta)      # u next to one: inner = -log x next to zero
+    same(S, u_sum * 1e-6, u_leaf * 1e-6, theta)                  # u next to zero
+    tiny = theta.clone()
+    tiny[::3] = float("-inf")                                     # impossible edges and categories
+    same(S, u_sum, u_leaf, tiny)
