@@ -1,9 +1,13 @@
 // pcb_sample.cu — top-down sampling.
 //
-//  * pcb_sample_hard: Gumbel-max walk, one warp per sample.  At a sum node the lanes split the
-//    edges, each computes key = logp + g(u) in fp64 with the shared host/device routine of
-//    include/pcb200_gumbel.h, and a shuffle arg-max (lowest index on ties) picks the edge; a
-//    product node pushes all its children; a leaf does the same arg-max over its categories.
+//  * pcb_sample_hard: Gumbel-max walk.  At a sum node the lanes of a warp split the edges, the
+//    arg-max of key = logp + g(u) (lowest index on ties) picks the edge; a product node passes all
+//    its children on; a leaf does the same arg-max over its categories.  The keys that decide are
+//    fp64 values of the shared host/device routine of include/pcb200_gumbel.h; an fp32 evaluation
+//    with an error bound first removes the entries that cannot win (warp_select64).  One CTA per
+//    sample takes the pending nodes of a round in parallel (sample_hard_cta_kernel); one warp per
+//    sample with a stack (sample_hard_kernel) serves very wide circuits and the entry point that
+//    allocates nothing.
 //    This is the temperature -> 0 limit of the reference's relaxed sampler
 //    (VariationalJuice.jl/src/queries/sample.jl:8-148,233-296), fed with caller-supplied
 //    uniforms instead of the in-kernel rand(Float32) of sample.jl:45.
@@ -221,7 +225,10 @@ __global__ void sample_hard_kernel(uint32_t S, const float* __restrict__ params,
 // take the pending nodes of a round in parallel and push what they select to the next round's list
 // (two lists in shared memory, at most one pending node per variable, so V + 2 entries each); the
 // arg-max at a node is the same computation, so the samples are the same bit for bit.
-constexpr uint32_t CW = 4;   // warps per sample
+#ifndef PCB_SAMPLE_CTA_WARPS
+#define PCB_SAMPLE_CTA_WARPS 4
+#endif
+constexpr uint32_t CW = PCB_SAMPLE_CTA_WARPS;   // warps per sample
 __global__ void __launch_bounds__(CW * 32) sample_hard_cta_kernel(
     uint32_t S, const float* __restrict__ params, uint32_t Sp, const float* __restrict__ u_sum,
     const float* __restrict__ u_leaf, uint32_t R, uint32_t kmax, uint32_t cmax, uint32_t V, uint32_t N,
