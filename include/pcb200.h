@@ -191,8 +191,8 @@ int32_t pcb_em_step_ex(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence* ev
  * every sum edge divided by the flow of its node, and of every leaf parameter by its leaf's, as
  * log(flow / (sum + 1e-8) + 1e-8) (map_flows_kernel :496-528) and log(flow / sum)
  * (map_input_flows_kernel :549-593), written to out_dev [num_rows, P] column-major at the row's data
- * index.  params_dev = NULL: the circuit's own parameters (the call runs pcb_forward_ex and
- * pcb_backward on the workspace, statistics included); else [num_rows, P] log-parameters, one vector
+ * index.  params_dev = NULL: the circuit's own parameters (the call runs the forward and backward
+ * passes on the workspace; the statistics vector is not touched); else [num_rows, P] log-parameters, one vector
  * per data row (eval_circuit / flows_circuit with params, queries/likelihood.jl:119-302,
  * flow.jl:240-403).  Hard evidence without missing values, single-head circuits. */
 int32_t pcb_normalized_flows(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence* ev, const float* params_dev,

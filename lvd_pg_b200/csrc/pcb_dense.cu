@@ -295,6 +295,7 @@ int32_t pcb_dense_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cu
   uint32_t bt = (pcb_round_up(ws->B, 32) + TB - 1) / TB;
   dim3 grid(bt, (c->max_dense_K + TR - 1) / TR, o1 - o0);
   { PcbProfScope ps(c, st, PCB_K_DENSE_BWD_CHILD); dense_bwd_child_kernel<<<grid, NT, 0, st>>>(ws->flows, ws->mars, ws->blk_mx, ws->ld, c->dense + o0, c->theta); }
+  if (c->skip_stats) return PCB_OK;   // flows only
   uint32_t tiles = ((c->max_dense_R + ER - 1) / ER) * ((c->max_dense_K + ET - 1) / ET);
   // enough example slices to fill the GPU when the layer has few blocks
   uint32_t want = std::max(1u, (148u * 4u) / std::max(1u, tiles * (o1 - o0)));

@@ -961,10 +961,10 @@ int32_t pcb_dense_tc_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer,
   // Edge statistics: layers are visited top down and their blocks are stored layer after layer, so
   // consecutive layers extend one block range downwards.  The range is launched once it holds
   // enough tiles for a few waves of CTAs; most layers alone would fill only a few SMs.
-  if (c->edge_hi > c->edge_lo && c->edge_lo != o1) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
-  if (c->edge_hi <= c->edge_lo) c->edge_hi = o1;
-  c->edge_lo = o0;
-  {
+  if (!c->skip_stats) {
+    if (c->edge_hi > c->edge_lo && c->edge_lo != o1) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
+    if (c->edge_hi <= c->edge_lo) c->edge_hi = o1;
+    c->edge_lo = o0;
     uint32_t tiles = ((c->max_dense_R + TM - 1) / TM) * ((c->max_dense_K + TN_MAX - 1) / TN_MAX);
     if (!c->side || (c->edge_hi - c->edge_lo) * tiles >= c->edge_batch_tiles) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
   }

@@ -145,7 +145,7 @@ __global__ void sparse_down_kernel(float* __restrict__ flows, const float* __res
       }
       f.x *= __expf(child.x - pm.x); f.y *= __expf(child.y - pm.y);
       f.z *= __expf(child.z - pm.z); f.w *= __expf(child.w - pm.w);
-      if (en.flags & 1u) {
+      if (aggr && (en.flags & 1u)) {   // aggr == null: flows only (uniform over the grid)
         float s = warp_sum((a0 ? f.x : 0.0f) + (a1 ? f.y : 0.0f) + (a2 ? f.z : 0.0f) + (a3 ? f.w : 0.0f));
         if ((threadIdx.x & 31) == 0) atomicAdd(aggr + en.pid, s);
       }
@@ -822,7 +822,7 @@ static int32_t backward_impl(pcb_circuit* c, pcb_workspace* ws, const float* wei
     if (o1 > o0) {
       PcbProfScope ps(c, ss, PCB_K_SPARSE_DOWN);
       PCB_CUDA(pcb_launch_pdl(sparse_down_kernel, grid2v(o1 - o0, B), dim3(TPB), 0, ss, pdl, ws->flows, ws->mars, ws->ld,
-                              B, c->down_sparse + o0, c->N - 1, c->in_off, c->in_ent, c->theta, c->aggr, hi));
+                              B, c->down_sparse + o0, c->N - 1, c->in_off, c->in_ent, c->theta, c->skip_stats ? nullptr : c->aggr, hi));
     }
     return PCB_OK;
   };
@@ -846,7 +846,7 @@ static int32_t backward_impl(pcb_circuit* c, pcb_workspace* ws, const float* wei
       PCB_TRY(sparse_down(lay - 1, st, c->pdl));
     }
   }
-  if (c->use_tc) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
+  if (c->use_tc && !c->skip_stats) PCB_TRY(pcb_dense_tc_flush_edges(c, ws, st));
   if (split_comm) PCB_TRY(comm_edges_begin(c, st));
   if (early && c->side && c->use_tc && !c->prof.on) {
     // every edge statistic is final once this stream's kernels so far and the side stream's are done
@@ -857,7 +857,7 @@ static int32_t backward_impl(pcb_circuit* c, pcb_workspace* ws, const float* wei
     c->side_busy = true;
     early->done = true;
   }
-  if (c->n_inputs) {
+  if (c->n_inputs && !c->skip_stats) {
     PcbProfScope ps(c, st, PCB_K_LEAF_FLOW);
     // sorted segments pay off once a variable has enough values to keep a block's threads busy;
     // PCB_LEAF_FLOW_IMPL=atomic / sorted (read when the circuit is created) forces one of the two kernels

@@ -190,6 +190,7 @@ struct pcb_circuit {
   // of tiles at which the range is launched
   uint32_t edge_lo = 0, edge_hi = 0, edge_batch_tiles = 592;
   int* status = nullptr;
+  bool skip_stats = false;   // set around a backward pass that wants the flows only (no edge / leaf statistics)
 
   // ---- multi-GPU ----
   void* comm = nullptr;  // ncclComm_t

@@ -313,9 +313,12 @@ extern "C" int32_t pcb_normalized_flows(pcb_circuit* c, pcb_workspace* ws, const
   cudaStream_t st = (cudaStream_t)s;
   const Params p{params_dev, c->theta, ev->num_rows};
   if (!params_dev) {
-    // the circuit's own parameters: the ordinary passes (their statistics side effect included)
+    // the circuit's own parameters: the ordinary passes, flows only (the reference hands edge_aggr = nothing)
     PCB_TRY(pcb_forward_ex(c, ws, ev, nullptr, s));
-    PCB_TRY(pcb_backward(c, ws, nullptr, s));
+    c->skip_stats = true;
+    const int32_t rb = pcb_backward(c, ws, nullptr, s);
+    c->skip_stats = false;
+    PCB_TRY(rb);
   } else {
     ws->have_forward = false;
     ws->B = B; ws->data = ev->data_dev; ws->miss = ev->miss_dev; ws->num_rows = ev->num_rows;

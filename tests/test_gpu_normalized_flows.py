@@ -32,8 +32,11 @@ def test_normalized_flows_with_the_circuits_parameters(oracle, name, make, c, ro
     data, _ = random_data(rows, fc.num_vars, c, 4)
     m = api.CuMetaBitsProbCircuit(fc)
     want = oracle.per_sample_normalized_flows(fc, data)
+    aggr_before, heap_before = m.edge_aggr().copy(), m.heap().copy()
     got = api.per_sample_normalized_flows(m, data, batch_size=32).cpu().numpy()
     _compare(got, want)
+    # the call leaves the statistics alone (the reference hands edge_aggr = nothing)
+    assert np.array_equal(m.edge_aggr(), aggr_before) and np.array_equal(m.heap(), heap_before)
     _compare(api.per_sample_normalized_flows(m, data, batch_size=30).cpu().numpy(), want)   # a batch that ends inside a quad
     # every sum node's shares add up to one (up to the 1e-8 guards)
     ni = m.num_inner_params
