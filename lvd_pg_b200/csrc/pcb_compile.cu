@@ -589,8 +589,8 @@ extern "C" int32_t pcb_workspace_destroy(pcb_workspace* ws) {
   if (ws->step_exec) cudaGraphExecDestroy(ws->step_exec);
   if (ws->kld_exec) cudaGraphExecDestroy(ws->kld_exec);
   for (void* p : {(void*)ws->mars, (void*)ws->flows, (void*)ws->blk_mx, (void*)ws->klds, (void*)ws->grads,
-                  (void*)ws->eprob, (void*)ws->cum, (void*)ws->stack, (void*)ws->sample_status, (void*)ws->ids_stage, (void*)ws->ll_tmp, (void*)ws->kld_g1,
-                  (void*)ws->kld_g2, (void*)ws->kld_t_dev})
+                  (void*)ws->eprob, (void*)ws->cum, (void*)ws->stack, (void*)ws->sample_status, (void*)ws->ids_stage, (void*)ws->ll_tmp,
+                  (void*)ws->kld_t_dev})
     if (p) cudaFree(p);
   delete ws;
   return PCB_OK;

@@ -256,8 +256,6 @@ struct pcb_workspace {
   bool have_kld = false;
   // the fused KLD + gradient + Adam step (pcb_kld_adam_step): gradient buffers, the device word that
   // holds the step count, and the captured chain
-  float* kld_g1 = nullptr;
-  float* kld_g2 = nullptr;
   int* kld_t_dev = nullptr;
   int* kld_bump = nullptr;   // set while the fused step runs: the leaf kernel counts the step here
   int32_t kld_t_host = -1;
