@@ -306,6 +306,20 @@ int32_t pcb_comm_destroy(pcb_circuit* c);
  * updates from its own statistics).  For measuring how much of a step the communication leaves
  * exposed; not for training. */
 int32_t pcb_comm_set_enabled(pcb_circuit* c, int32_t enabled);
+/* Failure handling of the collective, all on the host; none of these waits on the device without a
+ * limit.  pcb_comm_poll asks NCCL for an asynchronous error of the communicator (a peer that died,
+ * a network fault) and returns PCB_ERR_NCCL with its text.  pcb_comm_wait is the bounded
+ * counterpart of a stream synchronisation: it polls the stream `s` and the communicator every
+ * 200 us until the stream has drained (PCB_OK), and on an asynchronous error or after timeout_ms
+ * it aborts the communicator and returns PCB_ERR_NCCL.  pcb_comm_abort ends the communicator
+ * without waiting for its collectives (ncclCommAbort: a collective in flight returns early, its
+ * output is undefined); afterwards pcb_em_step returns PCB_ERR_STATE until pcb_comm_destroy has been
+ * called, after which the circuit trains alone or takes a new communicator.  A training loop that
+ * wants ranks to learn of a lost peer BEFORE they launch the next collective keeps a heartbeat on
+ * the host (the Python mirror's RankWatch). */
+int32_t pcb_comm_poll(pcb_circuit* c);
+int32_t pcb_comm_wait(pcb_circuit* c, pcb_stream s, uint32_t timeout_ms);
+int32_t pcb_comm_abort(pcb_circuit* c);
 
 /* ---- launch accounting ---------------------------------------------------------------- */
 /* The library counts its kernel launches per kernel class; with profiling enabled every launch
@@ -318,6 +332,17 @@ int32_t pcb_profile_num_classes(void);
 const char* pcb_profile_class_name(int32_t i);
 int32_t pcb_profile_enable(pcb_circuit* c, int32_t on);
 int32_t pcb_profile_read(pcb_circuit* c, double* ms_out, uint64_t* launches_out, int32_t reset);
+
+/* ---- self-test of the bounded device waits ----------------------------------------------- */
+/* Every mbarrier wait of the tensor-core kernels gives up after a fixed number of polls, raises the
+ * circuit's status word (pcb_circuit_status) and lets the kernel drain and return.  This call runs
+ * that wait on `device` on a barrier that nothing arrives at, limited to `polls` polls (at most 2^20):
+ * *status_out = 1 (the word a circuit would report), *after_out = 2 (the kernel went on past the
+ * lost wait and returned), *ms_out = the kernel's duration, *production_polls_out (may be NULL) =
+ * the limit the production kernels use, so ms * production_polls / polls is how long a lost signal
+ * holds a kernel.  The context stays usable.  No counterpart in the reference. */
+int32_t pcb_selftest_wait_limit(int32_t device, uint32_t polls, int32_t* status_out, int32_t* after_out,
+                                float* ms_out, uint32_t* production_polls_out);
 
 /* ---- diagnostics -------------------------------------------------------------------------- */
 /* Only in a library built with -DPCB_DIAG and with PCB_TC_TRACE set in the environment, CTA (0,0,0)

@@ -78,6 +78,10 @@ SIGNATURES = {
     "pcb_comm_init": [_vp, _vp, _i32, _i32],
     "pcb_comm_destroy": [_vp],
     "pcb_comm_set_enabled": [_vp, _i32],
+    "pcb_selftest_wait_limit": [_i32, _u32, C.POINTER(_i32), C.POINTER(_i32), C.POINTER(_f32), C.POINTER(_u32)],
+    "pcb_comm_poll": [_vp],
+    "pcb_comm_wait": [_vp, _vp, _u32],
+    "pcb_comm_abort": [_vp],
     "pcb_profile_num_classes": [],
     "pcb_profile_enable": [_vp, _i32],
     "pcb_profile_read": [_vp, _vp, _vp, _i32],

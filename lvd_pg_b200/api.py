@@ -174,6 +174,21 @@ class CuMetaBitsProbCircuit:
         """Drop the communicator: later steps run on this GPU alone."""
         _lib.check(self.lib.pcb_comm_destroy(self.handle))
 
+    def comm_poll(self):
+        """Raise if NCCL reports an asynchronous error of the communicator."""
+        _lib.check(self.lib.pcb_comm_poll(self.handle))
+
+    def comm_wait(self, timeout_s: float, stream=None):
+        """Bounded replacement for `torch.cuda.synchronize()` after steps with a collective: returns
+        when the stream has drained; on an NCCL error or after `timeout_s` the communicator is
+        aborted and a PcbError raised (then `detach_comm()` before the next step)."""
+        st = torch.cuda.current_stream(self.device) if stream is None else stream
+        _lib.check(self.lib.pcb_comm_wait(self.handle, C.c_void_p(st.cuda_stream), int(timeout_s * 1000)))
+
+    def comm_abort(self):
+        """End the communicator without waiting for its collectives."""
+        _lib.check(self.lib.pcb_comm_abort(self.handle))
+
 
 def comm_unique_id() -> bytes:
     buf = (C.c_uint8 * 128)()

@@ -11,7 +11,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libpcb200.so")
-SOURCES = ["pcb_compile.cu", "pcb_em.cu", "pcb_dense.cu", "pcb_dense_tc.cu", "pcb_dense_mn.cu", "pcb_dense_edge.cu", "pcb_kld.cu", "pcb_sample.cu", "pcb_comm.cu", "pcb_persample.cu", "pcb_mi.cu"]
+SOURCES = ["pcb_compile.cu", "pcb_em.cu", "pcb_dense.cu", "pcb_dense_tc.cu", "pcb_dense_mn.cu", "pcb_dense_edge.cu", "pcb_kld.cu", "pcb_sample.cu", "pcb_comm.cu", "pcb_persample.cu", "pcb_mi.cu", "pcb_selftest.cu"]
 NVCC = os.environ.get("PCB_NVCC", "/usr/local/cuda/bin/nvcc")
 EXTRA = shlex.split(os.environ.get("PCB_NVCC_FLAGS", ""))   # e.g. -DPCB_DIAG for the timing-experiment build
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",

@@ -966,6 +966,8 @@ static int32_t em_step_impl(pcb_circuit* c, pcb_workspace* ws, pcb_evidence ev, 
   const uint32_t B = ev.B;
   PCB_REQUIRE(B >= 1 && B <= ws->max_batch, "batch size exceeds the workspace");
   PCB_REQUIRE(!c->n_heads || ev.head_mask_dev, "the flows of a multi-head circuit need a head mask");
+  if (c->comm_lost)
+    return pcb_fail(PCB_ERR_STATE, "the communicator was aborted: pcb_comm_destroy, then attach a new one or train alone");
   PCB_CUDA(cudaSetDevice(c->device));
   if (c->n_heads && !ws->ll_tmp) PCB_CUDA(cudaMalloc(&ws->ll_tmp, (size_t)ws->max_batch * sizeof(float)));
   const uint8_t* data_dev = ev.data_dev;

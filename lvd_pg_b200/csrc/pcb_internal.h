@@ -195,6 +195,7 @@ struct pcb_circuit {
   // ---- multi-GPU ----
   void* comm = nullptr;  // ncclComm_t
   int nranks = 1, rank = 0;
+  bool comm_lost = false;                // pcb_comm_abort ran: steps refuse until the communicator is destroyed
   bool comm_enabled = true;             // false: the step skips its collectives (timing of the exposed share only)
   bool comm_split = false;              // edge statistics summed on comm_stream while the leaf statistics are still formed
   cudaStream_t comm_stream = nullptr;   // created with the communicator

@@ -40,9 +40,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// bounded wait: false (and status raised) when the phase did not complete in time
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status) {
-  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+// bounded wait: false (and status raised) when the phase did not complete within `limit` polls
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, uint32_t limit = WAIT_LIMIT) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   atomicExch(status, 1);

@@ -527,6 +527,18 @@ comm_destroy(c::PcbCircuit) = check(ccall((:pcb_comm_destroy, libpcb200), Int32,
 "enabled = false skips the step's collectives (to time what they leave exposed; not for training)"
 comm_set_enabled(c::PcbCircuit, enabled::Bool) =
     check(ccall((:pcb_comm_set_enabled, libpcb200), Int32, (Ptr{Cvoid}, Int32), c.handle, enabled ? 1 : 0))
+"throws when NCCL reports an asynchronous error of the communicator (a lost peer, a network fault)"
+comm_poll(c::PcbCircuit) = check(ccall((:pcb_comm_poll, libpcb200), Int32, (Ptr{Cvoid},), c.handle))
+"""
+comm_wait(c; timeout_s, stream) — the bounded counterpart of CUDA.synchronize() after steps with a collective:
+returns when the stream has drained; on an NCCL error or after `timeout_s` the communicator is aborted and an
+error thrown (call comm_destroy before the next step).
+"""
+comm_wait(c::PcbCircuit; timeout_s::Real = 60, stream = stream()) =
+    check(ccall((:pcb_comm_wait, libpcb200), Int32, (Ptr{Cvoid}, Ptr{Cvoid}, UInt32), c.handle, stream,
+                round(UInt32, 1000 * timeout_s)))
+"ends the communicator without waiting for its collectives"
+comm_abort(c::PcbCircuit) = check(ccall((:pcb_comm_abort, libpcb200), Int32, (Ptr{Cvoid},), c.handle))
 
 """
 sample(mbpc, params, U_sum, U_leaf) — hard Gumbel-max sampling with caller-supplied uniforms.
