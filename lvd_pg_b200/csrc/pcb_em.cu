@@ -306,16 +306,22 @@ __global__ void __launch_bounds__(LTH) leaf_flow_chunk_kernel(
   }
 }
 
-// Leaf statistics without atomics on the histogram: the examples of the block's slice are sorted
-// by the variable's value once (counting sort in shared memory: `perm` lists the examples value by
-// value, `binoff` delimits each value's segment), then every leaf row of the group streams through
-// a three-deep ring of shared-memory buffers (one bulk copy per row) and thread x sums its
-// segment  sum_j row[perm[j]]  and adds it to slot x of the leaf.  A missing value sorts into the
+// Leaf statistics by sorted examples: the examples of the block's slice are sorted by the
+// variable's value once (counting sort in shared memory), and every thread keeps LSE consecutive
+// positions of the sorted order in registers for the whole group: the example behind each position,
+// its value segment and (if given) its weight.  Then every leaf row of the group streams through a
+// three-deep ring of shared-memory buffers (one bulk copy per row); a thread gathers its LSE values
+// (independent loads, the same work for every thread whatever the histogram of the values looks
+// like), sums runs of equal segment in registers and adds one partial sum per run to the row's
+// shared-memory histogram; after the barrier the histogram leaves with one RED per slot while the
+// next row is already being gathered into the other histogram.  A missing value sorts into the
 // extra segment C.  The group's leaves share one variable, so one sort serves up to 64 rows.
 constexpr int LSB = 2048;   // examples per block slice
-constexpr int LST = 256;    // threads; also the number of value segments a pass of the block covers
-constexpr int LSR = 3;      // row buffers
+constexpr int LST = 256;    // threads
+constexpr int LSE = LSB / LST;   // sorted positions per thread
+constexpr int LSR = 4;      // row buffers; the last one holds the sort's arrays until the sort is done
 constexpr int LSC = 508;    // most categories of a variable (static + dynamic shared memory stay under 48 KB)
+template <bool WEIGHTED>
 __global__ void __launch_bounds__(LST) leaf_flow_sorted_kernel(
     const float* __restrict__ flows, uint32_t ld, uint32_t B, float* __restrict__ aggr,
     const uint32_t* __restrict__ in_node, const uint32_t* __restrict__ in_cats, const uint64_t* __restrict__ in_foff,
@@ -324,12 +330,14 @@ __global__ void __launch_bounds__(LST) leaf_flow_sorted_kernel(
     const uint8_t* __restrict__ miss, uint64_t num_rows, const int32_t* __restrict__ row_ids, uint32_t row_start,
     const float* __restrict__ weights, int* __restrict__ status) {
   __shared__ __align__(128) float rowbuf[LSR][LSB];
-  __shared__ uint16_t xs[LSB];
-  __shared__ uint16_t perm[LSB];
-  __shared__ uint32_t binoff[LSC + 4];   // segment starts and the end
-  __shared__ uint32_t cursor[LSC + 4];
+  __shared__ uint32_t binoff[LSC + 4];   // segment starts and the end; afterwards histogram 0
+  __shared__ uint32_t cursor[LSC + 4];   // scatter cursors; afterwards histogram 1
+  __shared__ uint64_t s_fo[PCB_LEAF_GROUP];   // the group's leaves: first statistics slot, categories
+  __shared__ uint32_t s_cats[PCB_LEAF_GROUP];
   __shared__ __align__(8) uint64_t bar[LSR];
-  extern __shared__ float wsm[];          // [LSB] example weights, only when weights are given
+  static_assert(sizeof(float) * LSB == 2 * sizeof(uint16_t) * LSB, "the sort's two arrays fill one row buffer");
+  uint16_t* xs = reinterpret_cast<uint16_t*>(rowbuf[LSR - 1]);   // values of the examples
+  uint16_t* perm = xs + LSB;                                      // examples in sorted order
   const uint32_t grp = blockIdx.x, b0 = blockIdx.y * LSB, tid = threadIdx.x;
   const uint32_t nb = min((uint32_t)LSB, B - b0);
   const uint32_t l0 = lgrp_off[grp], nl = lgrp_off[grp + 1] - l0;
@@ -341,8 +349,12 @@ __global__ void __launch_bounds__(LST) leaf_flow_sorted_kernel(
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (uint32_t x = tid; x <= nbins; x += LST) { binoff[x] = 0; }
+  if (tid < nl) {
+    const uint32_t i = linputs[l0 + tid];
+    s_fo[tid] = in_foff[i];
+    s_cats[tid] = in_cats[i];
+  }
   stage_values(xs, b0, nb, lgrp_var[grp], data, miss, num_rows, row_ids, row_start);
-  if (weights) for (uint32_t b = tid; b < nb; b += LST) wsm[b] = weights[data_row(row_ids, row_start, b0 + b)];
   __syncthreads();
   // rows are requested as early as possible: the sort below hides their latency
   const uint32_t rowbytes = ((nb + 3u) & ~3u) * 4u;   // the pitch is a multiple of 32 floats: stays inside the row
@@ -351,7 +363,7 @@ __global__ void __launch_bounds__(LST) leaf_flow_sorted_kernel(
     pcbtc::mbar_arrive_expect_tx(&bar[l % LSR], rowbytes);
     pcbtc::bulk_g2s(rowbuf[l % LSR], flows + (size_t)in_node[i] * ld + b0, rowbytes, &bar[l % LSR]);
   };
-  if (tid == 0) for (uint32_t l = 0; l < min(nl, (uint32_t)LSR); ++l) request(l);
+  if (tid == 0) for (uint32_t l = 0; l < min(nl, (uint32_t)LSR - 1u); ++l) request(l);
   // counting sort of the examples by value
   for (uint32_t b = tid; b < nb; b += LST) {
     const uint32_t x = xs[b] == 0xffff ? miss_bin : (uint32_t)xs[b];
@@ -381,32 +393,76 @@ __global__ void __launch_bounds__(LST) leaf_flow_sorted_kernel(
     if (x <= miss_bin) perm[atomicAdd(&cursor[x], 1u)] = (uint16_t)b;
   }
   __syncthreads();
+  // this thread's sorted positions LSE * tid .. + LSE - 1: example, segment, weight
+  constexpr uint32_t NOSEG = 0xffffffffu;
+  uint32_t pos[LSE], seg[LSE];
+  float wv[LSE];
+  {
+    const uint32_t total = binoff[nbins], j0 = LSE * tid;
+    // segment of position j0: the last x with binoff[x] <= j0
+    uint32_t lo = 0, hi = nbins;   // invariant: binoff[lo] <= j0 (binoff[0] = 0), answer in [lo, hi)
+    while (hi - lo > 1) {
+      const uint32_t mid = (lo + hi) >> 1;
+      if (binoff[mid] <= j0) lo = mid; else hi = mid;
+    }
+    uint32_t x = lo;
+#pragma unroll
+    for (uint32_t e = 0; e < (uint32_t)LSE; ++e) {
+      const uint32_t j = j0 + e;
+      const bool in = j < total;
+      while (in && binoff[x + 1] <= j) ++x;   // empty segments are stepped over
+      pos[e] = in ? (uint32_t)perm[j] : 0u;
+      seg[e] = in ? x : NOSEG;
+      wv[e] = (WEIGHTED && in) ? weights[data_row(row_ids, row_start, b0 + pos[e])] : 1.0f;
+    }
+  }
+  __syncthreads();   // binoff, cursor and the sort's arrays have been read by everyone
+  if (tid == 0 && nl >= (uint32_t)LSR) {   // the last row buffer is free now
+    pcbtc::fence_proxy_async();
+    request(LSR - 1);
+  }
+  float* hist0 = reinterpret_cast<float*>(binoff);
+  float* hist1 = reinterpret_cast<float*>(cursor);
+  for (uint32_t x = tid; x < nbins; x += LST) { hist0[x] = 0.0f; hist1[x] = 0.0f; }
+  __syncthreads();
   bool ok = true;
   for (uint32_t l = 0; l < nl; ++l) {
-    const uint32_t i = linputs[l0 + l];
-    const uint64_t fo = in_foff[i];
-    const uint32_t C = in_cats[i];
+    const uint64_t fo = s_fo[l];
+    const uint32_t C = s_cats[l];
     ok = ok && pcbtc::mbar_wait(&bar[l % LSR], (l / LSR) & 1u, status);
     const float* row = rowbuf[l % LSR];
-    if (ok && fo != ~0ull) {
-      for (uint32_t x = tid; x < nbins; x += LST) {
-        // leaf slot: value x <= C -> x, missing -> C; values beyond the leaf's categories are dropped
-        const uint32_t slot = x == miss_bin ? C : x;
-        if (slot > C) continue;
-        float acc = 0.0f;
-        const uint32_t j1 = binoff[x + 1];
-        if (weights) for (uint32_t j = binoff[x]; j < j1; ++j) acc += row[perm[j]] * wsm[perm[j]];
-        else         for (uint32_t j = binoff[x]; j < j1; ++j) acc += row[perm[j]];
-        // one reduction per slot and block, never read back here: a fire-and-forget RED keeps the
-        // round trip of a read-modify-write off the loop (with one block per group it is the only
-        // addition to its address, so the sum does not depend on any order)
-        if (acc != 0.0f) atomicAdd(aggr + fo + slot, acc);
+    float* h = (l & 1u) ? hist1 : hist0;
+    const bool live = ok && fo != ~0ull;
+    if (live) {
+      float v[LSE];
+#pragma unroll
+      for (uint32_t e = 0; e < (uint32_t)LSE; ++e) v[e] = row[pos[e]];
+      float acc = 0.0f;
+#pragma unroll
+      for (uint32_t e = 0; e < (uint32_t)LSE; ++e) {
+        if (e > 0 && seg[e] != seg[e - 1]) {   // positions past the end come last and carry NOSEG
+          atomicAdd(h + seg[e - 1], acc);
+          acc = 0.0f;
+        }
+        acc += WEIGHTED ? v[e] * wv[e] : v[e];
       }
+      if (seg[LSE - 1] != NOSEG) atomicAdd(h + seg[LSE - 1], acc);
     }
-    __syncthreads();   // the buffer has been read by everyone
+    __syncthreads();   // the row has been read and its histogram is complete
     if (tid == 0 && ok && l + LSR < nl) {
       pcbtc::fence_proxy_async();
       request(l + LSR);
+    }
+    if (live) {
+      // one fire-and-forget RED per slot; the histogram is cleared for the row after the next
+      for (uint32_t x = tid; x < nbins; x += LST) {
+        const float a = h[x];
+        if (a == 0.0f) continue;
+        h[x] = 0.0f;
+        // leaf slot: value x <= C -> x, missing -> C; values beyond the leaf's categories are dropped
+        const uint32_t slot = x == miss_bin ? C : x;
+        if (slot <= C) atomicAdd(aggr + fo + slot, a);
+      }
     }
   }
   if (!ok && tid == 0) {   // a wait was lost: let the copies in flight land before the block ends
@@ -869,7 +925,8 @@ static int32_t backward_impl(pcb_circuit* c, pcb_workspace* ws, const float* wei
           (int32_t)ws->soft_width);
     } else if (c->max_cats <= LSC && want_sorted) {
       dim3 grid(c->n_lgrps, (B + LSB - 1) / LSB);
-      leaf_flow_sorted_kernel<<<grid, LST, weights_dev ? LSB * sizeof(float) : 0, st>>>(
+      auto* kern = weights_dev ? leaf_flow_sorted_kernel<true> : leaf_flow_sorted_kernel<false>;
+      kern<<<grid, LST, 0, st>>>(
           ws->flows, ws->ld, B, c->aggr, c->in_node, c->in_cats, c->in_foff, c->lgrp_var, c->lgrp_off,
           c->lchunk_inputs, c->max_cats, ws->data, ws->miss, ws->num_rows, ws->row_ids, ws->row_start, weights_dev,
           c->status);
