@@ -416,6 +416,7 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
     c->sample_walk_warp = flag("PCB_SAMPLE_WALK_WARP");
     c->sample_exact_keys = flag("PCB_SAMPLE_EXACT_KEYS");
     if (const char* e = getenv("PCB_LEAF_FLOW_IMPL")) c->leaf_flow_impl = !strcmp(e, "sorted") ? 2 : !strcmp(e, "atomic") ? 1 : 0;
+    if (const char* e = getenv("PCB_TC_KSPLIT")) { int v = atoi(e); c->tc_ksplit = (v == 1 || v == 2 || v == 4) ? v : 0; }
     if (const char* e = getenv("PCB_TC_NSPLIT")) { int v = atoi(e); c->tc_nsplit = (v == 1 || v == 2 || v == 4) ? v : 0; }
     if (const char* e = getenv("PCB_TC_A_STAGES")) { int v = atoi(e); c->tc_a_stages = (v == 2 || v == 4 || v == 8) ? v : 0; }
     if (const char* e = getenv("PCB_EDGE_IMPL")) c->edge_ld = !strcmp(e, "ld");
@@ -535,6 +536,17 @@ extern "C" int32_t pcb_workspace_create(pcb_circuit* c, uint32_t max_batch, int3
     int32_t st = pcb_dense_edge_prepare_ws(ws);
     if (st != PCB_OK) { pcb_workspace_destroy(ws); return st; }
   }
+  if (c->use_tc && c->n_dense) {
+    // scratch of the K-split dense tiles: a launch that splits K stays within 296 CTAs, each with a
+    // slot of at most 128 x 257 floats; one arrival counter per tile
+    const size_t part_bytes = (size_t)296 * 128 * 257 * sizeof(float), ticket_bytes = 296 * sizeof(uint32_t);
+    if (cudaMalloc((void**)&ws->mn_part, part_bytes) != cudaSuccess ||
+        cudaMalloc((void**)&ws->mn_tickets, ticket_bytes) != cudaSuccess ||
+        cudaMemset(ws->mn_tickets, 0, ticket_bytes) != cudaSuccess) {
+      pcb_workspace_destroy(ws);
+      return pcb_fail(PCB_ERR_CUDA, "workspace allocation: scratch of the K-split dense tiles");
+    }
+  }
   if (sets) {
     int32_t st = pcb_ws_ensure_sets(ws, max_batch, PCB_WS_NODES | PCB_WS_STACK | PCB_WS_EDGES);
     if (st != PCB_OK) { pcb_workspace_destroy(ws); return st; }
@@ -589,7 +601,7 @@ extern "C" int32_t pcb_workspace_destroy(pcb_workspace* ws) {
   if (ws->step_exec) cudaGraphExecDestroy(ws->step_exec);
   if (ws->kld_exec) cudaGraphExecDestroy(ws->kld_exec);
   for (void* p : {(void*)ws->mars, (void*)ws->flows, (void*)ws->blk_mx, (void*)ws->klds, (void*)ws->grads,
-                  (void*)ws->eprob, (void*)ws->cum, (void*)ws->stack, (void*)ws->sample_status, (void*)ws->ids_stage, (void*)ws->ll_tmp,
+                  (void*)ws->eprob, (void*)ws->cum, (void*)ws->stack, (void*)ws->sample_status, (void*)ws->ids_stage, (void*)ws->ll_tmp, (void*)ws->mn_part, (void*)ws->mn_tickets,
                   (void*)ws->kld_t_dev})
     if (p) cudaFree(p);
   delete ws;

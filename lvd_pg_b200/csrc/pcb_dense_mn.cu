@@ -74,18 +74,30 @@ struct MnArgs {
   uint32_t ld;
   uint32_t nsplit;   // CTAs sharing one 256-column tile (1, 2 or 4), each taking 256 / nsplit columns
   uint32_t a_stages; // stages of the A ring (a power of two up to A_MAX_STAGES); the launch sizes shared memory to it
+  uint32_t ksplit;   // CTAs sharing the K range of one tile (1, 2 or 4): each accumulates chunks / ksplit chunks
+  float* part;       // ksplit > 1: per CTA a slot of 128 x (256 / nsplit + 1) floats for its partial tile
+  uint32_t* tickets; // ksplit > 1: arrival counter per tile (zero between launches)
   unsigned long long* trace;   // -DPCB_DIAG builds: %globaltimer stamps of CTA (0,0,0), else null
 };
 
 // Timing stamps exist only in a build with -DPCB_DIAG; the default build compiles them out.
 #ifdef PCB_DIAG
+// running log of every launch (CTA (0,0,0)): [mode << 48 | blocks << 16 | ksplit, entered, dependencies done, exit]
+__device__ unsigned long long g_mn_log[4 * 2048];
+__device__ unsigned int g_mn_logn;
 __device__ int g_mn_halfw;   // timing experiments (results are wrong): 1 half of every weight chunk, 2 no row loads in the K loop, 4 no maximum pass
 #define MN_TRACE(slot)                                                                                   \
   do {                                                                                                   \
     if (a.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[(MODE == MN_FWD ? 0 : 256) + (slot)] = gtime(); \
   } while (0)
+// stamps of the CTA that completes K-split tile 0 (whichever part it is)
+#define MN_TRACE_F(slot)                                                                                 \
+  do {                                                                                                   \
+    if (a.trace && tile_id == 0 && tid == 0) a.trace[(MODE == MN_FWD ? 0 : 256) + (slot)] = gtime();     \
+  } while (0)
 #else
 #define MN_TRACE(slot) do { } while (0)
+#define MN_TRACE_F(slot) do { } while (0)
 #endif
 
 // byte offset of element (row, kk) inside a K-major tile with 64-byte rows and 64-byte swizzle
@@ -207,6 +219,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
   uint64_t* wgo = accfull + 1;                                // [1] FWD: the staging area is free for weights
   uint64_t* xbar = wgo + 1;                                   // [3] row-copy rounds
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + 3);
+  uint32_t* last_flag = tmem_slot + 1;                        // K split: this CTA completes the tile
   float* mxs = reinterpret_cast<float*>(ctl + 512);           // [128] per-example max of the tile
   float* part = reinterpret_cast<float*>(ctl + 1024);         // [PW/2][128] partial maxima (FWD)
 
@@ -218,10 +231,16 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
   // ---- tile coordinates ---------------------------------------------------------------------
   const uint32_t ncols = MODE == MN_FWD ? k.R : k.K, kdim = MODE == MN_FWD ? k.K : k.R;
   const uint32_t sw = TN / a.nsplit;
-  const uint32_t m0 = blockIdx.x * TM, jn = blockIdx.y / a.nsplit, part0 = (blockIdx.y % a.nsplit) * sw;
+  // blockIdx.y = (column tile, column part, K part)
+  const uint32_t ks = a.ksplit, yk = blockIdx.y / ks, kp = blockIdx.y - yk * ks;
+  const uint32_t m0 = blockIdx.x * TM, jn = yk / a.nsplit, part0 = (yk % a.nsplit) * sw;
   const uint32_t n0 = jn * TN + part0;
-  if (n0 >= ncols) return;
-  const uint32_t nchunks = (kdim + KC - 1) / KC;
+  if (n0 >= ncols) return;   // the same for every K part of the tile
+  // this CTA's chunks cb .. cb + nchunks - 1 of the block's K range (the launch splits K only when
+  // every block of the layer has a multiple of ksplit chunks)
+  const uint32_t nchunks = ((kdim + KC - 1) / KC) / ks, cb = kp * nchunks;
+  const uint32_t tile_id = (blockIdx.z * (gridDim.y / ks) + yk) * gridDim.x + blockIdx.x;
+  const size_t slot_floats = (size_t)TM * (sw + 1u);
   const PcbDenseImg im = a.imgs[blockIdx.z];
   const uint32_t img_rows = MODE == MN_FWD ? im.rows_f : im.rows_t;
   const uint32_t nch = MODE == MN_FWD ? im.nch_f : im.nch_t;
@@ -256,7 +275,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
   // Up to here only static circuit data was read: a launch with programmatic stream serialization
   // may have come this far while the previous kernel of the stream was still running.
   if (tid == 0) MN_TRACE(0);
+#ifdef PCB_DIAG
+  unsigned long long log_t0 = 0, log_t1 = 0;
+  if (tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) log_t0 = gtime();
+#endif
   pcb_grid_dep_wait();
+#ifdef PCB_DIAG
+  if (tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) log_t1 = gtime();
+#endif
   if (tid == 0) MN_TRACE(1);
   bool ok = true;
 
@@ -294,8 +320,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
           mbar_arrive_expect_tx(&xbar[R & 1u], nc * (has_sub ? 2u : 1u) * A_BYTES);
           for (uint32_t c = 0; c < nc; ++c) {
             uint8_t* slot = smem + ((R & 1u) * MAXP_CHUNKS + c) * A_STAGE;
-            tma_load_2d(slot, &tm_rows, (int32_t)m0, (int32_t)(k.c0 + (c_first + c) * KC), &xbar[R & 1u]);
-            if (has_sub) tma_load_2d(slot + A_BYTES, &tm_rows, (int32_t)m0, (int32_t)(k.d0 + (c_first + c) * KC), &xbar[R & 1u]);
+            tma_load_2d(slot, &tm_rows, (int32_t)m0, (int32_t)(k.c0 + (cb + c_first + c) * KC), &xbar[R & 1u]);
+            if (has_sub) tma_load_2d(slot + A_BYTES, &tm_rows, (int32_t)m0, (int32_t)(k.d0 + (cb + c_first + c) * KC), &xbar[R & 1u]);
           }
         }
       };
@@ -311,7 +337,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
 #pragma unroll
           for (uint32_t ps = 0; ps < 2; ++ps) {
             const uint32_t row = ps * 8u + warp;
-            if (got && (R * MAXP_CHUNKS + c) * KC + row < kdim) {
+            if (got && R * MAXP_CHUNKS + c < nchunks && (cb + R * MAXP_CHUNKS + c) * KC + row < kdim) {
               float4 v = lds4(slot + row * ROW_BYTES);
               if (has_sub) { const float4 q = lds4(slot + A_BYTES + row * ROW_BYTES); v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w; }
               mx = f4max(mx, v);
@@ -337,8 +363,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
       if (!bok) mx = ninf4;
       if (warp == 0) {
         *reinterpret_cast<float4*>(mxs + 4u * lane) = mx;   // for the epilogue (read after the barrier behind the K loop)
-        // kept for the backward kernels (one CTA per example tile writes)
-        if (bok && blockIdx.y == 0) *reinterpret_cast<float4*>(a.blk_mx + (size_t)k.mx_row * ld + bq) = mx;
+        // kept for the backward kernels (one CTA per example tile writes; with a K split the CTA that
+        // completes the tile writes the maximum over all parts)
+        if (bok && blockIdx.y == 0 && ks == 1) *reinterpret_cast<float4*>(a.blk_mx + (size_t)k.mx_row * ld + bq) = mx;
       }
       if (tid == 0) MN_TRACE(2);   // per-example maximum known
       // a masked example (outside the batch, or no child possible): exp(x - inf) = 0
@@ -360,7 +387,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
 #endif
 #pragma unroll
           for (uint32_t ps = 0; ps < 2; ++ps) {
-            const uint32_t t = i * KC + ps * 8u + warp;
+            const uint32_t t = (cb + i) * KC + ps * 8u + warp;
             const size_t o = (size_t)(t < kdim ? t : 0u) * ld;
             r.x[ps] = ldg4(rowsA + o);
             if (has_sub) r.y[ps] = ldg4(rowsB + o);
@@ -375,7 +402,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
             float4 v = r.x[ps];
             if (has_sub) { v.x += r.y[ps].x; v.y += r.y[ps].y; v.z += r.y[ps].z; v.w += r.y[ps].w; }
             v.x = __expf(v.x - mx4.x); v.y = __expf(v.y - mx4.y); v.z = __expf(v.z - mx4.z); v.w = __expf(v.w - mx4.w);
-            if (i * KC + ps * 8u + warp >= kdim) v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if ((cb + i) * KC + ps * 8u + warp >= kdim) v = make_float4(0.f, 0.f, 0.f, 0.f);
             const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
             const uint32_t o = aoff + ps * 4096u;
             *reinterpret_cast<float4*>(a_hi + o) = h;
@@ -409,7 +436,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
       auto load = [&](uint32_t i, Regs& r) {
 #pragma unroll
         for (uint32_t ps = 0; ps < 2; ++ps) {
-          const uint32_t t = i * KC + ps * 8u + warp;
+          const uint32_t t = (cb + i) * KC + ps * 8u + warp;
           const size_t o = (size_t)(t < kdim ? t : 0u) * ld;
           r.x[ps] = ldg4(rowsA + o);
           r.y[ps] = ldg4(rowsB + o);
@@ -424,7 +451,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
           float4 v;   // x: mars of the parent, y: flows of the parent
           v.x = r.y[ps].x * __expf(mx4.x - r.x[ps].x); v.y = r.y[ps].y * __expf(mx4.y - r.x[ps].y);
           v.z = r.y[ps].z * __expf(mx4.z - r.x[ps].z); v.w = r.y[ps].w * __expf(mx4.w - r.x[ps].w);
-          if (i * KC + ps * 8u + warp >= kdim) v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if ((cb + i) * KC + ps * 8u + warp >= kdim) v = make_float4(0.f, 0.f, 0.f, 0.f);
           const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
           const uint32_t o = aoff + ps * 4096u;
           *reinterpret_cast<float4*>(a_hi + o) = h;
@@ -457,22 +484,92 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
     const uint32_t row = q4 * 32 + lane, b = m0 + row;
     const float mx = mxs[row];
     float acc[16];
+    // K split: every CTA of the tile leaves its partial accumulators (and, FWD, the maximum they are
+    // relative to) in its slot and takes a ticket; the CTA that draws the last ticket completes the
+    // tile from its own tensor memory and the other slots.  Nobody waits for anybody.
+    float* my_slot = ks > 1 ? a.part + ((size_t)tile_id * ks + kp) * slot_floats : nullptr;
+    auto take_ticket = [&]() -> bool {   // called by every producer thread
+      __threadfence();                   // this thread's slot writes are visible before the ticket is
+      asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");
+      if (tid == 0) {
+        const uint32_t t = atomicAdd(a.tickets + tile_id, 1u);
+        const bool last = t == ks - 1u;
+        if (last) a.tickets[tile_id] = 0u;   // ready for the next launch
+        __threadfence();
+        *last_flag = last ? 1u : 0u;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(NPROD) : "memory");
+      return *last_flag != 0u;
+    };
     if (MODE == MN_FWD) {
-      if (ok) {
+      // a thread owns one example and walks 16 columns at a time
+      const uint32_t CG = max(16u, ((n_tile + 31u) / 32u) * 16u);   // columns per half, a multiple of 16
+      const uint32_t c_begin = half * CG, c_end = min(n_tile, c_begin + CG);
+      bool finish = true;
+      float gm = mx, own_scale = 1.0f, sc[3] = {0.f, 0.f, 0.f};
+      const float* oslot[3] = {nullptr, nullptr, nullptr};   // the other parts' slots: parts kp + 1 + q (mod ksplit)
+      if (ks > 1) {
+        if (ok) {
+          tc_fence_after();
+          if (half == 0) my_slot[row] = mx;
+          for (uint32_t c0 = c_begin; c0 < c_end; c0 += 16) {
+            tmem_ld16(tmem_base + ((q4 * 32u) << 16) + c0, acc);
+#pragma unroll
+            for (uint32_t j = 0; j < 16; ++j) my_slot[TM + (size_t)(c0 + j) * TM + row] = acc[j];
+          }
+        }
+        finish = take_ticket();
+        if (finish) MN_TRACE_F(7);
+        if (finish) {
+          // the sums of a part are relative to its own maximum: rescale to the maximum over the parts
+          float pm[3];
+#pragma unroll
+          for (uint32_t q = 0; q < 3; ++q) {
+            oslot[q] = a.part + ((size_t)tile_id * ks + ((kp + 1u + q) & (ks - 1u))) * slot_floats;
+            pm[q] = q + 1u < ks ? __ldcg(oslot[q] + row) : -INFINITY;
+            gm = fmaxf(gm, pm[q]);
+          }
+#pragma unroll
+          for (uint32_t q = 0; q < 3; ++q) sc[q] = pm[q] != -INFINITY ? __expf(pm[q] - gm) : 0.0f;
+          own_scale = mx == -INFINITY ? 0.0f : __expf(mx - gm);
+          if (yk == 0 && half == 0 && b < ld) a.blk_mx[(size_t)k.mx_row * ld + b] = gm;
+        }
+      }
+      if (ok && finish) {
         tc_fence_after();
-        // a thread owns one example and walks 16 columns at a time
-        const uint32_t CG = max(16u, ((n_tile + 31u) / 32u) * 16u);   // columns per half, a multiple of 16
-        const uint32_t c_begin = half * CG, c_end = min(n_tile, c_begin + CG);
         for (uint32_t c0 = c_begin; c0 < c_end; c0 += 16) {
+          float pv[3][16];
+          if (ks > 1 && b < ld) {   // all loads of the round first: one latency, not one per part
+#pragma unroll
+            for (uint32_t q = 0; q < 3; ++q) {
+              if (q + 1u < ks) {
+                const float* ps = oslot[q] + TM + (size_t)c0 * TM + row;
+#pragma unroll
+                for (uint32_t j = 0; j < 16; ++j) pv[q][j] = __ldcg(ps + (size_t)j * TM);
+              }
+            }
+          }
           tmem_ld16(tmem_base + ((q4 * 32u) << 16) + c0, acc);
           if (b >= ld) continue;
+          if (ks > 1) {
+#pragma unroll
+            for (uint32_t j = 0; j < 16; ++j) acc[j] *= own_scale;
+#pragma unroll
+            for (uint32_t q = 0; q < 3; ++q) {
+              if (q + 1u < ks) {
+#pragma unroll
+                for (uint32_t j = 0; j < 16; ++j) acc[j] = fmaf(pv[q][j], sc[q], acc[j]);
+              }
+            }
+          }
 #pragma unroll
           for (uint32_t j = 0; j < 16; ++j) {
             const uint32_t r = n0 + c0 + j;
-            if (r < k.R) a.mars[(size_t)(k.p0 + r) * ld + b] = mx == -INFINITY ? -INFINITY : __logf(acc[j]) + mx;
+            if (r < k.R) a.mars[(size_t)(k.p0 + r) * ld + b] = gm == -INFINITY ? -INFINITY : __logf(acc[j]) + gm;
           }
         }
       }
+      if (ks > 1 && finish) MN_TRACE_F(8);
     } else {
       // Child flows f[t][b] = acc[b][t] * exp(M[t][b] - mx[b]) need the children's value rows: copied 32
       // columns per round into the idle 96 KB (32 KB per round: [32 prime rows | 32 sub rows]), three
@@ -494,13 +591,46 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
           }
         }
       };
+      bool finish = true;
+      if (ks > 1) {   // the partial sums are linear in the K range: the completing CTA adds the other slots
+        if (ok) {
+          tc_fence_after();
+          for (uint32_t c0 = half * 16u; c0 < n_tile; c0 += EPI_COLS) {
+            tmem_ld16(tmem_base + ((q4 * 32u) << 16) + c0, acc);
+#pragma unroll
+            for (uint32_t j = 0; j < 16; ++j) my_slot[TM + (size_t)(c0 + j) * TM + row] = acc[j];
+          }
+        }
+        finish = take_ticket();
+        if (finish) MN_TRACE_F(7);
+      }
       fence_proxy_async();
-      for (uint32_t R = 0; R < min(3u, nrounds); ++R) issue_round(R);
-      for (uint32_t R = 0; R < nrounds; ++R) {
+      for (uint32_t R = 0; R < min(3u, nrounds) && finish; ++R) issue_round(R);
+      for (uint32_t R = 0; R < nrounds && finish; ++R) {
         const bool got = wait_warp(&xbar[R % 3u], (R / 3u) & 1u);
         const uint32_t c0 = R * EPI_COLS + half * 16u;   // first column of this warp in the round (within the CTA's tile)
         if (c0 < n_tile) {
+          float pv[3][16];
+          if (ok && ks > 1) {   // all loads of the round first: one latency, not one per part
+#pragma unroll
+            for (uint32_t q = 0; q < 3; ++q) {
+              if (q + 1u < ks) {
+                const float* ps = a.part + ((size_t)tile_id * ks + ((kp + 1u + q) & (ks - 1u))) * slot_floats + TM + (size_t)c0 * TM + row;
+#pragma unroll
+                for (uint32_t j = 0; j < 16; ++j) pv[q][j] = __ldcg(ps + (size_t)j * TM);
+              }
+            }
+          }
           if (ok) { tc_fence_after(); tmem_ld16(tmem_base + ((q4 * 32u) << 16) + c0, acc); }
+          if (ok && ks > 1) {
+#pragma unroll
+            for (uint32_t q = 0; q < 3; ++q) {
+              if (q + 1u < ks) {
+#pragma unroll
+                for (uint32_t j = 0; j < 16; ++j) acc[j] += pv[q][j];
+              }
+            }
+          }
           if (ok && got && b < ld) {
             const uint8_t* sp = smem + (R % 3u) * (EPI_COLS * 1024u) + (half * 16u) * ROW_BYTES + row * 4u;
 #pragma unroll
@@ -522,6 +652,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
         }
       }
     }
+    if (MODE != MN_FWD && ks > 1) MN_TRACE_F(8);   // (only the completing CTA gets here with work done; others stamp earlier)
     if (tid == 0) MN_TRACE(5);   // epilogue of warp 0 done
   } else if (warp == MMA_WARP) {
     // =========================== MMA issuer ==================================================
@@ -561,7 +692,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
         const uint32_t sb = i % w_stages, pb = (i / w_stages) & 1u;
         if (w_reuse && !mbar_wait(&wempty[sb], pb ^ 1u, a.status)) break;
         uint8_t* dst = wring + sb * 2u * w_part;
-        const float* src = img_tile + (size_t)i * 2 * img_rows * KC;   // hi part, then lo part img_rows x 16 floats later
+        const float* src = img_tile + (size_t)(cb + i) * 2 * img_rows * KC;   // hi part, then lo part img_rows x 16 floats later
         if (i < 32) MN_TRACE(128 + i);   // copies of chunk i issued
 #ifdef PCB_DIAG
         const uint32_t wb = (g_mn_halfw & 1) ? w_part / 2 : w_part;
@@ -586,6 +717,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
   tc_fence_before();
   __syncthreads();
   if (tid == 0) MN_TRACE(6);
+#ifdef PCB_DIAG
+  if (tid == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) {
+    const unsigned int i = atomicAdd(&g_mn_logn, 1u) % 2048u;
+    g_mn_log[4 * i] = ((unsigned long long)MODE << 48) | ((unsigned long long)gridDim.z << 16) | a.ksplit;
+    g_mn_log[4 * i + 1] = log_t0; g_mn_log[4 * i + 2] = log_t1; g_mn_log[4 * i + 3] = gtime();
+  }
+#endif
   if (warp == MMA_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -647,6 +785,27 @@ uint32_t pick_a_stages(dim3 grid, const pcb_circuit* c) {
   return (uint64_t)grid.x * grid.y * grid.z <= 148 ? A_MAX_STAGES : A_STAGES;
 }
 
+// A layer that still leaves most of the GPU idle after the column split also splits the K range:
+// four CTAs accumulate a quarter of the chunks each, leave their partial tiles in a scratch slot and
+// the one that finishes last completes the tile.  The K loop, which the single issuing thread paces
+// (about 0.75 us per chunk), is the longest piece of such a layer's kernel, and these layers form
+// the dependent chain of the circuit.  Measured per layer of one 256 x 256 block at 2048 examples:
+// forward 22.2 -> 15.6 us, child flows 24.0 -> 19.5 us; a two-way split (layers of two blocks) gains
+// nothing over the cost of the hand-over and is only taken when forced (PCB_TC_KSPLIT=2).  Only
+// when every block of the layer has a multiple of ksplit chunks with at least two chunks per part,
+// and while the launch stays within two CTAs per SM.
+template <class Blocks>
+uint32_t pick_ksplit(uint32_t ctas, const Blocks& blocks, uint32_t o0, uint32_t o1, bool fwd, int forced) {
+  if (forced == 1) return 1;
+  const uint32_t ks = forced ? (uint32_t)forced : 4u;
+  if ((uint64_t)ctas * ks > 296) return 1;
+  for (uint32_t i = o0; i < o1; ++i) {
+    const uint32_t nch = ((fwd ? blocks[i].K : blocks[i].R) + KC - 1) / KC;
+    if (nch % ks != 0 || nch / ks < 2) return 1;
+  }
+  return ks;
+}
+
 uint32_t pick_nsplit(uint32_t ctas, uint32_t max_cols, int forced) {
   if (forced == 1 || forced == 2 || forced == 4) return (uint32_t)forced;
   uint32_t n = 1;
@@ -701,14 +860,26 @@ int32_t pcb_dense_mn_refresh(pcb_circuit* c, cudaStream_t st) {
 // Diagnostic (-DPCB_DIAG builds with PCB_TC_TRACE set): the stamps of the last traced launches,
 // forward in words [0, 256), child flows in [256, 512); null otherwise.
 unsigned long long* pcb_dense_mn_trace() { return mn_trace(); }
+#ifdef PCB_DIAG
+// Diagnostic builds only: the running launch log (4 words per launch, the last 2048 launches) and its count.
+extern "C" int32_t pcb_debug_mn_log(unsigned long long* out, unsigned int* n, int reset) {
+  cudaDeviceSynchronize();
+  if (out && cudaMemcpyFromSymbol(out, g_mn_log, sizeof(g_mn_log)) != cudaSuccess) return PCB_ERR_CUDA;
+  if (n && cudaMemcpyFromSymbol(n, g_mn_logn, sizeof(unsigned int)) != cudaSuccess) return PCB_ERR_CUDA;
+  if (reset) { unsigned int z = 0; cudaMemcpyToSymbol(g_mn_logn, &z, sizeof(z)); }
+  return PCB_OK;
+}
+#endif
 
 int32_t pcb_dense_mn_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st) {
   uint32_t o0 = c->h_dense_off[layer], o1 = c->h_dense_off[layer + 1];
   if (o1 == o0) return PCB_OK;
   const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM, ct = (c->max_dense_R + TN - 1) / TN;
   MnArgs args{ws->mars, ws->flows, ws->blk_mx, c->w_img16, c->dense + o0, c->dense_img16 + o0, c->status, ws->ld,
-              pick_nsplit(bt * ct * (o1 - o0), c->max_dense_R, c->tc_nsplit), A_STAGES, mn_trace_for(o1 - o0)};
-  dim3 grid(bt, ct * args.nsplit, o1 - o0);
+              pick_nsplit(bt * ct * (o1 - o0), c->max_dense_R, c->tc_nsplit), A_STAGES, 1, ws->mn_part, ws->mn_tickets,
+              mn_trace_for(o1 - o0)};
+  args.ksplit = ws->mn_part ? pick_ksplit(bt * ct * args.nsplit * (o1 - o0), c->h_dense, o0, o1, true, c->tc_ksplit) : 1;
+  dim3 grid(bt, ct * args.nsplit * args.ksplit, o1 - o0);
   args.a_stages = pick_a_stages(grid, c);
   PcbProfScope ps(c, st, PCB_K_DENSE_FWD);
   return launch<MN_FWD>(grid, ws, args, st, c->pdl);
@@ -719,8 +890,10 @@ int32_t pcb_dense_mn_backward_child(pcb_circuit* c, pcb_workspace* ws, uint32_t 
   if (o1 == o0) return PCB_OK;
   const uint32_t bt = (pcb_round_up(ws->B, 32) + TM - 1) / TM, ct = (c->max_dense_K + TN - 1) / TN;
   MnArgs args{ws->mars, ws->flows, ws->blk_mx, c->w_img16, c->dense + o0, c->dense_img16 + o0, c->status, ws->ld,
-              pick_nsplit(bt * ct * (o1 - o0), c->max_dense_K, c->tc_nsplit), A_STAGES, mn_trace_for(o1 - o0)};
-  dim3 grid(bt, ct * args.nsplit, o1 - o0);
+              pick_nsplit(bt * ct * (o1 - o0), c->max_dense_K, c->tc_nsplit), A_STAGES, 1, ws->mn_part, ws->mn_tickets,
+              mn_trace_for(o1 - o0)};
+  args.ksplit = ws->mn_part ? pick_ksplit(bt * ct * args.nsplit * (o1 - o0), c->h_dense, o0, o1, false, c->tc_ksplit) : 1;
+  dim3 grid(bt, ct * args.nsplit * args.ksplit, o1 - o0);
   args.a_stages = pick_a_stages(grid, c);
   PcbProfScope ps(c, st, PCB_K_DENSE_BWD_CHILD);
   return launch<MN_BWD_CHILD>(grid, ws, args, st, c->pdl);

@@ -181,6 +181,7 @@ struct pcb_circuit {
   bool fwd_split = true, bwd_split = true;   // side-stream splits of the forward / backward layer loops
   bool early_update = false;                 // single-GPU step: sum update + weight images beside the leaf statistics (measured neutral)
   int leaf_flow_impl = 0;                    // 0 by category count, 1 shared-memory histograms, 2 sorted segments
+  int tc_ksplit = 0;                         // 0 automatic, else 1 / 2 / 4 K parts of a dense tile (PCB_TC_KSPLIT)
   int tc_nsplit = 0;                         // 0 automatic, else 1 / 2 / 4 column splits of a dense tile
   int tc_a_stages = 0;                       // 0 automatic, else 2 / 4 / 8 stages of the dense kernels' A ring
   bool edge_ld = false;                      // edge statistics by the load-fed kernel instead of tensor-map copies
@@ -208,6 +209,8 @@ struct pcb_workspace {
   float* mars = nullptr;    // [N][ld]
   float* flows = nullptr;   // [N][ld]
   float* blk_mx = nullptr;  // [n_dense][ld] per-example max of a dense block's children
+  float* mn_part = nullptr;        // partial tiles of the dense kernels' K split (296 slots of 128 x 257 floats)
+  uint32_t* mn_tickets = nullptr;  // arrival counter per K-split tile, zero between launches
   // One EM step as a CUDA graph: a step called twice in a row with the same arguments is captured
   // on the second call and replayed from then on (the row ids are staged in ids_stage so that
   // their address does not change from step to step).
