@@ -591,6 +591,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
           }
         }
       };
+      // The first rounds of child rows are requested before the hand-over of a K split: every CTA of
+      // the tile fetches them although only the completing one uses them, whose epilogue then starts
+      // with the rows already there (these layers leave the memory system idle).
+      fence_proxy_async();
+      const uint32_t first_rounds = min(3u, nrounds);
+      for (uint32_t R = 0; R < first_rounds; ++R) issue_round(R);
       bool finish = true;
       if (ks > 1) {   // the partial sums are linear in the K range: the completing CTA adds the other slots
         if (ok) {
@@ -603,9 +609,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
         }
         finish = take_ticket();
         if (finish) MN_TRACE_F(7);
+        if (!finish)   // the copies in flight land before the CTA gives its memory back
+          for (uint32_t R = 0; R < first_rounds; ++R) wait_warp(&xbar[R], 0u);
       }
-      fence_proxy_async();
-      for (uint32_t R = 0; R < min(3u, nrounds) && finish; ++R) issue_round(R);
       for (uint32_t R = 0; R < nrounds && finish; ++R) {
         const bool got = wait_warp(&xbar[R % 3u], (R / 3u) & 1u);
         const uint32_t c0 = R * EPI_COLS + half * 16u;   // first column of this warp in the round (within the CTA's tile)
@@ -797,13 +803,17 @@ uint32_t pick_a_stages(dim3 grid, const pcb_circuit* c) {
 template <class Blocks>
 uint32_t pick_ksplit(uint32_t ctas, const Blocks& blocks, uint32_t o0, uint32_t o1, bool fwd, int forced) {
   if (forced == 1) return 1;
-  const uint32_t ks = forced ? (uint32_t)forced : 4u;
-  if ((uint64_t)ctas * ks > 296) return 1;
-  for (uint32_t i = o0; i < o1; ++i) {
-    const uint32_t nch = ((fwd ? blocks[i].K : blocks[i].R) + KC - 1) / KC;
-    if (nch % ks != 0 || nch / ks < 2) return 1;
+  for (uint32_t ks = 4; ks >= 2; ks >>= 1) {
+    if (forced && (uint32_t)forced != ks) continue;
+    if ((uint64_t)ctas * ks > 296) continue;
+    bool fits = true;
+    for (uint32_t i = o0; i < o1 && fits; ++i) {
+      const uint32_t nch = ((fwd ? blocks[i].K : blocks[i].R) + KC - 1) / KC;
+      fits = nch % ks == 0 && nch / ks >= 2;
+    }
+    if (fits) return ks;
   }
-  return ks;
+  return 1;
 }
 
 uint32_t pick_nsplit(uint32_t ctas, uint32_t max_cols, int forced) {
