@@ -85,7 +85,7 @@ struct MnArgs {
 // running log of every launch (CTA (0,0,0)): [mode << 48 | blocks << 16 | ksplit, entered, dependencies done, exit]
 __device__ unsigned long long g_mn_log[4 * 2048];
 __device__ unsigned int g_mn_logn;
-__device__ int g_mn_halfw;   // timing experiments (results are wrong): 1 half of every weight chunk, 2 no row loads in the K loop, 4 no maximum pass
+__device__ int g_mn_halfw;   // timing experiments (results are wrong): 1 half of every weight chunk, 2 no row loads in the K loop, 4 no maximum pass, 8 one MMA pass instead of three
 #define MN_TRACE(slot)                                                                                   \
   do {                                                                                                   \
     if (a.trace && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) a.trace[(MODE == MN_FWD ? 0 : 256) + (slot)] = gtime(); \
@@ -679,6 +679,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) dense_mn_kernel(const __grid_cons
           const uint64_t d_bhi = desc_k64(wa) + (uint64_t)((ks * 32u) >> 4);
           const uint64_t d_blo = desc_k64(wa + w_part) + (uint64_t)((ks * 32u) >> 4);
           umma_tf32(tmem_base, d_ahi, d_bhi, idesc, (i | ks) ? 1u : 0u);
+#ifdef PCB_DIAG
+          if (g_mn_halfw & 8) continue;   // timing experiment: one pass instead of three
+#endif
           umma_tf32(tmem_base, d_alo, d_bhi, idesc, 1u);
           umma_tf32(tmem_base, d_ahi, d_blo, idesc, 1u);
         }
