@@ -123,6 +123,44 @@ def test_example_major_and_k_major_tensor_core_kernels_agree(monkeypatch):
             assert rel_err(o[3], outs[0][3]) <= TOL
 
 
+def test_k_split_of_small_dense_layers_agrees_with_the_unsplit_kernels(oracle, monkeypatch):
+    """Layers of one or two blocks split the K range over 2 or 4 CTAs that hand their partial tiles over
+    through a scratch slot (PCB_TC_KSPLIT forces the split, 1 turns it off): values, flows, statistics and
+    the updated parameters against the unsplit kernels and the oracle; the second and third step replay
+    the captured graph, i.e. run on the arrival counters the step before left behind."""
+    torch, api = _cuda()
+    for fc, rows, c in ((random_hclt(5, 256, 3, 41), 200, 3), (random_hclt(7, 128, 4, 42), 131, 4), (random_hclt(6, 64, 2, 43), 64, 2)):
+        data, miss = random_data(rows, fc.num_vars, c, 6, 0.1)
+        ref = fc.copy()
+        mars_ref = oracle.forward(ref, data, miss=miss)
+        flows_ref, _ = oracle.backward(ref, mars_ref)
+        outs = []
+        for ks in ("1", "2", "4"):
+            monkeypatch.setenv("PCB_TC_KSPLIT", ks)
+            m = api.CuMetaBitsProbCircuit(fc.copy())
+            dd = api.DeviceData(data, m.device, miss)
+            ll = torch.zeros(1, device=m.device)
+            ws = api.em_step(m, dd, pseudocount=0.1, inertia=0.5, ll_sum=ll)
+            first = (m.mars(ws, rows), m.flows(ws, rows), m.edge_aggr(), ll.item())
+            for _ in range(2):
+                api.em_step(m, dd, pseudocount=0.1, inertia=0.5, ll_sum=ll)
+            outs.append(first + (api.vectorize_parameters(m), ll.item()))
+            _lib_check_status(m)
+        assert np.abs(outs[0][0] - mars_ref).max() <= TOL * max(1.0, np.abs(mars_ref).max())
+        for o in outs:
+            assert np.isfinite(o[3]) and np.isfinite(o[5])
+            assert np.abs(o[0] - mars_ref).max() <= TOL * max(1.0, np.abs(mars_ref).max())
+            assert rel_err(o[1], flows_ref) <= TOL
+            assert rel_err(o[2], outs[0][2]) <= TOL
+            assert abs(o[5] - outs[0][5]) <= 1e-5 * abs(outs[0][5])
+            assert np.abs(np.exp(o[4]) - np.exp(outs[0][4])).max() <= TOL
+
+
+def _lib_check_status(m):
+    from lvd_pg_b200 import _lib
+    _lib.check(m.lib.pcb_circuit_status(m.handle))
+
+
 def test_em_steps_track_oracle_with_row_ids(oracle):
     torch, api = _cuda()
     fc = random_hclt(10, 16, 3, 5)
