@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(LTH) leaf_flow_chunk_kernel(
 }
 
 // Leaf statistics by sorted examples: the examples of the block's slice are sorted by the
-// variable's value once (counting sort in shared memory), and every thread keeps LSE consecutive
+// variable's value once (counting sort in shared memory), and every thread keeps up to LSE consecutive
 // positions of the sorted order in registers for the whole group: the example behind each position,
 // its value segment and (if given) its weight.  Then every leaf row of the group streams through a
 // three-deep ring of shared-memory buffers (one bulk copy per row); a thread gathers its LSE values
@@ -398,7 +398,9 @@ __global__ void __launch_bounds__(LST) leaf_flow_sorted_kernel(
   uint32_t pos[LSE], seg[LSE];
   float wv[LSE];
   {
-    const uint32_t total = binoff[nbins], j0 = LSE * tid;
+    // the sorted examples are dealt out evenly: a slice of fewer than 2048 examples still keeps every
+    // thread busy, with fewer positions each
+    const uint32_t total = binoff[nbins], per = (total + LST - 1u) / LST, j0 = per * tid;
     // segment of position j0: the last x with binoff[x] <= j0
     uint32_t lo = 0, hi = nbins;   // invariant: binoff[lo] <= j0 (binoff[0] = 0), answer in [lo, hi)
     while (hi - lo > 1) {
@@ -409,7 +411,7 @@ __global__ void __launch_bounds__(LST) leaf_flow_sorted_kernel(
 #pragma unroll
     for (uint32_t e = 0; e < (uint32_t)LSE; ++e) {
       const uint32_t j = j0 + e;
-      const bool in = j < total;
+      const bool in = e < per && j < total;
       while (in && binoff[x + 1] <= j) ++x;   // empty segments are stepped over
       pos[e] = in ? (uint32_t)perm[j] : 0u;
       seg[e] = in ? x : NOSEG;
@@ -754,6 +756,9 @@ static int32_t forward_impl(pcb_circuit* c, pcb_workspace* ws, const pcb_evidenc
   ws->soft = ev.soft_dev; ws->head_mask = ev.head_mask_dev;
   ws->soft_reg = ev.soft_dev ? 0.0f : ev.soft_reg; ws->soft_width = ev.soft_reg_width;
   if (c->use_tc) PCB_TRY(pcb_dense_tc_refresh(c, st));
+  // the arrival counters of the K-split dense tiles return to zero by themselves; a pass that a lost
+  // wait cut short must not leave a stale count to the next one
+  if (ws->mn_tickets) PCB_CUDA(cudaMemsetAsync(ws->mn_tickets, 0, 296 * sizeof(uint32_t), st));
   if (c->n_inputs) {
     PcbProfScope ps(c, st, PCB_K_LEAF_FWD);
     if (ws->soft || ws->soft_reg > 0.0f) {
