@@ -110,6 +110,7 @@ extern "C" int32_t pcb_comm_init(pcb_circuit* c, const uint8_t* id_128, int32_t 
   c->comm_enabled = true;
   c->comm_lost = false;
   if (const char* e = getenv("PCB_COMM_SPLIT")) c->comm_split = atoi(e) != 0;
+  if (const char* e = getenv("PCB_COMM_PIPE")) c->comm_pipe = atoi(e) != 0;
   if (!c->comm_stream) {
     PCB_CUDA(cudaStreamCreateWithFlags(&c->comm_stream, cudaStreamNonBlocking));
     for (cudaEvent_t* ev : {&c->ev_c0, &c->ev_c1, &c->ev_c2, &c->ev_c3})

@@ -1014,6 +1014,24 @@ static int32_t em_step_body(pcb_circuit* c, pcb_workspace* ws, const pcb_evidenc
   { PcbProfScope ps(c, st, PCB_K_MISC);
     ll_sum_kernel<<<1, 256, 0, st>>>(c->n_heads ? ws->ll_tmp : ws->mars + (size_t)(c->N - 1) * ws->ld, B,
                                      c->aggr + c->aggr_len - 1); }
+  const bool pipe = multi && !split && c->comm_pipe && !c->prof.on && c->n_inner && c->comm_stream;
+  if (pipe) {
+    // Two collectives on the communication stream, edge statistics first; this stream updates the sum
+    // parameters and rebuilds the weight images while the leaf slots are still being summed.
+    PCB_CUDA(cudaEventRecord(c->ev_c0, st));
+    PCB_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_c0, 0));
+    PCB_TRY(pcb_allreduce_range(c, 0, c->n_inner, c->comm_stream));
+    PCB_CUDA(cudaEventRecord(c->ev_c1, c->comm_stream));
+    PCB_TRY(pcb_allreduce_range(c, c->n_inner, c->aggr_len - c->n_inner, c->comm_stream));
+    PCB_CUDA(cudaEventRecord(c->ev_c3, c->comm_stream));
+    PCB_CUDA(cudaStreamWaitEvent(st, c->ev_c1, 0));
+    PCB_TRY(em_update_sums(c, pseudocount, inertia, st));
+    if (c->use_tc) PCB_TRY(pcb_dense_tc_refresh(c, st));
+    PCB_CUDA(cudaStreamWaitEvent(st, c->ev_c3, 0));
+    PCB_TRY(em_update_leaves(c, pseudocount, inertia, st));
+    PCB_CUDA(cudaGetLastError());
+    return PCB_OK;
+  }
   if (split) PCB_TRY(comm_rest_and_join(c, st));
   else if (multi) { PcbProfScope ps(c, st, PCB_K_ALLREDUCE); PCB_TRY(pcb_allreduce_aggr(c, st)); }
   if (early.done) PCB_TRY(em_update_leaves(c, pseudocount, inertia, st));

@@ -198,6 +198,7 @@ struct pcb_circuit {
   int nranks = 1, rank = 0;
   bool comm_lost = false;                // pcb_comm_abort ran: steps refuse until the communicator is destroyed
   bool comm_enabled = true;             // false: the step skips its collectives (timing of the exposed share only)
+  bool comm_pipe = true;                // sum parameters updated and weight images rebuilt while the leaf slots are summed (PCB_COMM_PIPE=0: one collective, then the update)
   bool comm_split = false;              // edge statistics summed on comm_stream while the leaf statistics are still formed
   cudaStream_t comm_stream = nullptr;   // created with the communicator
   cudaEvent_t ev_c0 = nullptr, ev_c1 = nullptr, ev_c2 = nullptr, ev_c3 = nullptr;
