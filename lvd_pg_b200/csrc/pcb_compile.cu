@@ -357,6 +357,12 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
   PCB_TRY(upload(&c->e_sub, e_sub, &bytes));
   PCB_TRY(upload(&c->in_node, in_node, &bytes));
   PCB_TRY(upload(&c->in_var, in_var, &bytes));
+  {  // per variable the smallest category count of its leaves: what an observed value must stay below
+    std::vector<uint32_t> var_cats(d->num_vars, 0xffffffffu);
+    for (uint32_t i = 0; i < NI; ++i) var_cats[in_var[i]] = std::min(var_cats[in_var[i]], in_cats[i]);
+    PCB_TRY(upload(&c->var_cats, var_cats, &bytes));
+    PCB_CUDA(cudaMalloc((void**)&c->check_word, 4 * sizeof(int32_t)));
+  }
   PCB_TRY(upload(&c->in_cats, in_cats, &bytes));
   PCB_TRY(upload(&c->in_poff, in_poff, &bytes));
   PCB_TRY(upload(&c->in_foff, in_foff, &bytes));
@@ -416,6 +422,7 @@ int32_t compile(const pcb_circuit_desc* d, pcb_circuit* c) {
     c->sample_walk_warp = flag("PCB_SAMPLE_WALK_WARP");
     c->sample_exact_keys = flag("PCB_SAMPLE_EXACT_KEYS");
     if (const char* e = getenv("PCB_LEAF_FLOW_IMPL")) c->leaf_flow_impl = !strcmp(e, "sorted") ? 2 : !strcmp(e, "atomic") ? 1 : 0;
+    if (const char* e = getenv("PCB_CHECKED")) c->checked = atoi(e) != 0;
     if (const char* e = getenv("PCB_TC_KSPLIT")) { int v = atoi(e); c->tc_ksplit = (v == 1 || v == 2 || v == 4) ? v : 0; }
     if (const char* e = getenv("PCB_TC_NSPLIT")) { int v = atoi(e); c->tc_nsplit = (v == 1 || v == 2 || v == 4) ? v : 0; }
     if (const char* e = getenv("PCB_TC_A_STAGES")) { int v = atoi(e); c->tc_a_stages = (v == 2 || v == 4 || v == 8) ? v : 0; }
@@ -450,7 +457,7 @@ void free_circuit(pcb_circuit* c) {
                   c->e_sub, c->in_node, c->in_var, c->in_cats, c->in_poff, c->in_foff, c->node2input,
                   c->up_all, c->up_sparse, c->down_all, c->down_sparse, c->in_off, c->in_ent, c->dense,
                   c->grp_node, c->lchunk_var, c->lchunk_off, c->lchunk_inputs, c->status, c->w_img, c->dense_img, c->w_img16, c->dense_img16,
-                  c->lgrp_var, c->lgrp_off, c->s_node, c->s_leaf, c->n_head, c->head_roots, c->up_same};
+                  c->lgrp_var, c->lgrp_off, c->s_node, c->s_leaf, c->n_head, c->head_roots, c->up_same, c->var_cats, c->check_word};
   for (void* p : ptrs) if (p) cudaFree(p);
   if (c->ev_g0) cudaEventDestroy(c->ev_g0);
   if (c->ev_g1) cudaEventDestroy(c->ev_g1);

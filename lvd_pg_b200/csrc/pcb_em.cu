@@ -739,6 +739,50 @@ dim3 grid2v(uint32_t items, uint32_t B) { return dim3(items, (B + 4 * TPB - 1) /
     if (_s != PCB_OK) return _s;   \
   } while (0)
 
+// ---- checked mode (PCB_CHECKED=1) ------------------------------------------------------------------
+// The circuit's own index arrays are validated on the host when it is compiled; what arrives on the
+// device at run time and is used as an index is the batch: row ids and observed categories.  The
+// reference reads both under @inbounds.  In checked mode every pass first runs this kernel, which
+// touches only what it has found in range, waits for it and refuses the pass with the first finding
+// (no kernel of the pass is launched on a bad index).  word: [code, example, variable, value],
+// code 1 = row id outside [1, num_rows], 2 = category not below the variable's category count.
+__global__ void check_batch_kernel(const int32_t* __restrict__ row_ids, uint32_t row_start, uint32_t B, uint64_t num_rows,
+                                   const uint8_t* __restrict__ data, const uint8_t* __restrict__ miss, uint32_t V,
+                                   const uint32_t* __restrict__ var_cats, int32_t* __restrict__ word) {
+  const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  const int64_t row = row_ids ? (int64_t)row_ids[b] - 1 : (int64_t)row_start - 1 + b;
+  if (row < 0 || (uint64_t)row >= num_rows) {
+    if (atomicCAS(word, 0, 1) == 0) { word[1] = (int32_t)b; word[2] = 0; word[3] = (int32_t)(row + 1); }
+    return;
+  }
+  if (!data) return;
+  for (uint32_t v = blockIdx.y; v < V; v += gridDim.y) {
+    const size_t di = (size_t)row + (size_t)num_rows * v;
+    if (miss && miss[di]) continue;
+    const uint32_t x = data[di];
+    if (x >= var_cats[v] && atomicCAS(word, 0, 2) == 0) { word[1] = (int32_t)b; word[2] = (int32_t)v; word[3] = (int32_t)x; }
+  }
+}
+
+int32_t pcb_check_batch(pcb_circuit* c, const pcb_evidence& ev, cudaStream_t st) {
+  PCB_CUDA(cudaMemsetAsync(c->check_word, 0, 4 * sizeof(int32_t), st));
+  dim3 grid((ev.B + 127) / 128, std::min<uint32_t>(std::max<uint32_t>(c->V, 1u), 64u));
+  check_batch_kernel<<<grid, 128, 0, st>>>(ev.row_ids_dev, ev.row_start, ev.B, ev.num_rows, ev.data_dev, ev.miss_dev, c->V,
+                                           c->var_cats, c->check_word);
+  int32_t w[4] = {0, 0, 0, 0};
+  PCB_CUDA(cudaMemcpyAsync(w, c->check_word, sizeof(w), cudaMemcpyDeviceToHost, st));
+  PCB_CUDA(cudaStreamSynchronize(st));
+  if (w[0] == 1)
+    return pcb_fail(PCB_ERR_INVALID, "checked mode: example " + std::to_string(w[1]) + " of the batch names row " +
+                                         std::to_string(w[3]) + ", outside 1 .. " + std::to_string(ev.num_rows));
+  if (w[0] == 2)
+    return pcb_fail(PCB_ERR_INVALID, "checked mode: example " + std::to_string(w[1]) + " of the batch has value " +
+                                         std::to_string(w[3]) + " for variable " + std::to_string(w[2] + 1) +
+                                         ", which has fewer categories");
+  return PCB_OK;
+}
+
 static int32_t forward_impl(pcb_circuit* c, pcb_workspace* ws, const pcb_evidence& ev, float* ll_out_dev,
                             cudaStream_t st) {
   const uint32_t B = ev.B;
@@ -751,6 +795,11 @@ static int32_t forward_impl(pcb_circuit* c, pcb_workspace* ws, const pcb_evidenc
   PCB_REQUIRE(ev.soft_reg == 0.0f || ev.soft_dev || ev.soft_reg_width >= 1, "soft_reg_width must be at least 1");
   PCB_REQUIRE(!ev.head_mask_dev || c->n_heads, "a head mask needs a multi-head circuit");
   PCB_CUDA(cudaSetDevice(c->device));
+  if (c->checked) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(st, &cap);
+    if (cap == cudaStreamCaptureStatusNone) PCB_TRY(pcb_check_batch(c, ev, st));
+  }
   ws->B = B; ws->data = ev.data_dev; ws->miss = ev.miss_dev; ws->num_rows = ev.num_rows;
   ws->row_ids = ev.row_ids_dev; ws->row_start = ev.row_start; ws->have_forward = false;
   ws->soft = ev.soft_dev; ws->head_mask = ev.head_mask_dev;
@@ -1068,6 +1117,7 @@ static int32_t em_step_impl(pcb_circuit* c, pcb_workspace* ws, pcb_evidence ev, 
   }
   row_ids_dev = ws->ids_stage;
   ev.row_ids_dev = row_ids_dev; ev.row_start = row_start;
+  if (c->checked) PCB_TRY(pcb_check_batch(c, ev, st));   // before the statistics are cleared
   // The log-likelihood leaves through a copy issued after the step (the update does not touch its
   // slot), outside any captured graph: a training loop hands in a different slot for every batch.
   auto ll_out = [&](cudaStream_t on) -> int32_t {
@@ -1079,7 +1129,7 @@ static int32_t em_step_impl(pcb_circuit* c, pcb_workspace* ws, pcb_evidence ev, 
     PCB_TRY(em_step_body(c, ws, ev, weights_dev, clear_rate, pseudocount, inertia, st));
     return ll_out(st);
   };
-  if (!c->graph_enabled || c->prof.on) return plain();
+  if (!c->graph_enabled || c->prof.on || c->checked) return plain();   // checked mode synchronises inside the pass
 
   pcb_workspace::StepKey key;
   memset(&key, 0, sizeof(key));

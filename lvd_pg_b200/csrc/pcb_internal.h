@@ -181,6 +181,9 @@ struct pcb_circuit {
   bool fwd_split = true, bwd_split = true;   // side-stream splits of the forward / backward layer loops
   bool early_update = false;                 // single-GPU step: sum update + weight images beside the leaf statistics (measured neutral)
   int leaf_flow_impl = 0;                    // 0 by category count, 1 shared-memory histograms, 2 sorted segments
+  bool checked = false;                      // PCB_CHECKED=1: every pass first validates the batch (row ids, categories) and synchronises
+  uint32_t* var_cats = nullptr;              // [V] smallest category count over a variable's leaves
+  int32_t* check_word = nullptr;             // [4] first finding of the validation kernel: code, example, variable, value
   int tc_ksplit = 0;                         // 0 automatic, else 1 / 2 / 4 K parts of a dense tile (PCB_TC_KSPLIT)
   int tc_nsplit = 0;                         // 0 automatic, else 1 / 2 / 4 column splits of a dense tile
   int tc_a_stages = 0;                       // 0 automatic, else 2 / 4 / 8 stages of the dense kernels' A ring
@@ -347,6 +350,8 @@ __device__ __forceinline__ void pcb_grid_dep_launch() { asm volatile("griddepcon
 
 // entry points implemented across translation units and used by pcb_em_step
 int32_t pcb_allreduce_aggr(pcb_circuit* c, cudaStream_t st);
+// checked mode: validates row ids and categories of a batch, synchronises, PCB_ERR_INVALID with the first finding
+int32_t pcb_check_batch(pcb_circuit* c, const pcb_evidence& ev, cudaStream_t st);
 int32_t pcb_allreduce_range(pcb_circuit* c, uint64_t first, uint64_t count, cudaStream_t st);
 int32_t pcb_dense_forward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);
 int32_t pcb_dense_backward(pcb_circuit* c, pcb_workspace* ws, uint32_t layer, cudaStream_t st);

@@ -320,6 +320,7 @@ extern "C" int32_t pcb_normalized_flows(pcb_circuit* c, pcb_workspace* ws, const
     c->skip_stats = false;
     PCB_TRY(rb);
   } else {
+    if (c->checked) PCB_TRY(pcb_check_batch(c, *ev, st));
     ws->have_forward = false;
     ws->B = B; ws->data = ev->data_dev; ws->miss = ev->miss_dev; ws->num_rows = ev->num_rows;
     ws->row_ids = ev->row_ids_dev; ws->row_start = ev->row_start;
