@@ -222,15 +222,20 @@ __global__ void __launch_bounds__(LTH) leaf_forward_chunk_kernel(
   // A thread takes four consecutive examples per pass (one 16-byte store per leaf and pass); its
   // examples are the same for every leaf of the group, so their values are fetched once.  The last
   // store of a row may reach into the padding of the row pitch (a multiple of 32).
+  // A slice of at most 512 examples (the shard of a many-GPU step) leaves most threads without
+  // examples: the block then walks several leaves at once, `tb` threads (whole warps) per leaf.
   constexpr uint32_t U = LBT / (4 * LTH);
+  uint32_t tb = LTH;
+  if (nb <= 2 * LTH) { tb = 32; while (4 * tb < nb) tb <<= 1; }
+  const uint32_t te = threadIdx.x % tb, leaf_lane = threadIdx.x / tb, leaf_lanes = LTH / tb;
   uint16_t xv[U][4];
 #pragma unroll
   for (uint32_t u = 0; u < U; ++u) {
-    const uint32_t b = 4 * threadIdx.x + 4 * LTH * u;
+    const uint32_t b = 4 * te + 4 * LTH * u;
 #pragma unroll
     for (uint32_t j = 0; j < 4; ++j) xv[u][j] = b + j < nb ? xs[b + j] : (uint16_t)0xffff;
   }
-  for (uint32_t li = lchunk_off[chunk]; li < lchunk_off[chunk + 1]; ++li) {
+  for (uint32_t li = lchunk_off[chunk] + leaf_lane; li < lchunk_off[chunk + 1]; li += leaf_lanes) {
     uint32_t i = lchunk_inputs[li];
     const float* tab = theta + in_poff[i];
     float* out = mars + (size_t)in_node[i] * ld + b0;
@@ -241,7 +246,7 @@ __global__ void __launch_bounds__(LTH) leaf_forward_chunk_kernel(
       for (uint32_t j = 0; j < 4; ++j) v[u][j] = xv[u][j] == 0xffff ? 0.0f : __ldg(tab + xv[u][j]);
 #pragma unroll
     for (uint32_t u = 0; u < U; ++u) {
-      const uint32_t b = 4 * threadIdx.x + 4 * LTH * u;
+      const uint32_t b = 4 * te + 4 * LTH * u;
       if (b < nb) *reinterpret_cast<float4*>(out + b) = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
     }
   }
