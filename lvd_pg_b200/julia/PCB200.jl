@@ -515,6 +515,18 @@ end
 "Waits for the device and throws if a kernel of this circuit gave up a bounded wait (call where the loop synchronises)."
 circuit_status(c::PcbCircuit) = check(ccall((:pcb_circuit_status, libpcb200), Int32, (Ptr{Cvoid},), c.handle))
 
+"""
+selftest_wait_limit(device = 0; polls = 2^16) — runs the bounded mbarrier wait of the tensor-core kernels on a barrier
+nothing arrives at: returns (status, after, ms, production_polls); status == 1 and after == 2 mean that the wait gave
+up, reported and let the kernel return.  ms * production_polls / polls is how long a lost signal holds a kernel.
+"""
+function selftest_wait_limit(device::Integer = 0; polls::Integer = 1 << 16)
+    status = Ref{Int32}(-1); after = Ref{Int32}(-1); ms = Ref{Float32}(0); prod = Ref{UInt32}(0)
+    check(ccall((:pcb_selftest_wait_limit, libpcb200), Int32,
+                (Int32, UInt32, Ref{Int32}, Ref{Int32}, Ref{Float32}, Ref{UInt32}), device, polls, status, after, ms, prod))
+    (status = status[], after = after[], ms = ms[], production_polls = prod[])
+end
+
 # ---- multi-GPU: one NCCL communicator per process (no counterpart in the reference) ------------------
 function comm_unique_id()
     id = zeros(UInt8, 128)
