@@ -130,6 +130,15 @@ function vectorize_parameters(c::PcbCircuit, params::CuVector{Float32})
     params
 end
 vectorize_parameters(c::PcbCircuit) = Array(vectorize_parameters(c, CUDA.zeros(Float32, num_parameters(c))))
+"the same into / from a host vector (the library synchronises and copies itself)"
+function vectorize_parameters(c::PcbCircuit, params::Vector{Float32})
+    check(ccall((:pcb_get_params, libpcb200), Int32, (Ptr{Cvoid}, Ptr{Cfloat}, UInt64), c.handle, params, length(params)))
+    params
+end
+function update_parameters(c::PcbCircuit, params::Vector{Float32})
+    check(ccall((:pcb_set_params, libpcb200), Int32, (Ptr{Cvoid}, Ptr{Cfloat}, UInt64), c.handle, params, length(params)))
+    nothing
+end
 
 "update_parameters(mbpc, params::CuVector) — src/misc.jl:73-102"
 function update_parameters(c::PcbCircuit, params::CuVector{Float32})
@@ -510,6 +519,88 @@ function mini_batch_em_for_multihead_pc(m::PcbMultiHeadCircuit, data::CuMatrix{U
                                         shuffle = :each_epoch, weights = nothing, verbose = true, kwargs...)
     em_loop(m.bpc, data, head_mask, num_epochs; batch_size, pseudocount, soft_reg, soft_reg_width, param_inertia,
             param_inertia_end, flow_memory, shuffle, weights, verbose)
+end
+
+# ---- the pieces of a step and the accessors the reference's tools read ------------------------------
+# (the reference runs eval_circuit / flows_circuit / update_params as separate calls in its tests and reads
+# edge_aggr afterwards, e.g. for pruning: src/structures/prune.jl:21-31)
+
+"mirror of pcb_circuit_info"
+struct CircuitInfo
+    num_nodes::UInt32; num_edges::UInt32; num_sum_edges::UInt32; num_up_layers::UInt32
+    num_inner_params::UInt32; num_input_params::UInt32; num_param_groups::UInt32; num_dense_blocks::UInt32
+    num_sum_regions::UInt32; max_group_size::UInt32; max_num_cats::UInt32
+    num_dense_edges::UInt64; device_bytes::UInt64; num_heads::UInt32; reserved::UInt32
+end
+function circuit_info(c::PcbCircuit)
+    info = Ref{CircuitInfo}()
+    check(ccall((:pcb_circuit_get_info, libpcb200), Int32, (Ptr{Cvoid}, Ref{CircuitInfo}), c.handle, info))
+    info[]
+end
+version() = ccall((:pcb_version, libpcb200), Int32, ())
+
+"clear_flows: edge_aggr .= 0 (rate = 0) or edge_aggr .*= rate (flow memory), regularization/reg_em.jl:276-284"
+clear_flows(c::PcbCircuit, rate::Real = 0) =
+    check(ccall((:pcb_clear_flows, libpcb200), Int32, (Ptr{Cvoid}, Cfloat, Ptr{Cvoid}), c.handle, rate, stream()))
+
+"flows_circuit after a forward pass on the same workspace (queries/flow.jl:108-159); weights: per-example CuVector or nothing"
+function backward(c::PcbCircuit, ws::Ptr{Cvoid}; weights = nothing)
+    wptr = weights === nothing ? CU_NULL : pointer(weights)
+    check(ccall((:pcb_backward, libpcb200), Int32, (Ptr{Cvoid}, Ptr{Cvoid}, CuPtr{Cfloat}, Ptr{Cvoid}),
+                c.handle, ws, wptr, stream()))
+end
+
+"add_pseudocount + aggr_node_flows + update_params + update_input_node_params (reg_em.jl:292-299)"
+em_update(c::PcbCircuit; pseudocount::Real, inertia::Real) =
+    check(ccall((:pcb_em_update, libpcb200), Int32, (Ptr{Cvoid}, Cfloat, Cfloat, Ptr{Cvoid}),
+                c.handle, pseudocount, inertia, stream()))
+
+"edge_aggr in the reference's down-edge order (sum edges filled), after a backward pass or a step"
+function edge_aggr(c::PcbCircuit)
+    out = zeros(Float32, length(c.bpc.edge_layers_down.vectors))
+    check(ccall((:pcb_get_edge_aggr, libpcb200), Int32, (Ptr{Cvoid}, Ptr{Cfloat}, UInt64), c.handle, out, length(out)))
+    out
+end
+"the leaf heap (parameters and flow slots) as bpc.heap lays it out"
+function heap(c::PcbCircuit)
+    out = zeros(Float32, length(c.bpc.heap))
+    check(ccall((:pcb_get_heap, libpcb200), Int32, (Ptr{Cvoid}, Ptr{Cfloat}, UInt64), c.handle, out, length(out)))
+    out
+end
+"edge2param of CuMetaBitsProbCircuit (bits_circuit.jl:39-113): parameter id per up-edge, 0 for product edges"
+function edge2param(c::PcbCircuit)
+    out = zeros(UInt32, length(c.bpc.edge_layers_up.vectors))
+    check(ccall((:pcb_get_edge2param, libpcb200), Int32, (Ptr{Cvoid}, Ptr{UInt32}, UInt64), c.handle, out, length(out)))
+    out
+end
+"sum region (scope class) per node, 0 for non-sum nodes: the R index of the sampling noise"
+function sum_regions(c::PcbCircuit)
+    out = zeros(UInt32, length(c.bpc.nodes))
+    check(ccall((:pcb_get_sum_regions, libpcb200), Int32, (Ptr{Cvoid}, Ptr{UInt32}, UInt64), c.handle, out, length(out)))
+    out
+end
+"mars / flows of the last pass on a workspace as (B, num_nodes) host matrices"
+function node_matrix(sym::Symbol, c::PcbCircuit, ws::Ptr{Cvoid}, B::Integer)
+    out = zeros(Float32, B, length(c.bpc.nodes))
+    if sym === :mars
+        check(ccall((:pcb_get_mars, libpcb200), Int32, (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cfloat}, UInt64), c.handle, ws, out, length(out)))
+    else
+        check(ccall((:pcb_get_flows, libpcb200), Int32, (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cfloat}, UInt64), c.handle, ws, out, length(out)))
+    end
+    out
+end
+get_mars(c::PcbCircuit, ws::Ptr{Cvoid}, B::Integer) = node_matrix(:mars, c, ws, B)
+get_flows(c::PcbCircuit, ws::Ptr{Cvoid}, B::Integer) = node_matrix(:flows, c, ws, B)
+
+# launch accounting: what the reference's debug = true prints with CUDA.@time (queries/likelihood.jl:86-92)
+profile_enable(c::PcbCircuit, on::Bool) =
+    check(ccall((:pcb_profile_enable, libpcb200), Int32, (Ptr{Cvoid}, Int32), c.handle, on ? 1 : 0))
+"Dict(kernel class => (milliseconds under event timing, launches)) since the last reset"
+function profile_read(c::PcbCircuit; reset::Bool = true)
+    n = ccall((:pcb_profile_num_classes, libpcb200), Int32, ())
+    ms = zeros(Float64, n); cnt = zeros(UInt64, n)
+    check(ccall((:pcb_profile_read, libpcb200), Int32, (Ptr{Cvoid}, Ptr{Float64}, Ptr{UInt64}, Int32), c.handle, ms, cnt, reset ? 1 : 0))
+    Dict(unsafe_string(ccall((:pcb_profile_class_name, libpcb200), Cstring, (Int32,), i - 1)) => (ms[i], Int(cnt[i])) for i in 1:n)
 end
 
 "Waits for the device and throws if a kernel of this circuit gave up a bounded wait (call where the loop synchronises)."

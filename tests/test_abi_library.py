@@ -44,3 +44,15 @@ def test_product_code_does_not_import_the_oracle():
         for f in files:
             if f.endswith((".py", ".cu", ".h", ".jl")):
                 assert "oracle" not in open(os.path.join(dirpath, f)).read().replace("the oracle", ""), f
+
+
+def test_both_host_wrappers_bind_every_entry_point():
+    """The Python mirror declares a signature for, and the shipped Julia wrapper `ccall`s, every entry point
+    of the header (the two %globaltimer trace readers of diagnostic builds aside)."""
+    from lvd_pg_b200 import _lib
+    syms = [s for s in declared_symbols() if not s.startswith("pcb_debug_")]
+    jl = open(os.path.join(ROOT, "lvd_pg_b200", "julia", "PCB200.jl")).read()
+    missing_jl = [s for s in syms if f"(:{s}," not in jl]
+    assert not missing_jl, missing_jl
+    no_signature = [s for s in syms if s not in _lib.SIGNATURES and s not in ("pcb_last_error", "pcb_profile_class_name")]
+    assert not no_signature, no_signature
