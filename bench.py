@@ -47,42 +47,69 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs.
+
+    nvidia-smi needs a few hundred milliseconds to come up (longer on a box with eight GPUs), during which it
+    queries every GPU of the machine: `start()` therefore launches it ahead of the warm-up steps and waits (at
+    most three seconds) for its first line, `begin()` / `end()` bracket the timed region, and `summary()` uses
+    the lines that arrived in between.  Used as a context manager it does all of that around the block.  One
+    sampler per job is enough: ranks other than 0 pass enabled=False and run nothing."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index: int, enabled: bool = True, period_ms: int = 100):
+        self.index, self.enabled, self.period_ms = index, enabled, period_ms
+        self.rows, self.proc, self.t_begin, self.t_end = [], None, None, None
 
-    def __enter__(self):
+    def start(self, wait_s: float = 3.0):
+        if not self.enabled or self.proc:
+            return self
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
+            deadline = time.perf_counter() + wait_s
+            while not self.rows and time.perf_counter() < deadline and self.proc.poll() is None:
+                time.sleep(0.01)
         except Exception:
             self.proc = None
         return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.perf_counter(), [x.strip() for x in line.split(",")]))
 
-    def __exit__(self, *a):
+    def begin(self):
+        self.t_begin = time.perf_counter()
+
+    def end(self):
+        self.t_end = time.perf_counter()
         if self.proc:
-            time.sleep(0.15)
+            time.sleep(1.5e-3 * self.period_ms)   # one more line, taken while the last kernels still ran or just after
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except Exception:
                 self.proc.kill()
 
+    def __enter__(self):
+        self.start()
+        self.begin()
+        return self
+
+    def __exit__(self, *a):
+        self.end()
+
     def summary(self):
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        lo = (self.t_begin or 0.0)
+        hi = (self.t_end or float("inf")) + 2e-3 * self.period_ms
+        rows = [r for t, r in self.rows if lo <= t <= hi]
+        sm = [float(r[0]) for r in rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in rows)]
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(sm)}
 
@@ -508,17 +535,19 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    clocks = ClockSampler(local_rank, enabled=(rank == 0)).start()   # up before the warm-up, one per job
     for i in range(args.warmup):
         step(i)
     m.profile_read(reset=True)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
-        e0.record()
-        for i in range(args.warmup, n_steps_total):
-            step(i)
-        e1.record()
-        barrier()
+    clocks.begin()
+    e0.record()
+    for i in range(args.warmup, n_steps_total):
+        step(i)
+    e1.record()
+    barrier()
+    clocks.end()
     ms = e0.elapsed_time(e1)
     launches = sum(v[1] for v in m.profile_read(reset=True).values())
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
