@@ -1059,11 +1059,12 @@ static int32_t em_step_body(pcb_circuit* c, pcb_workspace* ws, const pcb_evidenc
   const float carried = (c->comm && c->nranks > 1) ? clear_rate / (float)c->nranks : clear_rate;
   PCB_TRY(pcb_clear_flows(c, carried, s));
   // multi-head circuits: the per-example log-likelihoods mix the heads (em.jl:71 of multi_head_pc)
-  PCB_TRY(forward_impl(c, ws, ev, c->n_heads ? ws->ll_tmp : nullptr, st));
+  { PcbNvtxRange r("pcb forward"); PCB_TRY(forward_impl(c, ws, ev, c->n_heads ? ws->ll_tmp : nullptr, st)); }
   const bool multi = c->comm && c->nranks > 1 && c->comm_enabled;
   const bool split = multi && c->comm_split && !c->prof.on;   // per-class timing wants every class alone on the GPU
   EarlyUpdate early{pseudocount, inertia, false};
-  PCB_TRY(backward_impl(c, ws, weights_dev, st, split, (!multi && c->early_update) ? &early : nullptr));
+  { PcbNvtxRange r("pcb backward"); PCB_TRY(backward_impl(c, ws, weights_dev, st, split, (!multi && c->early_update) ? &early : nullptr)); }
+  PcbNvtxRange r_update("pcb reduce + update");
   // batch log-likelihood into the last slot of the statistics vector, so it is reduced with them
   { PcbProfScope ps(c, st, PCB_K_MISC);
     ll_sum_kernel<<<1, 256, 0, st>>>(c->n_heads ? ws->ll_tmp : ws->mars + (size_t)(c->N - 1) * ws->ld, B,

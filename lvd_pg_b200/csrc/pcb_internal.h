@@ -314,9 +314,23 @@ struct PcbPerDeviceOnce {
 };
 
 // Counts a launch of class `cls`; with profiling on, brackets it with two events on `st`.
+// A build with -DPCB_NVTX additionally wraps every launch scope (and the passes of a step, PcbNvtxRange) in an
+// NVTX range named after its kernel class, for timeline tools; the default build has no NVTX calls.
+#ifdef PCB_NVTX
+#include <nvtx3/nvToolsExt.h>
+struct PcbNvtxRange {
+  explicit PcbNvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~PcbNvtxRange() { nvtxRangePop(); }
+};
+#else
+struct PcbNvtxRange { explicit PcbNvtxRange(const char*) {} };
+#endif
+extern "C" const char* pcb_profile_class_name(int32_t i);
+
 struct PcbProfScope {
   pcb_circuit* c; cudaStream_t st; cudaEvent_t e1 = nullptr;
-  PcbProfScope(pcb_circuit* c_, cudaStream_t st_, int cls) : c(c_), st(st_) {
+  PcbNvtxRange nvtx;
+  PcbProfScope(pcb_circuit* c_, cudaStream_t st_, int cls) : c(c_), st(st_), nvtx(pcb_profile_class_name(cls)) {
     ++c->prof.launches[cls];
     if (c->prof.on) {
       cudaEvent_t e0;
